@@ -1,0 +1,390 @@
+"""Differentiable hot ops of the framework.
+
+Every op has two implementations with one signature:
+
+* the sm_100a kernels of ``libeasyllm_b200.so`` (``ops.cuda``), used for CUDA bf16 tensors —
+  the product path; a missing library on a GPU machine raises instead of falling back;
+* the PyTorch statement in ``ops.reference`` — what runs on CPU (gloo tests, fp32 parity
+  configs), the numerical oracle of the kernel tests, and, with ``set_backend("torch")``, the
+  unfused library path used for A/B comparison on a GPU (cuBLAS matmul + library attention).
+
+Weights may carry a ``main_grad`` attribute (an fp32 view into the engine's flat gradient
+buffer).  When present, weight gradients are accumulated straight into it by the kernels
+(wgrad GEMM with beta = 1, norm weight-gradient reduce) and autograd receives ``None``.
+"""
+from __future__ import annotations
+
+import math
+import os
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import reference as ref
+
+_BACKEND = os.environ.get("EASYLLM_OPS", "b200")          # b200 | torch
+_GEMM = os.environ.get("EASYLLM_GEMM", "tcgen05")         # tcgen05 | cublas
+_ATTN = os.environ.get("EASYLLM_ATTN", "auto")            # auto | kernel | library
+
+
+def set_backend(name):
+    global _BACKEND
+    if name not in ("b200", "torch"):
+        raise ValueError(name)
+    _BACKEND = name
+
+
+def get_backend():
+    return _BACKEND
+
+
+def set_gemm_backend(name):
+    global _GEMM
+    if name not in ("tcgen05", "cublas"):
+        raise ValueError(name)
+    _GEMM = name
+
+
+def get_gemm_backend():
+    return _GEMM
+
+
+def set_attention_backend(name):
+    global _ATTN
+    _ATTN = name
+
+
+def _kern(x):
+    return _BACKEND == "b200" and x.is_cuda and x.dtype == torch.bfloat16
+
+
+def _cu():
+    from . import cuda
+    return cuda
+
+
+def kernel_launches():
+    from . import cuda
+    return cuda.LAUNCHES
+
+
+def _grad_to(param, g32):
+    """Deliver an fp32 weight gradient: into ``param.main_grad`` (returns None) or as a tensor."""
+    mg = getattr(param, "main_grad", None)
+    if mg is not None:
+        mg.add_(g32.view_as(mg))
+        return None
+    return g32.to(param.dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+# RMSNorm (+ residual add)
+# ---------------------------------------------------------------------------------------------
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        y, _, rstd = _cu().rmsnorm_fwd(x, None, w, eps)
+        ctx.save_for_backward(x, w, rstd)
+        ctx.wref = w
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd = ctx.saved_tensors
+        mg = getattr(ctx.wref, "main_grad", None)
+        if mg is not None:
+            dx, _ = _cu().rmsnorm_bwd(dy.contiguous(), x, w, rstd, None, dw_out=mg, accumulate=True)
+            return dx, None, None
+        dx, dw = _cu().rmsnorm_bwd(dy.contiguous(), x, w, rstd)
+        return dx, dw.to(w.dtype), None
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, w, eps):
+        y, h, rstd = _cu().rmsnorm_fwd(x, residual, w, eps)
+        ctx.save_for_backward(h, w, rstd)
+        ctx.wref = w
+        ctx.mark_non_differentiable()
+        return y, h
+
+    @staticmethod
+    def backward(ctx, dy, dh_in):
+        h, w, rstd = ctx.saved_tensors
+        mg = getattr(ctx.wref, "main_grad", None)
+        dres = dh_in.contiguous() if dh_in is not None else None
+        if mg is not None:
+            dh, _ = _cu().rmsnorm_bwd(dy.contiguous(), h, w, rstd, dres, dw_out=mg, accumulate=True)
+            return dh, dh, None, None
+        dh, dw = _cu().rmsnorm_bwd(dy.contiguous(), h, w, rstd, dres)
+        return dh, dh, dw.to(w.dtype), None
+
+
+def rmsnorm(x, weight, eps=1e-6):
+    if _kern(x) and x.dim() == 2 and x.shape[1] % 8 == 0 and x.shape[1] <= 8192:
+        return _RMSNorm.apply(x.contiguous(), weight, eps)
+    return ref.rmsnorm(x, weight, eps)
+
+
+def add_rmsnorm(x, residual, weight, eps=1e-6):
+    """Returns (norm(x + residual), x + residual)."""
+    if _kern(x) and x.dim() == 2 and x.shape[1] % 8 == 0 and x.shape[1] <= 8192:
+        return _AddRMSNorm.apply(x.contiguous(), residual.contiguous(), weight, eps)
+    return ref.add_rmsnorm(x, residual, weight, eps)
+
+
+# ---------------------------------------------------------------------------------------------
+# Linear:  y = x · Wᵀ (+ b)
+# ---------------------------------------------------------------------------------------------
+def _gemm_ok(*ts):
+    return _GEMM == "tcgen05" and all(t.shape[-1] % 8 == 0 for t in ts)
+
+
+def matmul_nt(a, b, bias=None):
+    """a [M,K] · b [N,K]ᵀ → [M,N] (bf16)."""
+    if _kern(a) and _gemm_ok(a, b) and b.shape[0] % 8 == 0:
+        return _cu().gemm(a, b, bias=bias)
+    return F.linear(a, b, bias)
+
+
+def matmul_nn(a, b):
+    """a [M,K] · b [K,N] → [M,N]; b is read in place as an MN-major operand."""
+    if _kern(a) and _gemm_ok(a, b):
+        return _cu().gemm(a, b, b_mn=True)
+    return a @ b
+
+
+def matmul_tn_accum(a, b, out32=None):
+    """aᵀ [K,M]ᵀ·b [K,N] → [M,N] fp32, accumulated into ``out32`` when given."""
+    if _kern(a) and _gemm_ok(a, b) and a.shape[1] % 8 == 0:
+        if out32 is None:
+            return _cu().gemm(a, b, a_mn=True, b_mn=True, out_mode=2)
+        return _cu().gemm(a, b, out=out32, a_mn=True, b_mn=True, out_mode=1)
+    r = (a.t() @ b).float()
+    if out32 is None:
+        return r
+    out32.add_(r)
+    return out32
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        ctx.save_for_backward(x, w)
+        ctx.wref, ctx.bref = w, bias
+        return matmul_nt(x, w, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = matmul_nn(dy, w) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(ctx.wref, "main_grad", None)
+            if mg is not None:
+                matmul_tn_accum(dy, x, mg)
+            else:
+                dw = matmul_tn_accum(dy, x).to(w.dtype)
+        db = None
+        if ctx.bref is not None and ctx.needs_input_grad[2]:
+            db = _grad_to(ctx.bref, dy.float().sum(0))
+        return dx, dw, db
+
+
+def linear(x, w, bias=None):
+    if _kern(x) and x.dim() == 2:
+        return _Linear.apply(x.contiguous(), w, bias)
+    return F.linear(x, w, bias)
+
+
+# ---------------------------------------------------------------------------------------------
+# RoPE on the packed QKV rows, SwiGLU on the fused gate|up rows
+# ---------------------------------------------------------------------------------------------
+class _RopePacked(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, pos, n_rot_heads, head_dim):
+        ctx.save_for_backward(cos, sin, pos)
+        ctx.meta = (n_rot_heads, head_dim)
+        _cu().rope_(qkv, cos, sin, pos, n_rot_heads, head_dim)
+        ctx.mark_dirty(qkv)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin, pos = ctx.saved_tensors
+        g = g.contiguous().clone() if not g.is_contiguous() else g.clone()
+        _cu().rope_(g, cos, sin, pos, *ctx.meta, backward=True)
+        return g, None, None, None, None, None
+
+
+def rope_packed(qkv, cos, sin, pos, n_q_heads, n_kv_heads, head_dim):
+    """Rotate the q and k heads of ``qkv [T, (Hq+2Hk)·D]`` (layout q|k|v) at positions ``pos``."""
+    if _kern(qkv) and head_dim % 16 == 0:
+        pos32 = pos if pos.dtype == torch.int32 else pos.to(torch.int32)
+        return _RopePacked.apply(qkv, cos, sin, pos32, n_q_heads + n_kv_heads, head_dim)
+    T = qkv.shape[0]
+    nq, nk = n_q_heads * head_dim, n_kv_heads * head_dim
+    q = qkv[:, :nq].reshape(T, n_q_heads, head_dim)
+    k = qkv[:, nq:nq + nk].reshape(T, n_kv_heads, head_dim)
+    q, k = ref.rope(q, k, cos, sin, pos.long())
+    return torch.cat((q.reshape(T, nq), k.reshape(T, nk), qkv[:, nq + nk:]), dim=1)
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        ctx.save_for_backward(gu)
+        return _cu().swiglu_fwd(gu)
+
+    @staticmethod
+    def backward(ctx, d):
+        (gu,) = ctx.saved_tensors
+        return _cu().swiglu_bwd(d.contiguous(), gu)
+
+
+def glu(gate_up, activation="silu"):
+    """``act(gate) * up`` on fused rows ``[T, 2F]`` (gate columns first)."""
+    if _kern(gate_up) and activation in ("silu", "swiglu") and gate_up.dim() == 2 and gate_up.shape[1] % 16 == 0:
+        return _SwiGLU.apply(gate_up.contiguous())
+    F_ = gate_up.shape[-1] // 2
+    return ref.GLU_ACTIVATIONS[activation](gate_up[..., :F_], gate_up[..., F_:])
+
+
+# ---------------------------------------------------------------------------------------------
+# Attention
+# ---------------------------------------------------------------------------------------------
+def _library_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale):
+    """cuDNN / library attention (counts as a library call, like cuBLAS)."""
+    T, Hq, D = q.shape
+    if cu_seqlens is None or cu_seqlens.numel() == 2:
+        o = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0),
+                                           v.transpose(0, 1).unsqueeze(0), is_causal=causal, scale=scale,
+                                           enable_gqa=k.shape[1] != Hq)
+        return o.squeeze(0).transpose(0, 1).contiguous()
+    cs = cu_seqlens.to(torch.int32)
+    try:
+        from torch.nn.attention.varlen import varlen_attn
+        if causal:
+            return varlen_attn(q, k, v, cs, cs, max_seqlen, max_seqlen, scale=scale, window_size=(-1, 0))
+        return varlen_attn(q, k, v, cs, cs, max_seqlen, max_seqlen, scale=scale)
+    except Exception:
+        from flash_attn import flash_attn_varlen_func
+        return flash_attn_varlen_func(q, k, v, cs, cs, max_seqlen, max_seqlen, softmax_scale=scale, causal=causal)
+
+
+def flash_attention(q, k, v, cu_seqlens=None, max_seqlen=None, causal=True, scale=None, alibi_slopes=None):
+    """Attention over packed documents: q ``[T,Hq,D]``, k/v ``[T,Hk,D]`` → ``[T,Hq,D]``."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and alibi_slopes is None:
+        if max_seqlen is None:
+            max_seqlen = q.shape[0] if cu_seqlens is None else int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
+        if _BACKEND == "b200" and _ATTN in ("auto", "kernel"):
+            from . import attention
+            if attention.supported(q, k, v):
+                return attention.flash_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+            if _ATTN == "kernel":
+                raise RuntimeError("attention kernel does not support this shape")
+        return _library_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+    return ref.attention_varlen(q, k, v, cu_seqlens, causal, scale, alibi_slopes)
+
+
+# ---------------------------------------------------------------------------------------------
+# Vocab-parallel cross entropy (stand-alone and fused with the LM head)
+# ---------------------------------------------------------------------------------------------
+def _tp_info():
+    from ..parallel.grid import get_grid
+    g = get_grid()
+    return g.tp_group, g.tp, g.tp_rank
+
+
+def _combine_parts(mx, se, tl, group, tp):
+    """Cross-rank combine of (max, sumexp, target-logit): returns (lse, target_logit)."""
+    if tp > 1:
+        gmx = mx.clone()
+        dist.all_reduce(gmx, op=dist.ReduceOp.MAX, group=group)
+        pair = torch.stack((se * torch.exp(mx - gmx), tl), dim=0)
+        dist.all_reduce(pair, group=group)
+        se, tl, mx = pair[0], pair[1], gmx
+    return torch.log(se) + mx, tl
+
+
+class _VocabParallelCE(torch.autograd.Function):
+    """Per-token loss from vocab-parallel logits.  Parity with
+    llm/models/mg_models/base_modules/functions/cross_entropy.py:22-112, including ``cut_size``
+    (padded vocab tail on the last rank excluded)."""
+
+    @staticmethod
+    def forward(ctx, logits, target, cut_size, inplace_backward):
+        group, tp, rank = _tp_info()
+        Vp = logits.shape[-1]
+        valid = Vp - cut_size if (cut_size and rank == tp - 1) else Vp
+        start = rank * Vp
+        flat = logits.reshape(-1, Vp)
+        tflat = target.reshape(-1)
+        if _kern(flat):
+            flat = flat.contiguous()
+            parts = _cu().ce_fwd(flat, tflat.contiguous(), start, valid)
+            mx, se, tl = parts[:, 0].contiguous(), parts[:, 1].contiguous(), parts[:, 2].contiguous()
+        else:
+            mx, se, tl = ref.cross_entropy_parts(flat, tflat, start, valid)
+        lse, tl = _combine_parts(mx, se, tl, group, tp)
+        ctx.save_for_backward(flat, tflat, lse)
+        ctx.meta = (start, valid, logits.shape, inplace_backward)
+        return (lse - tl).view(target.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        flat, tflat, lse = ctx.saved_tensors
+        start, valid, shape, inplace = ctx.meta
+        g = g.reshape(-1).float().contiguous()
+        if _kern(flat):
+            buf = flat if inplace else flat.clone()
+            _cu().ce_bwd_(buf, tflat, lse, g, start, valid)
+            return buf.view(shape), None, None, None
+        lf = flat.float()
+        p = torch.exp(lf - lse.unsqueeze(1))
+        if valid < lf.shape[1]:
+            p[:, valid:] = 0
+        loc = tflat - start
+        hit = (loc >= 0) & (loc < valid)
+        rows = torch.nonzero(hit).squeeze(1)
+        p[rows, loc[rows]] -= 1.0
+        return (p * g.unsqueeze(1)).to(flat.dtype).view(shape), None, None, None
+
+
+def vocab_parallel_cross_entropy(vocab_parallel_logits, target, cut_size=None, inplace_backward=False):
+    return _VocabParallelCE.apply(vocab_parallel_logits, target, cut_size, inplace_backward)
+
+
+def lm_head_cross_entropy(hidden, weight, target, cut_size=None):
+    """LM head GEMM + vocab-parallel CE → per-token losses ``[T]`` (fp32).  The bf16 logits
+    live only between the two ops; their buffer is overwritten by dlogits in backward."""
+    logits = linear(hidden, weight)
+    return vocab_parallel_cross_entropy(logits, target, cut_size, inplace_backward=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# Fused Adam on flat buffers
+# ---------------------------------------------------------------------------------------------
+def fused_adam_(p32, g32, m, v, p_lowp, lr, betas, eps, weight_decay, step, adamw=True, grad_scale=1.0,
+                scale_tensor=None, bias_correction=True):
+    if p32.is_cuda and _BACKEND == "b200":
+        _cu().adam(p32, g32, m, v, p_lowp, lr, betas[0], betas[1], eps, weight_decay, step, adamw, grad_scale,
+                   scale_tensor, bias_correction)
+        return
+    gs = grad_scale * (float(scale_tensor) if scale_tensor is not None else 1.0)
+    ref.adam_step(p32, g32, m, v, lr, betas[0], betas[1], eps, weight_decay, step, adamw, gs, bias_correction)
+    if p_lowp is not None:
+        p_lowp.copy_(p32)
+
+
+def sumsq(x32):
+    """Σ x² of an fp32 buffer as a 1-element fp32 tensor (no host sync)."""
+    out = torch.zeros(1, dtype=torch.float32, device=x32.device)
+    if x32.is_cuda and _BACKEND == "b200" and x32.dtype == torch.float32:
+        _cu().sumsq(x32, out)
+        return out
+    return (x32.float() ** 2).sum().view(1)

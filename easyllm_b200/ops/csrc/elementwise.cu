@@ -1,0 +1,146 @@
+// RoPE and SwiGLU kernels for sm_100a (HBM-bound elementwise ops, 16-byte vector access).
+//
+// RoPE is applied in place on the q and k heads of the packed QKV GEMM output
+// `[T, (Hq + 2·Hk) · D]` (NeoX half rotation, positions gathered per token so packed documents
+// restart at 0).  The backward is the same rotation with -sin.  Replaces the eager /
+// Triton rotary of the reference (llm/models/mg_models/llama/positional_embeddings.py:94-122).
+//
+// SwiGLU reads the fused gate|up GEMM output `[T, 2F]` (gate columns first) and writes
+// `silu(gate) * up` `[T, F]`; the backward recomputes the activation from gate|up
+// (llm/models/mg_models/llama/transformer.py:217-225 materialises both halves and the SiLU).
+#include "common.cuh"
+
+namespace ell {
+
+// One thread rotates 8 (x1) + 8 (x2) elements of one head: D/2 must be a multiple of 8.
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cos_t,
+                            const float* __restrict__ sin_t, const int* __restrict__ pos, int T, int row_stride,
+                            int n_rot_heads, int D, float sin_sign) {
+  const int half = D / 2, vec_per_head = half / 8;
+  const long long total = (long long)T * n_rot_heads * vec_per_head;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(i % vec_per_head);
+    const int hd = (int)((i / vec_per_head) % n_rot_heads);
+    const int t = (int)(i / ((long long)vec_per_head * n_rot_heads));
+    const int p = pos[t];
+    __nv_bfloat16* base = qkv + (size_t)t * row_stride + (size_t)hd * D + v * 8;
+    float x1[8], x2[8], c[8], s[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(base), x1);
+    unpack8(*reinterpret_cast<const bf16x8*>(base + half), x2);
+    const float4* cp = reinterpret_cast<const float4*>(cos_t + (size_t)p * half + v * 8);
+    const float4* sp = reinterpret_cast<const float4*>(sin_t + (size_t)p * half + v * 8);
+    float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+    c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+    s[0] = s0.x; s[1] = s0.y; s[2] = s0.z; s[3] = s0.w; s[4] = s1.x; s[5] = s1.y; s[6] = s1.z; s[7] = s1.w;
+    float o1[8], o2[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sj = s[j] * sin_sign;
+      o1[j] = x1[j] * c[j] - x2[j] * sj;
+      o2[j] = x2[j] * c[j] + x1[j] * sj;
+    }
+    *reinterpret_cast<bf16x8*>(base) = pack8(o1);
+    *reinterpret_cast<bf16x8*>(base + half) = pack8(o2);
+  }
+}
+
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int T, int F) {
+  const int fv = F / 8;
+  const long long total = (long long)T * fv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / fv), c = (int)(i % fv);
+    float g[8], u[8], o[8];
+    unpack8(reinterpret_cast<const bf16x8*>(gu + (size_t)t * 2 * F)[c], g);
+    unpack8(reinterpret_cast<const bf16x8*>(gu + (size_t)t * 2 * F + F)[c], u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    reinterpret_cast<bf16x8*>(out + (size_t)t * F)[c] = pack8(o);
+  }
+}
+
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ gu,
+                                  __nv_bfloat16* __restrict__ dgu, int T, int F) {
+  const int fv = F / 8;
+  const long long total = (long long)T * fv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / fv), c = (int)(i % fv);
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(reinterpret_cast<const bf16x8*>(gu + (size_t)t * 2 * F)[c], g);
+    unpack8(reinterpret_cast<const bf16x8*>(gu + (size_t)t * 2 * F + F)[c], u);
+    unpack8(reinterpret_cast<const bf16x8*>(dout + (size_t)t * F)[c], d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = 1.f / (1.f + __expf(-g[j]));
+      const float silu = g[j] * sg;
+      du[j] = d[j] * silu;
+      dg[j] = d[j] * u[j] * sg * (1.f + g[j] * (1.f - sg));
+    }
+    reinterpret_cast<bf16x8*>(dgu + (size_t)t * 2 * F)[c] = pack8(dg);
+    reinterpret_cast<bf16x8*>(dgu + (size_t)t * 2 * F + F)[c] = pack8(du);
+  }
+}
+
+// out(fp32) += in(bf16): gradient accumulation of one parameter into the fp32 flat buffer.
+__global__ void accum_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in, float* __restrict__ out, long long n) {
+  const long long nv = n / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
+       i += (long long)gridDim.x * blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const bf16x8*>(in)[i], f);
+    float4* o = reinterpret_cast<float4*>(out) + 2 * i;
+    float4 a = o[0], b = o[1];
+    a.x += f[0]; a.y += f[1]; a.z += f[2]; a.w += f[3];
+    b.x += f[4]; b.y += f[5]; b.z += f[6]; b.w += f[7];
+    o[0] = a; o[1] = b;
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
+    const long long j = nv * 8 + threadIdx.x;
+    out[j] += __bfloat162float(in[j]);
+  }
+}
+
+inline int ew_grid(long long work_items, int threads) {
+  long long b = (work_items + threads - 1) / threads;
+  long long cap = (long long)kNumSMs * 16;
+  return (int)(b < 1 ? 1 : (b < cap ? b : cap));
+}
+
+}  // namespace ell
+
+using namespace ell;
+
+ELL_API int ell_rope(void* qkv, const float* cos_t, const float* sin_t, const int* pos, int T, int row_stride,
+                     int n_rot_heads, int D, int backward, cudaStream_t stream) {
+  if (D % 16) return -1;
+  long long total = (long long)T * n_rot_heads * (D / 16);
+  if (total == 0) return 0;
+  rope_kernel<<<ew_grid(total, 256), 256, 0, stream>>>((__nv_bfloat16*)qkv, cos_t, sin_t, pos, T, row_stride,
+                                                       n_rot_heads, D, backward ? -1.f : 1.f);
+  return launch_status();
+}
+
+ELL_API int ell_swiglu_fwd(const void* gu, void* out, int T, int F, cudaStream_t stream) {
+  if (F % 8) return -1;
+  long long total = (long long)T * (F / 8);
+  if (total == 0) return 0;
+  swiglu_fwd_kernel<<<ew_grid(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F);
+  return launch_status();
+}
+
+ELL_API int ell_swiglu_bwd(const void* dout, const void* gu, void* dgu, int T, int F, cudaStream_t stream) {
+  if (F % 8) return -1;
+  long long total = (long long)T * (F / 8);
+  if (total == 0) return 0;
+  swiglu_bwd_kernel<<<ew_grid(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)gu,
+                                                            (__nv_bfloat16*)dgu, T, F);
+  return launch_status();
+}
+
+ELL_API int ell_accum_bf16_to_f32(const void* in, float* out, long long n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  accum_bf16_to_f32_kernel<<<ew_grid(n / 8 + 1, 256), 256, 0, stream>>>((const __nv_bfloat16*)in, out, n);
+  return launch_status();
+}

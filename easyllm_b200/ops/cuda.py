@@ -1,0 +1,223 @@
+"""ctypes bridge to ``libeasyllm_b200.so`` (the in-tree sm_100a kernel library).
+
+Each wrapper takes torch CUDA tensors, checks dtype / layout, and launches on the current
+torch stream.  A missing library on a machine with a GPU is an error, never a silent
+fallback: ``lib()`` raises with the build command.  ``LAUNCHES`` counts kernel launches of
+this library (benchmarks report it).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libeasyllm_b200.so")
+_lib = None
+LAUNCHES = 0
+_err_flags = {}
+_scratch = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def available():
+    return os.path.exists(_LIB_PATH)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise KernelError(f"{_LIB_PATH} is missing: run `python -m easyllm_b200.ops.build` "
+                              "(or __graft_entry__.build()) before using the CUDA ops")
+        _lib = ctypes.CDLL(_LIB_PATH)
+        _lib.ell_rmsnorm_bwd_scratch_elems.restype = c_longlong
+    return _lib
+
+
+def _p(t):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc, name):
+    global LAUNCHES
+    if rc != 0:
+        raise KernelError(f"{name} failed with code {rc}"
+                          + (f" ({torch.cuda.get_device_name()})" if rc > 0 else " (bad arguments)"))
+    LAUNCHES += 1
+
+
+def _bf16c(t, name):
+    if t.dtype != torch.bfloat16 or not t.is_cuda:
+        raise TypeError(f"{name}: expected a CUDA bf16 tensor, got {t.dtype} on {t.device}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name}: tensor must be contiguous")
+    return t
+
+
+def err_flag(device=None):
+    """Per-device int32 word the kernels write when one of their bounded waits expires."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    f = _err_flags.get(dev)
+    if f is None:
+        f = torch.zeros(1, dtype=torch.int32, device=dev)
+        _err_flags[dev] = f
+    return f
+
+
+def check_err_flag():
+    """Synchronising read of the error word; raises if a kernel reported a timed-out wait."""
+    f = err_flag()
+    v = int(f.item())
+    if v:
+        f.zero_()
+        raise KernelError(f"a kernel gave up a bounded wait (code {v}: 1 producer, 2 mma, 3 epilogue)")
+
+
+def scratch(nelem, dtype=torch.float32, tag="default"):
+    """Grow-only scratch buffer (per device, per tag) so hot ops do not allocate every call."""
+    dev = torch.cuda.current_device()
+    key = (dev, tag, dtype)
+    b = _scratch.get(key)
+    if b is None or b.numel() < nelem:
+        b = torch.empty(max(int(nelem), 1), dtype=dtype, device=torch.device("cuda", dev))
+        _scratch[key] = b
+    return b
+
+
+# ---- norm ------------------------------------------------------------------------------------
+def rmsnorm_fwd(x, residual, w, eps):
+    """Returns (y, h, rstd); h is x (+ residual) — the new residual stream — or x itself."""
+    _bf16c(x, "x"); _bf16c(w, "weight")
+    rows, cols = x.shape
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    h = torch.empty_like(x) if residual is not None else x
+    if residual is not None:
+        _bf16c(residual, "residual")
+    rc = lib().ell_rmsnorm_fwd(_p(x), _p(residual), _p(w), _p(y), _p(h if residual is not None else None),
+                               _p(rstd), c_int(rows), c_int(cols), c_float(eps), _stream())
+    _check(rc, "rmsnorm_fwd")
+    return y, h, rstd
+
+
+def rmsnorm_bwd(dy, h, w, rstd, dres=None, dw_out=None, accumulate=False):
+    """Returns (dh, dw fp32).  ``dres`` (grad arriving on the residual path) is added into dh."""
+    _bf16c(dy, "dy"); _bf16c(h, "h")
+    rows, cols = h.shape
+    dh = torch.empty_like(h)
+    dw = dw_out if dw_out is not None else torch.empty(cols, dtype=torch.float32, device=h.device)
+    sc = scratch(lib().ell_rmsnorm_bwd_scratch_elems(c_int(rows), c_int(cols)), tag="rmsnorm_bwd")
+    if dres is not None:
+        _bf16c(dres, "dres")
+    rc = lib().ell_rmsnorm_bwd(_p(dy), _p(h), _p(w), _p(rstd), _p(dres), _p(dh), _p(dw), _p(sc), c_int(rows),
+                               c_int(cols), c_int(1 if accumulate else 0), _stream())
+    _check(rc, "rmsnorm_bwd")
+    global LAUNCHES
+    LAUNCHES += 1  # the column reduce is a second launch
+    return dh, dw
+
+
+# ---- rope / swiglu ----------------------------------------------------------------------------
+def rope_(qkv, cos, sin, pos, n_rot_heads, head_dim, backward=False):
+    """In-place rotary embedding on the first ``n_rot_heads`` heads of each row of ``qkv [T, W]``."""
+    _bf16c(qkv, "qkv")
+    if pos.dtype != torch.int32:
+        pos = pos.to(torch.int32)
+    T, W = qkv.shape
+    rc = lib().ell_rope(_p(qkv), _p(cos), _p(sin), _p(pos), c_int(T), c_int(W), c_int(n_rot_heads),
+                        c_int(head_dim), c_int(1 if backward else 0), _stream())
+    _check(rc, "rope")
+    return qkv
+
+
+def swiglu_fwd(gu):
+    _bf16c(gu, "gate_up")
+    T, F2 = gu.shape
+    out = torch.empty(T, F2 // 2, dtype=gu.dtype, device=gu.device)
+    _check(lib().ell_swiglu_fwd(_p(gu), _p(out), c_int(T), c_int(F2 // 2), _stream()), "swiglu_fwd")
+    return out
+
+
+def swiglu_bwd(dout, gu):
+    _bf16c(dout, "dout"); _bf16c(gu, "gate_up")
+    T, F2 = gu.shape
+    dgu = torch.empty_like(gu)
+    _check(lib().ell_swiglu_bwd(_p(dout), _p(gu), _p(dgu), c_int(T), c_int(F2 // 2), _stream()), "swiglu_bwd")
+    return dgu
+
+
+def accum_bf16_to_f32(src, dst):
+    _check(lib().ell_accum_bf16_to_f32(_p(src), _p(dst), c_longlong(src.numel()), _stream()), "accum")
+
+
+# ---- optimizer --------------------------------------------------------------------------------
+def adam(p, g, m, v, p_lowp, lr, beta1, beta2, eps, weight_decay, step, adamw=True, grad_scale=1.0,
+         scale_ptr=None, bias_correction=True):
+    c1 = 1.0 - beta1 ** step if bias_correction else 1.0
+    c2 = 1.0 - beta2 ** step if bias_correction else 1.0
+    rc = lib().ell_adam(_p(p), _p(g), _p(m), _p(v), _p(p_lowp), c_longlong(p.numel()), c_float(lr), c_float(beta1),
+                        c_float(beta2), c_float(eps), c_float(weight_decay), c_float(c1), c_float(c2),
+                        c_float(grad_scale), c_int(1 if adamw else 0), _p(scale_ptr), _stream())
+    _check(rc, "adam")
+
+
+def sumsq(x, out):
+    _check(lib().ell_sumsq(_p(x), c_longlong(x.numel()), _p(out), _stream()), "sumsq")
+
+
+# ---- cross entropy ----------------------------------------------------------------------------
+def ce_fwd(logits, target, vocab_start, valid_cols):
+    _bf16c(logits, "logits")
+    T, V = logits.shape
+    parts = torch.empty(T, 3, dtype=torch.float32, device=logits.device)
+    rc = lib().ell_ce_fwd(_p(logits), _p(target), _p(parts), c_int(T), c_int(V), c_int(valid_cols),
+                          c_longlong(vocab_start), _stream())
+    _check(rc, "ce_fwd")
+    return parts
+
+
+def ce_bwd_(logits, target, lse, scale, vocab_start, valid_cols):
+    T, V = logits.shape
+    rc = lib().ell_ce_bwd(_p(logits), _p(target), _p(lse), _p(scale), c_int(T), c_int(V), c_int(V),
+                          c_int(valid_cols), c_longlong(vocab_start), _stream())
+    _check(rc, "ce_bwd")
+    return logits
+
+
+# ---- GEMM -------------------------------------------------------------------------------------
+def gemm(a, b, out=None, bias=None, a_mn=False, b_mn=False, out_mode=0, bn=0):
+    """``C = op(A) · op(B)ᵀ`` on tcgen05.  K-major operands are row-major ``[rows, K]``; MN-major
+    operands are row-major ``[K, rows]``.  out_mode 0: bf16 C; 1: fp32 C += ; 2: fp32 C =."""
+    _bf16c(a, "a"); _bf16c(b, "b")
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"gemm: reduction dims differ ({K} vs {Kb})")
+    if (a.shape[1] % 8) or (b.shape[1] % 8) or (N % 8):
+        raise ValueError("gemm: row lengths must be multiples of 8 elements (16-byte TMA strides)")
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16 if out_mode == 0 else torch.float32, device=a.device)
+    want = torch.bfloat16 if out_mode == 0 else torch.float32
+    if out.dtype != want or not out.is_contiguous() or tuple(out.shape) != (M, N):
+        raise ValueError("gemm: bad output tensor")
+    rc = lib().ell_gemm_bf16(_p(a), _p(b), _p(out), _p(bias), c_int(M), c_int(N), c_int(K), c_int(a.shape[1]),
+                             c_int(b.shape[1]), c_int(N), c_int(1 if a_mn else 0), c_int(1 if b_mn else 0),
+                             c_int(out_mode), c_int(bn), _p(err_flag(a.device)), _stream())
+    _check(rc, "gemm_bf16")
+    return out

@@ -1,0 +1,146 @@
+"""Tensor-parallel linear maps with Megatron-style sequence parallelism.
+
+``column_parallel_linear``: the input is sequence-sharded ``[T/tp, K]`` (SP) or replicated
+``[T, K]``; output ``[T, N/tp]``.  ``row_parallel_linear``: input ``[T, K/tp]``, output
+reduce-scattered to ``[T/tp, N]`` (SP) or all-reduced ``[T, N]``.
+
+Parity: llm/models/mg_models/base_modules/layers/column_parallel_linear.py:13-106 (forward
+all-gather → GEMM; backward re-gather ‖ dgrad, reduce-scatter(dgrad) ‖ wgrad) and
+row_parallel_linear.py:105-132.  Here one gather serves the fused q|k|v (or gate|up)
+projection, so a layer gathers twice instead of five times.  These are the composition
+forms (collective + GEMM as separate kernels, overlapped with async collectives); the fused
+all-gather→GEMM / GEMM→reduce-scatter kernels register themselves through ``set_fused_impl``
+and take over for CUDA bf16 inputs when a symmetric-memory workspace is installed.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from .buffers import get_global_memory_buffer
+from .grid import get_grid
+from . import mappings as mp
+
+_FUSED = {"ag_gemm": None, "gemm_rs": None}
+
+
+def set_fused_impl(ag_gemm=None, gemm_rs=None):
+    """Install fused kernels: ``ag_gemm(x_local, w, bias) -> (y, x_gathered)`` and
+    ``gemm_rs(x, w) -> y_local``.  ``None`` restores the composition."""
+    _FUSED["ag_gemm"], _FUSED["gemm_rs"] = ag_gemm, gemm_rs
+
+
+def _use_fused(x):
+    return x.is_cuda and x.dtype == torch.bfloat16 and ops.get_backend() == "b200"
+
+
+def _ag_start(x, name):
+    g = get_grid()
+    shape = list(x.shape)
+    shape[0] *= g.tp
+    out = get_global_memory_buffer().get_tensor(shape, x.dtype, name, device=x.device)
+    work = dist.all_gather_into_tensor(out, x.contiguous(), group=g.tp_group, async_op=True)
+    return out, work
+
+
+def _rs_start(x):
+    g = get_grid()
+    if dist.get_backend(g.tp_group) == "gloo":
+        return mp.reduce_scatter_first_dim(x), None
+    shape = list(x.shape)
+    shape[0] //= g.tp
+    out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    work = dist.reduce_scatter_tensor(out, x.contiguous(), group=g.tp_group, async_op=True)
+    return out, work
+
+
+def _wgrad(ctx_w, dy, x):
+    """dW = dyᵀ·x delivered into main_grad (None returned) or as a tensor."""
+    mg = getattr(ctx_w, "main_grad", None)
+    if mg is not None:
+        ops.matmul_tn_accum(dy, x, mg)
+        return None
+    return ops.matmul_tn_accum(dy, x).to(ctx_w.dtype)
+
+
+class _ColumnSP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        ctx.wref, ctx.bref = w, bias
+        fused = _FUSED["ag_gemm"] if _use_fused(x) else None
+        if fused is not None:
+            y, _ = fused(x, w, bias)
+        else:
+            xg, work = _ag_start(x, "sp_gather")
+            work.wait()
+            y = ops.matmul_nt(xg, w, bias)
+        ctx.save_for_backward(x, w)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        xg, ag_work = _ag_start(x, "sp_gather_bwd")          # re-gather ‖ dgrad GEMM
+        fused_rs = _FUSED["gemm_rs"] if _use_fused(dy) else None
+        if fused_rs is not None:
+            dx = fused_rs(dy, w, b_mn=True)
+            rs_work = None
+        else:
+            dxg = ops.matmul_nn(dy, w)
+            dx, rs_work = _rs_start(dxg)                      # reduce-scatter ‖ wgrad GEMM
+        ag_work.wait()
+        dw = _wgrad(ctx.wref, dy, xg) if ctx.needs_input_grad[1] else None
+        db = None
+        if ctx.bref is not None and ctx.needs_input_grad[2]:
+            db = ops._grad_to(ctx.bref, dy.float().sum(0))
+        if rs_work is not None:
+            rs_work.wait()
+        return dx, dw, db
+
+
+class _RowSP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.wref = w
+        ctx.save_for_backward(x, w)
+        fused = _FUSED["gemm_rs"] if _use_fused(x) else None
+        if fused is not None:
+            return fused(x, w)
+        y = ops.matmul_nt(x, w)
+        out, work = _rs_start(y)
+        if work is not None:
+            work.wait()
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dyg, work = _ag_start(dy.contiguous(), "sp_gather_row_bwd")
+        work.wait()
+        dx = ops.matmul_nn(dyg, w) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(ctx.wref, dyg, x) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def column_parallel_linear(x, w, bias=None, sequence_parallel=False):
+    g = get_grid()
+    if g.tp == 1:
+        return ops.linear(x, w, bias)
+    if sequence_parallel:
+        return _ColumnSP.apply(x, w, bias)
+    return ops.linear(mp.copy_to_tensor_model_parallel_region(x), w, bias)
+
+
+def row_parallel_linear(x, w, bias=None, sequence_parallel=False):
+    g = get_grid()
+    if g.tp == 1:
+        return ops.linear(x, w, bias)
+    if sequence_parallel:
+        y = _RowSP.apply(x, w)
+    else:
+        y = mp.reduce_from_tensor_model_parallel_region(ops.linear(x, w))
+    if bias is not None:
+        y = y + bias
+    return y
