@@ -273,7 +273,7 @@ class ParallelAttention(nn.Module):
             sl = alibi_slopes(a.num_attention_heads)[g.tp_rank * self.hq:(g.tp_rank + 1) * self.hq]
             self.alibi = torch.tensor(sl, dtype=torch.float32)
         self._register_state_dict_hook(_split_fused_hook("qkv", "wqkv" if a.qkv_pack else None))
-        self._register_load_state_dict_pre_hook(_merge_fused_hook(self.qkv, "qkv", "wqkv" if a.qkv_pack else None))
+        self.register_load_state_dict_pre_hook(_merge_fused_hook(self.qkv, "qkv", "wqkv" if a.qkv_pack else None))
 
     def forward(self, x, meta, kv_cache: Optional[KVCache] = None):
         """x: ``[T(/tp), h]``; meta: dict(position_ids [T], cu_seqlens, max_seqlen, batch)."""
@@ -315,7 +315,7 @@ class ParallelMLP(nn.Module):
         self.down_proj = RowParallelLinear(f, a.hidden_size, sequence_parallel=a.sequence_parallel,
                                            sigma=a.output_sigma(), dtype=a.params_dtype)
         self._register_state_dict_hook(_split_fused_hook("gate_up", None))
-        self._register_load_state_dict_pre_hook(_merge_fused_hook(self.gate_up, "gate_up", None))
+        self.register_load_state_dict_pre_hook(_merge_fused_hook(self.gate_up, "gate_up", None))
 
     def forward(self, x):
         return self.down_proj(ops.glu(self.gate_up(x), self.act))

@@ -1,0 +1,282 @@
+"""Mixed-precision optimizer on flat buffers with ZeRO-0/1/2 sharding over the DP group.
+
+What the reference obtains from DeepSpeed (``BF16_Optimizer`` / ZeRO stage 0-2 wrapped
+around apex FusedAdam: llm/utils/model/optimizer_helper.py:70-98,
+llm/runners/base_llm_runner.py:194-213) re-designed around three flat buffers:
+
+* ``param_buf``  — every trainable parameter of this rank re-homed into one contiguous
+  buffer in the compute dtype (bf16 / fp16 / fp32); module parameters become views.
+* ``grad_buf``   — fp32, same layout; each parameter gets ``main_grad`` (a view) that the
+  wgrad GEMM / norm kernels accumulate into directly across micro-batches.
+* ``master / m / v`` — fp32, only this DP rank's shard when ``stage >= 1``.
+
+One step = [TP all-reduce of sequence-parallel replicated grads] → DP reduce-scatter
+(stage ≥ 1) or all-reduce (stage 0) of ``grad_buf`` → squared-norm partials → one world
+all-reduce → clip coefficient kept on the device → fused Adam over the shard (writes the
+low-precision shard of ``param_buf``) → DP all-gather of ``param_buf``.  No step of this
+needs a host synchronisation except the optional fp16 overflow check.
+
+Buffer order: [TP-sharded, decay][TP-sharded, no-decay][replicated, decay][replicated,
+no-decay][replicated under sequence parallelism], so weight decay, norm de-duplication and
+the TP gradient all-reduce each act on one contiguous range.
+"""
+from __future__ import annotations
+
+import math
+from typing import Iterable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..parallel.grid import get_grid
+
+_ALIGN = 8  # elements; keeps every shard boundary 16-byte aligned in bf16
+
+
+def _no_decay(name, p):
+    return name.endswith(".bias") or p.dim() == 1 or getattr(p, "no_weight_decay", False)
+
+
+class DynamicLossScaler:
+    """fp16 loss scaling (``optimizer.cur_scale`` in the reference's logger hook)."""
+
+    def __init__(self, init_scale=2.0 ** 16, growth_interval=1000, factor=2.0, min_scale=1.0, hysteresis=2):
+        self.cur_scale, self.growth_interval, self.factor = float(init_scale), growth_interval, factor
+        self.min_scale, self.hysteresis, self._hyst, self._good = min_scale, hysteresis, hysteresis, 0
+
+    def update(self, overflow: bool):
+        if overflow:
+            self._hyst -= 1
+            if self._hyst <= 0:
+                self.cur_scale = max(self.cur_scale / self.factor, self.min_scale)
+            self._good = 0
+        else:
+            self._good += 1
+            if self._good % self.growth_interval == 0:
+                self.cur_scale *= self.factor
+                self._hyst = self.hysteresis
+
+    def state_dict(self):
+        return {"cur_scale": self.cur_scale, "good": self._good, "hyst": self._hyst}
+
+    def load_state_dict(self, s):
+        self.cur_scale, self._good, self._hyst = s["cur_scale"], s["good"], s["hyst"]
+
+
+class ZeroOptimizer:
+    def __init__(self, named_params: Iterable, lr=1e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
+                 adamw=True, stage=1, grad_clip=0.0, fp16=False, bias_correction=True, loss_scale_cfg=None,
+                 nan_policy="count"):
+        g = get_grid()
+        self.grid = g
+        self.stage = stage if g.dp > 1 or stage == 0 else stage
+        self.dp, self.dp_rank, self.dp_group = g.dp, g.dp_rank, g.dp_group
+        self.defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
+        self.param_groups = [dict(self.defaults, name="all")]   # lr schedulers poke param_groups[i]['lr']
+        self.adamw, self.grad_clip, self.bias_correction = adamw, grad_clip, bias_correction
+        self.step_count = 0
+        self.nan_policy = nan_policy
+        self.skipped_steps = 0
+        self.scaler = DynamicLossScaler(**(loss_scale_cfg or {})) if fp16 else None
+        self._global_grad_norm = None
+
+        named = [(n, p) for n, p in named_params if p.requires_grad]
+        if not named:
+            raise ValueError("no trainable parameters")
+        self.dtype = named[0][1].dtype
+        self.device = named[0][1].device
+
+        def klass(n, p):
+            sharded = bool(getattr(p, "tensor_model_parallel", False))
+            sp = bool(getattr(p, "sequence_parallel", False))
+            if sp:
+                return 4
+            return (0 if sharded else 2) + (1 if _no_decay(n, p) else 0)
+
+        order = sorted(range(len(named)), key=lambda i: (klass(*named[i]), i))
+        self.names = [named[i][0] for i in order]
+        self.params = [named[i][1] for i in order]
+        klasses = [klass(named[i][0], named[i][1]) for i in order]
+        self.offsets, off = [], 0
+        bounds = {}
+        for k, p in zip(klasses, self.params):
+            bounds.setdefault(k, off)
+            self.offsets.append(off)
+            off += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
+        self.used = off
+        # class range starts (monotone); missing classes collapse to the next start
+        starts = []
+        nxt = off
+        for k in (4, 3, 2, 1, 0):
+            nxt = bounds.get(k, nxt)
+            starts.append(nxt)
+        self.start_sp, self.start_rep_nd, self.start_rep, self.start_shard_nd, _ = starts
+        chunk = _ALIGN * self.dp
+        self.total = (off + chunk - 1) // chunk * chunk
+        self.shard_size = self.total // self.dp if self.stage >= 1 else self.total
+        self.shard_lo = self.dp_rank * self.shard_size if self.stage >= 1 else 0
+        self.shard_hi = self.shard_lo + self.shard_size
+
+        self.param_buf = torch.zeros(self.total, dtype=self.dtype, device=self.device)
+        self.grad_buf = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+        for p, o in zip(self.params, self.offsets):
+            view = self.param_buf[o:o + p.numel()].view_as(p)
+            view.copy_(p.data)
+            p.data = view
+            p.main_grad = self.grad_buf[o:o + p.numel()].view_as(p)
+        self.master = self.param_buf[self.shard_lo:self.shard_hi].to(torch.float32, copy=True)
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+        self._clip_coef = torch.ones(1, dtype=torch.float32, device=self.device)
+
+    # ---- gradient plumbing --------------------------------------------------------------
+    @property
+    def cur_scale(self):
+        return self.scaler.cur_scale if self.scaler else 1.0
+
+    def accumulate_grads(self):
+        """Fold autograd ``.grad`` tensors (reference / CPU path) into ``main_grad``."""
+        for p in self.params:
+            if p.grad is not None:
+                if p.grad.is_cuda and p.grad.dtype == torch.bfloat16 and ops.get_backend() == "b200" \
+                        and p.grad.is_contiguous():
+                    from ..ops import cuda
+                    cuda.accum_bf16_to_f32(p.grad, p.main_grad)
+                else:
+                    p.main_grad.add_(p.grad.float())
+                p.grad = None
+
+    def zero_grad(self):
+        self.grad_buf.zero_()
+        for p in self.params:
+            p.grad = None
+
+    def _segment_sumsq(self, lo, hi):
+        lo, hi = max(lo, self.shard_lo), min(hi, self.shard_hi)
+        if hi <= lo:
+            return torch.zeros(1, dtype=torch.float32, device=self.device)
+        return ops.sumsq(self._grad_shard()[lo - self.shard_lo:hi - self.shard_lo])
+
+    def _grad_shard(self):
+        return self.grad_buf[self.shard_lo:self.shard_hi]
+
+    def reduce_gradients(self):
+        g = self.grid
+        if g.tp > 1 and self.start_sp < self.used:
+            dist.all_reduce(self.grad_buf[self.start_sp:self.used], group=g.tp_group)
+        if self.dp > 1:
+            self.grad_buf.div_(self.dp)
+            if self.stage >= 1 and dist.get_backend(self.dp_group) != "gloo":
+                dist.reduce_scatter_tensor(self._grad_shard(), self.grad_buf, group=self.dp_group)
+            else:
+                dist.all_reduce(self.grad_buf, group=self.dp_group)
+
+    def compute_grad_norm(self):
+        """Global L2 norm of the (unscaled) gradients as a device tensor, every parameter
+        counted once: replicated ranges only on tp_rank 0, ZeRO shards summed over DP."""
+        g = self.grid
+        sq = self._segment_sumsq(0, self.start_rep)
+        if g.tp_rank == 0:
+            sq = sq + self._segment_sumsq(self.start_rep, self.used)
+        if dist.is_initialized() and g.world > 1:
+            if self.stage >= 1:
+                dist.all_reduce(sq)                       # dp shards × tp × pp
+            elif g.mp_group is not None and g.tp * g.pp > 1:
+                dist.all_reduce(sq, group=g.mp_group)
+        norm = sq.sqrt() / self.cur_scale
+        self._global_grad_norm = norm
+        return norm
+
+    def get_global_grad_norm(self):
+        return None if self._global_grad_norm is None else float(self._global_grad_norm)
+
+    # ---- the step ---------------------------------------------------------------------------
+    def step(self):
+        """reduce → norm/clip → Adam on the shard → all-gather.  Returns False if skipped."""
+        self.reduce_gradients()
+        norm = self.compute_grad_norm()
+        finite_needed = self.scaler is not None or self.nan_policy in ("skip", "abort")
+        if finite_needed:
+            ok = bool(torch.isfinite(norm))
+            if self.scaler is not None:
+                self.scaler.update(not ok)
+            if not ok:
+                if self.nan_policy == "abort":
+                    raise FloatingPointError("non-finite gradient norm")
+                self.skipped_steps += 1
+                self.zero_grad()
+                return False
+        if self.grad_clip and self.grad_clip > 0:
+            torch.clamp(self.grad_clip / (norm + 1e-6), max=1.0, out=self._clip_coef)
+        else:
+            self._clip_coef.fill_(1.0)
+        self.step_count += 1
+        pg = self.param_groups[0]
+        lr, betas, eps, wd = pg["lr"], pg["betas"], pg["eps"], pg["weight_decay"]
+        inv_scale = 1.0 / self.cur_scale
+        # weight decay applies to [0, start_shard_nd) ∪ [start_rep, start_rep_nd)
+        cuts = [0, self.start_shard_nd, self.start_rep, self.start_rep_nd, self.total]
+        wds = [wd, 0.0, wd, 0.0]
+        lowp = self.param_buf[self.shard_lo:self.shard_hi]
+        gsh = self._grad_shard()
+        for (a, b), w in zip(zip(cuts[:-1], cuts[1:]), wds):
+            lo, hi = max(a, self.shard_lo) - self.shard_lo, min(b, self.shard_hi) - self.shard_lo
+            if hi <= lo:
+                continue
+            ops.fused_adam_(self.master[lo:hi], gsh[lo:hi], self.exp_avg[lo:hi], self.exp_avg_sq[lo:hi], lowp[lo:hi],
+                            lr, betas, eps, w, self.step_count, self.adamw, inv_scale, self._clip_coef,
+                            self.bias_correction)
+        if self.stage >= 1 and self.dp > 1:
+            if dist.get_backend(self.dp_group) == "gloo":
+                parts = [torch.empty_like(lowp) for _ in range(self.dp)]
+                dist.all_gather(parts, lowp.contiguous(), group=self.dp_group)
+                self.param_buf.copy_(torch.cat(parts))
+            else:
+                dist.all_gather_into_tensor(self.param_buf, lowp, group=self.dp_group)
+        self.zero_grad()
+        return True
+
+    def refresh_fp32_params(self):
+        """Re-derive the fp32 master shard from the (just loaded) low-precision parameters."""
+        self.master.copy_(self.param_buf[self.shard_lo:self.shard_hi].float())
+
+    # ---- checkpoint ---------------------------------------------------------------------------
+    def state_dict(self):
+        return {"step": self.step_count, "stage": self.stage, "dp": self.dp, "dp_rank": self.dp_rank,
+                "total": self.total, "used": self.used, "shard_lo": self.shard_lo, "shard_hi": self.shard_hi,
+                "names": self.names, "offsets": self.offsets, "numels": [p.numel() for p in self.params],
+                "master": self.master.cpu(), "exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu(),
+                "param_groups": [{k: v for k, v in pg.items()} for pg in self.param_groups],
+                "scaler": self.scaler.state_dict() if self.scaler else None, "skipped_steps": self.skipped_steps}
+
+    def load_state_dict(self, sd, load_param_groups=True):
+        if sd["total"] != self.total or sd["shard_lo"] != self.shard_lo or sd["shard_hi"] != self.shard_hi:
+            raise ValueError("optimizer shard layout differs; use load_resharded() with all shards")
+        self.step_count = sd["step"]
+        self.master.copy_(sd["master"])
+        self.exp_avg.copy_(sd["exp_avg"])
+        self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        if load_param_groups:
+            for pg, s in zip(self.param_groups, sd["param_groups"]):
+                pg.update(s)
+        if self.scaler and sd.get("scaler"):
+            self.scaler.load_state_dict(sd["scaler"])
+        self.skipped_steps = sd.get("skipped_steps", 0)
+
+    def load_resharded(self, shards: List[dict]):
+        """Load from the optimizer shards of a run with a different DP size: the flat fp32
+        state is re-assembled by parameter name, then re-sliced for this rank."""
+        full = {}
+        for key in ("master", "exp_avg", "exp_avg_sq"):
+            cat = torch.cat([s[key] for s in sorted(shards, key=lambda s: s["shard_lo"])])
+            full[key] = cat
+        src = shards[0]
+        by_name = {n: (o, k) for n, o, k in zip(src["names"], src["offsets"], src["numels"])}
+        for key, dst in (("master", self.master), ("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
+            flat = torch.zeros(self.total, dtype=torch.float32)
+            for n, o, p in zip(self.names, self.offsets, self.params):
+                so, k = by_name[n]
+                flat[o:o + k] = full[key][so:so + k]
+            dst.copy_(flat[self.shard_lo:self.shard_hi])
+        self.step_count = src["step"]
