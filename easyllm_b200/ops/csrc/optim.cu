@@ -99,3 +99,7 @@ ELL_API int ell_sumsq(const float* x, long long n, float* out, cudaStream_t stre
   sumsq_kernel<<<grid, 256, 0, stream>>>(x, n, out);
   return launch_status();
 }
+
+// Make `dev`'s primary context current on the calling thread.  Worker threads (for example the
+// autograd engine's) may reach a launcher before any runtime call was made on them.
+ELL_API int ell_set_device(int dev) { return (int)cudaSetDevice(dev); }

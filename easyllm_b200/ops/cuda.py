@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import threading
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -44,7 +45,18 @@ def _p(t):
     return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
 
 
+_tls = threading.local()
+
+
 def _stream():
+    """Current torch stream; also makes the device's context current on this thread for the
+    library's own CUDA runtime (worker threads such as autograd's start without one)."""
+    dev = torch.cuda.current_device()
+    if getattr(_tls, "dev", None) != dev:
+        rc = lib().ell_set_device(c_int(dev))
+        if rc != 0:
+            raise KernelError(f"cudaSetDevice({dev}) failed with code {rc}")
+        _tls.dev = dev
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -221,3 +233,11 @@ def gemm(a, b, out=None, bias=None, a_mn=False, b_mn=False, out_mode=0, bn=0):
                              c_int(out_mode), c_int(bn), _p(err_flag(a.device)), _stream())
     _check(rc, "gemm_bf16")
     return out
+
+
+def has_symbol(name):
+    try:
+        getattr(lib(), name)
+        return True
+    except AttributeError:
+        return False

@@ -1,0 +1,92 @@
+"""tcgen05 GEMM (all operand layouts and output modes) against fp32 matmul of the same bf16 inputs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cu():
+    if not torch.cuda.is_available():
+        pytest.skip("no GPU")
+    import easyllm_b200.ops.cuda as cu
+    cu.lib()
+    return cu
+
+
+def _check(out, ref, K):
+    err = (out.float() - ref).abs().max().item()
+    tol = 2e-2 * max(1.0, ref.abs().max().item()) if out.dtype == torch.bfloat16 else 1e-3 * (K ** 0.5)
+    assert err <= tol, (err, tol)
+
+
+SHAPES = [(128, 256, 64), (128, 128, 128), (200, 136, 72), (512, 768, 512), (1000, 520, 264), (4096, 4096, 1024)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_nt(cu, M, N, K):
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    out = cu.gemm(a, b)
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    _check(out, a.float() @ b.float().t(), K)
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_nt_bias_and_bn128(cu, M, N, K):
+    torch.manual_seed(1)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    _check(cu.gemm(a, b, bias=bias), ref + bias.float(), K)
+    _check(cu.gemm(a, b, bn=128), ref, K)
+    cu.check_err_flag()
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_nn_dgrad_layout(cu, M, N, K):
+    """dx = dy · W with W stored [K_red, N_out] (MN-major B)."""
+    torch.manual_seed(2)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    out = cu.gemm(a, b, b_mn=True)
+    cu.check_err_flag()
+    _check(out, a.float() @ b.float(), K)
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_tn_wgrad_layout(cu, M, N, K):
+    """dW = dyᵀ · x with both operands stored [K_red, rows] (MN-major A and B), fp32 out."""
+    torch.manual_seed(3)
+    a = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    ref = a.float().t() @ b.float()
+    out = cu.gemm(a, b, a_mn=True, b_mn=True, out_mode=2)
+    _check(out, ref, K)
+    acc = torch.ones(M, N, device="cuda")
+    cu.gemm(a, b, out=acc, a_mn=True, b_mn=True, out_mode=1)
+    _check(acc - 1, ref, K)
+    out16 = cu.gemm(a, b, a_mn=True, b_mn=True)
+    _check(out16, ref, K)
+    cu.check_err_flag()
+
+
+def test_linear_autograd_matches_torch(cu):
+    from easyllm_b200 import ops
+    torch.manual_seed(5)
+    x = torch.randn(384, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(768, 512, device="cuda")).to(torch.bfloat16).requires_grad_()
+    b = torch.randn(768, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn(384, 768, device="cuda", dtype=torch.bfloat16)
+    ops.set_gemm_backend("tcgen05")
+    y = ops.linear(x, w, b)
+    y.backward(dy)
+    xf, wf, bf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_(), b.detach().float().requires_grad_()
+    yr = torch.nn.functional.linear(xf, wf, bf)
+    yr.backward(dy.float())
+    for got, want in ((y, yr), (x.grad, xf.grad), (w.grad, wf.grad), (b.grad, bf.grad)):
+        assert (got.float() - want).abs().max().item() <= 3e-2 * max(1.0, want.abs().max().item())
+    cu.check_err_flag()

@@ -1,0 +1,129 @@
+"""sm_100a elementwise / reduction kernels against fp32 PyTorch statements of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cu():
+    if not torch.cuda.is_available():
+        pytest.skip("no GPU")
+    import easyllm_b200.ops.cuda as cu
+    cu.lib()
+    return cu
+
+
+def _close(a, b, atol, rtol):
+    assert torch.allclose(a.float(), b.float(), atol=atol, rtol=rtol), (a.float() - b.float()).abs().max().item()
+
+
+@pytest.mark.parametrize("rows,cols", [(7, 256), (300, 4096), (1024, 5120), (33, 8192)])
+def test_rmsnorm_fwd_bwd(cu, rows, cols):
+    from easyllm_b200.ops import reference as ref
+    torch.manual_seed(0)
+    x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn_like(x)
+    w = (1 + 0.1 * torch.randn(cols, device="cuda")).to(torch.bfloat16)
+    y, _, rstd = cu.rmsnorm_fwd(x, None, w, 1e-5)
+    _close(y, ref.rmsnorm(x.float(), w.float(), 1e-5), 2e-2, 2e-2)
+    y2, h, rstd2 = cu.rmsnorm_fwd(x, res, w, 1e-5)
+    hr = (x.float() + res.float()).to(torch.bfloat16)
+    assert torch.equal(h, hr)
+    _close(y2, ref.rmsnorm(hr.float(), w.float(), 1e-5), 2e-2, 2e-2)
+    # backward vs autograd of the fp32 statement
+    dy = torch.randn_like(x)
+    dres = torch.randn_like(x)
+    hf = hr.float().requires_grad_()
+    wf = w.float().requires_grad_()
+    ref.rmsnorm(hf, wf, 1e-5).backward(dy.float())
+    dh, dw = cu.rmsnorm_bwd(dy, h, w, rstd2, dres)
+    _close(dh, hf.grad + dres.float(), 3e-2, 3e-2)
+    _close(dw, wf.grad, 5e-2 * max(1.0, wf.grad.abs().max().item()), 3e-2)
+    # accumulate mode adds onto an existing fp32 buffer
+    acc = torch.ones(cols, device="cuda")
+    cu.rmsnorm_bwd(dy, h, w, rstd2, None, dw_out=acc, accumulate=True)
+    _close(acc - 1, wf.grad, 5e-2 * max(1.0, wf.grad.abs().max().item()), 3e-2)
+
+
+@pytest.mark.parametrize("T,hq,hk,D", [(64, 4, 4, 128), (257, 8, 2, 128), (33, 4, 1, 64)])
+def test_rope_packed(cu, T, hq, hk, D):
+    from easyllm_b200.ops import reference as ref
+    torch.manual_seed(1)
+    W = (hq + 2 * hk) * D
+    qkv = torch.randn(T, W, device="cuda", dtype=torch.bfloat16)
+    pos = torch.randint(0, 500, (T,), device="cuda", dtype=torch.int32)
+    cos, sin = ref.rope_tables(D, 512, device="cuda")
+    q = qkv[:, :hq * D].reshape(T, hq, D).float()
+    k = qkv[:, hq * D:(hq + hk) * D].reshape(T, hk, D).float()
+    rq, rk = ref.rope(q, k, cos, sin, pos.long())
+    v_before = qkv[:, (hq + hk) * D:].clone()
+    orig = qkv.clone()
+    cu.rope_(qkv, cos, sin, pos, hq + hk, D)
+    _close(qkv[:, :hq * D].reshape(T, hq, D), rq, 2e-2, 2e-2)
+    _close(qkv[:, hq * D:(hq + hk) * D].reshape(T, hk, D), rk, 2e-2, 2e-2)
+    assert torch.equal(qkv[:, (hq + hk) * D:], v_before)
+    cu.rope_(qkv, cos, sin, pos, hq + hk, D, backward=True)   # inverse rotation
+    _close(qkv, orig, 3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("T,F", [(5, 64), (300, 11008), (128, 3456)])
+def test_swiglu(cu, T, F):
+    torch.manual_seed(2)
+    gu = torch.randn(T, 2 * F, device="cuda", dtype=torch.bfloat16)
+    out = cu.swiglu_fwd(gu)
+    g, u = gu[:, :F].float().requires_grad_(), gu[:, F:].float().requires_grad_()
+    r = torch.nn.functional.silu(g) * u
+    _close(out, r, 2e-2, 2e-2)
+    d = torch.randn(T, F, device="cuda", dtype=torch.bfloat16)
+    r.backward(d.float())
+    dgu = cu.swiglu_bwd(d, gu)
+    _close(dgu[:, :F], g.grad, 3e-2, 3e-2)
+    _close(dgu[:, F:], u.grad, 3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("n", [1000, 1 << 20, (1 << 20) + 3])
+def test_adam_and_sumsq(cu, n):
+    from easyllm_b200.ops import reference as ref
+    torch.manual_seed(3)
+    p = torch.randn(n, device="cuda"); g = torch.randn(n, device="cuda")
+    m = torch.rand(n, device="cuda") * 0.1; v = torch.rand(n, device="cuda") * 0.01
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    low = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    scale = torch.tensor([0.5], device="cuda")
+    cu.adam(p, g, m, v, low, 1e-3, 0.9, 0.95, 1e-8, 0.1, 7, True, 2.0, scale)
+    ref.adam_step(pr, g, mr, vr, 1e-3, 0.9, 0.95, 1e-8, 0.1, 7, True, 1.0)
+    _close(p, pr, 1e-6, 1e-5); _close(m, mr, 1e-6, 1e-5); _close(v, vr, 1e-7, 1e-5)
+    assert torch.equal(low, p.to(torch.bfloat16))
+    out = torch.zeros(1, device="cuda")
+    cu.sumsq(g, out)
+    _close(out, (g.double() ** 2).sum().float().view(1), 1e-2, 1e-4)
+
+
+@pytest.mark.parametrize("T,V,valid", [(17, 1000, 1000), (256, 32000, 32000), (64, 38016, 38000)])
+def test_cross_entropy(cu, T, V, valid):
+    torch.manual_seed(4)
+    logits = (3 * torch.randn(T, V, device="cuda")).to(torch.bfloat16)
+    tgt = torch.randint(0, valid, (T,), device="cuda")
+    parts = cu.ce_fwd(logits, tgt, 0, valid)
+    lf = logits.float()[:, :valid].requires_grad_()
+    ref_loss = torch.nn.functional.cross_entropy(lf, tgt, reduction="none")
+    lse = torch.log(parts[:, 1]) + parts[:, 0]
+    _close(lse - parts[:, 2], ref_loss, 2e-3, 2e-3)
+    scale = torch.rand(T, device="cuda")
+    (ref_loss * scale).sum().backward()
+    work = logits.clone()
+    cu.ce_bwd_(work, tgt, lse.contiguous(), scale, 0, valid)
+    _close(work[:, :valid], lf.grad, 2e-3, 2e-2)
+    if valid < V:
+        assert work[:, valid:].abs().max().item() == 0
+    # a shard that does not own the targets contributes target-logit 0
+    parts2 = cu.ce_fwd(logits, tgt, V, valid)
+    assert parts2[:, 2].abs().max().item() == 0
+
+
+def test_accumulate_bf16_into_fp32(cu):
+    x = torch.randn(100003, device="cuda").to(torch.bfloat16)
+    acc = torch.ones(100003, device="cuda")
+    cu.accum_bf16_to_f32(x, acc)
+    _close(acc, 1 + x.float(), 1e-6, 1e-6)

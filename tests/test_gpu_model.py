@@ -1,0 +1,54 @@
+"""Flagship model on the GPU: kernel path vs the PyTorch (library) path on the same weights,
+and the smoke entry point."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _need_gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("no GPU")
+
+
+def _run(backend, gemm, sd=None):
+    from easyllm_b200 import ops
+    from easyllm_b200.models import llama_custom
+    ops.set_backend(backend)
+    ops.set_gemm_backend(gemm)
+    torch.manual_seed(0)
+    m = llama_custom(num_layers=2, hidden_size=512, num_attention_heads=4, num_kv_attention_heads=2,
+                     intermediate_size=1408, vocab_size=32000, bf16=True, seq_length=256,
+                     checkpoint_activations=False)
+    if sd is not None:
+        m.load_state_dict(sd)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, 32000, (2, 256), generator=g).cuda()
+    lab = torch.roll(tok, -1, 1)
+    loss = m((tok, None, None), (lab, torch.ones_like(lab)))
+    loss.backward()
+    grads = {n: p.grad.float().clone() for n, p in m.named_parameters()}
+    return loss.item(), grads, m.state_dict()
+
+
+def test_kernel_path_matches_library_path():
+    _need_gpu()
+    from easyllm_b200 import ops
+    try:
+        l_ref, g_ref, sd = _run("torch", "cublas")
+        l_k, g_k, _ = _run("b200", "tcgen05", sd)
+    finally:
+        ops.set_backend("b200"); ops.set_gemm_backend("tcgen05")
+    assert abs(l_ref - l_k) < 3e-2, (l_ref, l_k)
+    for n in g_ref:
+        a, b = g_ref[n], g_k[n]
+        denom = a.abs().max().item() + 1e-6
+        assert (a - b).abs().max().item() / denom < 8e-2, n
+    import easyllm_b200.ops.cuda as cu
+    cu.check_err_flag()
+
+
+def test_smoke_entry():
+    _need_gpu()
+    import __graft_entry__ as ge
+    ge.smoke()
