@@ -40,6 +40,8 @@ MODELS = {
                       intermediate_size=11008),
     "llama2_13b": dict(num_layers=40, hidden_size=5120, num_attention_heads=40, num_kv_attention_heads=40,
                        intermediate_size=13824),
+    "llama2_7b_4l": dict(num_layers=4, hidden_size=4096, num_attention_heads=32, num_kv_attention_heads=32,
+                         intermediate_size=11008),
     "dev_1b": dict(num_layers=8, hidden_size=2048, num_attention_heads=16, num_kv_attention_heads=16,
                    intermediate_size=5632),
 }

@@ -36,7 +36,84 @@ constexpr int kABytes = kBM * kBK * 2;     // 16 KiB
 constexpr int kEpiBufBytes = 128 * 64 * 2; // one 128x64 bf16 store box
 
 enum GemmOut { kOutBf16 = 0, kOutF32Accum = 1, kOutF32 = 2 };
-enum GemmErr { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3 };
+enum GemmErr { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3, kErrComm = 4, kErrFlagWait = 5 };
+
+// ---- fusion with the tensor-parallel collective (sequence parallelism) ------------------------------
+//  kFuseAG  all-gather -> GEMM: the A operand is the concatenation over ranks of row shards.  CTAs
+//           [0, n_comm) copy this rank's shard into every rank's gathered buffer through peer pointers
+//           (plain 16-byte loads/stores over NVLink), one 128-row tile at a time, and publish a flag per
+//           tile; the GEMM CTAs start on the local shard and take remote shards in ring order, waiting
+//           on a tile's flag only before its first TMA load (always a load of local memory into one CTA).
+//  kFuseRS  GEMM -> reduce-scatter: every rank computes the full partial product; finished bf16 tiles
+//           go to a local staging buffer (TMA store) and a flag is raised on the tile's owner rank; CTAs
+//           [0, n_comm) of the owner sum the tp staged copies (peer loads, fp32 add, fixed order so the
+//           result is deterministic) into the local output shard while the main loop is still running.
+// Flags are epoch counters that only grow; a per-peer `done` word tells a producer that the consumer
+// has finished the previous epoch before a buffer is overwritten.  Every wait is bounded.
+enum GemmFuse { kFuseNone = 0, kFuseAG = 1, kFuseRS = 2 };
+constexpr int kMaxTp = 8;
+constexpr int kGroupM = 16;   // tiles are walked in groups of 16 M-tiles x all N-tiles for L2 reuse
+
+struct FuseArgs {
+  int rank, tp, n_comm, rows_per_rank, flags_per_src;
+  uint32_t epoch;
+  const __nv_bfloat16* x_local;          // AG: this rank's shard [rows_per_rank, K]
+  __nv_bfloat16* data_ptrs[kMaxTp];      // AG: gathered buffers [M, K]; RS: staging buffers [M, N]
+  uint32_t* flag_ptrs[kMaxTp];           // [tp][flags_per_src] on every rank
+  uint32_t* done_ptrs[kMaxTp];           // [tp] on every rank
+  unsigned int* counter;                 // local, monotonic: finished CTAs
+  __nv_bfloat16* y_local;                // RS: output shard [rows_per_rank, N]
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Bounded spin until *flag >= want.  False on timeout / abort.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, volatile int* abort_flag) {
+  if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while ((int32_t)(ld_acquire_sys(flag) - want) < 0) {
+    if ((++spins & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitTimeoutNs) return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void swizzle_tile(int idx, int tiles_m, int tiles_n, int& mt, int& nt) {
+  const int width = kGroupM * tiles_n;
+  const int group = idx / width, rem = idx % width;
+  const int first_m = group * kGroupM;
+  const int gsz = min(tiles_m - first_m, kGroupM);
+  mt = first_m + rem % gsz;
+  nt = rem / gsz;
+}
+
+template <int FUSE>
+__device__ __forceinline__ void map_tile(int idx, int tiles_m, int tiles_n, const FuseArgs& f, int& mt, int& nt) {
+  if (FUSE == kFuseAG) {
+    const int tpr = tiles_m / f.tp, per_phase = tpr * tiles_n;
+    const int phase = idx / per_phase;
+    int mi;
+    swizzle_tile(idx % per_phase, tpr, tiles_n, mi, nt);
+    mt = ((f.rank + phase) % f.tp) * tpr + mi;
+  } else if (FUSE == kFuseRS) {
+    int mp;
+    swizzle_tile(idx, tiles_m, tiles_n, mp, nt);
+    mt = (mp % f.tp) * (tiles_m / f.tp) + mp / f.tp;   // interleave owners so every owner is fed evenly
+  } else {
+    swizzle_tile(idx, tiles_m, tiles_n, mt, nt);
+  }
+}
 
 template <int BN>
 struct GemmCfg {
@@ -57,10 +134,102 @@ struct GemmShared {
   int epi_abort;
 };
 
-template <int BN, bool A_MN, bool B_MN, int OUT, bool HAS_BIAS>
+
+// ---- communication roles (CTAs [0, n_comm) of a fused launch) ---------------------------------------
+// All-gather side: copy 128-row tiles of the local shard into every rank's gathered buffer.
+__device__ void ag_comm_role(const FuseArgs& f, int K, int* err) {
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  const int tiles = f.rows_per_rank / kBM;
+  const size_t vec_per_tile = (size_t)kBM * K / 8;
+  for (int i = 0; i < f.tp; ++i) {
+    // self first (the local GEMM starts there), then the rank that needs this shard soonest
+    const int dest = (f.rank - i + f.tp) % f.tp;
+    if (dest != f.rank) {
+      // the destination must have consumed the previous epoch before its buffer is overwritten
+      if (threadIdx.x == 0 && !wait_flag_ge(f.done_ptrs[f.rank] + dest, f.epoch - 1, &s_abort)) {
+        s_abort = 1;
+        atomicCAS(err, 0, kErrComm);
+      }
+      __syncthreads();
+      if (s_abort) return;
+    }
+    __nv_bfloat16* dst_base = f.data_ptrs[dest] + (size_t)f.rank * f.rows_per_rank * K;
+    for (int t = blockIdx.x; t < tiles; t += f.n_comm) {
+      const uint4* src = reinterpret_cast<const uint4*>(f.x_local + (size_t)t * kBM * K);
+      uint4* dst = reinterpret_cast<uint4*>(dst_base + (size_t)t * kBM * K);
+      size_t v = threadIdx.x;
+      for (; v + 3 * kGemmThreads < vec_per_tile; v += 4 * kGemmThreads) {
+        uint4 a = src[v], b = src[v + kGemmThreads], c = src[v + 2 * kGemmThreads], d = src[v + 3 * kGemmThreads];
+        dst[v] = a;
+        dst[v + kGemmThreads] = b;
+        dst[v + 2 * kGemmThreads] = c;
+        dst[v + 3 * kGemmThreads] = d;
+      }
+      for (; v < vec_per_tile; v += kGemmThreads) dst[v] = src[v];
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0)
+        st_release_sys(f.flag_ptrs[dest] + (size_t)f.rank * f.flags_per_src + t, f.epoch);
+    }
+  }
+}
+
+// Reduce-scatter side: sum the tp staged copies of every tile this rank owns into y_local.
+template <int BN>
+__device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err) {
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  const int tpr = f.rows_per_rank / kBM;
+  const int owned = tpr * tiles_n;
+  const int gm = max(1, kGroupM / f.tp);          // matches the order in which producers emit owned tiles
+  for (int j = blockIdx.x; j < owned; j += f.n_comm) {
+    const int width = gm * tiles_n, g = j / width, rem = j % width;
+    const int first = g * gm, gsz = min(tpr - first, gm);
+    const int mi = first + rem % gsz, nt = rem / gsz;
+    if ((int)threadIdx.x < f.tp) {
+      const uint32_t* fl = f.flag_ptrs[f.rank] + (size_t)threadIdx.x * f.flags_per_src + mi * tiles_n + nt;
+      if (!wait_flag_ge(fl, f.epoch, &s_abort)) {
+        s_abort = 1;
+        atomicCAS(err, 0, kErrComm);
+      }
+    }
+    __syncthreads();
+    if (s_abort) return;
+    const int cols = min(BN, N - nt * BN), cvec = cols / 8;
+    const size_t grow0 = (size_t)f.rank * f.rows_per_rank + (size_t)mi * kBM;
+    for (int v = threadIdx.x; v < kBM * cvec; v += kGemmThreads) {
+      const int r = v / cvec, c = (v % cvec) * 8 + nt * BN;
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int s = 0; s < f.tp; ++s) {
+        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(f.data_ptrs[s] + (grow0 + r) * N + c));
+        float t[8];
+        unpack8(*reinterpret_cast<const bf16x8*>(&raw), t);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += t[e];
+      }
+      *reinterpret_cast<bf16x8*>(f.y_local + ((size_t)mi * kBM + r) * N + c) = pack8(acc);
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int old = atomicAdd(f.counter, 1u);
+    if ((old + 1) % (unsigned int)f.n_comm == 0) {
+      for (int p = 0; p < f.tp; ++p)
+        if (p != f.rank) st_release_sys(f.done_ptrs[p] + f.rank, f.epoch);
+    }
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, int OUT, bool HAS_BIAS, int FUSE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, float* __restrict__ Cf32,
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ FuseArgs fuse,
                  const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc, int* __restrict__ err) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -74,6 +243,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + kBK - 1) / kBK;
+  const int n_comm = FUSE == kFuseNone ? 0 : fuse.n_comm;
+  const int cta0 = (int)blockIdx.x - n_comm;            // index among the GEMM CTAs
+  const int cta_stride = (int)gridDim.x - n_comm;
+
+  if (FUSE != kFuseNone && (int)blockIdx.x < n_comm) {
+    if (FUSE == kFuseAG) ag_comm_role(fuse, K, err);
+    else rs_reduce_role<BN>(fuse, N, tiles_n, err);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -89,7 +267,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
-    if (OUT == kOutBf16) tma_prefetch_desc(&tmC);
+    tma_prefetch_desc(&tmC);
   }
   if (warp == 1) tmem_alloc<Cfg::kTmemCols>(&sh->tmem_base);
   tc_fence_before();
@@ -104,8 +282,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * kBM, n0 = (tile / tiles_m) * BN;
+      for (int tile = cta0; tile < num_tiles && ok; tile += cta_stride) {
+        int mt, nt;
+        map_tile<FUSE>(tile, tiles_m, tiles_n, fuse, mt, nt);
+        const int m0 = mt * kBM, n0 = nt * BN;
+        if (FUSE == kFuseAG) {
+          // rows of this tile come from rank `src`; its copy into the local gathered buffer is flagged
+          const int src = m0 / fuse.rows_per_rank;
+          const uint32_t* fl = fuse.flag_ptrs[fuse.rank] + (size_t)src * fuse.flags_per_src +
+                               (m0 - src * fuse.rows_per_rank) / kBM;
+          if (!wait_flag_ge(fl, fuse.epoch, abort_flag)) {
+            ok = false;
+            atomicCAS(err, 0, kErrFlagWait);
+            break;
+          }
+          fence_proxy_async_all();   // peer stores (generic proxy) -> TMA reads (async proxy)
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) {
             ok = false;
@@ -152,7 +344,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = cta0; tile < num_tiles && ok; tile += cta_stride, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&sh->tmem_empty[acc], acc_phase ^ 1, abort_flag)) {
@@ -195,8 +387,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool leader = (threadIdx.x == 64);
     int it = 0;
     uint32_t store_count = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
-      const int m0 = (tile % tiles_m) * kBM, n0 = (tile / tiles_m) * BN;
+    if (FUSE == kFuseRS && leader) {
+      // peers must have finished reading last epoch's staged tiles before they are overwritten
+      for (int p = 0; p < fuse.tp; ++p)
+        if (p != fuse.rank && !wait_flag_ge(fuse.done_ptrs[fuse.rank] + p, fuse.epoch - 1, abort_flag)) {
+          sh->epi_abort = 1;
+          atomicCAS(err, 0, kErrFlagWait);
+        }
+    }
+    for (int tile = cta0; tile < num_tiles; tile += cta_stride, ++it) {
+      int mt, nt;
+      map_tile<FUSE>(tile, tiles_m, tiles_n, fuse, mt, nt);
+      const int m0 = mt * kBM, n0 = nt * BN;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&sh->tmem_full[acc], acc_phase, abort_flag)) sh->epi_abort = 1;
@@ -244,35 +446,42 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           ++store_count;
         }
+        if (FUSE == kFuseRS && leader) {
+          // the staged tile is complete in global memory: raise its flag on the owner rank
+          tma_store_wait_all<0>();
+          __threadfence_system();
+          const int owner = m0 / fuse.rows_per_rank;
+          const int mi = (m0 - owner * fuse.rows_per_rank) / kBM;
+          st_release_sys(fuse.flag_ptrs[owner] + (size_t)fuse.rank * fuse.flags_per_src + mi * tiles_n + nt,
+                         fuse.epoch);
+        }
       } else {
-        const int row = m0 + row_in_tile;
+        // fp32 output: 128 x 32 sub-tiles staged in swizzled smem, then a TMA store (overwrite) or
+        // a TMA reduce-add (gradient accumulation: the add happens at L2, the SM never reads C)
 #pragma unroll 1
         for (int j = 0; j < BN / 32; ++j) {
+          uint8_t* buf = sC + (store_count & 1) * kEpiBufBytes;
+          if (leader) tma_store_wait_read<1>();
+          named_bar_sync(1, kEpiThreads);
           uint32_t r[32];
-          tmem_ld_32x32(t_row + j * 32, r);   // warp-collective: every lane participates
+          tmem_ld_32x32(t_row + j * 32, r);
           tmem_ld_wait();
-          const int col0 = n0 + j * 32;
-          if (row < M && col0 < N) {
-            float* dst = Cf32 + (size_t)row * ldc + col0;
-            if (col0 + 32 <= N && (ldc & 3) == 0) {
+          uint8_t* row_ptr = buf + row_in_tile * 128;
 #pragma unroll
-              for (int c = 0; c < 8; ++c) {
-                float4 v = make_float4(__uint_as_float(r[4 * c]), __uint_as_float(r[4 * c + 1]),
-                                       __uint_as_float(r[4 * c + 2]), __uint_as_float(r[4 * c + 3]));
-                if (OUT == kOutF32Accum) {
-                  float4 o = reinterpret_cast<float4*>(dst)[c];
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                reinterpret_cast<float4*>(dst)[c] = v;
-              }
-            } else {
-              for (int c = 0; c < 32 && col0 + c < N; ++c) {
-                float v = __uint_as_float(r[c]);
-                if (OUT == kOutF32Accum) v += dst[c];
-                dst[c] = v;
-              }
-            }
+          for (int c = 0; c < 8; ++c) {
+            uint4 v = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+            *reinterpret_cast<uint4*>(row_ptr + ((c ^ (row_in_tile & 7)) << 4)) = v;
           }
+          fence_proxy_async_smem();
+          named_bar_sync(1, kEpiThreads);
+          if (leader) {
+            if (n0 + j * 32 < N) {
+              if (OUT == kOutF32Accum) tma_reduce_add_2d(&tmC, buf, n0 + j * 32, m0);
+              else tma_store_2d(&tmC, buf, n0 + j * 32, m0);
+            }
+            tma_store_commit();
+          }
+          ++store_count;
         }
       }
       tc_fence_before();
@@ -282,7 +491,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       sh->abort_flag = 1;
       atomicCAS(err, 0, kErrEpilogue);
     }
-    if (OUT == kOutBf16 && leader) tma_store_wait_all<0>();
+    if (leader) tma_store_wait_all<0>();
   }
 
   __syncthreads();
@@ -296,6 +505,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<Cfg::kTmemCols>(tmem_base);
+  }
+  if (FUSE == kFuseAG && threadIdx.x == 0) {
+    // last GEMM CTA of this rank: tell every peer that its pushes of this epoch were consumed
+    __threadfence();
+    const unsigned int old = atomicAdd(fuse.counter, 1u);
+    if ((old + 1) % (unsigned int)cta_stride == 0) {
+      for (int p = 0; p < fuse.tp; ++p)
+        if (p != fuse.rank) st_release_sys(fuse.done_ptrs[p] + fuse.rank, fuse.epoch);
+    }
   }
 }
 
@@ -317,8 +535,21 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows of `row_stride_bytes`.
+static int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* ptr, uint64_t inner, uint64_t outer,
+                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
+
 int make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                       uint32_t box_inner, uint32_t box_outer) {
+  return make_tmap_2d(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, ptr, inner, outer, row_stride_bytes, box_inner, box_outer);
+}
+
+int make_tmap_f32_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                     uint32_t box_inner, uint32_t box_outer) {
+  return make_tmap_2d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, ptr, inner, outer, row_stride_bytes, box_inner, box_outer);
+}
+
+static int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* ptr, uint64_t inner, uint64_t outer,
+                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -10;
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (row_stride_bytes & 15)) return -11;
@@ -326,17 +557,17 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_
   cuuint64_t strides[1] = {row_stride_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  CUresult r = fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -12;
 }
 
-template <int BN, bool A_MN, bool B_MN, int OUT, bool HAS_BIAS>
-static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, float* Cf32,
+template <int BN, bool A_MN, bool B_MN, int OUT, bool HAS_BIAS, int FUSE = kFuseNone>
+static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, const FuseArgs& fuse,
                        const __nv_bfloat16* bias, int M, int N, int K, int ldc, int* err, int max_ctas,
                        cudaStream_t stream) {
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OUT, HAS_BIAS>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OUT, HAS_BIAS, FUSE>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::kSmemBytes);
@@ -344,8 +575,8 @@ static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
     configured = true;
   }
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
-  int grid = tiles < max_ctas ? tiles : max_ctas;
-  kern<<<grid, kGemmThreads, GemmCfg<BN>::kSmemBytes, stream>>>(tA, tB, tC, Cf32, bias, M, N, K, ldc, err);
+  int grid = (FUSE != kFuseNone || tiles >= max_ctas) ? max_ctas : tiles;   // fused launches keep a fixed grid
+  kern<<<grid, kGemmThreads, GemmCfg<BN>::kSmemBytes, stream>>>(tA, tB, tC, fuse, bias, M, N, K, ldc, err);
   return launch_status();
 }
 
@@ -385,10 +616,11 @@ ELL_API int ell_gemm_bf16(const void* A, const void* B, void* C, const void* bia
     rc = make_tmap_bf16_2d(&tC, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64, 128);
     if (rc) return rc;
   } else {
-    tC = tA;
+    rc = make_tmap_f32_2d(&tC, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 4, 32, 128);
+    if (rc) return rc;
   }
   const int ctas = sm_count();
-  float* Cf = reinterpret_cast<float*>(C);
+  FuseArgs Cf{};
   const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(bias);
 #define ELL_GEMM_CASE(BN_, AM_, BM_, OUT_, BIAS_)                                                             \
   if (BN == BN_ && (bool)a_mn == AM_ && (bool)b_mn == BM_ && out_mode == OUT_ && (bias != nullptr) == BIAS_) \
@@ -405,4 +637,81 @@ ELL_API int ell_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   ELL_GEMM_BN(256)
   ELL_GEMM_BN(128)
   return -3;
+}
+
+static void fill_fuse(FuseArgs& f, int rank, int tp, int n_comm, int rows_per_rank, int flags_per_src,
+                      unsigned int epoch, void* const* data_ptrs, void* const* flag_ptrs, void* const* done_ptrs,
+                      void* counter) {
+  f.rank = rank; f.tp = tp; f.n_comm = n_comm; f.rows_per_rank = rows_per_rank; f.flags_per_src = flags_per_src;
+  f.epoch = epoch;
+  for (int i = 0; i < tp; ++i) {
+    f.data_ptrs[i] = (__nv_bfloat16*)data_ptrs[i];
+    f.flag_ptrs[i] = (uint32_t*)flag_ptrs[i];
+    f.done_ptrs[i] = (uint32_t*)done_ptrs[i];
+  }
+  f.counter = (unsigned int*)counter;
+}
+
+// All-gather -> GEMM.  out[tp*rows_per_rank, N] = gather(x_local)[.., K] · W[N, K]^T (+ bias).
+// gathered_ptrs[r] is rank r's gathered buffer [tp*rows_per_rank, K] (peer pointers; entry `rank` is local);
+// flag_ptrs[r] / done_ptrs[r] are rank r's flag ([tp][flags_per_src]) and done ([tp]) words.
+ELL_API int ell_gemm_ag(const void* x_local, const void* W, void* out, const void* bias, int rows_per_rank, int N,
+                        int K, int rank, int tp, unsigned int epoch, int n_comm, void* const* gathered_ptrs,
+                        void* const* flag_ptrs, void* const* done_ptrs, void* counter, int flags_per_src, int* err,
+                        cudaStream_t stream) {
+  if (tp < 1 || tp > kMaxTp || rows_per_rank % kBM || rows_per_rank / kBM > flags_per_src) return -2;
+  const int M = rows_per_rank * tp;
+  const int BN = N >= 256 ? 256 : 128;
+  CUtensorMap tA, tB, tC;
+  int rc = make_tmap_bf16_2d(&tA, gathered_ptrs[rank], (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBK, kBM);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tB, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, kBK, BN);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tC, out, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 128);
+  if (rc) return rc;
+  FuseArgs f{};
+  fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, gathered_ptrs, flag_ptrs, done_ptrs, counter);
+  f.x_local = (const __nv_bfloat16*)x_local;
+  const int ctas = sm_count();
+  if (n_comm < 1 || n_comm >= ctas) return -2;
+  const __nv_bfloat16* bp = (const __nv_bfloat16*)bias;
+  if (BN == 256) {
+    if (bias) return launch_gemm<256, false, false, kOutBf16, true, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream);
+    return launch_gemm<256, false, false, kOutBf16, false, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream);
+  }
+  if (bias) return launch_gemm<128, false, false, kOutBf16, true, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream);
+  return launch_gemm<128, false, false, kOutBf16, false, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream);
+}
+
+// GEMM -> reduce-scatter.  y_local[rows_per_rank, N] = sum over ranks of (x[M, K] · op(W))[own rows].
+// b_mn = 0: W is [N, K] (forward of a row-parallel linear); b_mn = 1: W is [K, N] (its use as dgrad of a
+// column-parallel linear).  stage_ptrs[r] is rank r's staging buffer [M, N].
+ELL_API int ell_gemm_rs(const void* x, const void* W, void* y_local, int rows_per_rank, int N, int K, int b_mn,
+                        int rank, int tp, unsigned int epoch, int n_comm, void* const* stage_ptrs,
+                        void* const* flag_ptrs, void* const* done_ptrs, void* counter, int flags_per_src, int* err,
+                        cudaStream_t stream) {
+  if (tp < 1 || tp > kMaxTp || rows_per_rank % kBM || N % 8) return -2;
+  const int M = rows_per_rank * tp;
+  const int BN = N >= 256 ? 256 : 128;
+  const int tiles_n = (N + BN - 1) / BN;
+  if ((rows_per_rank / kBM) * tiles_n > flags_per_src) return -2;
+  CUtensorMap tA, tB, tC;
+  int rc = make_tmap_bf16_2d(&tA, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBK, kBM);
+  if (rc) return rc;
+  if (!b_mn) rc = make_tmap_bf16_2d(&tB, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, kBK, BN);
+  else       rc = make_tmap_bf16_2d(&tB, W, (uint64_t)N, (uint64_t)K, (uint64_t)N * 2, 64, kBK);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tC, stage_ptrs[rank], (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 128);
+  if (rc) return rc;
+  FuseArgs f{};
+  fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, stage_ptrs, flag_ptrs, done_ptrs, counter);
+  f.y_local = (__nv_bfloat16*)y_local;
+  const int ctas = sm_count();
+  if (n_comm < 1 || n_comm >= ctas) return -2;
+  if (BN == 256) {
+    if (b_mn) return launch_gemm<256, false, true, kOutBf16, false, kFuseRS>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);
+    return launch_gemm<256, false, false, kOutBf16, false, kFuseRS>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);
+  }
+  if (b_mn) return launch_gemm<128, false, true, kOutBf16, false, kFuseRS>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);
+  return launch_gemm<128, false, false, kOutBf16, false, kFuseRS>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);
 }

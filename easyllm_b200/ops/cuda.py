@@ -241,3 +241,61 @@ def has_symbol(name):
         return True
     except AttributeError:
         return False
+
+
+# ---- flash attention -------------------------------------------------------------------------
+def _row_start(cu_seqlens, T, device):
+    if cu_seqlens is None:
+        return torch.zeros(T, dtype=torch.int32, device=device)
+    cu = cu_seqlens.to(device=device, dtype=torch.int64)
+    return torch.repeat_interleave(cu[:-1], cu[1:] - cu[:-1], output_size=T).to(torch.int32)
+
+
+def flash_attn_fwd(q, k, v, row_start, scale):
+    """q [T,Hq,128], k/v [T,Hk,128] (last two dims contiguous, any row stride) → (out, lse [Hq,T])."""
+    T, Hq, D = q.shape
+    Hk = k.shape[1]
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        if t.dtype != torch.bfloat16 or t.stride(2) != 1 or t.stride(1) != D:
+            raise ValueError(f"flash_attn_fwd: {n} must be bf16 with contiguous [heads, 128] rows")
+    if D != 128 or k.stride(0) != v.stride(0):
+        raise ValueError("flash_attn_fwd: head_dim must be 128 and k/v must share a row stride")
+    out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+    rc = lib().ell_flash_attn_fwd(_p(q), _p(k), _p(v), _p(out), _p(lse), _p(row_start), c_int(T), c_int(Hq), c_int(Hk),
+                                  c_int(q.stride(0)), c_int(k.stride(0)), c_float(scale), _p(err_flag(q.device)),
+                                  _stream())
+    _check(rc, "flash_attn_fwd")
+    return out, lse
+
+
+class _FlashAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, scale):
+        T = q.shape[0]
+        rs = _row_start(cu_seqlens, T, q.device)
+        out, lse = flash_attn_fwd(q, k, v, rs, scale)
+        ctx.save_for_backward(q, k, v, out, lse, rs, cu_seqlens if cu_seqlens is not None else torch.empty(0))
+        ctx.meta = (max_seqlen, scale, cu_seqlens is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, out, lse, rs, cu = ctx.saved_tensors
+        max_seqlen, scale, has_cu = ctx.meta
+        if has_symbol("ell_flash_attn_bwd"):
+            dq, dk, dv = flash_attn_bwd(do.contiguous(), q, k, v, out, lse, rs, scale)
+            return dq, dk, dv, None, None, None
+        # until the backward kernel is built: differentiate the library attention on the same inputs
+        from . import _library_attention
+        with torch.enable_grad():
+            qq, kk, vv = (t.detach().requires_grad_() for t in (q, k, v))
+            o = _library_attention(qq, kk, vv, cu if has_cu else None, max_seqlen, True, scale)
+            dq, dk, dv = torch.autograd.grad(o, (qq, kk, vv), do)
+        return dq, dk, dv, None, None, None
+
+
+def flash_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale):
+    if not causal:
+        raise ValueError("the attention kernel is causal-only")
+    return _FlashAttn.apply(q, k, v, cu_seqlens, max_seqlen, scale)

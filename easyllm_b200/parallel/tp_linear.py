@@ -69,8 +69,9 @@ class _ColumnSP(torch.autograd.Function):
     def forward(ctx, x, w, bias):
         ctx.wref, ctx.bref = w, bias
         fused = _FUSED["ag_gemm"] if _use_fused(x) else None
-        if fused is not None:
-            y, _ = fused(x, w, bias)
+        res = fused(x, w, bias) if fused is not None else None
+        if res is not None:
+            y = res[0]
         else:
             xg, work = _ag_start(x, "sp_gather")
             work.wait()
@@ -84,10 +85,9 @@ class _ColumnSP(torch.autograd.Function):
         dy = dy.contiguous()
         xg, ag_work = _ag_start(x, "sp_gather_bwd")          # re-gather ‖ dgrad GEMM
         fused_rs = _FUSED["gemm_rs"] if _use_fused(dy) else None
-        if fused_rs is not None:
-            dx = fused_rs(dy, w, b_mn=True)
-            rs_work = None
-        else:
+        dx = fused_rs(dy, w, b_mn=True) if fused_rs is not None else None
+        rs_work = None
+        if dx is None:
             dxg = ops.matmul_nn(dy, w)
             dx, rs_work = _rs_start(dxg)                      # reduce-scatter ‖ wgrad GEMM
         ag_work.wait()
@@ -107,7 +107,9 @@ class _RowSP(torch.autograd.Function):
         ctx.save_for_backward(x, w)
         fused = _FUSED["gemm_rs"] if _use_fused(x) else None
         if fused is not None:
-            return fused(x, w)
+            out = fused(x, w)
+            if out is not None:
+                return out
         y = ops.matmul_nt(x, w)
         out, work = _rs_start(y)
         if work is not None:

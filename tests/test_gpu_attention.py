@@ -1,0 +1,69 @@
+"""tcgen05 flash attention (causal, GQA, packed documents) against fp32 exact attention."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cu():
+    if not torch.cuda.is_available():
+        pytest.skip("no GPU")
+    import easyllm_b200.ops.cuda as cu
+    cu.lib()
+    return cu
+
+
+CASES = [  # T, Hq, Hk, cu_seqlens
+    (128, 2, 2, None), (256, 4, 4, None), (300, 4, 2, None), (1024, 8, 1, None),
+    (512, 4, 4, [0, 100, 101, 350, 512]), (777, 2, 1, [0, 128, 256, 640, 777]), (4096, 4, 4, None),
+]
+
+
+@pytest.mark.parametrize("T,Hq,Hk,cu_list", CASES)
+def test_flash_fwd(cu, T, Hq, Hk, cu_list):
+    from easyllm_b200.ops import reference as ref
+    torch.manual_seed(T + Hq)
+    W = (Hq + 2 * Hk) * 128
+    qkv = torch.randn(T, W, device="cuda", dtype=torch.bfloat16)      # views into a packed buffer
+    q = qkv[:, :Hq * 128].view(T, Hq, 128)
+    k = qkv[:, Hq * 128:(Hq + Hk) * 128].view(T, Hk, 128)
+    v = qkv[:, (Hq + Hk) * 128:].view(T, Hk, 128)
+    cs = torch.tensor(cu_list, dtype=torch.int32, device="cuda") if cu_list else None
+    rs = cu._row_start(cs, T, q.device)
+    scale = 128 ** -0.5
+    out, lse = cu.flash_attn_fwd(q, k, v, rs, scale)
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    want = ref.attention_varlen(q.float(), k.float(), v.float(), cs, True, scale)
+    err = (out.float() - want).abs().max().item()
+    assert err < 2e-2, err
+    # log-sum-exp of the first head against the exact one
+    rep = Hq // Hk
+    s = torch.einsum("td,sd->ts", q[:, 0].float(), k[:, 0].float()) * scale
+    idx = torch.arange(T, device="cuda")
+    mask = (idx[None, :] > idx[:, None]) | (idx[None, :] < rs[:, None])
+    s = s.masked_fill(mask, float("-inf"))
+    assert (torch.logsumexp(s, -1) - lse[0]).abs().max().item() < 2e-2
+
+
+def test_flash_autograd_path(cu):
+    from easyllm_b200 import ops
+    from easyllm_b200.ops import reference as ref
+    torch.manual_seed(0)
+    T, H = 384, 2
+    q = torch.randn(T, H, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(T, H, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(T, H, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    ops.set_attention_backend("kernel")
+    try:
+        o = ops.flash_attention(q, k, v, None, T, True)
+        do = torch.randn_like(o)
+        o.backward(do)
+    finally:
+        ops.set_attention_backend("auto")
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    of = ref.attention_varlen(qf, kf, vf, None, True)
+    of.backward(do.float())
+    for a, b in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
+        assert (a.float() - b).abs().max().item() < 5e-2 * max(1.0, b.abs().max().item())
