@@ -106,6 +106,7 @@ def main():
     ap.add_argument("--ops", default=None, choices=[None, "b200", "torch"])
     ap.add_argument("--recompute-layers", type=int, default=0, help="leading layers per stage to recompute")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--no-fused-tp", action="store_true", help="use the NCCL + GEMM composition for TP linears")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -146,6 +147,11 @@ def main():
         dc = {"enabled": True, "size_map": {1 << 30: args.recompute_layers}}
     model = llama_custom(vocab_size=32000, seq_length=args.seq, bf16=True, sequence_parallel=g.tp > 1,
                          checkpoint_activations=False, dynamic_checkpoint=dc, pp_partition_method="parameters", **shape)
+    fused_tp = False
+    if g.tp > 1 and not args.no_fused_tp and ops.get_backend() == "b200":
+        from easyllm_b200.parallel import symm
+        symm.install(args.seq, shape["hidden_size"])
+        fused_tp = True
     opt = ZeroOptimizer(model.named_parameters(), lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
                         stage=args.zero, grad_clip=1.0)
     n_micro = args.seqs_per_gpu * g.tp * g.pp          # per DP rank: global / dp
@@ -223,7 +229,7 @@ def main():
                "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq,
                           "parallelism": f"tp{g.tp}pp{g.pp}dp{g.dp}-zero{args.zero}" + ("-sp" if g.tp > 1 else ""),
                           "micro_batch": 1, "grad_accum": n_micro, "optimizer": "fused Adam wd 0.1 clip 1.0",
-                          "gemm": ops.get_gemm_backend(), "ops": ops.get_backend(),
+                          "gemm": ops.get_gemm_backend(), "ops": ops.get_backend(), "fused_tp": fused_tp,
                           "recompute_layers": args.recompute_layers,
                           "l2": "inputs (weights+activations) far larger than L2; no flush",
                           "vs_baseline_note": "per-GPU tokens/s over the published 4304 tok/s/GPU "

@@ -48,8 +48,11 @@ def merge_opts_into_cfg(opts, cfg):
         val = try_decode(raw)
         if "-" in key:
             head, tail = key.split("-", 1)
-            list_key, want_type = head.split(".", 1)
-            entries = cfg.setdefault(list_key, [])
+            *list_path, want_type = head.split(".")
+            node = cfg
+            for k in list_path[:-1]:
+                node = node.setdefault(k, {})
+            entries = node.setdefault(list_path[-1], [])
             hit = False
             for entry in entries:
                 if entry.get("type") == want_type:

@@ -136,86 +136,173 @@ struct GemmShared {
 
 
 // ---- communication roles (CTAs [0, n_comm) of a fused launch) ---------------------------------------
-// All-gather side: copy 128-row tiles of the local shard into every rank's gathered buffer.
-__device__ void ag_comm_role(const FuseArgs& f, int K, int* err) {
-  __shared__ int s_abort;
-  if (threadIdx.x == 0) s_abort = 0;
-  __syncthreads();
+// Both roles move data with the bulk-copy engine (cp.async.bulk through a shared-memory ring), driven by
+// one thread, so a CTA keeps ~190 KB in flight: NVLink latency is hidden without many threads or SMs.
+constexpr int kCommStages = 6;
+constexpr int kCommChunkBytes = 32768;
+
+struct CommShared {
+  uint64_t full[kCommStages];
+  uint64_t empty[kCommStages];
+  int abort_flag;
+};
+
+// All-gather side: copy the local shard, tile by tile, into the gathered buffer of every other rank.
+// (The local GEMM reads its own shard in place; nothing is copied to self.)
+__device__ void ag_comm_role(const FuseArgs& f, int K, int* err, uint8_t* smem) {
+  CommShared* cs = reinterpret_cast<CommShared*>(smem + kCommStages * kCommChunkBytes);
+  if (threadIdx.x != 0) return;
+  for (int s = 0; s < kCommStages; ++s) mbar_init(&cs->full[s], 1);
+  cs->abort_flag = 0;
+  fence_barrier_init();
+  volatile int* abort_flag = &cs->abort_flag;
   const int tiles = f.rows_per_rank / kBM;
-  const size_t vec_per_tile = (size_t)kBM * K / 8;
-  for (int i = 0; i < f.tp; ++i) {
-    // self first (the local GEMM starts there), then the rank that needs this shard soonest
-    const int dest = (f.rank - i + f.tp) % f.tp;
-    if (dest != f.rank) {
-      // the destination must have consumed the previous epoch before its buffer is overwritten
-      if (threadIdx.x == 0 && !wait_flag_ge(f.done_ptrs[f.rank] + dest, f.epoch - 1, &s_abort)) {
-        s_abort = 1;
+  const size_t tile_bytes = (size_t)kBM * K * 2;
+  const int chunks = (int)((tile_bytes + kCommChunkBytes - 1) / kCommChunkBytes);
+  // destinations must have consumed the previous epoch before their buffers are overwritten
+  for (int d = 0; d < f.tp; ++d)
+    if (d != f.rank && !wait_flag_ge(f.done_ptrs[f.rank] + d, f.epoch - 1, abort_flag)) {
+      atomicCAS(err, 0, kErrComm);
+      return;
+    }
+  uint32_t issued = 0, landed = 0;   // chunk counters across tiles select ring stage and parity
+  for (int t = blockIdx.x; t < tiles; t += f.n_comm) {
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(f.x_local) + (size_t)t * tile_bytes;
+    const size_t dst_off = ((size_t)f.rank * f.rows_per_rank + (size_t)t * kBM) * K * 2;
+    int next_load = 0;
+    auto issue_load = [&](int c) {
+      const uint32_t st = issued % kCommStages;
+      const uint32_t bytes = (uint32_t)min((size_t)kCommChunkBytes, tile_bytes - (size_t)c * kCommChunkBytes);
+      mbar_expect_tx(&cs->full[st], bytes);
+      bulk_load(smem + st * kCommChunkBytes, src + (size_t)c * kCommChunkBytes, bytes, &cs->full[st]);
+      ++issued;
+    };
+    for (; next_load < chunks && next_load < kCommStages - 1; ++next_load) issue_load(next_load);
+    for (int c = 0; c < chunks; ++c) {
+      const uint32_t st = landed % kCommStages;
+      if (!mbar_wait(&cs->full[st], (landed / kCommStages) & 1, abort_flag)) {
         atomicCAS(err, 0, kErrComm);
+        return;
       }
-      __syncthreads();
-      if (s_abort) return;
-    }
-    __nv_bfloat16* dst_base = f.data_ptrs[dest] + (size_t)f.rank * f.rows_per_rank * K;
-    for (int t = blockIdx.x; t < tiles; t += f.n_comm) {
-      const uint4* src = reinterpret_cast<const uint4*>(f.x_local + (size_t)t * kBM * K);
-      uint4* dst = reinterpret_cast<uint4*>(dst_base + (size_t)t * kBM * K);
-      size_t v = threadIdx.x;
-      for (; v + 3 * kGemmThreads < vec_per_tile; v += 4 * kGemmThreads) {
-        uint4 a = src[v], b = src[v + kGemmThreads], c = src[v + 2 * kGemmThreads], d = src[v + 3 * kGemmThreads];
-        dst[v] = a;
-        dst[v + kGemmThreads] = b;
-        dst[v + 2 * kGemmThreads] = c;
-        dst[v + 3 * kGemmThreads] = d;
+      ++landed;
+      const uint32_t bytes = (uint32_t)min((size_t)kCommChunkBytes, tile_bytes - (size_t)c * kCommChunkBytes);
+      for (int i = 1; i < f.tp; ++i) {
+        const int dest = (f.rank - i + f.tp) % f.tp;   // the rank that needs this shard soonest first
+        bulk_store(reinterpret_cast<uint8_t*>(f.data_ptrs[dest]) + dst_off + (size_t)c * kCommChunkBytes,
+                   smem + st * kCommChunkBytes, bytes);
       }
-      for (; v < vec_per_tile; v += kGemmThreads) dst[v] = src[v];
-      __threadfence_system();
-      __syncthreads();
-      if (threadIdx.x == 0)
-        st_release_sys(f.flag_ptrs[dest] + (size_t)f.rank * f.flags_per_src + t, f.epoch);
+      tma_store_commit();
+      if (next_load < chunks) {
+        tma_store_wait_read<1>();   // the stage about to be refilled was last read by the previous group
+        issue_load(next_load++);
+      }
     }
+    tma_store_wait_all<0>();        // the whole tile has been written on every destination
+    fence_proxy_async_all();
+    __threadfence_system();
+    for (int d = 0; d < f.tp; ++d)
+      if (d != f.rank) st_release_sys(f.flag_ptrs[d] + (size_t)f.rank * f.flags_per_src + t, f.epoch);
   }
+}
+
+// Staged tile layout of GEMM->reduce-scatter: every 128x64 bf16 sub-tile is one contiguous 16 KiB block
+// (rows of 128 B, 16-byte chunks XOR-swizzled by row & 7, exactly as the epilogue wrote them to smem).
+template <int BN>
+__device__ __forceinline__ size_t stage_block(int mt, int nt, int j, int tiles_n) {
+  return ((size_t)(mt * tiles_n + nt) * (BN / 64) + j) * kEpiBufBytes;
 }
 
 // Reduce-scatter side: sum the tp staged copies of every tile this rank owns into y_local.
 template <int BN>
-__device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err) {
-  __shared__ int s_abort;
-  if (threadIdx.x == 0) s_abort = 0;
+__device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err, uint8_t* smem) {
+  CommShared* cs = reinterpret_cast<CommShared*>(smem + kCommStages * kCommChunkBytes);
+  constexpr int kConsumers = kGemmThreads - 32;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kCommStages; ++s) {
+      mbar_init(&cs->full[s], 1);
+      mbar_init(&cs->empty[s], kConsumers);
+    }
+    cs->abort_flag = 0;
+    fence_barrier_init();
+  }
   __syncthreads();
+  volatile int* abort_flag = &cs->abort_flag;
   const int tpr = f.rows_per_rank / kBM;
   const int owned = tpr * tiles_n;
-  const int gm = max(1, kGroupM / f.tp);          // matches the order in which producers emit owned tiles
-  for (int j = blockIdx.x; j < owned; j += f.n_comm) {
+  const int gm = max(1, kGroupM / f.tp);      // matches the order in which producers emit owned tiles
+  const int R = 256 / f.tp;                   // rows per ring stage: tp sources x R rows x 128 B = 32 KiB
+  const int parts = kBM / R;
+  const uint32_t src_bytes = (uint32_t)R * 128;
+  auto tile_of = [&](int j, int& mi, int& nt) {
     const int width = gm * tiles_n, g = j / width, rem = j % width;
     const int first = g * gm, gsz = min(tpr - first, gm);
-    const int mi = first + rem % gsz, nt = rem / gsz;
-    if ((int)threadIdx.x < f.tp) {
-      const uint32_t* fl = f.flag_ptrs[f.rank] + (size_t)threadIdx.x * f.flags_per_src + mi * tiles_n + nt;
-      if (!wait_flag_ge(fl, f.epoch, &s_abort)) {
-        s_abort = 1;
-        atomicCAS(err, 0, kErrComm);
+    mi = first + rem % gsz;
+    nt = rem / gsz;
+  };
+  if (threadIdx.x == 0) {
+    uint32_t item = 0;
+    bool ok = true;
+    for (int j = blockIdx.x; j < owned && ok; j += f.n_comm) {
+      int mi, nt;
+      tile_of(j, mi, nt);
+      for (int s = 0; s < f.tp && ok; ++s) {
+        const uint32_t* fl = f.flag_ptrs[f.rank] + (size_t)s * f.flags_per_src + mi * tiles_n + nt;
+        ok = wait_flag_ge(fl, f.epoch, abort_flag);
+      }
+      if (!ok) break;
+      fence_proxy_async_all();
+      const int mt = f.rank * tpr + mi;
+      for (int sub = 0; sub < BN / 64 && ok; ++sub) {
+        const size_t blk = stage_block<BN>(mt, nt, sub, tiles_n);
+        for (int p = 0; p < parts; ++p, ++item) {
+          const uint32_t st = item % kCommStages;
+          if (!mbar_wait(&cs->empty[st], ((item / kCommStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&cs->full[st], src_bytes * f.tp);
+          for (int s = 0; s < f.tp; ++s)
+            bulk_load(smem + st * kCommChunkBytes + s * src_bytes,
+                      reinterpret_cast<const uint8_t*>(f.data_ptrs[s]) + blk + (size_t)p * src_bytes, src_bytes,
+                      &cs->full[st]);
+        }
       }
     }
-    __syncthreads();
-    if (s_abort) return;
-    const int cols = min(BN, N - nt * BN), cvec = cols / 8;
-    const size_t grow0 = (size_t)f.rank * f.rows_per_rank + (size_t)mi * kBM;
-    for (int v = threadIdx.x; v < kBM * cvec; v += kGemmThreads) {
-      const int r = v / cvec, c = (v % cvec) * 8 + nt * BN;
-      float acc[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      for (int s = 0; s < f.tp; ++s) {
-        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(f.data_ptrs[s] + (grow0 + r) * N + c));
-        float t[8];
-        unpack8(*reinterpret_cast<const bf16x8*>(&raw), t);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += t[e];
-      }
-      *reinterpret_cast<bf16x8*>(f.y_local + ((size_t)mi * kBM + r) * N + c) = pack8(acc);
+    if (!ok) {
+      cs->abort_flag = 1;
+      atomicCAS(err, 0, kErrComm);
     }
-    __syncthreads();
+  } else if (threadIdx.x >= 32) {
+    const int ct = threadIdx.x - 32;
+    uint32_t item = 0;
+    bool ok = true;
+    for (int j = blockIdx.x; j < owned && ok; j += f.n_comm) {
+      int mi, nt;
+      tile_of(j, mi, nt);
+      for (int sub = 0; sub < BN / 64 && ok; ++sub) {
+        for (int p = 0; p < parts; ++p, ++item) {
+          const uint32_t st = item % kCommStages;
+          if (!mbar_wait(&cs->full[st], (item / kCommStages) & 1, abort_flag)) { ok = false; break; }
+          const uint8_t* base = smem + st * kCommChunkBytes;
+          for (int q = ct; q < R * 8; q += kConsumers) {
+            const int rl = q >> 3, cphys = q & 7;
+            float acc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+            for (int s = 0; s < f.tp; ++s) {
+              float t[8];
+              unpack8(*reinterpret_cast<const bf16x8*>(base + s * src_bytes + q * 16), t);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[e] += t[e];
+            }
+            const int row = p * R + rl;
+            const int col = nt * BN + sub * 64 + ((cphys ^ (row & 7)) << 3);
+            if (col < N)
+              *reinterpret_cast<bf16x8*>(f.y_local + ((size_t)mi * kBM + row) * N + col) = pack8(acc);
+          }
+          mbar_arrive(&cs->empty[st]);
+        }
+      }
+    }
   }
+  __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
     const unsigned int old = atomicAdd(f.counter, 1u);
@@ -229,7 +316,8 @@ __device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err) 
 template <int BN, bool A_MN, bool B_MN, int OUT, bool HAS_BIAS, int FUSE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ FuseArgs fuse,
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmA2,
+                 const __grid_constant__ FuseArgs fuse,
                  const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc, int* __restrict__ err) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -248,8 +336,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int cta_stride = (int)gridDim.x - n_comm;
 
   if (FUSE != kFuseNone && (int)blockIdx.x < n_comm) {
-    if (FUSE == kFuseAG) ag_comm_role(fuse, K, err);
-    else rs_reduce_role<BN>(fuse, N, tiles_n, err);
+    if (FUSE == kFuseAG) ag_comm_role(fuse, K, err, smem);
+    else rs_reduce_role<BN>(fuse, N, tiles_n, err, smem);
     return;
   }
 
@@ -286,17 +374,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int mt, nt;
         map_tile<FUSE>(tile, tiles_m, tiles_n, fuse, mt, nt);
         const int m0 = mt * kBM, n0 = nt * BN;
+        const CUtensorMap* a_map = &tmA;
+        int a_row = m0;
         if (FUSE == kFuseAG) {
-          // rows of this tile come from rank `src`; its copy into the local gathered buffer is flagged
+          // rows of this tile come from rank `src`: the local shard is read in place, a remote shard
+          // from the local gathered buffer once the peer's copy of this tile is flagged
           const int src = m0 / fuse.rows_per_rank;
-          const uint32_t* fl = fuse.flag_ptrs[fuse.rank] + (size_t)src * fuse.flags_per_src +
-                               (m0 - src * fuse.rows_per_rank) / kBM;
-          if (!wait_flag_ge(fl, fuse.epoch, abort_flag)) {
-            ok = false;
-            atomicCAS(err, 0, kErrFlagWait);
-            break;
+          if (src == fuse.rank) {
+            a_map = &tmA2;
+            a_row = m0 - src * fuse.rows_per_rank;
+          } else {
+            const uint32_t* fl = fuse.flag_ptrs[fuse.rank] + (size_t)src * fuse.flags_per_src +
+                                 (m0 - src * fuse.rows_per_rank) / kBM;
+            if (!wait_flag_ge(fl, fuse.epoch, abort_flag)) {
+              ok = false;
+              atomicCAS(err, 0, kErrFlagWait);
+              break;
+            }
+            fence_proxy_async_all();   // peer writes -> TMA reads (async proxy)
           }
-          fence_proxy_async_all();   // peer stores (generic proxy) -> TMA reads (async proxy)
         }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) {
@@ -307,7 +403,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* a_dst = sA + stage * kABytes;
           uint8_t* b_dst = sB + stage * Cfg::kBBytes;
           if (!A_MN) {
-            tma_load_2d(a_dst, &tmA, &sh->full[stage], kb * kBK, m0);
+            tma_load_2d(a_dst, a_map, &sh->full[stage], kb * kBK, a_row);
           } else {
 #pragma unroll
             for (int i = 0; i < kBM / 64; ++i)
@@ -441,7 +537,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           fence_proxy_async_smem();
           named_bar_sync(1, kEpiThreads);
           if (leader) {
-            if (n0 + j * 64 < N) tma_store_2d(&tmC, buf, n0 + j * 64, m0);
+            if (FUSE == kFuseRS) {
+              bulk_store(reinterpret_cast<uint8_t*>(fuse.data_ptrs[fuse.rank]) + stage_block<BN>(mt, nt, j, tiles_n),
+                         buf, kEpiBufBytes);
+            } else if (n0 + j * 64 < N) {
+              tma_store_2d(&tmC, buf, n0 + j * 64, m0);
+            }
             tma_store_commit();
           }
           ++store_count;
@@ -449,6 +550,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (FUSE == kFuseRS && leader) {
           // the staged tile is complete in global memory: raise its flag on the owner rank
           tma_store_wait_all<0>();
+          fence_proxy_async_all();
           __threadfence_system();
           const int owner = m0 / fuse.rows_per_rank;
           const int mi = (m0 - owner * fuse.rows_per_rank) / kBM;
@@ -566,7 +668,7 @@ static int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* pt
 template <int BN, bool A_MN, bool B_MN, int OUT, bool HAS_BIAS, int FUSE = kFuseNone>
 static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, const FuseArgs& fuse,
                        const __nv_bfloat16* bias, int M, int N, int K, int ldc, int* err, int max_ctas,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const CUtensorMap* tA2 = nullptr) {
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OUT, HAS_BIAS, FUSE>;
   static bool configured = false;
   if (!configured) {
@@ -576,7 +678,8 @@ static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
   }
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
   int grid = (FUSE != kFuseNone || tiles >= max_ctas) ? max_ctas : tiles;   // fused launches keep a fixed grid
-  kern<<<grid, kGemmThreads, GemmCfg<BN>::kSmemBytes, stream>>>(tA, tB, tC, fuse, bias, M, N, K, ldc, err);
+  kern<<<grid, kGemmThreads, GemmCfg<BN>::kSmemBytes, stream>>>(tA, tB, tC, tA2 ? *tA2 : tA, fuse, bias, M, N, K, ldc,
+                                                                err);
   return launch_status();
 }
 
@@ -669,6 +772,9 @@ ELL_API int ell_gemm_ag(const void* x_local, const void* W, void* out, const voi
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tC, out, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 128);
   if (rc) return rc;
+  CUtensorMap tA2;
+  rc = make_tmap_bf16_2d(&tA2, x_local, (uint64_t)K, (uint64_t)rows_per_rank, (uint64_t)K * 2, kBK, kBM);
+  if (rc) return rc;
   FuseArgs f{};
   fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, gathered_ptrs, flag_ptrs, done_ptrs, counter);
   f.x_local = (const __nv_bfloat16*)x_local;
@@ -676,11 +782,11 @@ ELL_API int ell_gemm_ag(const void* x_local, const void* W, void* out, const voi
   if (n_comm < 1 || n_comm >= ctas) return -2;
   const __nv_bfloat16* bp = (const __nv_bfloat16*)bias;
   if (BN == 256) {
-    if (bias) return launch_gemm<256, false, false, kOutBf16, true, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream);
-    return launch_gemm<256, false, false, kOutBf16, false, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream);
+    if (bias) return launch_gemm<256, false, false, kOutBf16, true, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream, &tA2);
+    return launch_gemm<256, false, false, kOutBf16, false, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream, &tA2);
   }
-  if (bias) return launch_gemm<128, false, false, kOutBf16, true, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream);
-  return launch_gemm<128, false, false, kOutBf16, false, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream);
+  if (bias) return launch_gemm<128, false, false, kOutBf16, true, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream, &tA2);
+  return launch_gemm<128, false, false, kOutBf16, false, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream, &tA2);
 }
 
 // GEMM -> reduce-scatter.  y_local[rows_per_rank, N] = sum over ranks of (x[M, K] · op(W))[own rows].

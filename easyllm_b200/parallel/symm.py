@@ -21,6 +21,7 @@ row_parallel_linear.py:116-117).
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_uint, c_void_p
 
 import torch
@@ -41,7 +42,8 @@ class FusedTPWorkspace:
         self.group = group if group is not None else g.tp_group
         self.tp, self.rank = g.tp, g.tp_rank
         self.max_tokens, self.hidden = max_tokens, hidden
-        self.n_comm_ag, self.n_comm_rs = n_comm_ag, n_comm_rs
+        self.n_comm_ag = int(os.environ.get("ELL_NCOMM_AG", n_comm_ag))
+        self.n_comm_rs = int(os.environ.get("ELL_NCOMM_RS", n_comm_rs))
         dev = torch.device("cuda", torch.cuda.current_device())
         data_elems = max_tokens * hidden
         flag_words = 2 * (self.tp * _MAX_FLAGS + 64)             # AG set + RS set (flags + done)
@@ -103,8 +105,9 @@ class FusedTPWorkspace:
         if M % self.tp:
             return None
         rows = M // self.tp
-        tiles_n = (N + 255) // 256 if N >= 256 else (N + 127) // 128
-        if not self._ok(rows, N) or (rows // 128) * tiles_n > _MAX_FLAGS or K % 8:
+        bn = 256 if N >= 256 else 128
+        tiles_n = (N + bn - 1) // bn
+        if not self._ok(rows, N) or N % bn or (rows // 128) * tiles_n > _MAX_FLAGS or K % 8:
             return None
         x = x.contiguous()
         y = torch.empty(rows, N, dtype=torch.bfloat16, device=x.device)
