@@ -262,6 +262,24 @@ class PipelineEngine:
             return None
         return outs[0] if M == 1 else outs
 
+    @torch.no_grad()
+    def forward_tokens(self, tokens, position_ids):
+        """Inference forward of raw tokens through every stage (KV caches of the model are used
+        when allocated).  Logits ``[b, s, V(/tp)]`` on the last stage, None elsewhere."""
+        g = self.g
+        io = None
+        if g.is_first_stage():
+            io = self.module.parse_batch((tokens, position_ids, None))
+        if g.pp > 1 and not g.is_first_stage():
+            self.link.dynamic = True
+            io, _ = self.link.exchange(recv_fwd=True)
+        out = self.module.forward_stage(io, None, return_logits=True)
+        if g.pp > 1 and not g.is_last_stage():
+            self.link.dynamic = True
+            self.link.exchange(send_fwd=out)
+            return None
+        return out
+
     # ---- checkpoint (delegated) ----------------------------------------------------------------------
     def save_checkpoint(self, save_dir, tag=None, client_state=None, save_base_state=True, save_zero=True,
                         save_optim=True):

@@ -337,6 +337,11 @@ def _split_fused_hook(fused_name, packed_name):
             for (name, _), n in zip(fused.segments, fused.local_sizes):
                 state[f"{prefix}{name}.{kind}"] = t[off:off + n]
                 off += n
+        # adapters of the fused projection: <fused>.lora.<segment>.lora_X_weight -> <segment>.lora_X_weight
+        lead = f"{prefix}{fused_name}.lora."
+        for key in [k for k in state if k.startswith(lead)]:
+            seg, leaf = key[len(lead):].split(".", 1)
+            state[f"{prefix}{seg}.{leaf}"] = state.pop(key)
     return hook
 
 
@@ -349,6 +354,11 @@ def _merge_fused_hook(fused, fused_name, packed_name):
             keys = [f"{prefix}{name}.{kind}" for name, _ in fused.segments]
             if all(k in state for k in keys):
                 state[f"{prefix}{fused_name}.{kind}"] = torch.cat([state.pop(k) for k in keys], dim=0)
+        for name, _ in fused.segments:
+            for leaf in ("lora_A_weight", "lora_B_weight"):
+                k = f"{prefix}{name}.{leaf}"
+                if k in state:
+                    state[f"{prefix}{fused_name}.lora.{name}.{leaf}"] = state.pop(k)
     return hook
 
 
@@ -428,7 +438,11 @@ class LMHead(nn.Module):
         return mp.copy_to_tensor_model_parallel_region(x) if get_grid().tp > 1 else x
 
     def forward(self, x):
-        logits = ops.linear(self.gathered_input(x), self.word_embeddings.weight)
+        xin = self.gathered_input(x)
+        logits = ops.linear(xin, self.word_embeddings.weight)
+        if getattr(self, "lora_head", False):
+            from .lora import head_lora_logits
+            logits = logits + head_lora_logits(self, xin)
         if not self.args.parallel_output:
             logits = mp.gather_from_tensor_model_parallel_region(logits)
         return logits

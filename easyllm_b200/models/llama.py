@@ -210,7 +210,8 @@ class LlamaModelPipe(nn.Module):
 
     def compute_loss(self, head, x, io, labels):
         lab = labels[0]
-        fused = (self.args.fused_lm_head_loss and type(self.loss_fn).__name__ == "CrossEntropy")
+        fused = (self.args.fused_lm_head_loss and type(self.loss_fn).__name__ == "CrossEntropy"
+                 and not getattr(head, "lora_head", False))
         if fused:
             xin = head.gathered_input(x)
             safe = lab.reshape(-1).masked_fill(lab.reshape(-1) == -100, 0)

@@ -47,7 +47,8 @@ enum GemmErr { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3, kErrComm = 4, kE
 //  kFuseRS  GEMM -> reduce-scatter: every rank computes the full partial product; finished bf16 tiles
 //           go to a local staging buffer (TMA store) and a flag is raised on the tile's owner rank; CTAs
 //           [0, n_comm) of the owner sum the tp staged copies (peer loads, fp32 add, fixed order so the
-//           result is deterministic) into the local output shard while the main loop is still running.
+//           result is deterministic) into the local output shard while the main loop is still running,
+//           and every GEMM CTA joins that reduction as soon as its own tiles are done.
 // Flags are epoch counters that only grow; a per-peer `done` word tells a producer that the consumer
 // has finished the previous epoch before a buffer is overwritten.  Every wait is bounded.
 enum GemmFuse { kFuseNone = 0, kFuseAG = 1, kFuseRS = 2 };
@@ -214,7 +215,7 @@ __device__ __forceinline__ size_t stage_block(int mt, int nt, int j, int tiles_n
 
 // Reduce-scatter side: sum the tp staged copies of every tile this rank owns into y_local.
 template <int BN>
-__device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err, uint8_t* smem) {
+__device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err, uint8_t* smem, int part, int nparts) {
   CommShared* cs = reinterpret_cast<CommShared*>(smem + kCommStages * kCommChunkBytes);
   constexpr int kConsumers = kGemmThreads - 32;
   if (threadIdx.x == 0) {
@@ -242,7 +243,7 @@ __device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err, 
   if (threadIdx.x == 0) {
     uint32_t item = 0;
     bool ok = true;
-    for (int j = blockIdx.x; j < owned && ok; j += f.n_comm) {
+    for (int j = part; j < owned && ok; j += nparts) {
       int mi, nt;
       tile_of(j, mi, nt);
       for (int s = 0; s < f.tp && ok; ++s) {
@@ -273,7 +274,7 @@ __device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err, 
     const int ct = threadIdx.x - 32;
     uint32_t item = 0;
     bool ok = true;
-    for (int j = blockIdx.x; j < owned && ok; j += f.n_comm) {
+    for (int j = part; j < owned && ok; j += nparts) {
       int mi, nt;
       tile_of(j, mi, nt);
       for (int sub = 0; sub < BN / 64 && ok; ++sub) {
@@ -306,7 +307,7 @@ __device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err, 
   if (threadIdx.x == 0) {
     __threadfence();
     const unsigned int old = atomicAdd(f.counter, 1u);
-    if ((old + 1) % (unsigned int)f.n_comm == 0) {
+    if ((old + 1) % (unsigned int)nparts == 0) {
       for (int p = 0; p < f.tp; ++p)
         if (p != f.rank) st_release_sys(f.done_ptrs[p] + f.rank, f.epoch);
     }
@@ -337,7 +338,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (FUSE != kFuseNone && (int)blockIdx.x < n_comm) {
     if (FUSE == kFuseAG) ag_comm_role(fuse, K, err, smem);
-    else rs_reduce_role<BN>(fuse, N, tiles_n, err, smem);
+    else rs_reduce_role<BN>(fuse, N, tiles_n, err, smem, (int)blockIdx.x, (int)gridDim.x);
     return;
   }
 
@@ -608,6 +609,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc<Cfg::kTmemCols>(tmem_base);
   }
+  if (FUSE == kFuseRS) {
+    // the main loop is done: this CTA now helps summing the staged tiles its rank owns (the
+    // dedicated CTAs [0, n_comm) have been doing so since launch)
+    __syncthreads();
+    rs_reduce_role<BN>(fuse, N, tiles_n, err, smem, (int)blockIdx.x, (int)gridDim.x);
+  }
   if (FUSE == kFuseAG && threadIdx.x == 0) {
     // last GEMM CTA of this rank: tell every peer that its pushes of this epoch were consumed
     __threadfence();
@@ -813,7 +820,7 @@ ELL_API int ell_gemm_rs(const void* x, const void* W, void* y_local, int rows_pe
   fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, stage_ptrs, flag_ptrs, done_ptrs, counter);
   f.y_local = (__nv_bfloat16*)y_local;
   const int ctas = sm_count();
-  if (n_comm < 1 || n_comm >= ctas) return -2;
+  if (n_comm < 0 || n_comm >= ctas) return -2;
   if (BN == 256) {
     if (b_mn) return launch_gemm<256, false, true, kOutBf16, false, kFuseRS>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);
     return launch_gemm<256, false, false, kOutBf16, false, kFuseRS>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);

@@ -89,7 +89,7 @@ class ZeroOptimizer:
 
         def klass(n, p):
             sharded = bool(getattr(p, "tensor_model_parallel", False))
-            sp = bool(getattr(p, "sequence_parallel", False))
+            sp = bool(getattr(p, "sequence_parallel", False)) or bool(getattr(p, "tp_reduce_grad", False))
             if sp:
                 return 4
             return (0 if sharded else 2) + (1 if _no_decay(n, p) else 0)

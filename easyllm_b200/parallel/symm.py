@@ -32,7 +32,7 @@ from .grid import get_grid
 
 _MAX_FLAGS = 8192        # flag words per source rank
 _N_COMM_AG = 8
-_N_COMM_RS = 16
+_N_COMM_RS = 8
 
 
 class FusedTPWorkspace:
