@@ -63,6 +63,8 @@ struct FuseArgs {
   uint32_t* flag_ptrs[kMaxTp];           // [tp][flags_per_src] on every rank
   uint32_t* done_ptrs[kMaxTp];           // [tp] on every rank
   unsigned int* counter;                 // local, monotonic: finished CTAs
+  unsigned int* queue;                   // RS: local, monotonic: next owned tile to reduce
+  unsigned int queue_base;               // RS: value of *queue when this launch starts (tracked by the host)
   __nv_bfloat16* y_local;                // RS: output shard [rows_per_rank, N]
 };
 
@@ -145,6 +147,7 @@ constexpr int kCommChunkBytes = 32768;
 struct CommShared {
   uint64_t full[kCommStages];
   uint64_t empty[kCommStages];
+  int meta[kCommStages];
   int abort_flag;
 };
 
@@ -214,8 +217,10 @@ __device__ __forceinline__ size_t stage_block(int mt, int nt, int j, int tiles_n
 }
 
 // Reduce-scatter side: sum the tp staged copies of every tile this rank owns into y_local.
+// Owned tiles are handed out through a global queue in the order producers emit them, so the dedicated
+// CTAs keep pace with the main loop and the GEMM CTAs only pick up what is left when they finish.
 template <int BN>
-__device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err, uint8_t* smem, int part, int nparts) {
+__device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err, uint8_t* smem, int nparts) {
   CommShared* cs = reinterpret_cast<CommShared*>(smem + kCommStages * kCommChunkBytes);
   constexpr int kConsumers = kGemmThreads - 32;
   if (threadIdx.x == 0) {
@@ -234,18 +239,16 @@ __device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err, 
   const int R = 256 / f.tp;                   // rows per ring stage: tp sources x R rows x 128 B = 32 KiB
   const int parts = kBM / R;
   const uint32_t src_bytes = (uint32_t)R * 128;
-  auto tile_of = [&](int j, int& mi, int& nt) {
-    const int width = gm * tiles_n, g = j / width, rem = j % width;
-    const int first = g * gm, gsz = min(tpr - first, gm);
-    mi = first + rem % gsz;
-    nt = rem / gsz;
-  };
+  const unsigned int queue_base = f.queue_base;
   if (threadIdx.x == 0) {
     uint32_t item = 0;
     bool ok = true;
-    for (int j = part; j < owned && ok; j += nparts) {
-      int mi, nt;
-      tile_of(j, mi, nt);
+    while (ok) {
+      const int j = (int)(atomicAdd(f.queue, 1u) - queue_base);
+      if (j >= owned) break;
+      const int width = gm * tiles_n, g = j / width, rem = j % width;
+      const int first = g * gm, gsz = min(tpr - first, gm);
+      const int mi = first + rem % gsz, nt = rem / gsz;
       for (int s = 0; s < f.tp && ok; ++s) {
         const uint32_t* fl = f.flag_ptrs[f.rank] + (size_t)s * f.flags_per_src + mi * tiles_n + nt;
         ok = wait_flag_ge(fl, f.epoch, abort_flag);
@@ -258,6 +261,7 @@ __device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err, 
         for (int p = 0; p < parts; ++p, ++item) {
           const uint32_t st = item % kCommStages;
           if (!mbar_wait(&cs->empty[st], ((item / kCommStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          cs->meta[st] = ((mi * tiles_n + nt) * (BN / 64) + sub) * parts + p;
           mbar_expect_tx(&cs->full[st], src_bytes * f.tp);
           for (int s = 0; s < f.tp; ++s)
             bulk_load(smem + st * kCommChunkBytes + s * src_bytes,
@@ -266,41 +270,47 @@ __device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err, 
         }
       }
     }
+    if (ok) {
+      // end marker for the consumers
+      const uint32_t st = item % kCommStages;
+      if (mbar_wait(&cs->empty[st], ((item / kCommStages) & 1) ^ 1, abort_flag)) {
+        cs->meta[st] = -1;
+        mbar_arrive(&cs->full[st]);
+      } else {
+        ok = false;
+      }
+    }
     if (!ok) {
       cs->abort_flag = 1;
       atomicCAS(err, 0, kErrComm);
     }
   } else if (threadIdx.x >= 32) {
     const int ct = threadIdx.x - 32;
-    uint32_t item = 0;
-    bool ok = true;
-    for (int j = part; j < owned && ok; j += nparts) {
-      int mi, nt;
-      tile_of(j, mi, nt);
-      for (int sub = 0; sub < BN / 64 && ok; ++sub) {
-        for (int p = 0; p < parts; ++p, ++item) {
-          const uint32_t st = item % kCommStages;
-          if (!mbar_wait(&cs->full[st], (item / kCommStages) & 1, abort_flag)) { ok = false; break; }
-          const uint8_t* base = smem + st * kCommChunkBytes;
-          for (int q = ct; q < R * 8; q += kConsumers) {
-            const int rl = q >> 3, cphys = q & 7;
-            float acc[8];
+    for (uint32_t item = 0;; ++item) {
+      const uint32_t st = item % kCommStages;
+      if (!mbar_wait(&cs->full[st], (item / kCommStages) & 1, abort_flag)) break;
+      int code = cs->meta[st];
+      if (code < 0) break;
+      const int p = code % parts; code /= parts;
+      const int sub = code % (BN / 64); code /= (BN / 64);
+      const int nt = code % tiles_n, mi = code / tiles_n;
+      const uint8_t* base = smem + st * kCommChunkBytes;
+      for (int q = ct; q < R * 8; q += kConsumers) {
+        const int rl = q >> 3, cphys = q & 7;
+        float acc[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-            for (int s = 0; s < f.tp; ++s) {
-              float t[8];
-              unpack8(*reinterpret_cast<const bf16x8*>(base + s * src_bytes + q * 16), t);
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int s = 0; s < f.tp; ++s) {
+          float t[8];
+          unpack8(*reinterpret_cast<const bf16x8*>(base + s * src_bytes + q * 16), t);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) acc[e] += t[e];
-            }
-            const int row = p * R + rl;
-            const int col = nt * BN + sub * 64 + ((cphys ^ (row & 7)) << 3);
-            if (col < N)
-              *reinterpret_cast<bf16x8*>(f.y_local + ((size_t)mi * kBM + row) * N + col) = pack8(acc);
-          }
-          mbar_arrive(&cs->empty[st]);
+          for (int e = 0; e < 8; ++e) acc[e] += t[e];
         }
+        const int row = p * R + rl;
+        const int col = nt * BN + sub * 64 + ((cphys ^ (row & 7)) << 3);
+        if (col < N) *reinterpret_cast<bf16x8*>(f.y_local + ((size_t)mi * kBM + row) * N + col) = pack8(acc);
       }
+      mbar_arrive(&cs->empty[st]);
     }
   }
   __syncthreads();
@@ -338,7 +348,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (FUSE != kFuseNone && (int)blockIdx.x < n_comm) {
     if (FUSE == kFuseAG) ag_comm_role(fuse, K, err, smem);
-    else rs_reduce_role<BN>(fuse, N, tiles_n, err, smem, (int)blockIdx.x, (int)gridDim.x);
+    else rs_reduce_role<BN>(fuse, N, tiles_n, err, smem, (int)gridDim.x);
     return;
   }
 
@@ -484,6 +494,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool leader = (threadIdx.x == 64);
     int it = 0;
     uint32_t store_count = 0;
+    uint32_t* pending_flag = nullptr;   // RS: flag of the last staged tile, raised once its stores completed
     if (FUSE == kFuseRS && leader) {
       // peers must have finished reading last epoch's staged tiles before they are overwritten
       for (int p = 0; p < fuse.tp; ++p)
@@ -549,14 +560,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           ++store_count;
         }
         if (FUSE == kFuseRS && leader) {
-          // the staged tile is complete in global memory: raise its flag on the owner rank
-          tma_store_wait_all<0>();
-          fence_proxy_async_all();
-          __threadfence_system();
+          // Publish the flag of the PREVIOUS tile: its bulk stores were committed BN/64 groups ago, so
+          // waiting until at most BN/64 groups are pending does not stall behind this tile's stores.
+          if (pending_flag != nullptr) {
+            tma_store_wait_all<BN / 64>();
+            fence_proxy_async_all();
+            st_release_sys(pending_flag, fuse.epoch);
+          }
           const int owner = m0 / fuse.rows_per_rank;
           const int mi = (m0 - owner * fuse.rows_per_rank) / kBM;
-          st_release_sys(fuse.flag_ptrs[owner] + (size_t)fuse.rank * fuse.flags_per_src + mi * tiles_n + nt,
-                         fuse.epoch);
+          pending_flag = fuse.flag_ptrs[owner] + (size_t)fuse.rank * fuse.flags_per_src + mi * tiles_n + nt;
         }
       } else {
         // fp32 output: 128 x 32 sub-tiles staged in swizzled smem, then a TMA store (overwrite) or
@@ -594,7 +607,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       sh->abort_flag = 1;
       atomicCAS(err, 0, kErrEpilogue);
     }
-    if (leader) tma_store_wait_all<0>();
+    if (leader) {
+      tma_store_wait_all<0>();
+      if (FUSE == kFuseRS && pending_flag != nullptr) {
+        fence_proxy_async_all();
+        st_release_sys(pending_flag, fuse.epoch);
+      }
+    }
   }
 
   __syncthreads();
@@ -613,7 +632,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // the main loop is done: this CTA now helps summing the staged tiles its rank owns (the
     // dedicated CTAs [0, n_comm) have been doing so since launch)
     __syncthreads();
-    rs_reduce_role<BN>(fuse, N, tiles_n, err, smem, (int)blockIdx.x, (int)gridDim.x);
+    rs_reduce_role<BN>(fuse, N, tiles_n, err, smem, (int)gridDim.x);
   }
   if (FUSE == kFuseAG && threadIdx.x == 0) {
     // last GEMM CTA of this rank: tell every peer that its pushes of this epoch were consumed
@@ -760,6 +779,7 @@ static void fill_fuse(FuseArgs& f, int rank, int tp, int n_comm, int rows_per_ra
     f.done_ptrs[i] = (uint32_t*)done_ptrs[i];
   }
   f.counter = (unsigned int*)counter;
+  f.queue = f.counter + 1;
 }
 
 // All-gather -> GEMM.  out[tp*rows_per_rank, N] = gather(x_local)[.., K] · W[N, K]^T (+ bias).
@@ -798,11 +818,13 @@ ELL_API int ell_gemm_ag(const void* x_local, const void* W, void* out, const voi
 
 // GEMM -> reduce-scatter.  y_local[rows_per_rank, N] = sum over ranks of (x[M, K] · op(W))[own rows].
 // b_mn = 0: W is [N, K] (forward of a row-parallel linear); b_mn = 1: W is [K, N] (its use as dgrad of a
-// column-parallel linear).  stage_ptrs[r] is rank r's staging buffer [M, N].
+// column-parallel linear).  stage_ptrs[r] is rank r's staging buffer [M, N].  `queue_base` is the running value
+// of the tile queue: every launch advances it by (owned tiles + number of CTAs); ell_gemm_rs_queue_advance
+// returns that amount.
 ELL_API int ell_gemm_rs(const void* x, const void* W, void* y_local, int rows_per_rank, int N, int K, int b_mn,
                         int rank, int tp, unsigned int epoch, int n_comm, void* const* stage_ptrs,
-                        void* const* flag_ptrs, void* const* done_ptrs, void* counter, int flags_per_src, int* err,
-                        cudaStream_t stream) {
+                        void* const* flag_ptrs, void* const* done_ptrs, void* counter, int flags_per_src,
+                        unsigned int queue_base, int* err, cudaStream_t stream) {
   if (tp < 1 || tp > kMaxTp || rows_per_rank % kBM || N % 8) return -2;
   const int M = rows_per_rank * tp;
   const int BN = N >= 256 ? 256 : 128;
@@ -819,6 +841,7 @@ ELL_API int ell_gemm_rs(const void* x, const void* W, void* y_local, int rows_pe
   FuseArgs f{};
   fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, stage_ptrs, flag_ptrs, done_ptrs, counter);
   f.y_local = (__nv_bfloat16*)y_local;
+  f.queue_base = queue_base;
   const int ctas = sm_count();
   if (n_comm < 0 || n_comm >= ctas) return -2;
   if (BN == 256) {
@@ -827,4 +850,9 @@ ELL_API int ell_gemm_rs(const void* x, const void* W, void* y_local, int rows_pe
   }
   if (b_mn) return launch_gemm<128, false, true, kOutBf16, false, kFuseRS>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);
   return launch_gemm<128, false, false, kOutBf16, false, kFuseRS>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);
+}
+
+ELL_API int ell_gemm_rs_queue_advance(int rows_per_rank, int N) {
+  const int BN = N >= 256 ? 256 : 128;
+  return (rows_per_rank / kBM) * ((N + BN - 1) / BN) + sm_count();
 }

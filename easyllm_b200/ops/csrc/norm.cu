@@ -5,16 +5,19 @@
 //          dw = sum_rows dy * xhat   (per-CTA partials in scratch, then a column reduce)
 //
 // The op is HBM-bound: one read of each input and one write of each output per element.
-// A CTA of 256 threads owns one row at a time and keeps it in registers (hidden <= 8192);
-// the grid is persistent (a multiple of the SM count) and strides over rows.
+// A warp owns one row at a time (hidden <= 8192), eight rows per CTA in flight;
+// the grid is persistent and strides over rows.
 // Replaces flash_attn.ops.rms_norm / dropout_layer_norm used by the reference
 // (llm/models/mg_models/base_modules/layers/fused_layer_norm.py:49-57).
 #include "common.cuh"
 
 namespace ell {
 
+// One warp per row (no block barriers on the critical path), two passes over the row: the second
+// pass re-reads the 8-16 KB row from L1/L2.  8 rows are in flight per CTA, several CTAs per SM.
 constexpr int kNormThreads = 256;
-constexpr int kNormMaxVec = 4;  // 256 threads * 4 * 8 elements = 8192 columns
+constexpr int kNormWarps = kNormThreads / 32;
+constexpr int kNormMaxCols = 8192;
 
 template <bool kHasRes>
 __global__ void __launch_bounds__(kNormThreads)
@@ -22,117 +25,99 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int rows, int cols,
                    float eps) {
-  __shared__ float red[33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = cols / 8;
-  float wv[kNormMaxVec][8];
-#pragma unroll
-  for (int i = 0; i < kNormMaxVec; ++i) {
-    int c = threadIdx.x + i * kNormThreads;
-    if (c < nvec) unpack8(reinterpret_cast<const bf16x8*>(w)[c], wv[i]);
-  }
-  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+  const bf16x8* wv = reinterpret_cast<const bf16x8*>(w);
+  for (int r = blockIdx.x * kNormWarps + warp; r < rows; r += gridDim.x * kNormWarps) {
     const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)r * cols);
     const bf16x8* rr = kHasRes ? reinterpret_cast<const bf16x8*>(res + (size_t)r * cols) : nullptr;
-    float v[kNormMaxVec][8];
+    bf16x8* hr = kHasRes ? reinterpret_cast<bf16x8*>(h_out + (size_t)r * cols) : nullptr;
     float ss = 0.f;
+#pragma unroll 4
+    for (int c = lane; c < nvec; c += 32) {
+      float v[8];
+      unpack8(xr[c], v);
+      if (kHasRes) {
+        float t[8];
+        unpack8(rr[c], t);
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
-      int c = threadIdx.x + i * kNormThreads;
-      if (c < nvec) {
-        unpack8(xr[c], v[i]);
-        if (kHasRes) {
-          float t[8];
-          unpack8(rr[c], t);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[i][j] += t[j];
-          // the residual stream is stored in bf16: statistics use the rounded value
-          bf16x8 hp = pack8(v[i]);
-          reinterpret_cast<bf16x8*>(h_out + (size_t)r * cols)[c] = hp;
-          unpack8(hp, v[i]);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+        for (int j = 0; j < 8; ++j) v[j] += t[j];
+        bf16x8 hp = pack8(v);      // the residual stream is stored in bf16: statistics use the rounded value
+        hr[c] = hp;
+        unpack8(hp, v);
       }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
     }
-    ss = block_sum(ss, red);
+    ss = warp_sum(ss);
     const float rstd = rsqrtf(ss / (float)cols + eps);
-    if (threadIdx.x == 0) rstd_out[r] = rstd;
+    if (lane == 0) rstd_out[r] = rstd;
+    const bf16x8* src = kHasRes ? hr : xr;
+    bf16x8* yr = reinterpret_cast<bf16x8*>(y + (size_t)r * cols);
+#pragma unroll 4
+    for (int c = lane; c < nvec; c += 32) {
+      float v[8], g[8], o[8];
+      unpack8(src[c], v);
+      unpack8(wv[c], g);
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
-      int c = threadIdx.x + i * kNormThreads;
-      if (c < nvec) {
-        float o[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * wv[i][j];
-        reinterpret_cast<bf16x8*>(y + (size_t)r * cols)[c] = pack8(o);
-      }
+      for (int j = 0; j < 8; ++j) o[j] = v[j] * rstd * g[j];
+      yr[c] = pack8(o);
     }
   }
 }
 
+// Backward: dw is accumulated per CTA in shared memory (fp32 atomics), then written as one partial row.
 template <bool kHasDres>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dh,
                    float* __restrict__ dw_partial, int rows, int cols) {
-  __shared__ float red[33];
+  extern __shared__ float s_dw[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = cols / 8;
-  float wv[kNormMaxVec][8], dwacc[kNormMaxVec][8];
-#pragma unroll
-  for (int i = 0; i < kNormMaxVec; ++i) {
-    int c = threadIdx.x + i * kNormThreads;
-    if (c < nvec) unpack8(reinterpret_cast<const bf16x8*>(w)[c], wv[i]);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
-  }
-  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+  for (int c = threadIdx.x; c < cols; c += kNormThreads) s_dw[c] = 0.f;
+  __syncthreads();
+  const bf16x8* wv = reinterpret_cast<const bf16x8*>(w);
+  for (int r = blockIdx.x * kNormWarps + warp; r < rows; r += gridDim.x * kNormWarps) {
     const float rstd = rstd_in[r];
-    float g[kNormMaxVec][8], xh[kNormMaxVec][8];
+    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + (size_t)r * cols);
+    const bf16x8* hr = reinterpret_cast<const bf16x8*>(h + (size_t)r * cols);
     float dot = 0.f;
+#pragma unroll 2
+    for (int c = lane; c < nvec; c += 32) {
+      float d[8], x[8], g[8];
+      unpack8(dyr[c], d);
+      unpack8(hr[c], x);
+      unpack8(wv[c], g);
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
-      int c = threadIdx.x + i * kNormThreads;
-      if (c < nvec) {
-        float d[8];
-        unpack8(reinterpret_cast<const bf16x8*>(dy + (size_t)r * cols)[c], d);
-        unpack8(reinterpret_cast<const bf16x8*>(h + (size_t)r * cols)[c], xh[i]);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[i][j] *= rstd;
-          dwacc[i][j] += d[j] * xh[i][j];
-          g[i][j] = d[j] * wv[i][j];
-          dot += g[i][j] * xh[i][j];
-        }
+      for (int j = 0; j < 8; ++j) {
+        const float xh = x[j] * rstd;
+        dot += d[j] * g[j] * xh;
+        atomicAdd(&s_dw[c * 8 + j], d[j] * xh);
       }
     }
-    dot = block_sum(dot, red) / (float)cols;
+    dot = warp_sum(dot) / (float)cols;
+    bf16x8* dhr = reinterpret_cast<bf16x8*>(dh + (size_t)r * cols);
+#pragma unroll 2
+    for (int c = lane; c < nvec; c += 32) {
+      float d[8], x[8], g[8], o[8];
+      unpack8(dyr[c], d);
+      unpack8(hr[c], x);
+      unpack8(wv[c], g);
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
-      int c = threadIdx.x + i * kNormThreads;
-      if (c < nvec) {
-        float o[8];
+      for (int j = 0; j < 8; ++j) o[j] = rstd * (d[j] * g[j] - x[j] * rstd * dot);
+      if (kHasDres) {
+        float t[8];
+        unpack8(reinterpret_cast<const bf16x8*>(dres + (size_t)r * cols)[c], t);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * dot);
-        if (kHasDres) {
-          float t[8];
-          unpack8(reinterpret_cast<const bf16x8*>(dres + (size_t)r * cols)[c], t);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += t[j];
-        }
-        reinterpret_cast<bf16x8*>(dh + (size_t)r * cols)[c] = pack8(o);
+        for (int j = 0; j < 8; ++j) o[j] += t[j];
       }
+      dhr[c] = pack8(o);
     }
   }
-#pragma unroll
-  for (int i = 0; i < kNormMaxVec; ++i) {
-    int c = threadIdx.x + i * kNormThreads;
-    if (c < nvec) {
-      float4* dst = reinterpret_cast<float4*>(dw_partial + (size_t)blockIdx.x * cols + (size_t)c * 8);
-      dst[0] = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
-      dst[1] = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
-    }
-  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < cols; c += kNormThreads) dw_partial[(size_t)blockIdx.x * cols + c] = s_dw[c];
 }
 
 // dw[c] (+)= sum_p partial[p][c]; one thread per column, coalesced across the warp.
@@ -146,8 +131,9 @@ __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, floa
 }
 
 inline int norm_grid(int rows) {
-  int g = kNumSMs * 4;
-  return rows < g ? rows : g;
+  const int want = (rows + kNormWarps - 1) / kNormWarps;
+  const int g = kNumSMs * 2;
+  return want < g ? want : g;
 }
 
 }  // namespace ell
@@ -159,9 +145,10 @@ ELL_API long long ell_rmsnorm_bwd_scratch_elems(int rows, int cols) { return (lo
 
 ELL_API int ell_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out, float* rstd,
                             int rows, int cols, float eps, cudaStream_t stream) {
-  if (cols % 8 || cols > kNormThreads * kNormMaxVec * 8) return -1;
+  if (cols % 8 || cols > kNormMaxCols) return -1;
   if (rows == 0) return 0;
-  dim3 grid(norm_grid(rows)), block(kNormThreads);
+  dim3 grid((rows + kNormWarps - 1) / kNormWarps < kNumSMs * 8 ? (rows + kNormWarps - 1) / kNormWarps : kNumSMs * 8),
+      block(kNormThreads);
   if (res)
     rmsnorm_fwd_kernel<true><<<grid, block, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res,
                                                          (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
@@ -176,16 +163,16 @@ ELL_API int ell_rmsnorm_fwd(const void* x, const void* res, const void* w, void*
 ELL_API int ell_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dres,
                             void* dh, float* dw, float* scratch, int rows, int cols, int accumulate_dw,
                             cudaStream_t stream) {
-  if (cols % 8 || cols > kNormThreads * kNormMaxVec * 8) return -1;
+  if (cols % 8 || cols > kNormMaxCols) return -1;
   if (rows == 0) return 0;
   const int parts = norm_grid(rows);
   dim3 grid(parts), block(kNormThreads);
   if (dres)
-    rmsnorm_bwd_kernel<true><<<grid, block, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)h,
+    rmsnorm_bwd_kernel<true><<<grid, block, cols * sizeof(float), stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)h,
                                                          (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
                                                          (__nv_bfloat16*)dh, scratch, rows, cols);
   else
-    rmsnorm_bwd_kernel<false><<<grid, block, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)h,
+    rmsnorm_bwd_kernel<false><<<grid, block, cols * sizeof(float), stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)h,
                                                           (const __nv_bfloat16*)w, rstd, nullptr, (__nv_bfloat16*)dh,
                                                           scratch, rows, cols);
   rmsnorm_dw_reduce_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(scratch, dw, parts, cols, accumulate_dw);

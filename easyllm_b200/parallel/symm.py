@@ -68,9 +68,10 @@ class FusedTPWorkspace:
         self.ag_done = [b + off_flags + self.tp * _MAX_FLAGS * 4 for b in base]
         self.rs_flags = [b + off_flags + set_bytes for b in base]
         self.rs_done = [b + off_flags + set_bytes + self.tp * _MAX_FLAGS * 4 for b in base]
-        self.counters = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.counters = torch.zeros(4, dtype=torch.int32, device=dev)   # [ag done-count, -, rs done-count, rs queue]
         self.epoch_ag = 0
         self.epoch_rs = 0
+        self.rs_queue = 0
         self._arr = lambda ptrs: (c_void_p * len(ptrs))(*ptrs)
         logger.info(f"fused TP workspace: {nbytes / 2**20:.0f} MiB symmetric memory over {self.tp} ranks")
 
@@ -115,9 +116,10 @@ class FusedTPWorkspace:
         rc = cu.lib().ell_gemm_rs(cu._p(x), cu._p(w), cu._p(y), c_int(rows), c_int(N), c_int(K), c_int(1 if b_mn else 0),
                                   c_int(self.rank), c_int(self.tp), c_uint(self.epoch_rs), c_int(self.n_comm_rs),
                                   self._arr(self.stage_ptrs), self._arr(self.rs_flags), self._arr(self.rs_done),
-                                  c_void_p(self.counters.data_ptr() + 4), c_int(_MAX_FLAGS),
-                                  cu._p(cu.err_flag(x.device)), cu._stream())
+                                  c_void_p(self.counters.data_ptr() + 8), c_int(_MAX_FLAGS),
+                                  c_uint(self.rs_queue & 0xFFFFFFFF), cu._p(cu.err_flag(x.device)), cu._stream())
         cu._check(rc, "gemm_rs")
+        self.rs_queue += cu.lib().ell_gemm_rs_queue_advance(c_int(rows), c_int(N))
         return y
 
 
