@@ -37,7 +37,7 @@ class Hook:
     def before_train(self):
         pass
 
-    def before_train_iter(self, cur_iter):
+    def before_train_iter(self, cur_iter, batch=None):
         pass
 
     def after_train_iter(self, cur_iter, output=None):
