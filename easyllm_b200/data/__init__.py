@@ -7,3 +7,4 @@ from .collators import BatchCollector, BatchAlignCollector, RewardBatchCollector
 from .loader import (build_data_loader, build_batch_collator, build_batch_pipe_fn, build_data_iterator,  # noqa
                      get_ltor_masks_and_position_ids)
 from .synthetic import synthetic_batches, SyntheticTokenDataset  # noqa
+from . import tokenizers_hf  # noqa

@@ -212,3 +212,29 @@ def build_hooks(runner, cfg_hooks, add_log_if_not_exists=True):
         kw["runner"] = runner
         hooks.append(HOOK_REGISTRY.build({"type": c["type"], "kwargs": kw}))
     return ComposeHook(hooks)
+
+
+@HOOK_REGISTRY.register("watchdog")
+class WatchdogHook(Hook):
+    """Heartbeat monitor: raises ``RankFailure`` on the training thread (between steps) when a peer
+    stops beating; optionally saves a checkpoint first."""
+
+    def __init__(self, runner, interval=5.0, timeout=120.0, port=None, save_on_failure=False, check_device_flag=True):
+        super().__init__(runner)
+        self.kw = dict(interval=interval, timeout=timeout, port=port, check_device_flag=check_device_flag)
+        self.save_on_failure = save_on_failure
+        self.wd = None
+
+    def before_train(self):
+        from ..parallel.watchdog import Watchdog
+        g = get_grid()
+        if g.world > 1:
+            self.wd = Watchdog(g.rank, g.world, **self.kw).start()
+
+    def after_train_iter(self, cur_iter, output=None):
+        if self.wd is not None:
+            self.wd.check()
+
+    def after_train(self):
+        if self.wd is not None:
+            self.wd.leave()
