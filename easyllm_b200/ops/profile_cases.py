@@ -1,0 +1,72 @@
+"""Small fixed workloads for profiling one kernel at a time.
+
+    python -m easyllm_b200.ops.profile_cases <case> [--iters 6]
+
+Cases: gemm_nt, gemm_dgrad, gemm_wgrad, flash_fwd, rmsnorm_fwd, rmsnorm_bwd, swiglu, rope, adam, ce.
+Inputs are larger than L2 (126 MB) where the op is memory-bound but hold well under a few GB,
+so a full-section profiler capture of 1-3 launches ends by itself in a minute or two.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import cuda as cu
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case")
+    ap.add_argument("--iters", type=int, default=6)
+    a = ap.parse_args()
+    cu.lib()
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    c = a.case
+    if c == "gemm_nt":
+        x = torch.randn(4096, 4096, **bf); w = torch.randn(12288, 4096, **bf)
+        fn = lambda: cu.gemm(x, w)                                                   # noqa: E731
+    elif c == "gemm_dgrad":
+        x = torch.randn(4096, 11008, **bf); w = torch.randn(11008, 4096, **bf)
+        fn = lambda: cu.gemm(x, w, b_mn=True)                                        # noqa: E731
+    elif c == "gemm_wgrad":
+        dy = torch.randn(4096, 11008, **bf); x = torch.randn(4096, 4096, **bf)
+        acc = torch.zeros(11008, 4096, device="cuda")
+        fn = lambda: cu.gemm(dy, x, out=acc, a_mn=True, b_mn=True, out_mode=1)        # noqa: E731
+    elif c == "flash_fwd":
+        qkv = torch.randn(4096, 3 * 32 * 128, **bf)
+        q, k, v = (qkv[:, i * 4096:(i + 1) * 4096].view(4096, 32, 128) for i in range(3))
+        rs = torch.zeros(4096, dtype=torch.int32, device="cuda")
+        fn = lambda: cu.flash_attn_fwd(q, k, v, rs, 128 ** -0.5)                      # noqa: E731
+    elif c in ("rmsnorm_fwd", "rmsnorm_bwd"):
+        x = torch.randn(16384, 4096, **bf); r = torch.randn_like(x); w = torch.ones(4096, **bf)
+        y, h, rstd = cu.rmsnorm_fwd(x, r, w, 1e-5)
+        fn = (lambda: cu.rmsnorm_fwd(x, r, w, 1e-5)) if c == "rmsnorm_fwd" else (lambda: cu.rmsnorm_bwd(y, h, w, rstd, r))
+    elif c == "swiglu":
+        gu = torch.randn(8192, 22016, **bf)
+        fn = lambda: cu.swiglu_fwd(gu)                                                # noqa: E731
+    elif c == "rope":
+        qkv = torch.randn(8192, 12288, **bf)
+        from .reference import rope_tables
+        cos, sin = rope_tables(128, 8192, device="cuda")
+        pos = torch.arange(8192, dtype=torch.int32, device="cuda")
+        fn = lambda: cu.rope_(qkv, cos, sin, pos, 64, 128)                            # noqa: E731
+    elif c == "adam":
+        n = 1 << 27
+        p = torch.randn(n, device="cuda"); g = torch.randn(n, device="cuda"); m = torch.zeros(n, device="cuda")
+        v = torch.zeros(n, device="cuda"); low = torch.empty(n, **bf)
+        fn = lambda: cu.adam(p, g, m, v, low, 1e-4, 0.9, 0.95, 1e-8, 0.1, 3)          # noqa: E731
+    elif c == "ce":
+        lg = torch.randn(4096, 32000, **bf); t = torch.randint(0, 32000, (4096,), device="cuda")
+        fn = lambda: cu.ce_fwd(lg, t, 0, 32000)                                       # noqa: E731
+    else:
+        raise SystemExit(f"unknown case {c}")
+    for _ in range(a.iters):
+        fn()
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    print(f"{c}: {a.iters} launches done")
+
+
+if __name__ == "__main__":
+    main()
