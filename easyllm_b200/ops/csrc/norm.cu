@@ -178,3 +178,73 @@ ELL_API int ell_rmsnorm_bwd(const void* dy, const void* h, const void* w, const 
   rmsnorm_dw_reduce_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(scratch, dw, parts, cols, accumulate_dw);
   return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the backward: the per-CTA partials live in a fixed device array.
+// ---------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+#include <mutex>
+
+static __device__ __align__(256) float g_static_norm_scratch[ELL_STATIC_NORM_SCRATCH_ELEMS];
+
+namespace {
+constexpr int kStaticMaxDevices = 64;
+float* g_static_scratch_ptr[kStaticMaxDevices] = {};
+std::mutex g_static_mu;
+
+// Device address of the scratch array on the current device; looked up once per device.
+int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) return ELL_STATIC_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_scratch_ptr[dev]) {
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_norm_scratch);
+    if (e != cudaSuccess || !p) {
+      (void)cudaGetLastError();
+      return ELL_STATIC_ERR_SYMBOL;
+    }
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return ELL_STATIC_OK;
+}
+}  // namespace
+
+ELL_API const char* ell_static_strerror(int code) {
+  switch (code) {
+    case ELL_STATIC_OK: return "ok";
+    case ELL_STATIC_ERR_SHAPE: return "rmsnorm_bwd_static: cols must be a positive multiple of 8 and rows >= 0";
+    case ELL_STATIC_ERR_TOO_LARGE: return "rmsnorm_bwd_static: cols exceeds the fixed scratch (max 8192 columns)";
+    case ELL_STATIC_ERR_SYMBOL: return "rmsnorm_bwd_static: cudaGetSymbolAddress failed for the scratch array";
+    case ELL_STATIC_ERR_DEVICE: return "rmsnorm_bwd_static: no current CUDA device, or ordinal >= 64";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "rmsnorm_bwd_static: unknown error";
+  }
+}
+
+ELL_API int ell_rmsnorm_bwd_static(const void* dy, const void* h, const void* w, const float* rstd, const void* dres,
+                                   void* dh, float* dw, int rows, int cols, int accumulate_dw, cudaStream_t stream) {
+  if (cols <= 0 || cols % 8 || rows < 0) return ELL_STATIC_ERR_SHAPE;
+  if (cols > ELL_STATIC_NORM_MAX_COLS) return ELL_STATIC_ERR_TOO_LARGE;
+  if (rows == 0) return ELL_STATIC_OK;
+  float* scratch = nullptr;
+  if (int rc = static_scratch_for_current_device(&scratch)) return rc;
+  int parts = norm_grid(rows);
+  const int cap = ELL_STATIC_NORM_SCRATCH_ELEMS / cols;   // >= 144 CTAs for every admitted cols
+  if (parts > cap) parts = cap;
+  dim3 grid(parts), block(kNormThreads);
+  // Every partial row [0, parts) is written in full by the first kernel before the second reads it,
+  // so stale contents of the shared scratch are never observed.
+  if (dres)
+    rmsnorm_bwd_kernel<true><<<grid, block, cols * sizeof(float), stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
+        (__nv_bfloat16*)dh, scratch, rows, cols);
+  else
+    rmsnorm_bwd_kernel<false><<<grid, block, cols * sizeof(float), stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd, nullptr, (__nv_bfloat16*)dh,
+        scratch, rows, cols);
+  rmsnorm_dw_reduce_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(scratch, dw, parts, cols, accumulate_dw);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? ELL_STATIC_OK : (int)e;
+}
