@@ -13,111 +13,212 @@
 
 namespace ell {
 
-// One warp per row (no block barriers on the critical path), two passes over the row: the second
-// pass re-reads the 8-16 KB row from L1/L2.  8 rows are in flight per CTA, several CTAs per SM.
+// A CTA of 256 threads owns kNormRows rows at a time; thread t holds the 16-byte vectors t, t+256, ... of
+// each row in registers (kVpt <= 4 vectors for hidden <= 8192), so every element is read from HBM exactly
+// once and never re-read from L1/L2.  The next rows are prefetched into registers before the current ones
+// are reduced, which keeps ~64 KB per SM in flight across the one block barrier per iteration.
 constexpr int kNormThreads = 256;
 constexpr int kNormWarps = kNormThreads / 32;
 constexpr int kNormMaxCols = 8192;
+// Rows per CTA iteration and CTAs per SM by vectors per thread: the register file bounds what can be in flight.
+__host__ __device__ constexpr int norm_rows(int vpt) { return vpt <= 2 ? 2 : 1; }
+__host__ __device__ constexpr int norm_min_ctas(int vpt) { return vpt <= 1 ? 3 : 2; }
+constexpr int kNormRowsMax = 2;
 
-template <bool kHasRes>
-__global__ void __launch_bounds__(kNormThreads)
+__host__ __device__ constexpr int norm_rows_bwd(int vpt) { return vpt <= 1 ? 2 : 1; }
+__host__ __device__ constexpr int norm_min_ctas_bwd(int vpt) { return vpt <= 2 ? 2 : 1; }
+
+template <int kVpt, int kNormRows>
+struct RowRegs {
+  bf16x8 v[kNormRows][kVpt];
+};
+
+template <int kVpt, int kNormRows>
+__device__ __forceinline__ void load_rows(RowRegs<kVpt, kNormRows>& d, const __nv_bfloat16* __restrict__ base, int r0, int rows,
+                                          int cols, int nvec) {
+#pragma unroll
+  for (int k = 0; k < kNormRows; ++k)
+#pragma unroll
+    for (int i = 0; i < kVpt; ++i) {
+      const int c = threadIdx.x + i * kNormThreads;
+      if (r0 + k < rows && c < nvec)
+        d.v[k][i] = reinterpret_cast<const bf16x8*>(base + (size_t)(r0 + k) * cols)[c];
+      else
+        d.v[k][i] = bf16x8{};
+    }
+}
+
+// Sum over the CTA of kNormRows partials; `red` is one of two alternating buffers (one barrier per call).
+template <int kNormRows>
+__device__ __forceinline__ void rows_block_sum(float (&p)[kNormRows], float (*red)[kNormRowsMax]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int k = 0; k < kNormRows; ++k) {
+    p[k] = warp_sum(p[k]);
+    if (lane == 0) red[warp][k] = p[k];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < kNormRows; ++k) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kNormWarps; ++w) t += red[w][k];
+    p[k] = t;
+  }
+}
+
+template <int kVpt, bool kHasRes>
+__global__ void __launch_bounds__(kNormThreads, norm_min_ctas(kVpt))
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int rows, int cols,
                    float eps) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __shared__ float s_red[2][kNormWarps][kNormRowsMax];
+  constexpr int kNormRows = norm_rows(kVpt);
   const int nvec = cols / 8;
-  const bf16x8* wv = reinterpret_cast<const bf16x8*>(w);
-  for (int r = blockIdx.x * kNormWarps + warp; r < rows; r += gridDim.x * kNormWarps) {
-    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)r * cols);
-    const bf16x8* rr = kHasRes ? reinterpret_cast<const bf16x8*>(res + (size_t)r * cols) : nullptr;
-    bf16x8* hr = kHasRes ? reinterpret_cast<bf16x8*>(h_out + (size_t)r * cols) : nullptr;
-    float ss = 0.f;
-#pragma unroll 4
-    for (int c = lane; c < nvec; c += 32) {
-      float v[8];
-      unpack8(xr[c], v);
-      if (kHasRes) {
-        float t[8];
-        unpack8(rr[c], t);
+  bf16x8 wv[kVpt];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] += t[j];
-        bf16x8 hp = pack8(v);      // the residual stream is stored in bf16: statistics use the rounded value
-        hr[c] = hp;
-        unpack8(hp, v);
+  for (int i = 0; i < kVpt; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+    wv[i] = c < nvec ? reinterpret_cast<const bf16x8*>(w)[c] : bf16x8{};
+  }
+  const int stride = gridDim.x * kNormRows;
+  int r0 = blockIdx.x * kNormRows;
+  RowRegs<kVpt, kNormRows> nx, nr;
+  load_rows<kVpt, kNormRows>(nx, x, r0, rows, cols, nvec);
+  if (kHasRes) load_rows<kVpt, kNormRows>(nr, res, r0, rows, cols, nvec);
+  for (int it = 0; r0 < rows; r0 += stride, ++it) {
+    RowRegs<kVpt, kNormRows> cx = nx, cr;
+    if (kHasRes) cr = nr;
+    load_rows<kVpt, kNormRows>(nx, x, r0 + stride, rows, cols, nvec);
+    if (kHasRes) load_rows<kVpt, kNormRows>(nr, res, r0 + stride, rows, cols, nvec);
+    float ss[kNormRows];
+#pragma unroll
+    for (int k = 0; k < kNormRows; ++k) {
+      ss[k] = 0.f;
+#pragma unroll
+      for (int i = 0; i < kVpt; ++i) {
+        const int c = threadIdx.x + i * kNormThreads;
+        float v[8];
+        unpack8(cx.v[k][i], v);
+        if (kHasRes) {
+          float t[8];
+          unpack8(cr.v[k][i], t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] += t[j];
+          cx.v[k][i] = pack8(v);   // the residual stream is stored in bf16: statistics use the rounded value
+          if (r0 + k < rows && c < nvec) reinterpret_cast<bf16x8*>(h_out + (size_t)(r0 + k) * cols)[c] = cx.v[k][i];
+          unpack8(cx.v[k][i], v);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss[k] += v[j] * v[j];
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
     }
-    ss = warp_sum(ss);
-    const float rstd = rsqrtf(ss / (float)cols + eps);
-    if (lane == 0) rstd_out[r] = rstd;
-    const bf16x8* src = kHasRes ? hr : xr;
-    bf16x8* yr = reinterpret_cast<bf16x8*>(y + (size_t)r * cols);
-#pragma unroll 4
-    for (int c = lane; c < nvec; c += 32) {
-      float v[8], g[8], o[8];
-      unpack8(src[c], v);
-      unpack8(wv[c], g);
+    rows_block_sum<kNormRows>(ss, s_red[it & 1]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = v[j] * rstd * g[j];
-      yr[c] = pack8(o);
+    for (int k = 0; k < kNormRows; ++k) {
+      if (r0 + k >= rows) break;
+      const float rstd = rsqrtf(ss[k] / (float)cols + eps);
+      if (threadIdx.x == 0) rstd_out[r0 + k] = rstd;
+#pragma unroll
+      for (int i = 0; i < kVpt; ++i) {
+        const int c = threadIdx.x + i * kNormThreads;
+        if (c >= nvec) break;
+        float v[8], g[8], o[8];
+        unpack8(cx.v[k][i], v);
+        unpack8(wv[i], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = v[j] * rstd * g[j];
+        reinterpret_cast<bf16x8*>(y + (size_t)(r0 + k) * cols)[c] = pack8(o);
+      }
     }
   }
 }
 
-// Backward: dw is accumulated per CTA in shared memory (fp32 atomics), then written as one partial row.
-template <bool kHasDres>
-__global__ void __launch_bounds__(kNormThreads)
+// Backward: each thread accumulates dw for the columns it owns in registers over all rows of the CTA and
+// writes them once as this CTA's partial row.
+template <int kVpt, bool kHasDres>
+__global__ void __launch_bounds__(kNormThreads, norm_min_ctas_bwd(kVpt))
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dh,
                    float* __restrict__ dw_partial, int rows, int cols) {
-  extern __shared__ float s_dw[];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __shared__ float s_red[2][kNormWarps][kNormRowsMax];
+  constexpr int kNormRows = norm_rows_bwd(kVpt);
   const int nvec = cols / 8;
-  for (int c = threadIdx.x; c < cols; c += kNormThreads) s_dw[c] = 0.f;
-  __syncthreads();
-  const bf16x8* wv = reinterpret_cast<const bf16x8*>(w);
-  for (int r = blockIdx.x * kNormWarps + warp; r < rows; r += gridDim.x * kNormWarps) {
-    const float rstd = rstd_in[r];
-    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + (size_t)r * cols);
-    const bf16x8* hr = reinterpret_cast<const bf16x8*>(h + (size_t)r * cols);
-    float dot = 0.f;
-#pragma unroll 2
-    for (int c = lane; c < nvec; c += 32) {
-      float d[8], x[8], g[8];
-      unpack8(dyr[c], d);
-      unpack8(hr[c], x);
-      unpack8(wv[c], g);
+  bf16x8 wv[kVpt];
+  float dw[kVpt][8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float xh = x[j] * rstd;
-        dot += d[j] * g[j] * xh;
-        atomicAdd(&s_dw[c * 8 + j], d[j] * xh);
+  for (int i = 0; i < kVpt; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+    wv[i] = c < nvec ? reinterpret_cast<const bf16x8*>(w)[c] : bf16x8{};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw[i][j] = 0.f;
+  }
+  const int stride = gridDim.x * kNormRows;
+  int r0 = blockIdx.x * kNormRows;
+  RowRegs<kVpt, kNormRows> nd, nh;
+  load_rows<kVpt, kNormRows>(nd, dy, r0, rows, cols, nvec);
+  load_rows<kVpt, kNormRows>(nh, h, r0, rows, cols, nvec);
+  for (int it = 0; r0 < rows; r0 += stride, ++it) {
+    RowRegs<kVpt, kNormRows> cd = nd, ch = nh, cres;
+    float rstd[kNormRows];
+#pragma unroll
+    for (int k = 0; k < kNormRows; ++k) rstd[k] = r0 + k < rows ? rstd_in[r0 + k] : 0.f;
+    if (kHasDres) load_rows<kVpt, kNormRows>(cres, dres, r0, rows, cols, nvec);
+    load_rows<kVpt, kNormRows>(nd, dy, r0 + stride, rows, cols, nvec);
+    load_rows<kVpt, kNormRows>(nh, h, r0 + stride, rows, cols, nvec);
+    float dot[kNormRows];
+#pragma unroll
+    for (int k = 0; k < kNormRows; ++k) {
+      dot[k] = 0.f;
+#pragma unroll
+      for (int i = 0; i < kVpt; ++i) {
+        float d[8], x[8], g[8];
+        unpack8(cd.v[k][i], d);
+        unpack8(ch.v[k][i], x);
+        unpack8(wv[i], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = x[j] * rstd[k];
+          dot[k] += d[j] * g[j] * xh;
+          dw[i][j] += d[j] * xh;
+        }
       }
     }
-    dot = warp_sum(dot) / (float)cols;
-    bf16x8* dhr = reinterpret_cast<bf16x8*>(dh + (size_t)r * cols);
-#pragma unroll 2
-    for (int c = lane; c < nvec; c += 32) {
-      float d[8], x[8], g[8], o[8];
-      unpack8(dyr[c], d);
-      unpack8(hr[c], x);
-      unpack8(wv[c], g);
+    rows_block_sum<kNormRows>(dot, s_red[it & 1]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = rstd * (d[j] * g[j] - x[j] * rstd * dot);
-      if (kHasDres) {
-        float t[8];
-        unpack8(reinterpret_cast<const bf16x8*>(dres + (size_t)r * cols)[c], t);
+    for (int k = 0; k < kNormRows; ++k) {
+      if (r0 + k >= rows) break;
+      const float m = dot[k] / (float)cols;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] += t[j];
+      for (int i = 0; i < kVpt; ++i) {
+        const int c = threadIdx.x + i * kNormThreads;
+        if (c >= nvec) break;
+        float d[8], x[8], g[8], o[8];
+        unpack8(cd.v[k][i], d);
+        unpack8(ch.v[k][i], x);
+        unpack8(wv[i], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd[k] * (d[j] * g[j] - x[j] * rstd[k] * m);
+        if (kHasDres) {
+          float t[8];
+          unpack8(cres.v[k][i], t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += t[j];
+        }
+        reinterpret_cast<bf16x8*>(dh + (size_t)(r0 + k) * cols)[c] = pack8(o);
       }
-      dhr[c] = pack8(o);
     }
   }
-  __syncthreads();
-  for (int c = threadIdx.x; c < cols; c += kNormThreads) dw_partial[(size_t)blockIdx.x * cols + c] = s_dw[c];
+#pragma unroll
+  for (int i = 0; i < kVpt; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+    if (c >= nvec) break;
+    float4* dst = reinterpret_cast<float4*>(dw_partial + (size_t)blockIdx.x * cols + (size_t)c * 8);
+    dst[0] = make_float4(dw[i][0], dw[i][1], dw[i][2], dw[i][3]);
+    dst[1] = make_float4(dw[i][4], dw[i][5], dw[i][6], dw[i][7]);
+  }
 }
 
 // dw[c] (+)= sum_p partial[p][c]; one thread per column, coalesced across the warp.
@@ -130,10 +231,53 @@ __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, floa
   dw[c] = accumulate ? dw[c] + s : s;
 }
 
-inline int norm_grid(int rows) {
-  const int want = (rows + kNormWarps - 1) / kNormWarps;
-  const int g = kNumSMs * 2;
+// Persistent grid for the backward: a few CTAs per SM, never more than there are row groups.
+inline int norm_vpt(int cols) { return (cols / 8 + kNormThreads - 1) / kNormThreads; }
+
+inline int norm_grid(int rows, int cols, bool bwd) {
+  const int v = norm_vpt(cols);
+  const int r = bwd ? norm_rows_bwd(v) : norm_rows(v);
+  const int want = (rows + r - 1) / r;
+  const int g = kNumSMs * (bwd ? norm_min_ctas_bwd(v) : norm_min_ctas(v));
   return want < g ? want : g;
+}
+
+template <bool kHasRes>
+void launch_norm_fwd(int vpt, dim3 grid, cudaStream_t stream, const __nv_bfloat16* x, const __nv_bfloat16* res,
+                     const __nv_bfloat16* w, __nv_bfloat16* y, __nv_bfloat16* h_out, float* rstd, int rows, int cols,
+                     float eps) {
+  dim3 block(kNormThreads);
+  switch (vpt) {
+    case 1: rmsnorm_fwd_kernel<1, kHasRes><<<grid, block, 0, stream>>>(x, res, w, y, h_out, rstd, rows, cols, eps); break;
+    case 2: rmsnorm_fwd_kernel<2, kHasRes><<<grid, block, 0, stream>>>(x, res, w, y, h_out, rstd, rows, cols, eps); break;
+    case 3: rmsnorm_fwd_kernel<3, kHasRes><<<grid, block, 0, stream>>>(x, res, w, y, h_out, rstd, rows, cols, eps); break;
+    default: rmsnorm_fwd_kernel<4, kHasRes><<<grid, block, 0, stream>>>(x, res, w, y, h_out, rstd, rows, cols, eps); break;
+  }
+}
+
+template <bool kHasDres>
+void launch_norm_bwd(int vpt, dim3 grid, cudaStream_t stream, const __nv_bfloat16* dy, const __nv_bfloat16* h,
+                     const __nv_bfloat16* w, const float* rstd, const __nv_bfloat16* dres, __nv_bfloat16* dh,
+                     float* partial, int rows, int cols) {
+  dim3 block(kNormThreads);
+  switch (vpt) {
+    case 1: rmsnorm_bwd_kernel<1, kHasDres><<<grid, block, 0, stream>>>(dy, h, w, rstd, dres, dh, partial, rows, cols); break;
+    case 2: rmsnorm_bwd_kernel<2, kHasDres><<<grid, block, 0, stream>>>(dy, h, w, rstd, dres, dh, partial, rows, cols); break;
+    case 3: rmsnorm_bwd_kernel<3, kHasDres><<<grid, block, 0, stream>>>(dy, h, w, rstd, dres, dh, partial, rows, cols); break;
+    default: rmsnorm_bwd_kernel<4, kHasDres><<<grid, block, 0, stream>>>(dy, h, w, rstd, dres, dh, partial, rows, cols); break;
+  }
+}
+
+// Both kernels and the column reduce for `parts` CTAs; `partial` holds parts * cols floats.
+inline void run_norm_bwd(int parts, cudaStream_t stream, const void* dy, const void* h, const void* w, const float* rstd,
+                         const void* dres, void* dh, float* dw, float* partial, int rows, int cols, int accumulate_dw) {
+  if (dres)
+    launch_norm_bwd<true>(norm_vpt(cols), dim3(parts), stream, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h,
+                          (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dh, partial, rows, cols);
+  else
+    launch_norm_bwd<false>(norm_vpt(cols), dim3(parts), stream, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h,
+                           (const __nv_bfloat16*)w, rstd, nullptr, (__nv_bfloat16*)dh, partial, rows, cols);
+  rmsnorm_dw_reduce_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(partial, dw, parts, cols, accumulate_dw);
 }
 
 }  // namespace ell
@@ -141,21 +285,19 @@ inline int norm_grid(int rows) {
 using namespace ell;
 
 // Number of fp32 scratch elements rmsnorm_bwd needs for its per-CTA weight-gradient partials.
-ELL_API long long ell_rmsnorm_bwd_scratch_elems(int rows, int cols) { return (long long)norm_grid(rows) * cols; }
+ELL_API long long ell_rmsnorm_bwd_scratch_elems(int rows, int cols) { return (long long)norm_grid(rows, cols, true) * cols; }
 
 ELL_API int ell_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out, float* rstd,
                             int rows, int cols, float eps, cudaStream_t stream) {
   if (cols % 8 || cols > kNormMaxCols) return -1;
   if (rows == 0) return 0;
-  dim3 grid((rows + kNormWarps - 1) / kNormWarps < kNumSMs * 8 ? (rows + kNormWarps - 1) / kNormWarps : kNumSMs * 8),
-      block(kNormThreads);
+  dim3 grid(norm_grid(rows, cols, false));
   if (res)
-    rmsnorm_fwd_kernel<true><<<grid, block, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res,
-                                                         (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
-                                                         (__nv_bfloat16*)h_out, rstd, rows, cols, eps);
+    launch_norm_fwd<true>(norm_vpt(cols), grid, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)res,
+                          (const __nv_bfloat16*)w, (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, rows, cols, eps);
   else
-    rmsnorm_fwd_kernel<false><<<grid, block, 0, stream>>>((const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w,
-                                                          (__nv_bfloat16*)y, nullptr, rstd, rows, cols, eps);
+    launch_norm_fwd<false>(norm_vpt(cols), grid, stream, (const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w,
+                           (__nv_bfloat16*)y, nullptr, rstd, rows, cols, eps);
   return launch_status();
 }
 
@@ -165,17 +307,7 @@ ELL_API int ell_rmsnorm_bwd(const void* dy, const void* h, const void* w, const 
                             cudaStream_t stream) {
   if (cols % 8 || cols > kNormMaxCols) return -1;
   if (rows == 0) return 0;
-  const int parts = norm_grid(rows);
-  dim3 grid(parts), block(kNormThreads);
-  if (dres)
-    rmsnorm_bwd_kernel<true><<<grid, block, cols * sizeof(float), stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)h,
-                                                         (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
-                                                         (__nv_bfloat16*)dh, scratch, rows, cols);
-  else
-    rmsnorm_bwd_kernel<false><<<grid, block, cols * sizeof(float), stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)h,
-                                                          (const __nv_bfloat16*)w, rstd, nullptr, (__nv_bfloat16*)dh,
-                                                          scratch, rows, cols);
-  rmsnorm_dw_reduce_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(scratch, dw, parts, cols, accumulate_dw);
+  run_norm_bwd(norm_grid(rows, cols, true), stream, dy, h, w, rstd, dres, dh, dw, scratch, rows, cols, accumulate_dw);
   return launch_status();
 }
 
@@ -230,21 +362,12 @@ ELL_API int ell_rmsnorm_bwd_static(const void* dy, const void* h, const void* w,
   if (rows == 0) return ELL_STATIC_OK;
   float* scratch = nullptr;
   if (int rc = static_scratch_for_current_device(&scratch)) return rc;
-  int parts = norm_grid(rows);
+  int parts = norm_grid(rows, cols, true);
   const int cap = ELL_STATIC_NORM_SCRATCH_ELEMS / cols;   // >= 144 CTAs for every admitted cols
   if (parts > cap) parts = cap;
-  dim3 grid(parts), block(kNormThreads);
   // Every partial row [0, parts) is written in full by the first kernel before the second reads it,
   // so stale contents of the shared scratch are never observed.
-  if (dres)
-    rmsnorm_bwd_kernel<true><<<grid, block, cols * sizeof(float), stream>>>(
-        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
-        (__nv_bfloat16*)dh, scratch, rows, cols);
-  else
-    rmsnorm_bwd_kernel<false><<<grid, block, cols * sizeof(float), stream>>>(
-        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd, nullptr, (__nv_bfloat16*)dh,
-        scratch, rows, cols);
-  rmsnorm_dw_reduce_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(scratch, dw, parts, cols, accumulate_dw);
+  run_norm_bwd(parts, stream, dy, h, w, rstd, dres, dh, dw, scratch, rows, cols, accumulate_dw);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? ELL_STATIC_OK : (int)e;
 }
