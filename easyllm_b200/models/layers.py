@@ -280,11 +280,19 @@ class ParallelAttention(nn.Module):
         qkv = self.qkv(x)                                    # [T, (hq+2hk)·D]
         T = qkv.shape[0]
         pos = meta["position_ids"]
+        rope = None
         if self.rotary is not None:
             need = int(meta.get("max_position", 0)) or (int(pos.max()) + 1 if pos.numel() else 1)
             cos, sin = self.rotary.get(need, qkv.device)
-            qkv = ops.rope_packed(qkv, cos, sin, pos, self.hq, self.hk, self.D)
+            rope = (cos, sin, pos)
         nq, nk = self.hq * self.D, self.hk * self.D
+        if kv_cache is None:
+            slopes = self.alibi.to(qkv.device) if self.alibi is not None else None
+            o = ops.flash_attention_packed(qkv, self.hq, self.hk, self.D, meta.get("cu_seqlens"),
+                                           meta.get("max_seqlen"), alibi_slopes=slopes, rope=rope)
+            return self.o_proj(o)
+        if rope is not None:
+            qkv = ops.rope_packed(qkv, cos, sin, pos, self.hq, self.hk, self.D)
         q = qkv[:, :nq].view(T, self.hq, self.D)
         k = qkv[:, nq:nq + nk].view(T, self.hk, self.D)
         v = qkv[:, nq + nk:].view(T, self.hk, self.D)

@@ -291,6 +291,32 @@ def flash_attention(q, k, v, cu_seqlens=None, max_seqlen=None, causal=True, scal
     return ref.attention_varlen(q, k, v, cu_seqlens, causal, scale, alibi_slopes)
 
 
+def flash_attention_packed(qkv, n_q_heads, n_kv_heads, head_dim, cu_seqlens=None, max_seqlen=None, scale=None,
+                           alibi_slopes=None, rope=None):
+    """(RoPE +) causal attention on the fused projection output ``qkv [T, (Hq+2Hk)·D]`` (layout q|k|v)
+    → ``[T, Hq·D]``.  ``rope`` = (cos, sin, position_ids) rotates the q and k heads first.
+
+    On the kernel path the rotation is in place and the backward writes one packed gradient."""
+    T = qkv.shape[0]
+    nq, nk = n_q_heads * head_dim, n_kv_heads * head_dim
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    if (_kern(qkv) and alibi_slopes is None and head_dim == 128 and _ATTN in ("auto", "kernel") and qkv.dim() == 2
+            and qkv.is_contiguous()):
+        if max_seqlen is None:
+            max_seqlen = T if cu_seqlens is None else int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
+        if rope is not None:
+            cos, sin, pos = rope
+            rope = (cos, sin, pos if pos.dtype == torch.int32 else pos.to(torch.int32))
+        return _cu().flash_attention_packed(qkv, n_q_heads, n_kv_heads, head_dim, cu_seqlens, max_seqlen, scale, rope)
+    if rope is not None:
+        qkv = rope_packed(qkv, rope[0], rope[1], rope[2], n_q_heads, n_kv_heads, head_dim)
+    q = qkv[:, :nq].view(T, n_q_heads, head_dim)
+    k = qkv[:, nq:nq + nk].view(T, n_kv_heads, head_dim)
+    v = qkv[:, nq + nk:].view(T, n_kv_heads, head_dim)
+    return flash_attention(q, k, v, cu_seqlens, max_seqlen, True, scale, alibi_slopes).reshape(T, nq)
+
+
 # ---------------------------------------------------------------------------------------------
 # Vocab-parallel cross entropy (stand-alone and fused with the LM head)
 # ---------------------------------------------------------------------------------------------
@@ -359,9 +385,50 @@ def vocab_parallel_cross_entropy(vocab_parallel_logits, target, cut_size=None, i
     return _VocabParallelCE.apply(vocab_parallel_logits, target, cut_size, inplace_backward)
 
 
+class _LMHeadCE(torch.autograd.Function):
+    """LM-head GEMM whose epilogue also produces the vocab-parallel cross-entropy statistics (row max,
+    sum-exp, target logit) while each logits tile is still in registers; only 3 floats per token cross the
+    TP group.  Backward turns the stored bf16 logits into dlogits in place, then runs dgrad and wgrad.
+    Fuses llm/models/mg_models/base_modules/layers/lm_head.py:49-71 with
+    llm/models/mg_models/base_modules/functions/cross_entropy.py:22-112."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, target, cut_size):
+        group, tp, rank = _tp_info()
+        Vp = weight.shape[0]
+        valid = Vp - cut_size if (cut_size and rank == tp - 1) else Vp
+        start = rank * Vp
+        tflat = target.reshape(-1).contiguous()
+        logits, parts = _cu().gemm_ce(hidden, weight, tflat, start, valid)
+        lse, tl = _combine_parts(parts[:, 0].contiguous(), parts[:, 1].contiguous(), parts[:, 2].contiguous(),
+                                 group, tp)
+        ctx.save_for_backward(hidden, weight, logits, tflat, lse)
+        ctx.wref = weight
+        ctx.meta = (start, valid)
+        return (lse - tl).view(target.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        hidden, weight, logits, tflat, lse = ctx.saved_tensors
+        start, valid = ctx.meta
+        dlogits = _cu().ce_bwd_(logits, tflat, lse, g.reshape(-1).float().contiguous(), start, valid)
+        dx = matmul_nn(dlogits, weight) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(ctx.wref, "main_grad", None)
+            if mg is not None:
+                matmul_tn_accum(dlogits, hidden, mg)
+            else:
+                dw = matmul_tn_accum(dlogits, hidden).to(weight.dtype)
+        return dx, dw, None, None
+
+
 def lm_head_cross_entropy(hidden, weight, target, cut_size=None):
-    """LM head GEMM + vocab-parallel CE → per-token losses ``[T]`` (fp32).  The bf16 logits
-    live only between the two ops; their buffer is overwritten by dlogits in backward."""
+    """LM head GEMM + vocab-parallel CE → per-token losses (fp32, shape of ``target``).  The bf16 logits
+    live only between forward and backward; their buffer is overwritten by dlogits in backward."""
+    if (_kern(hidden) and hidden.dim() == 2 and _GEMM == "tcgen05" and hidden.shape[1] % 8 == 0
+            and weight.shape[0] % 8 == 0):
+        return _LMHeadCE.apply(hidden.contiguous(), weight, target, cut_size)
     logits = linear(hidden, weight)
     return vocab_parallel_cross_entropy(logits, target, cut_size, inplace_backward=True)
 

@@ -92,6 +92,12 @@ def bench_norm(iters):
                      "frac_of_peak": by / t / 1e6 / _PEAKS["hbm_gbs"]})
         print(f"add_rmsnorm fwd {T}x{H}: {t:.4f} ms {by / t / 1e6:.0f} GB/s "
               f"({100 * rows[-1]['frac_of_peak']:.1f}% of {_PEAKS['source']} copy)", flush=True)
+        y, h, rstd = cu.rmsnorm_fwd(x, r, w, 1e-5)
+        t = timed(lambda: cu.rmsnorm_bwd(y, h, w, rstd, r), iters)
+        rows.append({"name": f"add_rmsnorm bwd {T}x{H}", "ms": t, "gbs": by / t / 1e6,
+                     "frac_of_peak": by / t / 1e6 / _PEAKS["hbm_gbs"]})
+        print(f"add_rmsnorm bwd {T}x{H}: {t:.4f} ms {by / t / 1e6:.0f} GB/s "
+              f"({100 * rows[-1]['frac_of_peak']:.1f}% of {_PEAKS['source']} copy)", flush=True)
         gu = torch.randn(T, 2 * 11008, device="cuda", dtype=torch.bfloat16)
         t = timed(lambda: cu.swiglu_fwd(gu), iters)
         by = 3 * T * 11008 * 2
@@ -129,6 +135,19 @@ def bench_attn(iters):
         rows.append({"name": f"attn fwd causal T={T} H={Hq}/{Hk}", "kernel_ms": res["kernel"], "library_ms": res["library"],
                      "kernel_tflops": fl / res["kernel"] / 1e9 if res["kernel"] else None,
                      "library_tflops": fl / res["library"] / 1e9 if res["library"] else None})
+        print(rows[-1], flush=True)
+        # backward: the tcgen05 kernel against differentiating the library attention (its forward + backward)
+        qkv = torch.randn(T, (Hq + 2 * Hk) * 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        do = torch.randn(T, Hq * 128, device="cuda", dtype=torch.bfloat16)
+        o = ops.flash_attention_packed(qkv, Hq, Hk, 128, None, T)
+        bres = {}
+        for name in ("kernel", "library"):
+            cu.set_attention_backward(name)
+            bres[name] = timed(lambda: torch.autograd.grad(o, qkv, do, retain_graph=True), iters)
+        cu.set_attention_backward("kernel")
+        rows.append({"name": f"attn bwd causal T={T} H={Hq}/{Hk}", "kernel_ms": bres["kernel"],
+                     "library_ms": bres["library"], "kernel_tflops": 2.5 * fl / bres["kernel"] / 1e9,
+                     "library_tflops": 2.5 * fl / bres["library"] / 1e9})
         print(rows[-1], flush=True)
     return rows
 

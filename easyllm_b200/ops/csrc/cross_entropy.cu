@@ -112,3 +112,31 @@ ELL_API int ell_ce_bwd(void* logits, const long long* target, const float* lse, 
                                                  vocab_start);
   return launch_status();
 }
+
+namespace ell {
+// parts[T, 3] = merge over column tiles of part[tiles][3][T] (max, sum-exp relative to that max, target logit).
+__global__ void ce_combine_kernel(const float* __restrict__ part, float* __restrict__ parts, int tiles, int T) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  float m = -INFINITY, s = 0.f, tl = 0.f;
+  for (int i = 0; i < tiles; ++i) {
+    const float* p = part + (size_t)i * 3 * T + t;
+    const float mi = p[0], si = p[(size_t)T];
+    tl += p[(size_t)2 * T];
+    if (mi > -INFINITY) {
+      const float nm = fmaxf(m, mi);
+      s = s * __expf(m - nm) + si * __expf(mi - nm);
+      m = nm;
+    }
+  }
+  parts[(size_t)t * 3] = m;
+  parts[(size_t)t * 3 + 1] = s;
+  parts[(size_t)t * 3 + 2] = tl;
+}
+}  // namespace ell
+
+ELL_API int ell_ce_combine(const float* part, float* parts, int tiles, int T, cudaStream_t stream) {
+  if (T == 0) return 0;
+  ell::ce_combine_kernel<<<(T + 255) / 256, 256, 0, stream>>>(part, parts, tiles, T);
+  return ell::launch_status();
+}

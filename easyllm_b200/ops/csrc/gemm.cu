@@ -35,7 +35,9 @@ constexpr int kEpiThreads = 128;
 constexpr int kABytes = kBM * kBK * 2;     // 16 KiB
 constexpr int kEpiBufBytes = 128 * 64 * 2; // one 128x64 bf16 store box
 
-enum GemmOut { kOutBf16 = 0, kOutF32Accum = 1, kOutF32 = 2 };
+// kOutBf16CE: bf16 C plus, per row and column tile, the cross-entropy statistics (max, sum-exp, target logit)
+// of the rounded logits, computed in the epilogue while the tile is in registers.
+enum GemmOut { kOutBf16 = 0, kOutF32Accum = 1, kOutF32 = 2, kOutBf16CE = 3 };
 enum GemmErr { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3, kErrComm = 4, kErrFlagWait = 5 };
 
 // ---- fusion with the tensor-parallel collective (sequence parallelism) ------------------------------
@@ -66,6 +68,12 @@ struct FuseArgs {
   unsigned int* queue;                   // RS: local, monotonic: next owned tile to reduce
   unsigned int queue_base;               // RS: value of *queue when this launch starts (tracked by the host)
   __nv_bfloat16* y_local;                // RS: output shard [rows_per_rank, N]
+  // kOutBf16CE: targets [M] (global vocab ids), partials [tiles_n][3][M], first vocab id of column 0,
+  // number of leading columns that are real vocabulary (the padded tail is excluded)
+  const long long* ce_target;
+  float* ce_part;
+  long long ce_vocab_start;
+  int ce_valid;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -514,7 +522,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (*(volatile int*)&sh->epi_abort) break;   // uniform across the 128 epilogue threads
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      if (OUT == kOutBf16) {
+      float ce_m = -INFINITY, ce_s = 0.f, ce_t = 0.f;
+      int ce_tcol = -1;                          // target column inside this tile, if any
+      if (OUT == kOutBf16CE) {
+        const int row = m0 + row_in_tile;
+        if (row < M) {
+          const long long tc = fuse.ce_target[row] - fuse.ce_vocab_start - n0;
+          if (tc >= 0 && tc < BN && tc + n0 < fuse.ce_valid) ce_tcol = (int)tc;
+        }
+      }
+      if (OUT == kOutBf16 || OUT == kOutBf16CE) {
 #pragma unroll 1
         for (int j = 0; j < BN / 64; ++j) {
           uint8_t* buf = sC + (store_count & 1) * kEpiBufBytes;
@@ -530,6 +547,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               const int col = n0 + j * 64 + c;
               const float b = col < N ? __bfloat162float(bias[col]) : 0.f;
               r[c] = __float_as_uint(__uint_as_float(r[c]) + b);
+            }
+          }
+          if (OUT == kOutBf16CE) {
+            // statistics of the logits as stored (rounded to bf16), so that backward's exp(logit - lse) sums to 1
+            const int cbase = n0 + j * 64;
+            float cm = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+              const float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[c])));
+              r[c] = __float_as_uint(x);
+              if (cbase + c < fuse.ce_valid) cm = fmaxf(cm, x);
+              if (j * 64 + c == ce_tcol) ce_t = x;
+            }
+            if (cm > -INFINITY) {
+              const float nm = fmaxf(ce_m, cm);
+              float acc_s = ce_s * __expf(ce_m - nm);
+#pragma unroll
+              for (int c = 0; c < 64; ++c)
+                if (cbase + c < fuse.ce_valid) acc_s += __expf(__uint_as_float(r[c]) - nm);
+              ce_s = acc_s;
+              ce_m = nm;
             }
           }
           uint8_t* row_ptr = buf + row_in_tile * 128;
@@ -558,6 +596,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tma_store_commit();
           }
           ++store_count;
+        }
+        if (OUT == kOutBf16CE) {
+          const int row = m0 + row_in_tile;
+          if (row < M) {
+            float* part = fuse.ce_part + (size_t)nt * 3 * M + row;
+            part[0] = ce_m;
+            part[(size_t)M] = ce_s;
+            part[(size_t)2 * M] = ce_t;
+          }
         }
         if (FUSE == kFuseRS && leader) {
           // Publish the flag of the PREVIOUS tile: its bulk stores were committed BN/64 groups ago, so
@@ -732,6 +779,7 @@ ELL_API int ell_gemm_bf16(const void* A, const void* B, void* C, const void* bia
                           cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (bias && out_mode != kOutBf16) return -2;
+  if (out_mode == kOutBf16CE) return -2;   // needs the statistics arguments: use ell_gemm_ce
   int BN = (bn_hint == 128 || bn_hint == 256) ? bn_hint : (N >= 256 ? 256 : 128);
   CUtensorMap tA, tB, tC;
   int rc;
@@ -766,6 +814,30 @@ ELL_API int ell_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   ELL_GEMM_BN(256)
   ELL_GEMM_BN(128)
   return -3;
+}
+
+// Column tiles the cross-entropy epilogue produces partials for (BN = 256).
+ELL_API int ell_gemm_ce_tiles(int N) { return (N + 255) / 256; }
+
+// logits[M, N] (bf16) = X[M, K] · W[N, K]^T and, fused into the epilogue, per-(row, column tile) partial
+// statistics part[tiles_n][3][M] = (max, sum exp(x - max), logit of the target if it falls in the tile else 0)
+// over the first `valid_cols` columns; target holds global vocabulary ids, column 0 is id vocab_start.
+ELL_API int ell_gemm_ce(const void* X, const void* W, void* logits, const long long* target, float* part, int M, int N,
+                        int K, long long vocab_start, int valid_cols, int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  CUtensorMap tA, tB, tC;
+  int rc = make_tmap_bf16_2d(&tA, X, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBK, kBM);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tB, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, kBK, 256);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tC, logits, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 128);
+  if (rc) return rc;
+  FuseArgs f{};
+  f.ce_target = target;
+  f.ce_part = part;
+  f.ce_vocab_start = vocab_start;
+  f.ce_valid = valid_cols < N ? valid_cols : N;
+  return launch_gemm<256, false, false, kOutBf16CE, false>(tA, tB, tC, f, nullptr, M, N, K, N, err, sm_count(), stream);
 }
 
 static void fill_fuse(FuseArgs& f, int rank, int tp, int n_comm, int rows_per_rank, int flags_per_src,

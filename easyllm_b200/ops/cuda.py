@@ -235,6 +235,29 @@ def gemm(a, b, out=None, bias=None, a_mn=False, b_mn=False, out_mode=0, bn=0):
     return out
 
 
+def gemm_ce(x, w, target, vocab_start, valid_cols):
+    """LM-head GEMM with the cross-entropy statistics fused into its epilogue.
+
+    Returns ``(logits [T, V] bf16, parts [T, 3] fp32)`` with parts = (row max, Σ exp(l − max), target logit or 0)
+    over the first ``valid_cols`` columns — the same triple ``ce_fwd`` computes from stored logits."""
+    _bf16c(x, "x"); _bf16c(w, "w")
+    T, K = x.shape
+    V = w.shape[0]
+    if K % 8 or V % 8:
+        raise ValueError("gemm_ce: K and V must be multiples of 8")
+    logits = torch.empty(T, V, dtype=torch.bfloat16, device=x.device)
+    tiles = lib().ell_gemm_ce_tiles(c_int(V))
+    part = scratch(tiles * 3 * T, tag="gemm_ce_part")
+    parts = torch.empty(T, 3, dtype=torch.float32, device=x.device)
+    tgt = target if target.dtype == torch.int64 else target.to(torch.int64)
+    rc = lib().ell_gemm_ce(_p(x), _p(w), _p(logits), _p(tgt.contiguous()), _p(part), c_int(T), c_int(V), c_int(K),
+                           c_longlong(vocab_start), c_int(valid_cols), _p(err_flag(x.device)), _stream())
+    _check(rc, "gemm_ce")
+    rc = lib().ell_ce_combine(_p(part), _p(parts), c_int(tiles), c_int(T), _stream())
+    _check(rc, "ce_combine")
+    return logits, parts
+
+
 def has_symbol(name):
     try:
         getattr(lib(), name)
@@ -269,6 +292,50 @@ def flash_attn_fwd(q, k, v, row_start, scale):
     return out, lse
 
 
+def flash_attn_bwd(do, q, k, v, out, lse, row_start, scale, dq=None, dk=None, dv=None):
+    """Gradients of the causal attention.  ``dq/dk/dv`` may be views into one packed ``[T, (Hq+2Hk)·128]``
+    buffer (row stride shared by dk and dv); they are allocated (contiguous) when not given."""
+    T, Hq, D = q.shape
+    Hk = k.shape[1]
+    if not has_symbol("ell_flash_attn_bwd"):
+        raise RuntimeError("libeasyllm_b200.so was built without ell_flash_attn_bwd")
+    do = do.contiguous()
+    out = out.contiguous()
+    if dq is None:
+        dq = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+        dk = torch.empty(T, Hk, D, dtype=torch.bfloat16, device=q.device)
+        dv = torch.empty(T, Hk, D, dtype=torch.bfloat16, device=q.device)
+    if dk.stride(0) != dv.stride(0):
+        raise ValueError("flash_attn_bwd: dk and dv must share a row stride")
+    acc = scratch(T * Hq * D, tag="fa_bwd_dq")
+    delta = scratch(T * Hq, tag="fa_bwd_delta")
+    rc = lib().ell_flash_attn_bwd(_p(q), _p(k), _p(v), _p(out), _p(do), _p(lse), _p(row_start), _p(dq), _p(dk), _p(dv),
+                                  _p(acc), _p(delta), c_int(T), c_int(Hq), c_int(Hk), c_int(q.stride(0)),
+                                  c_int(k.stride(0)), c_int(dq.stride(0)), c_int(dk.stride(0)), c_float(scale),
+                                  _p(err_flag(q.device)), _stream())
+    _check(rc, "flash_attn_bwd")
+    global LAUNCHES
+    LAUNCHES += 3  # memset, delta and dq-convert launches beside the main kernel
+    return dq, dk, dv
+
+
+_FA_BWD = "kernel"   # "kernel": tcgen05 backward; "library": differentiate the library attention
+
+
+def set_attention_backward(which):
+    global _FA_BWD
+    assert which in ("kernel", "library")
+    _FA_BWD = which
+
+
+def _library_bwd(q, k, v, do, cu, has_cu, max_seqlen, scale):
+    from . import _library_attention
+    with torch.enable_grad():
+        qq, kk, vv = (t.detach().requires_grad_() for t in (q, k, v))
+        o = _library_attention(qq, kk, vv, cu if has_cu else None, max_seqlen, True, scale)
+        return torch.autograd.grad(o, (qq, kk, vv), do)
+
+
 class _FlashAttn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens, max_seqlen, scale):
@@ -283,16 +350,62 @@ class _FlashAttn(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, out, lse, rs, cu = ctx.saved_tensors
         max_seqlen, scale, has_cu = ctx.meta
-        if has_symbol("ell_flash_attn_bwd"):
-            dq, dk, dv = flash_attn_bwd(do.contiguous(), q, k, v, out, lse, rs, scale)
-            return dq, dk, dv, None, None, None
-        # until the backward kernel is built: differentiate the library attention on the same inputs
-        from . import _library_attention
-        with torch.enable_grad():
-            qq, kk, vv = (t.detach().requires_grad_() for t in (q, k, v))
-            o = _library_attention(qq, kk, vv, cu if has_cu else None, max_seqlen, True, scale)
-            dq, dk, dv = torch.autograd.grad(o, (qq, kk, vv), do)
+        if _FA_BWD == "kernel":
+            dq, dk, dv = flash_attn_bwd(do, q, k, v, out, lse, rs, scale)
+        else:
+            dq, dk, dv = _library_bwd(q, k, v, do, cu, has_cu, max_seqlen, scale)
         return dq, dk, dv, None, None, None
+
+
+def _split_packed(qkv, hq, hk, D):
+    T = qkv.shape[0]
+    nq, nk = hq * D, hk * D
+    return (qkv[:, :nq].view(T, hq, D), qkv[:, nq:nq + nk].view(T, hk, D), qkv[:, nq + nk:].view(T, hk, D))
+
+
+class _FlashAttnPacked(torch.autograd.Function):
+    """(RoPE +) attention on the fused projection output ``qkv [T, (Hq+2Hk)·D]`` (layout q|k|v).
+
+    The rotation is applied to ``qkv`` in place (the projection's backward does not need its output), and the
+    backward writes dq, dk and dv straight into one packed gradient and un-rotates it in place, so neither
+    slice gradients nor a copy for the rotary backward are materialised."""
+
+    @staticmethod
+    def forward(ctx, qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, cos, sin, pos):
+        T = qkv.shape[0]
+        rs = _row_start(cu_seqlens, T, qkv.device)
+        if cos is not None:
+            rope_(qkv, cos, sin, pos, hq + hk, D)
+        q, k, v = _split_packed(qkv, hq, hk, D)
+        out, lse = flash_attn_fwd(q, k, v, rs, scale)
+        none = torch.empty(0)
+        ctx.save_for_backward(qkv, out, lse, rs, cu_seqlens if cu_seqlens is not None else none,
+                              *((cos, sin, pos) if cos is not None else (none, none, none)))
+        ctx.meta = (hq, hk, D, max_seqlen, scale, cu_seqlens is not None, cos is not None)
+        return out.view(T, hq * D)
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, out, lse, rs, cu, cos, sin, pos = ctx.saved_tensors
+        hq, hk, D, max_seqlen, scale, has_cu, has_rope = ctx.meta
+        T = qkv.shape[0]
+        q, k, v = _split_packed(qkv, hq, hk, D)
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = _split_packed(dqkv, hq, hk, D)
+        do = do.reshape(T, hq, D)
+        if _FA_BWD == "kernel":
+            flash_attn_bwd(do, q, k, v, out, lse, rs, scale, dq, dk, dv)
+        else:
+            gq, gk, gv = _library_bwd(q, k, v, do, cu, has_cu, max_seqlen, scale)
+            dq.copy_(gq); dk.copy_(gk); dv.copy_(gv)
+        if has_rope:
+            rope_(dqkv, cos, sin, pos, hq + hk, D, backward=True)
+        return (dqkv,) + (None,) * 9
+
+
+def flash_attention_packed(qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, rope=None):
+    cos, sin, pos = rope if rope is not None else (None, None, None)
+    return _FlashAttnPacked.apply(qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, cos, sin, pos)
 
 
 def flash_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale):

@@ -67,3 +67,86 @@ def test_flash_autograd_path(cu):
     of.backward(do.float())
     for a, b in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
         assert (a.float() - b).abs().max().item() < 5e-2 * max(1.0, b.abs().max().item())
+
+
+BWD_CASES = [  # T, Hq, Hk, cu_seqlens
+    (128, 1, 1, None), (256, 2, 2, None), (300, 4, 2, None), (1024, 8, 2, None),
+    (512, 4, 4, [0, 100, 101, 350, 512]), (777, 2, 1, [0, 128, 256, 640, 777]), (2048, 2, 2, None),
+]
+
+
+@pytest.mark.parametrize("T,Hq,Hk,cu_list", BWD_CASES)
+def test_flash_bwd_packed(cu, T, Hq, Hk, cu_list):
+    """Backward kernel on views of a packed buffer, gradients written into one packed dQKV."""
+    from easyllm_b200.ops import reference as ref
+    torch.manual_seed(T * 7 + Hq)
+    W = (Hq + 2 * Hk) * 128
+    qkv = torch.randn(T, W, device="cuda", dtype=torch.bfloat16)
+    q, k, v = cu._split_packed(qkv, Hq, Hk, 128)
+    cs = torch.tensor(cu_list, dtype=torch.int32, device="cuda") if cu_list else None
+    rs = cu._row_start(cs, T, q.device)
+    scale = 128 ** -0.5
+    out, lse = cu.flash_attn_fwd(q, k, v, rs, scale)
+    do = torch.randn(T, Hq, 128, device="cuda", dtype=torch.bfloat16)
+    dqkv = torch.full_like(qkv, float("nan"))
+    dq, dk, dv = cu._split_packed(dqkv, Hq, Hk, 128)
+    cu.flash_attn_bwd(do, q, k, v, out, lse, rs, scale, dq, dk, dv)
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    assert torch.isfinite(dqkv.float()).all()
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    of = ref.attention_varlen(qf, kf, vf, cs, True, scale)
+    of.backward(do.float())
+    for name, a, b in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
+        err = (a.float() - b).abs().max().item()
+        tol = 3e-2 * max(1.0, b.abs().max().item())
+        assert err < tol, (name, err, tol)
+
+
+def test_flash_packed_autograd_matches_library(cu):
+    from easyllm_b200 import ops
+    torch.manual_seed(3)
+    T, Hq, Hk = 640, 4, 2
+    cs = torch.tensor([0, 200, 640], dtype=torch.int32, device="cuda")
+    base = torch.randn(T, (Hq + 2 * Hk) * 128, device="cuda", dtype=torch.bfloat16)
+    do = torch.randn(T, Hq * 128, device="cuda", dtype=torch.bfloat16)
+    grads = {}
+    for which in ("kernel", "library"):
+        cu.set_attention_backward(which)
+        try:
+            x = base.clone().requires_grad_()
+            o = ops.flash_attention_packed(x, Hq, Hk, 128, cs, 440)
+            o.backward(do)
+            grads[which] = x.grad.float()
+        finally:
+            cu.set_attention_backward("kernel")
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    ref_max = grads["library"].abs().max().item()
+    assert (grads["kernel"] - grads["library"]).abs().max().item() < 3e-2 * max(1.0, ref_max)
+
+
+def test_packed_attention_with_rope_matches_reference(cu):
+    """RoPE folded into the packed attention op (in-place rotate, packed un-rotated gradient)."""
+    from easyllm_b200 import ops
+    from easyllm_b200.ops import reference as ref
+    torch.manual_seed(11)
+    T, Hq, Hk, D = 384, 4, 2, 128
+    cos, sin = ref.rope_tables(D, T, device="cuda")
+    pos = torch.arange(T, device="cuda")
+    base = torch.randn(T, (Hq + 2 * Hk) * D, device="cuda", dtype=torch.bfloat16)
+    do = torch.randn(T, Hq * D, device="cuda", dtype=torch.bfloat16)
+    x = base.clone().requires_grad_()
+    o = ops.flash_attention_packed(x * 1, Hq, Hk, D, None, T, rope=(cos, sin, pos))
+    o.backward(do)
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    xf = base.float().requires_grad_()
+    q = xf[:, :Hq * D].view(T, Hq, D)
+    k = xf[:, Hq * D:(Hq + Hk) * D].view(T, Hk, D)
+    v = xf[:, (Hq + Hk) * D:].view(T, Hk, D)
+    qr, kr = ref.rope(q, k, cos.float(), sin.float(), pos)
+    of = ref.attention_varlen(qr, kr, v, None, True).reshape(T, Hq * D)
+    of.backward(do.float())
+    assert (o.float() - of).abs().max().item() < 3e-2
+    assert (x.grad.float() - xf.grad).abs().max().item() < 3e-2 * max(1.0, xf.grad.abs().max().item())

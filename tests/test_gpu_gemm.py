@@ -90,3 +90,57 @@ def test_linear_autograd_matches_torch(cu):
     for got, want in ((y, yr), (x.grad, xf.grad), (w.grad, wf.grad), (b.grad, bf.grad)):
         assert (got.float() - want).abs().max().item() <= 3e-2 * max(1.0, want.abs().max().item())
     cu.check_err_flag()
+
+
+@pytest.mark.parametrize("T,V,K,cut,start", [(256, 512, 256, 0, 0), (300, 1000, 128, 24, 0), (1024, 32000, 512, 0, 0),
+                                             (128, 776, 64, 8, 776)])
+def test_gemm_ce_epilogue_statistics(cu, T, V, K, cut, start):
+    """LM-head GEMM with fused cross-entropy statistics against a plain fp32 log-softmax of the stored logits."""
+    torch.manual_seed(T + V)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(V, K, device="cuda") * 0.2).to(torch.bfloat16)
+    valid = V - cut
+    tgt = torch.randint(start, start + valid, (T,), device="cuda")
+    tgt[::7] = start + V + 5                      # targets owned by another vocabulary shard
+    logits, parts = cu.gemm_ce(x, w, tgt, start, valid)
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    want_logits = x.float() @ w.float().t()
+    assert (logits.float() - want_logits).abs().max().item() < 2e-2 * max(1.0, want_logits.abs().max().item())
+    lf = logits.float()[:, :valid]
+    mx = lf.max(1).values
+    se = torch.exp(lf - mx[:, None]).sum(1)
+    loc = tgt - start
+    hit = (loc >= 0) & (loc < valid)
+    tl = torch.where(hit, lf.gather(1, loc.clamp(0, valid - 1)[:, None]).squeeze(1), torch.zeros_like(mx))
+    torch.testing.assert_close(parts[:, 0], mx, rtol=0, atol=0)
+    torch.testing.assert_close(parts[:, 1], se, rtol=2e-3, atol=1e-3)
+    torch.testing.assert_close(parts[:, 2], tl, rtol=0, atol=0)
+    # and against the stand-alone statistics kernel on the same stored logits
+    ref_parts = cu.ce_fwd(logits, tgt, start, valid)
+    torch.testing.assert_close(parts, ref_parts, rtol=2e-3, atol=1e-3)
+
+
+def test_lm_head_ce_autograd_matches_unfused(cu):
+    from easyllm_b200 import ops
+    torch.manual_seed(5)
+    T, V, K = 512, 2048, 256
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(V, K, device="cuda") * 0.1).to(torch.bfloat16)
+    tgt = torch.randint(0, V, (T,), device="cuda")
+    outs = []
+    for fused in (True, False):
+        xx, ww = x.clone().requires_grad_(), w.clone().requires_grad_()
+        if fused:
+            loss = ops.lm_head_cross_entropy(xx, ww, tgt)
+        else:
+            loss = ops.vocab_parallel_cross_entropy(ops.linear(xx, ww), tgt, None, inplace_backward=True)
+        loss.mean().backward()
+        outs.append((loss.detach(), xx.grad.float(), ww.grad.float()))
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    torch.testing.assert_close(outs[0][0], outs[1][0], rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(outs[0][1], outs[1][1], rtol=2e-2, atol=1e-5)
+    torch.testing.assert_close(outs[0][2], outs[1][2], rtol=2e-2, atol=1e-5)
+    ref_loss = torch.nn.functional.cross_entropy(x.float() @ w.float().t(), tgt, reduction="none")
+    torch.testing.assert_close(outs[0][0], ref_loss, rtol=2e-2, atol=2e-2)
