@@ -42,6 +42,12 @@ MODELS = {
                        intermediate_size=13824),
     "llama2_7b_4l": dict(num_layers=4, hidden_size=4096, num_attention_heads=32, num_kv_attention_heads=32,
                          intermediate_size=11008),
+    # BASELINE config shapes beyond the headline: Qwen-14B (QKV bias, 152k vocabulary) and the Llama-2-70B layer
+    # shape truncated to 40 layers (GQA 64/8)
+    "qwen_14b": dict(num_layers=40, hidden_size=5120, num_attention_heads=40, num_kv_attention_heads=40,
+                     intermediate_size=13696, vocab_size=152064, attention_qkv_bias=True),
+    "llama2_70b_40l": dict(num_layers=40, hidden_size=8192, num_attention_heads=64, num_kv_attention_heads=8,
+                           intermediate_size=28672),
     "dev_1b": dict(num_layers=8, hidden_size=2048, num_attention_heads=16, num_kv_attention_heads=16,
                    intermediate_size=5632),
 }
@@ -141,11 +147,12 @@ def main():
     cu.lib()
     torch.manual_seed(1234 + g.rank)
 
-    shape = MODELS[args.model]
+    shape = dict(MODELS[args.model])
+    vocab = shape.pop("vocab_size", 32000)
     dc = None
     if args.recompute_layers:
         dc = {"enabled": True, "size_map": {1 << 30: args.recompute_layers}}
-    model = llama_custom(vocab_size=32000, seq_length=args.seq, bf16=True, sequence_parallel=g.tp > 1,
+    model = llama_custom(vocab_size=vocab, seq_length=args.seq, bf16=True, sequence_parallel=g.tp > 1,
                          checkpoint_activations=False, dynamic_checkpoint=dc, pp_partition_method="parameters", **shape)
     fused_tp = False
     if g.tp > 1 and not args.no_fused_tp and ops.get_backend() == "b200":
@@ -161,12 +168,12 @@ def main():
     tokens_per_step = global_batch * args.seq
     dev = torch.device("cuda", torch.cuda.current_device())
 
-    host_iter = synthetic_batches(32000, args.seq, 1, seed=0, pin=True)
+    host_iter = synthetic_batches(vocab, args.seq, 1, seed=0, pin=True)
 
     def device_iter():
         # a fixed pool of device-resident micro-batches (distinct data per micro-batch of a step)
         pool = []
-        src = synthetic_batches(32000, args.seq, 1, seed=1)
+        src = synthetic_batches(vocab, args.seq, 1, seed=1)
         for _ in range(min(n_micro, 64)):
             (tok, pos, _), (lab, msk) = next(src)
             pool.append(((tok.to(dev), pos.to(dev), None), (lab.to(dev), msk.to(dev))))

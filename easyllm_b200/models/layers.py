@@ -132,6 +132,8 @@ class VocabParallelEmbedding(nn.Module):
 
     def lookup(self, ids):
         """Local partial lookup (no reduction): rows for foreign ids are zero."""
+        if self.weight.is_cuda and self.weight.dtype == torch.bfloat16:
+            return ops.embedding(ids, self.weight, self.vocab_start)
         if get_grid().tp == 1:
             return F.embedding(ids, self.weight)
         mask = (ids < self.vocab_start) | (ids >= self.vocab_end)

@@ -200,6 +200,41 @@ def linear(x, w, bias=None):
 
 
 # ---------------------------------------------------------------------------------------------
+# Vocab-parallel embedding lookup (partial: rows of ids owned by other ranks are zero)
+# ---------------------------------------------------------------------------------------------
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, weight, vocab_start):
+        ctx.save_for_backward(ids)
+        ctx.wref = weight
+        ctx.start = vocab_start
+        return _cu().embedding_fwd(ids, weight, vocab_start)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids,) = ctx.saved_tensors
+        w = ctx.wref
+        mg = getattr(w, "main_grad", None)
+        dout = dout.contiguous()
+        if mg is not None:
+            _cu().embedding_bwd_(ids, dout, mg, ctx.start)
+            return None, None, None
+        g32 = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        _cu().embedding_bwd_(ids, dout, g32, ctx.start)
+        return None, g32.to(w.dtype), None
+
+
+def embedding(ids, weight, vocab_start=0):
+    """``weight[ids - vocab_start]`` with zero rows for ids outside this rank's vocabulary range."""
+    if _kern(weight) and weight.shape[1] % 8 == 0 and weight.is_contiguous():
+        return _Embedding.apply(ids, weight, vocab_start)
+    rows = weight.shape[0]
+    mask = (ids < vocab_start) | (ids >= vocab_start + rows)
+    out = F.embedding((ids - vocab_start).masked_fill(mask, 0), weight)
+    return out.masked_fill(mask.unsqueeze(-1), 0.0) if bool(mask.any()) else out
+
+
+# ---------------------------------------------------------------------------------------------
 # RoPE on the packed QKV rows, SwiGLU on the fused gate|up rows
 # ---------------------------------------------------------------------------------------------
 class _RopePacked(torch.autograd.Function):

@@ -144,3 +144,66 @@ ELL_API int ell_accum_bf16_to_f32(const void* in, float* out, long long n, cudaS
   accum_bf16_to_f32_kernel<<<ew_grid(n / 8 + 1, 256), 256, 0, stream>>>((const __nv_bfloat16*)in, out, n);
   return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Vocab-parallel embedding: masked row gather, and its backward as an fp32 scatter-add straight
+// into the weight's gradient accumulator (no bf16 gradient tensor, no sort).
+// Replaces F.embedding + mask writes of the reference
+// (llm/models/mg_models/base_modules/layers/vocab_parallel_emb.py:106-137).
+// ---------------------------------------------------------------------------------------------
+namespace ell {
+
+// out[t, :] = ids[t] in [vocab_start, vocab_start + rows) ? weight[ids[t] - vocab_start, :] : 0
+__global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ weight,
+                                     __nv_bfloat16* __restrict__ out, int T, int cols, long long vocab_start,
+                                     long long rows) {
+  const int nvec = cols / 8;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    const long long loc = ids[t] - vocab_start;
+    const bool mine = loc >= 0 && loc < rows;
+    const bf16x8* src = reinterpret_cast<const bf16x8*>(weight + (mine ? loc : 0) * cols);
+    bf16x8* dst = reinterpret_cast<bf16x8*>(out + (size_t)t * cols);
+    for (int c = threadIdx.x; c < nvec; c += blockDim.x) dst[c] = mine ? src[c] : bf16x8{};
+  }
+}
+
+// grad32[ids[t] - vocab_start, :] += dout[t, :] for the ids this rank owns (fp32 vector atomics)
+__global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
+                                     float* __restrict__ grad32, int T, int cols, long long vocab_start,
+                                     long long rows) {
+  const int nvec = cols / 8;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    const long long loc = ids[t] - vocab_start;
+    if (loc < 0 || loc >= rows) continue;
+    const bf16x8* src = reinterpret_cast<const bf16x8*>(dout + (size_t)t * cols);
+    float* dst = grad32 + loc * cols;
+    for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+      float f[8];
+      unpack8(src[c], f);
+      atomicAdd(reinterpret_cast<float4*>(dst + c * 8), make_float4(f[0], f[1], f[2], f[3]));
+      atomicAdd(reinterpret_cast<float4*>(dst + c * 8 + 4), make_float4(f[4], f[5], f[6], f[7]));
+    }
+  }
+}
+
+}  // namespace ell
+
+ELL_API int ell_embedding_fwd(const long long* ids, const void* weight, void* out, int T, int cols,
+                              long long vocab_start, long long rows, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (cols % 8) return -1;
+  const int grid = T < ell::kNumSMs * 16 ? T : ell::kNumSMs * 16;
+  ell::embedding_fwd_kernel<<<grid, 128, 0, stream>>>(ids, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, T, cols,
+                                                       vocab_start, rows);
+  return ell::launch_status();
+}
+
+ELL_API int ell_embedding_bwd(const long long* ids, const void* dout, float* grad32, int T, int cols,
+                              long long vocab_start, long long rows, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (cols % 8) return -1;
+  const int grid = T < ell::kNumSMs * 16 ? T : ell::kNumSMs * 16;
+  ell::embedding_bwd_kernel<<<grid, 128, 0, stream>>>(ids, (const __nv_bfloat16*)dout, grad32, T, cols, vocab_start,
+                                                       rows);
+  return ell::launch_status();
+}

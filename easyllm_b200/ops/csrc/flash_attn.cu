@@ -1,15 +1,19 @@
 // Causal flash attention forward on tcgen05 / TMEM for sm_100a: packed variable-length
 // documents, MHA and GQA, head_dim 128, bf16 in/out, fp32 softmax.
 //
-// One CTA per (128-query tile, query head); 192 threads:
-//   warp 0     TMA: Q tile once, then K and V tiles (128 keys) through 2-stage rings
-//   warp 1     one thread issues S = Q·Kᵀ (128x128x128) into one of two TMEM S buffers and
-//              O += P·V (P from shared memory, V read in place as an MN-major operand)
-//   warps 2-5  softmax: thread r owns query row r (its TMEM lane), so row max / row sum need
-//              no shuffles; exp2 with the scale folded in; P is written as bf16 into swizzled
-//              shared memory; the O accumulator in TMEM is rescaled only when a row maximum grew
-//              by more than 2^8 (stale-max trick: the final 1/l normalisation makes it exact).
-// S(j+1) is issued before softmax(j) finishes, so tensor-core work overlaps the exponentials.
+// One CTA per (pair of adjacent 128-query tiles, query head); 320 threads:
+//   warp 0     TMA: both Q tiles once, then K tiles (128 keys) through a 2-stage ring and V tiles one at a time
+//   warp 1     one thread issues, for every key tile j, S_t = Q_t·K_jᵀ (128x128x128) for both query tiles and
+//              O_t += P_t·V_j (P from shared memory, V read in place as an MN-major operand).
+//              TMEM columns: S_0 0-127, S_1 128-255, O_0 256-383, O_1 384-511.
+//   warps 2-5 / 6-9   one softmax group per query tile: thread r owns query row r (its TMEM lane), so row
+//              max / row sum need no shuffles.  The whole S row is pulled into registers at once (the S columns
+//              are handed back to the tensor core immediately, so S_t(j+1) overlaps the exponentials of step j),
+//              exp2 with the scale folded into one FMA, P written as bf16 into swizzled shared memory; the O
+//              accumulator is rescaled only when a row maximum grew by more than 2^8 (stale-max trick: the final
+//              1/l normalisation makes it exact).
+// Two groups per SM keep two warps on every scheduler, so one group's TMEM-load and MUFU latencies hide behind
+// the other's arithmetic, and each K/V tile fetched serves 256 queries.
 // Documents: row_start[t] is the first token of the document that token t belongs to; key j is
 // visible to query i iff row_start[i] <= j <= i, so tiles may straddle document boundaries.
 //
@@ -21,17 +25,16 @@
 namespace ell {
 using namespace sm100;
 
-constexpr int kFaThreads = 192;
+constexpr int kFaThreads = 320;
 constexpr int kFaM = 128, kFaN = 128, kFaD = 128;
 constexpr int kFaTileBytes = 128 * 128 * 2;  // 32 KiB: Q, K, V and P tiles are all 128x128 bf16
-constexpr int kFaSmemBytes = 6 * kFaTileBytes + 1024 + 256;
+constexpr int kFaSmemBytes = 7 * kFaTileBytes + 1024 + 512;   // Q x2, K x2, V, P x2
 constexpr float kFaRescaleThreshold = 8.0f;   // log2 units
 
 struct FaShared {
-  uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full, pv_done;
+  uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], s_free[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
   int abort_flag;
-  int sm_abort;
 };
 
 enum FaErr { kFaErrProducer = 11, kFaErrMma = 12, kFaErrSoftmax = 13 };
@@ -43,37 +46,42 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                  float scale_log2, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;
-  uint8_t* sK = smem + kFaTileBytes;          // 2 stages
-  uint8_t* sV = smem + 3 * kFaTileBytes;      // 2 stages
-  uint8_t* sP = smem + 5 * kFaTileBytes;
-  FaShared* sh = reinterpret_cast<FaShared*>(smem + 6 * kFaTileBytes);
+  uint8_t* sQ = smem;                          // 2 query tiles
+  uint8_t* sK = smem + 2 * kFaTileBytes;       // 2 stages
+  uint8_t* sV = smem + 4 * kFaTileBytes;       // 1 stage
+  uint8_t* sP = smem + 5 * kFaTileBytes;       // 2 query tiles
+  FaShared* sh = reinterpret_cast<FaShared*>(smem + 7 * kFaTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_qtiles = (T + kFaM - 1) / kFaM;
-  const int qt = n_qtiles - 1 - blockIdx.x;   // heaviest (latest) tiles first
+  const int n_pairs = (T + 2 * kFaM - 1) / (2 * kFaM);
+  const int pair = n_pairs - 1 - blockIdx.x;   // heaviest (latest) pairs first
   const int h = blockIdx.y;
   const int kvh = h / (Hq / Hk);
-  const int q0 = qt * kFaM;
-  const int q_last = min(q0 + kFaM, T) - 1;
+  const int q0 = pair * 2 * kFaM;              // first query row of tile 0; tile 1 starts at q0 + 128
   const int kv_lo = row_start[q0];
-  const int kv_hi = q_last + 1;
-  const int n_kv = (kv_hi - kv_lo + kFaN - 1) / kFaN;
-  const int max_row_start = row_start[q_last];
+  // key tiles each query tile walks: tile t covers keys kv_lo .. last row of the tile
+  int n_kv[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int first = q0 + t * kFaM;
+    const int last = min(first + kFaM, T) - 1;
+    n_kv[t] = first < T ? (last + 1 - kv_lo + kFaN - 1) / kFaN : 0;
+  }
+  const int n_kv_max = max(n_kv[0], n_kv[1]);
 
   if (threadIdx.x == 0) {
     mbar_init(&sh->q_full, 1);
+    mbar_init(&sh->v_full, 1);
+    mbar_init(&sh->v_empty, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sh->k_full[s], 1);
-      mbar_init(&sh->v_full[s], 1);
       mbar_init(&sh->k_empty[s], 1);
-      mbar_init(&sh->v_empty[s], 1);
       mbar_init(&sh->s_full[s], 1);
+      mbar_init(&sh->s_free[s], 128);
+      mbar_init(&sh->p_full[s], 128);
+      mbar_init(&sh->pv_done[s], 1);
     }
-    mbar_init(&sh->p_full, 128);
-    mbar_init(&sh->pv_done, 1);
-    sh->abort_flag = 0;
-    sh->sm_abort = 0;
+    sh->abort_flag = *(volatile int*)err;      // an earlier CTA already failed: do not wait on anything
     fence_barrier_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
@@ -84,27 +92,31 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
-  const uint32_t tmem_o = tmem_base + 256;
+  const bool dead_on_arrival = sh->abort_flag != 0;
   volatile int* abort_flag = &sh->abort_flag;
 
-  if (warp == 0) {
+  if (dead_on_arrival) {
+    // fall through to the common exit: nothing was issued
+  } else if (warp == 0) {
     if (lane == 0) {
       bool ok = true;
-      mbar_expect_tx(&sh->q_full, kFaTileBytes);
-      tma_load_2d(sQ, &tmQ, &sh->q_full, h * kFaD, q0);
-      tma_load_2d(sQ + kFaTileBytes / 2, &tmQ, &sh->q_full, h * kFaD + 64, q0);
-      for (int j = 0; j < n_kv && ok; ++j) {
+      mbar_expect_tx(&sh->q_full, 2 * kFaTileBytes);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {            // rows past T are zero-filled by the TMA unit
+        tma_load_2d(sQ + t * kFaTileBytes, &tmQ, &sh->q_full, h * kFaD, q0 + t * kFaM);
+        tma_load_2d(sQ + t * kFaTileBytes + kFaTileBytes / 2, &tmQ, &sh->q_full, h * kFaD + 64, q0 + t * kFaM);
+      }
+      for (int j = 0; j < n_kv_max && ok; ++j) {
         const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
         const int k0 = kv_lo + j * kFaN;
-        if (!mbar_wait(&sh->k_empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&sh->k_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
         mbar_expect_tx(&sh->k_full[s], kFaTileBytes);
         tma_load_2d(sK + s * kFaTileBytes, &tmK, &sh->k_full[s], kvh * kFaD, k0);
         tma_load_2d(sK + s * kFaTileBytes + kFaTileBytes / 2, &tmK, &sh->k_full[s], kvh * kFaD + 64, k0);
-        if (!mbar_wait(&sh->v_empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
-        mbar_expect_tx(&sh->v_full[s], kFaTileBytes);
-        tma_load_2d(sV + s * kFaTileBytes, &tmV, &sh->v_full[s], kvh * kFaD, k0);
-        tma_load_2d(sV + s * kFaTileBytes + kFaTileBytes / 2, &tmV, &sh->v_full[s], kvh * kFaD + 64, k0);
+        if (!mbar_wait(&sh->v_empty, (j & 1) ^ 1, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(&sh->v_full, kFaTileBytes);
+        tma_load_2d(sV, &tmV, &sh->v_full, kvh * kFaD, k0);
+        tma_load_2d(sV + kFaTileBytes / 2, &tmV, &sh->v_full, kvh * kFaD + 64, k0);
       }
       if (!ok) {
         sh->abort_flag = 1;
@@ -116,40 +128,49 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, false, true);
       bool ok = mbar_wait(&sh->q_full, 0, abort_flag);
-      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      const uint32_t v_addr = smem_u32(sV);
+      // S_t(j) = Q_t K_j^T for both query tiles that still walk key tile j
       auto issue_s = [&](int j) -> bool {
         const int s = j & 1;
         if (!mbar_wait(&sh->k_full[s], (j >> 1) & 1, abort_flag)) return false;
-        tc_fence_after();
         const uint32_t k_addr = smem_u32(sK + s * kFaTileBytes);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * (kFaTileBytes / 2) + (k & 3) * 32;
-          umma_bf16(tmem_base + s * 128, make_smem_desc(q_addr + off, 16, 1024), make_smem_desc(k_addr + off, 16, 1024),
-                    idesc_s, k != 0);
+        for (int t = 0; t < 2; ++t) {
+          if (j >= n_kv[t]) continue;
+          // the softmax group has pulled S_t(j-1) into registers
+          if (j > 0 && !mbar_wait(&sh->s_free[t], (j - 1) & 1, abort_flag)) return false;
+          tc_fence_after();
+          const uint32_t q_addr = smem_u32(sQ + t * kFaTileBytes);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = (k >> 2) * (kFaTileBytes / 2) + (k & 3) * 32;
+            umma_bf16(tmem_base + t * 128, make_smem_desc(q_addr + off, 16, 1024),
+                      make_smem_desc(k_addr + off, 16, 1024), idesc_s, k != 0);
+          }
+          umma_commit(&sh->s_full[t]);
         }
-        umma_commit(&sh->s_full[s]);
         umma_commit(&sh->k_empty[s]);
         return true;
       };
       if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) {
-          if (!issue_s(j + 1)) { ok = false; break; }
-        }
-        const int s = j & 1;
-        if (!mbar_wait(&sh->p_full, j & 1, abort_flag)) { ok = false; break; }
-        if (!mbar_wait(&sh->v_full[s], (j >> 1) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t v_addr = smem_u32(sV + s * kFaTileBytes);
+      for (int j = 0; j < n_kv_max && ok; ++j) {
+        if (j + 1 < n_kv_max && !issue_s(j + 1)) { ok = false; break; }
+        if (!mbar_wait(&sh->v_full, j & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t a_off = (k >> 2) * (kFaTileBytes / 2) + (k & 3) * 32;
-          umma_bf16(tmem_o, make_smem_desc(p_addr + a_off, 16, 1024),
-                    make_smem_desc(v_addr + k * 2048, kFaTileBytes / 2, 1024), idesc_o, (j | k) != 0);
+        for (int t = 0; t < 2; ++t) {
+          if (j >= n_kv[t] || !ok) continue;
+          if (!mbar_wait(&sh->p_full[t], j & 1, abort_flag)) { ok = false; continue; }
+          tc_fence_after();
+          const uint32_t p_addr = smem_u32(sP + t * kFaTileBytes);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t a_off = (k >> 2) * (kFaTileBytes / 2) + (k & 3) * 32;
+            umma_bf16(tmem_base + 256 + t * 128, make_smem_desc(p_addr + a_off, 16, 1024),
+                      make_smem_desc(v_addr + k * 2048, kFaTileBytes / 2, 1024), idesc_o, (j | k) != 0);
+          }
+          umma_commit(&sh->pv_done[t]);
         }
-        umma_commit(&sh->pv_done);
-        umma_commit(&sh->v_empty[s]);
+        umma_commit(&sh->v_empty);
       }
       if (!ok) {
         sh->abort_flag = 1;
@@ -157,132 +178,135 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else {
-    // ---------------- softmax / correction / epilogue: thread <-> query row ----------------
-    const int q = warp & 3;
-    const int r = q * 32 + lane;
-    const int row = q0 + r;
+    // ---------------- softmax / correction / epilogue: one group per query tile ----------------
+    const int t = (warp - 2) >> 2;               // query tile of this group
+    const int quad = warp & 3;                   // TMEM lane quadrant this warp may access
+    const int r = quad * 32 + lane;
+    const int row = q0 + t * kFaM + r;
     const bool row_valid = row < T;
     const int my_start = row_valid ? row_start[row] : 0x7fffffff;
-    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    const int tile_first = q0 + t * kFaM;
+    const int max_row_start = n_kv[t] > 0 ? row_start[min(tile_first + kFaM, T) - 1] : 0;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_off + t * 128;
+    const uint32_t t_o = tmem_base + lane_off + 256 + t * 128;
+    uint8_t* p_row = sP + t * kFaTileBytes + r * 128;
+    const int sw = r & 7;
     float m_used = -1e30f, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      const int sb = j & 1;
-      if (!mbar_wait(&sh->s_full[sb], (j >> 1) & 1, abort_flag)) sh->sm_abort = 1;
-      named_bar_sync(1, 128);
-      if (*(volatile int*)&sh->sm_abort) { ok = false; break; }
-      tc_fence_after();
-      const int k0 = kv_lo + j * kFaN;
-      const bool need_mask = (k0 + kFaN - 1 > q0) || (k0 < max_row_start);
-      const uint32_t t_s = tmem_base + lane_off + sb * 128;
-      // pass 1: row maximum (log2 domain)
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float t = __uint_as_float(v[i]) * scale_log2;
-          if (need_mask) {
-            const int kidx = k0 + c * 32 + i;
-            if (kidx > row || kidx < my_start) t = -INFINITY;
-          }
-          mx = fmaxf(mx, t);
-        }
-      }
-      const float m_new = fmaxf(m_used, mx);
-      const bool grow = (m_new - m_used) > kFaRescaleThreshold;
-      const bool any_grow = __any_sync(0xffffffffu, grow);
-      // P(j) overwrites the tile PV(j-1) reads, and a rescale touches O: wait for PV(j-1)
-      if (j > 0) {
-        if (!mbar_wait(&sh->pv_done, (j - 1) & 1, abort_flag)) sh->sm_abort = 1;
-      }
-      if (any_grow) {
-        const float alpha = grow ? exp2f(m_used - m_new) : 1.f;
-        if (grow) {
-          m_used = m_new;
-          l *= alpha;
-        }
-        if (j > 0) {
-          tc_fence_after();
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32(tmem_o + lane_off + c * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32(tmem_o + lane_off + c * 32, v);
-          }
-          tmem_st_wait();
-        }
-      }
-      // pass 2: P = exp2(t - m_used) -> bf16 -> swizzled smem; row sum
-      float psum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + c * 32, v);
-        tmem_ld_wait();
-        uint8_t* atom = sP + (c >> 1) * (kFaTileBytes / 2) + r * 128;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float p[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float t = __uint_as_float(v[g * 8 + i]) * scale_log2;
-            if (need_mask) {
-              const int kidx = k0 + c * 32 + g * 8 + i;
-              if (kidx > row || kidx < my_start) t = -INFINITY;
-            }
-            p[i] = exp2f(t - m_used);
-            psum += p[i];
-          }
-          bf16x8 pk = pack8(p);
-          const int chunk = (c & 1) * 4 + g;
-          *reinterpret_cast<bf16x8*>(atom + ((chunk ^ (r & 7)) << 4)) = pk;
-        }
-      }
-      l += psum;
-      tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive(&sh->p_full);
-    }
-    // ---------------- epilogue: O / l -> bf16 -> global; LSE ----------------
-    if (ok) {
-      if (!mbar_wait(&sh->pv_done, (n_kv - 1) & 1, abort_flag)) sh->sm_abort = 1;
-    }
-    named_bar_sync(1, 128);
-    if (!*(volatile int*)&sh->sm_abort) {
-      tc_fence_after();
-      const float inv_l = row_valid ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = out + ((size_t)row * Hq + h) * kFaD;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_o + lane_off + c * 32, v);
-        tmem_ld_wait();
-        if (row_valid) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float f[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[g * 8 + i]) * inv_l;
-            *reinterpret_cast<bf16x8*>(orow + c * 32 + g * 8) = pack8(f);
-          }
-        }
-      }
-      if (row_valid) lse[(size_t)h * T + row] = m_used * 0.6931471805599453f + logf(l);
-    } else if (threadIdx.x == 64) {
+    auto fail = [&]() {
+      ok = false;
       sh->abort_flag = 1;
       atomicCAS(err, 0, kFaErrSoftmax);
+    };
+    const int my_n = n_kv[t];
+    for (int j = 0; j < my_n; ++j) {
+      if (!mbar_wait(&sh->s_full[t], j & 1, abort_flag)) fail();
+      tc_fence_after();
+      uint32_t s[128];
+      tmem_ld_32x32(t_s, s);
+      tmem_ld_32x32(t_s + 32, s + 32);
+      tmem_ld_32x32(t_s + 64, s + 64);
+      tmem_ld_32x32(t_s + 96, s + 96);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&sh->s_free[t]);               // S_t(j+1) may overwrite the columns now
+      const int k0 = kv_lo + j * kFaN;
+      const bool need_mask = (k0 + kFaN - 1 > tile_first) || (k0 < max_row_start);
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          const int kidx = k0 + i;
+          if (kidx > row || kidx < my_start) s[i] = 0xff800000u;   // -inf
+        }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(s[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+      const float m_new = fmaxf(m_used, mx);
+      const bool grow = (m_new - m_used) > kFaRescaleThreshold;
+      float alpha = 1.f;
+      if (grow) {
+        alpha = exp2f(m_used - m_new);
+        m_used = m_new;
+        l *= alpha;
+      }
+      // P = exp2(s*scale - m_used) -> bf16 (kept in registers until the P tile is free)
+      uint32_t pk[64];
+      float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
+      const float neg_m = -m_used;
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+        const float p0 = exp2f(fmaf(__uint_as_float(s[i]), scale_log2, neg_m));
+        const float p1 = exp2f(fmaf(__uint_as_float(s[i + 1]), scale_log2, neg_m));
+        const float p2 = exp2f(fmaf(__uint_as_float(s[i + 2]), scale_log2, neg_m));
+        const float p3 = exp2f(fmaf(__uint_as_float(s[i + 3]), scale_log2, neg_m));
+        ps0 += p0; ps1 += p1; ps2 += p2; ps3 += p3;
+        __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1), b = __floats2bfloat162_rn(p2, p3);
+        pk[i / 2] = *reinterpret_cast<uint32_t*>(&a);
+        pk[i / 2 + 1] = *reinterpret_cast<uint32_t*>(&b);
+      }
+      l += (ps0 + ps1) + (ps2 + ps3);
+      // P(j) overwrites the tile PV(j-1) reads, and a rescale touches O: wait for PV(j-1)
+      if (j > 0 && !mbar_wait(&sh->pv_done[t], (j - 1) & 1, abort_flag)) fail();
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_o + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st_32x32(t_o + c * 32, v);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+#pragma unroll
+      for (int c = 0; c < 16; ++c)
+        *reinterpret_cast<uint4*>(p_row + (c >> 3) * (kFaTileBytes / 2) + (((c & 7) ^ sw) << 4)) =
+            make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
+      fence_proxy_async_smem();
+      mbar_arrive(&sh->p_full[t]);
+    }
+    // ---------------- epilogue: O / l -> bf16 -> global; LSE ----------------
+    if (my_n > 0) {
+      if (!mbar_wait(&sh->pv_done[t], (my_n - 1) & 1, abort_flag)) fail();
+      tc_fence_after();
+      if (ok && !*abort_flag) {
+        const float inv_l = row_valid ? 1.f / l : 0.f;
+        __nv_bfloat16* orow = out + ((size_t)row * Hq + h) * kFaD;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_o + c * 32, v);
+          tmem_ld_wait();
+          if (row_valid) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[g * 8 + i]) * inv_l;
+              *reinterpret_cast<bf16x8*>(orow + c * 32 + g * 8) = pack8(f);
+            }
+          }
+        }
+        if (row_valid) lse[(size_t)h * T + row] = m_used * 0.6931471805599453f + logf(l);
+      }
     }
   }
 
+  tc_fence_before();
   __syncthreads();
   if (*abort_flag && threadIdx.x == 0) {
+    // error path: give copies / MMAs still in flight time to land before smem and TMEM go away
     const unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) {
     }
@@ -322,7 +346,7 @@ ELL_API int ell_flash_attn_fwd(const void* q, const void* k, const void* v, void
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((T + kFaM - 1) / kFaM, Hq);
+  dim3 grid((T + 2 * kFaM - 1) / (2 * kFaM), Hq);
   flash_fwd_kernel<<<grid, kFaThreads, kFaSmemBytes, stream>>>(tq, tk, tv, (__nv_bfloat16*)out, lse, row_start, T, Hq,
                                                                Hk, scale * 1.4426950408889634f, err);
   return launch_status();

@@ -34,7 +34,7 @@ constexpr int kFbHalf = kFbTileBytes / 2;     // 16 KiB: one 64-column half of a
 constexpr int kFbSmemBytes = 6 * kFbTileBytes + 1024 + 256;
 
 struct FbShared {
-  uint64_t kv_full, qdo_full, qdo_empty, s_full, dp_full, p_full, ds_full, dq_full, dq_drained;
+  uint64_t kv_full, q_full, do_full, q_empty, do_empty, s_full, dp_full, p_full, ds_full, dq_full, dq_drained;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -60,8 +60,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                  const __grid_constant__ CUtensorMap tmDQ, const float* __restrict__ lse,
                  const float* __restrict__ delta, const int* __restrict__ row_start,
-                 __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, int dkv_stride, int T, int Hq,
-                 int Hk, float scale, int* __restrict__ err) {
+                 __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, int dkv_stride,
+                 float* __restrict__ dkv_acc, int nsplit, int T, int Hq, int Hk, float scale,
+                 int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
@@ -74,9 +75,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (T + kFbTile - 1) / kFbTile;
-  const int j = blockIdx.x;                    // key tile; j = 0 has the longest walk and is scheduled first
-  const int kvh = blockIdx.y;
-  const int G = Hq / Hk;
+  // blockIdx.y = key tile (j = 0 has the longest walk; with x varying fastest the heaviest CTAs of every head
+  // are scheduled first), blockIdx.x = kv head x split of its query-head group.
+  const int j = blockIdx.y;
+  const int kvh = blockIdx.x / nsplit;
+  const int G = Hq / Hk / nsplit;              // query heads walked by this CTA
+  const int h_first = kvh * (Hq / Hk) + (blockIdx.x % nsplit) * G;
   const int k0 = j * kFbTile;
   const int k_last = min(k0 + kFbTile, T) - 1;
   const int i_end = fb_last_qtile(row_start, j, n_qt, k_last, lane);
@@ -84,8 +88,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(&sh->kv_full, 1);
-    mbar_init(&sh->qdo_full, 1);
-    mbar_init(&sh->qdo_empty, 1);
+    mbar_init(&sh->q_full, 1);
+    mbar_init(&sh->do_full, 1);
+    mbar_init(&sh->q_empty, 1);
+    mbar_init(&sh->do_empty, 1);
     mbar_init(&sh->s_full, 1);
     mbar_init(&sh->dp_full, 1);
     mbar_init(&sh->p_full, 256);
@@ -122,14 +128,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tma_load_2d(sV + kFbHalf, &tmV, &sh->kv_full, kvh * kFbD + 64, k0);
       int it = 0;
       for (int g = 0; g < G && ok; ++g) {
-        const int h = kvh * G + g;
+        const int h = h_first + g;
         for (int i = j; i < i_end; ++i, ++it) {
-          if (it > 0 && !mbar_wait(&sh->qdo_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(&sh->qdo_full, 2 * kFbTileBytes);
-          tma_load_2d(sQ, &tmQ, &sh->qdo_full, h * kFbD, i * kFbTile);
-          tma_load_2d(sQ + kFbHalf, &tmQ, &sh->qdo_full, h * kFbD + 64, i * kFbTile);
-          tma_load_2d(sdO, &tmdO, &sh->qdo_full, h * kFbD, i * kFbTile);
-          tma_load_2d(sdO + kFbHalf, &tmdO, &sh->qdo_full, h * kFbD + 64, i * kFbTile);
+          // dO is released by the dV MMA (mid-step), Q by the dK MMA (end of step): the next tiles
+          // stream in while the current step computes dS and drains dQ
+          if (it > 0 && !mbar_wait(&sh->do_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&sh->do_full, kFbTileBytes);
+          tma_load_2d(sdO, &tmdO, &sh->do_full, h * kFbD, i * kFbTile);
+          tma_load_2d(sdO + kFbHalf, &tmdO, &sh->do_full, h * kFbD + 64, i * kFbTile);
+          if (it > 0 && !mbar_wait(&sh->q_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&sh->q_full, kFbTileBytes);
+          tma_load_2d(sQ, &tmQ, &sh->q_full, h * kFbD, i * kFbTile);
+          tma_load_2d(sQ + kFbHalf, &tmQ, &sh->q_full, h * kFbD + 64, i * kFbTile);
         }
       }
       if (!ok) {
@@ -148,7 +158,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       bool ok = mbar_wait(&sh->kv_full, 0, abort_flag);
       for (int it = 0; it < n_it && ok; ++it) {
         const uint32_t ph = it & 1;
-        if (!mbar_wait(&sh->qdo_full, ph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&sh->do_full, ph, abort_flag)) { ok = false; break; }
         tc_fence_after();
         // dP = dO V^T (the dP columns were released when dS of the previous step was published)
 #pragma unroll
@@ -159,6 +169,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         umma_commit(&sh->dp_full);
         // S = Q K^T into the columns the previous dQ tile is drained from
+        if (!mbar_wait(&sh->q_full, ph, abort_flag)) { ok = false; break; }
         if (it > 0 && !mbar_wait(&sh->dq_drained, (it - 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
@@ -175,6 +186,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int k = 0; k < 8; ++k)
           umma_bf16(t_dv, make_smem_desc(p_addr + k * 2048, kFbHalf, 1024),
                     make_smem_desc(do_addr + k * 2048, kFbHalf, 1024), idesc_mm, (it | k) != 0);
+        umma_commit(&sh->do_empty);
         // dK += dS^T Q ; dQ = dS K
         if (!mbar_wait(&sh->ds_full, ph, abort_flag)) { ok = false; break; }
         tc_fence_after();
@@ -188,8 +200,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_bf16(t_s, make_smem_desc(ds_addr + off, 16, 1024), make_smem_desc(k_addr + k * 2048, kFbHalf, 1024),
                     idesc_km, k != 0);
         }
-        umma_commit(&sh->dq_full);     // also: dV, dK of this step done; P, dS, Q, dO free
-        umma_commit(&sh->qdo_empty);
+        umma_commit(&sh->dq_full);     // also: dV, dK of this step done; P, dS, Q free
+        umma_commit(&sh->q_empty);
       }
       if (!ok) {
         sh->abort_flag = 1;
@@ -215,7 +227,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     };
     int it = 0;
     for (int g = 0; g < G; ++g) {
-      const int h = kvh * G + g;
+      const int h = h_first + g;
       for (int i = j; i < i_end; ++i, ++it) {
         const uint32_t ph = it & 1;
         const int q0 = i * kFbTile;
@@ -228,6 +240,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t pk[32];                         // P of this thread's 64 columns, packed bf16x2
         if (!mbar_wait(&sh->s_full, ph, abort_flag)) fail();
         tc_fence_after();
+        if (it > 0) {
+          // the previous dQ tile was staged in this group's halves of P / dS: the reduce-add must have
+          // read them before they are overwritten
+          if (r == 0) tma_store_wait_read<0>();
+          named_bar_sync(1 + wg, 128);
+        }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
@@ -297,15 +315,31 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tma_reduce_add_2d(&tmDQ, sP + wg * kFbHalf, h * kFbD + col_base, q0);
             tma_reduce_add_2d(&tmDQ, sdS + wg * kFbHalf, h * kFbD + col_base + 32, q0);
             tma_store_commit();
-            tma_store_wait_read<0>();
           }
         }
-        named_bar_sync(1 + wg, 128);
       }
     }
     // ---------------- epilogue: dV (group 0) / dK (group 1) -> bf16 -> global ----------------
     // dq_full of the last step covers every MMA into dV and dK.
-    if (n_it > 0 && ok && !*abort_flag) {
+    if (n_it > 0 && ok && !*abort_flag && nsplit > 1) {
+      // the query-head group is split over CTAs: add into the fp32 accumulators [2][T, Hk*128] (dk, dv)
+      const int key = k0 + r;
+      const uint32_t t_acc = (wg == 0 ? t_dv : t_dk) + lane_off;
+      float* dst = dkv_acc + (wg == 0 ? (size_t)T * Hk * kFbD : 0) + ((size_t)key * Hk + kvh) * kFbD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_acc + c * 32, v);
+        tmem_ld_wait();
+        if (key < T) {
+#pragma unroll
+          for (int g4 = 0; g4 < 8; ++g4)
+            atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + g4 * 4),
+                      make_float4(__uint_as_float(v[g4 * 4]), __uint_as_float(v[g4 * 4 + 1]),
+                                  __uint_as_float(v[g4 * 4 + 2]), __uint_as_float(v[g4 * 4 + 3])));
+        }
+      }
+    } else if (n_it > 0 && ok && !*abort_flag) {
       const int key = k0 + r;
       const uint32_t t_acc = (wg == 0 ? t_dv : t_dk) + lane_off;
       __nv_bfloat16* dst = (wg == 0 ? dv : dk) + (size_t)key * dkv_stride + (size_t)kvh * kFbD;
@@ -378,10 +412,11 @@ using namespace ell;
 // q [T, Hq, 128], k / v [T, Hk, 128] (row strides q_stride / kv_stride elements, views into a packed QKV
 // buffer are fine); out, dout [T, Hq, 128] contiguous; lse [Hq, T] from the forward.
 // Outputs: dq [T, Hq, 128] (row stride dq_stride), dk / dv [T, Hk, 128] (row stride dkv_stride) - views into
-// one packed dQKV buffer are fine.  Scratch: dq_acc fp32 [T, Hq*128] (zeroed here), delta fp32 [Hq, T].
+// one packed dQKV buffer are fine.  Scratch: dq_acc fp32 [T, Hq*128] (zeroed here), delta fp32 [Hq, T],
+// dkv_acc fp32 [2, T, Hk*128] (GQA only, may be null: used when the head group is split over CTAs).
 ELL_API int ell_flash_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
                                const float* lse, const int* row_start, void* dq, void* dk, void* dv, float* dq_acc,
-                               float* delta, int T, int Hq, int Hk, int q_stride, int kv_stride, int dq_stride,
+                               float* delta, float* dkv_acc, int T, int Hq, int Hk, int q_stride, int kv_stride, int dq_stride,
                                int dkv_stride, float scale, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (Hq % Hk) return -2;
@@ -404,8 +439,15 @@ ELL_API int ell_flash_attn_bwd(const void* q, const void* k, const void* v, cons
     configured = true;
   }
   const int W = Hq * kFbD;
+  const int n_kt = (T + kFbTile - 1) / kFbTile;
+  // few kv heads and a short sequence leave SMs idle: split each query-head group over CTAs
+  const int nsplit = (Hq > Hk && dkv_acc != nullptr && Hk * n_kt < 2 * kNumSMs) ? Hq / Hk : 1;
   cudaError_t e = cudaMemsetAsync(dq_acc, 0, (size_t)T * W * sizeof(float), stream);
   if (e != cudaSuccess) return (int)e;
+  if (nsplit > 1) {
+    e = cudaMemsetAsync(dkv_acc, 0, (size_t)2 * T * Hk * kFbD * sizeof(float), stream);
+    if (e != cudaSuccess) return (int)e;
+  }
   {
     const long long warps = (long long)T * Hq;
     const int threads = 256;
@@ -413,10 +455,18 @@ ELL_API int ell_flash_attn_bwd(const void* q, const void* k, const void* v, cons
     flash_bwd_delta_kernel<<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, delta,
                                                            T, Hq);
   }
-  dim3 grid((T + kFbTile - 1) / kFbTile, Hk);
+  dim3 grid(Hk * nsplit, n_kt);
   flash_bwd_kernel<<<grid, kFbThreads, kFbSmemBytes, stream>>>(tq, tk, tv, tdo, tdq, lse, delta, row_start,
-                                                               (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dkv_stride, T,
-                                                               Hq, Hk, scale, err);
+                                                               (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dkv_stride,
+                                                               dkv_acc, nsplit, T, Hq, Hk, scale, err);
+  if (nsplit > 1) {
+    const int Wk = Hk * kFbD;
+    const size_t n = (size_t)T * (Wk / 8);
+    flash_bwd_dq_convert_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(dkv_acc, (__nv_bfloat16*)dk, T, Wk,
+                                                                                 dkv_stride);
+    flash_bwd_dq_convert_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(dkv_acc + (size_t)T * Wk,
+                                                                                 (__nv_bfloat16*)dv, T, Wk, dkv_stride);
+  }
   {
     const size_t n = (size_t)T * (W / 8);
     flash_bwd_dq_convert_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, T, W,

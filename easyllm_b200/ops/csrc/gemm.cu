@@ -126,6 +126,32 @@ __device__ __forceinline__ void map_tile(int idx, int tiles_m, int tiles_n, cons
   }
 }
 
+// Work units of a plain (unfused) launch.  When the last wave would leave more than half of the CTAs idle,
+// each of its tiles is cut into two half-width tiles (BN/2 columns), so the tail costs half a wave:
+// units [0, num_full) are whole tiles, unit num_full + 2i + h is half h of tile num_full + i.
+struct TileUnit {
+  int mt, nt, n0, bn;
+};
+
+__host__ __device__ inline int split_tail_tiles(int num_tiles, int ctas, bool allowed) {
+  const int tail = num_tiles % ctas;
+  return (allowed && tail > 0 && 2 * tail <= ctas) ? tail : 0;
+}
+
+template <int BN, int FUSE>
+__device__ __forceinline__ TileUnit decode_unit(int unit, int tiles_m, int tiles_n, int num_full, const FuseArgs& f) {
+  TileUnit u;
+  int tile = unit, half = -1;
+  if (FUSE == kFuseNone && unit >= num_full) {
+    tile = num_full + ((unit - num_full) >> 1);
+    half = (unit - num_full) & 1;
+  }
+  map_tile<FUSE>(tile, tiles_m, tiles_n, f, u.mt, u.nt);
+  u.bn = half >= 0 ? BN / 2 : BN;
+  u.n0 = u.nt * BN + (half > 0 ? BN / 2 : 0);
+  return u;
+}
+
 template <int BN>
 struct GemmCfg {
   static constexpr int kBBytes = BN * kBK * 2;
@@ -353,6 +379,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int n_comm = FUSE == kFuseNone ? 0 : fuse.n_comm;
   const int cta0 = (int)blockIdx.x - n_comm;            // index among the GEMM CTAs
   const int cta_stride = (int)gridDim.x - n_comm;
+  const int n_split = split_tail_tiles(num_tiles, cta_stride, FUSE == kFuseNone && BN == 256 && OUT != kOutBf16CE);
+  const int num_full = num_tiles - n_split;
+  const int num_units = num_tiles + n_split;
 
   if (FUSE != kFuseNone && (int)blockIdx.x < n_comm) {
     if (FUSE == kFuseAG) ag_comm_role(fuse, K, err, smem);
@@ -389,10 +418,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = cta0; tile < num_tiles && ok; tile += cta_stride) {
-        int mt, nt;
-        map_tile<FUSE>(tile, tiles_m, tiles_n, fuse, mt, nt);
-        const int m0 = mt * kBM, n0 = nt * BN;
+      for (int tile = cta0; tile < num_units && ok; tile += cta_stride) {
+        const TileUnit u = decode_unit<BN, FUSE>(tile, tiles_m, tiles_n, num_full, fuse);
+        const int mt = u.mt, m0 = mt * kBM, n0 = u.n0;
+        // half-width units load B through the second map (box of BN/2 rows; plain launches only)
+        const CUtensorMap* b_map = (FUSE == kFuseNone && u.bn != BN) ? &tmA2 : &tmB;
+        const uint32_t stage_bytes = kABytes + (uint32_t)u.bn * kBK * 2;
         const CUtensorMap* a_map = &tmA;
         int a_row = m0;
         if (FUSE == kFuseAG) {
@@ -418,7 +449,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             ok = false;
             break;
           }
-          mbar_expect_tx(&sh->full[stage], Cfg::kStageBytes);
+          mbar_expect_tx(&sh->full[stage], stage_bytes);
           uint8_t* a_dst = sA + stage * kABytes;
           uint8_t* b_dst = sB + stage * Cfg::kBBytes;
           if (!A_MN) {
@@ -429,11 +460,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tma_load_2d(a_dst + i * (64 * kBK * 2), &tmA, &sh->full[stage], m0 + i * 64, kb * kBK);
           }
           if (!B_MN) {
-            tma_load_2d(b_dst, &tmB, &sh->full[stage], kb * kBK, n0);
+            tma_load_2d(b_dst, b_map, &sh->full[stage], kb * kBK, n0);
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i)
-              tma_load_2d(b_dst + i * (64 * kBK * 2), &tmB, &sh->full[stage], n0 + i * 64, kb * kBK);
+              if (i * 64 < u.bn) tma_load_2d(b_dst + i * (64 * kBK * 2), &tmB, &sh->full[stage], n0 + i * 64, kb * kBK);
           }
           if (++stage == Cfg::kStages) {
             stage = 0;
@@ -449,7 +480,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc_full = make_idesc_bf16(kBM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc_half = make_idesc_bf16(kBM, BN / 2, A_MN, B_MN);
       // K-major: 8-row groups 1024 B apart; one K=16 step is 32 B inside the swizzle row.
       // MN-major: 64-element MN groups one [64 x kBK] box (8 KiB) apart, 8-K groups 1024 B apart;
       // one K=16 step is two such groups (2 KiB).
@@ -459,7 +491,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int tile = cta0; tile < num_tiles && ok; tile += cta_stride, ++it) {
+      for (int tile = cta0; tile < num_units && ok; tile += cta_stride, ++it) {
+        const uint32_t idesc = (FUSE == kFuseNone && tile >= num_full) ? idesc_half : idesc_full;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&sh->tmem_empty[acc], acc_phase ^ 1, abort_flag)) {
@@ -511,10 +544,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           atomicCAS(err, 0, kErrFlagWait);
         }
     }
-    for (int tile = cta0; tile < num_tiles; tile += cta_stride, ++it) {
-      int mt, nt;
-      map_tile<FUSE>(tile, tiles_m, tiles_n, fuse, mt, nt);
-      const int m0 = mt * kBM, n0 = nt * BN;
+    for (int tile = cta0; tile < num_units; tile += cta_stride, ++it) {
+      const TileUnit u = decode_unit<BN, FUSE>(tile, tiles_m, tiles_n, num_full, fuse);
+      const int mt = u.mt, nt = u.nt, m0 = mt * kBM, n0 = u.n0;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&sh->tmem_full[acc], acc_phase, abort_flag)) sh->epi_abort = 1;
@@ -533,7 +565,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (OUT == kOutBf16 || OUT == kOutBf16CE) {
 #pragma unroll 1
-        for (int j = 0; j < BN / 64; ++j) {
+        for (int j = 0; j < u.bn / 64; ++j) {
           uint8_t* buf = sC + (store_count & 1) * kEpiBufBytes;
           if (leader) tma_store_wait_read<1>();
           named_bar_sync(1, kEpiThreads);
@@ -622,7 +654,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // fp32 output: 128 x 32 sub-tiles staged in swizzled smem, then a TMA store (overwrite) or
         // a TMA reduce-add (gradient accumulation: the add happens at L2, the SM never reads C)
 #pragma unroll 1
-        for (int j = 0; j < BN / 32; ++j) {
+        for (int j = 0; j < u.bn / 32; ++j) {
           uint8_t* buf = sC + (store_count & 1) * kEpiBufBytes;
           if (leader) tma_store_wait_read<1>();
           named_bar_sync(1, kEpiThreads);
@@ -799,9 +831,15 @@ ELL_API int ell_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   const int ctas = sm_count();
   FuseArgs Cf{};
   const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(bias);
+  // second B map with a box of BN/2 rows: used by the half-width tiles of a split tail wave
+  CUtensorMap tBh = tB;
+  if (!b_mn && BN == 256) {
+    rc = make_tmap_bf16_2d(&tBh, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kBK, BN / 2);
+    if (rc) return rc;
+  }
 #define ELL_GEMM_CASE(BN_, AM_, BM_, OUT_, BIAS_)                                                             \
   if (BN == BN_ && (bool)a_mn == AM_ && (bool)b_mn == BM_ && out_mode == OUT_ && (bias != nullptr) == BIAS_) \
-    return launch_gemm<BN_, AM_, BM_, OUT_, BIAS_>(tA, tB, tC, Cf, bp, M, N, K, ldc, err, ctas, stream);
+    return launch_gemm<BN_, AM_, BM_, OUT_, BIAS_>(tA, tB, tC, Cf, bp, M, N, K, ldc, err, ctas, stream, &tBh);
 #define ELL_GEMM_BN(BN_)                           \
   ELL_GEMM_CASE(BN_, false, false, kOutBf16, false) \
   ELL_GEMM_CASE(BN_, false, false, kOutBf16, true)  \

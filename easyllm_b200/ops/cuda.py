@@ -187,6 +187,32 @@ def sumsq(x, out):
     _check(lib().ell_sumsq(_p(x), c_longlong(x.numel()), _p(out), _stream()), "sumsq")
 
 
+# ---- embedding ----------------------------------------------------------------------------
+def embedding_fwd(ids, weight, vocab_start):
+    """Rows of ``weight [rows, h]`` for the ids in ``[vocab_start, vocab_start+rows)``, zeros for the others."""
+    _bf16c(weight, "weight")
+    flat = ids.reshape(-1).contiguous()
+    if flat.dtype != torch.int64:
+        flat = flat.to(torch.int64)
+    out = torch.empty(flat.numel(), weight.shape[1], dtype=torch.bfloat16, device=weight.device)
+    rc = lib().ell_embedding_fwd(_p(flat), _p(weight), _p(out), c_int(flat.numel()), c_int(weight.shape[1]),
+                                 c_longlong(vocab_start), c_longlong(weight.shape[0]), _stream())
+    _check(rc, "embedding_fwd")
+    return out.view(*ids.shape, weight.shape[1])
+
+
+def embedding_bwd_(ids, dout, grad32, vocab_start):
+    """``grad32[id - vocab_start] += dout[t]`` (fp32, in place) for the ids this rank owns."""
+    flat = ids.reshape(-1).contiguous()
+    if flat.dtype != torch.int64:
+        flat = flat.to(torch.int64)
+    d = dout.reshape(flat.numel(), -1)
+    _bf16c(d, "dout")
+    rc = lib().ell_embedding_bwd(_p(flat), _p(d), _p(grad32), c_int(flat.numel()), c_int(d.shape[1]),
+                                 c_longlong(vocab_start), c_longlong(grad32.shape[0]), _stream())
+    _check(rc, "embedding_bwd")
+
+
 # ---- cross entropy ----------------------------------------------------------------------------
 def ce_fwd(logits, target, vocab_start, valid_cols):
     _bf16c(logits, "logits")
@@ -309,8 +335,9 @@ def flash_attn_bwd(do, q, k, v, out, lse, row_start, scale, dq=None, dk=None, dv
         raise ValueError("flash_attn_bwd: dk and dv must share a row stride")
     acc = scratch(T * Hq * D, tag="fa_bwd_dq")
     delta = scratch(T * Hq, tag="fa_bwd_delta")
+    kv_acc = scratch(2 * T * Hk * D, tag="fa_bwd_dkv") if Hq > Hk else None
     rc = lib().ell_flash_attn_bwd(_p(q), _p(k), _p(v), _p(out), _p(do), _p(lse), _p(row_start), _p(dq), _p(dk), _p(dv),
-                                  _p(acc), _p(delta), c_int(T), c_int(Hq), c_int(Hk), c_int(q.stride(0)),
+                                  _p(acc), _p(delta), _p(kv_acc), c_int(T), c_int(Hq), c_int(Hk), c_int(q.stride(0)),
                                   c_int(k.stride(0)), c_int(dq.stride(0)), c_int(dk.stride(0)), c_float(scale),
                                   _p(err_flag(q.device)), _stream())
     _check(rc, "flash_attn_bwd")

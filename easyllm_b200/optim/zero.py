@@ -30,6 +30,7 @@ import torch.distributed as dist
 
 from .. import ops
 from ..parallel.grid import get_grid
+from ..utils.log import default_logger as logger
 
 _ALIGN = 8  # elements; keeps every shard boundary 16-byte aligned in bf16
 
@@ -118,8 +119,13 @@ class ZeroOptimizer:
         self.shard_lo = self.dp_rank * self.shard_size if self.stage >= 1 else 0
         self.shard_hi = self.shard_lo + self.shard_size
 
-        self.param_buf = torch.zeros(self.total, dtype=self.dtype, device=self.device)
-        self.grad_buf = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+        self.fused = False
+        self.param_buf = self.grad_buf = None
+        if self._want_fused():
+            self._alloc_symmetric()
+        if self.param_buf is None:
+            self.param_buf = torch.zeros(self.total, dtype=self.dtype, device=self.device)
+            self.grad_buf = torch.zeros(self.total, dtype=torch.float32, device=self.device)
         for p, o in zip(self.params, self.offsets):
             view = self.param_buf[o:o + p.numel()].view_as(p)
             view.copy_(p.data)
@@ -129,6 +135,49 @@ class ZeroOptimizer:
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
         self._clip_coef = torch.ones(1, dtype=torch.float32, device=self.device)
+
+    # ---- fused data-parallel path: buffers in symmetric memory, collectives issued by the kernels -------
+    def _want_fused(self):
+        import os
+        return (self.dp > 1 and self.stage >= 1 and self.device.type == "cuda" and self.dtype == torch.bfloat16
+                and ops.get_backend() == "b200" and os.environ.get("EASYLLM_ZERO_FUSED", "1") != "0"
+                and dist.get_backend(self.dp_group) == "nccl" and self.dp <= 16)
+
+    def _alloc_symmetric(self):
+        """Flat gradient / parameter buffers every DP rank can address (NVLink peer pointers)."""
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            name = self.dp_group.group_name
+            try:
+                symm_mem.enable_symm_mem_for_group(name)
+            except Exception:
+                pass
+            gbuf = symm_mem.empty(self.total, dtype=torch.float32, device=self.device)
+            pbuf = symm_mem.empty(self.total, dtype=self.dtype, device=self.device)
+            gbuf.zero_(); pbuf.zero_()
+            gh = symm_mem.rendezvous(gbuf, group=name)
+            ph = symm_mem.rendezvous(pbuf, group=name)
+            torch.cuda.synchronize()
+            dist.barrier(group=self.dp_group)
+            self._grad_ptrs = [int(x) for x in gh.buffer_ptrs]
+            self._param_ptrs = [int(x) for x in ph.buffer_ptrs]
+            self._symm_handles = (gh, ph)
+            self.grad_buf, self.param_buf = gbuf, pbuf
+            self._sumsq2 = torch.zeros(2, dtype=torch.float32, device=self.device)
+            self._dp_token = torch.zeros(1, dtype=torch.float32, device=self.device)
+            self._have_sumsq2 = False
+            self.fused = True
+            logger.info(f"ZeRO-{self.stage}: fused reduce-scatter / Adam+all-gather kernels over {self.dp} ranks "
+                        f"({self.total * 6 / 2**30:.1f} GiB symmetric memory)")
+        except Exception as e:   # no symmetric memory on this system: NCCL collectives instead
+            logger.warning(f"ZeRO fused path unavailable ({type(e).__name__}: {e}); using NCCL collectives")
+            self.fused = False
+            self.param_buf = self.grad_buf = None
+
+    def _dp_fence(self):
+        """Stream-ordered rendezvous of the DP group: every rank's earlier kernels finished before any rank's
+        later kernels start (a one-element all-reduce; no host synchronisation)."""
+        dist.all_reduce(self._dp_token, group=self.dp_group)
 
     # ---- gradient plumbing --------------------------------------------------------------
     @property
@@ -165,6 +214,19 @@ class ZeroOptimizer:
         g = self.grid
         if g.tp > 1 and self.start_sp < self.used:
             dist.all_reduce(self.grad_buf[self.start_sp:self.used], group=g.tp_group)
+        if self.fused:
+            from ctypes import c_int, c_longlong, c_void_p
+            from ..ops import cuda as cu
+            self._dp_fence()                      # every rank's backward (and TP reduce) is complete
+            self._sumsq2.zero_()
+            arr = (c_void_p * self.dp)(*self._grad_ptrs)
+            rc = cu.lib().ell_zero_reduce_scatter(arr, c_int(self.dp), c_int(self.dp_rank), c_longlong(self.shard_lo),
+                                                  c_longlong(self.shard_size), c_longlong(self.start_rep),
+                                                  cu._p(self._sumsq2), cu._stream())
+            cu._check(rc, "zero_reduce_scatter")
+            cu.LAUNCHES += 1
+            self._have_sumsq2 = True
+            return
         if self.dp > 1:
             self.grad_buf.div_(self.dp)
             if self.stage >= 1 and dist.get_backend(self.dp_group) != "gloo":
@@ -176,9 +238,15 @@ class ZeroOptimizer:
         """Global L2 norm of the (unscaled) gradients as a device tensor, every parameter
         counted once: replicated ranges only on tp_rank 0, ZeRO shards summed over DP."""
         g = self.grid
-        sq = self._segment_sumsq(0, self.start_rep)
-        if g.tp_rank == 0:
-            sq = sq + self._segment_sumsq(self.start_rep, self.used)
+        if self.fused and self._have_sumsq2:      # produced by the reduce-scatter kernel in the same pass
+            sq = self._sumsq2[0:1].clone()
+            if g.tp_rank == 0:
+                sq = sq + self._sumsq2[1:2]
+            self._have_sumsq2 = False
+        else:
+            sq = self._segment_sumsq(0, self.start_rep)
+            if g.tp_rank == 0:
+                sq = sq + self._segment_sumsq(self.start_rep, self.used)
         if dist.is_initialized() and g.world > 1:
             if self.stage >= 1:
                 dist.all_reduce(sq)                       # dp shards × tp × pp
@@ -224,10 +292,15 @@ class ZeroOptimizer:
             lo, hi = max(a, self.shard_lo) - self.shard_lo, min(b, self.shard_hi) - self.shard_lo
             if hi <= lo:
                 continue
+            if self.fused:
+                self._fused_adam_allgather(lo, hi, lr, betas, eps, w, inv_scale)
+                continue
             ops.fused_adam_(self.master[lo:hi], gsh[lo:hi], self.exp_avg[lo:hi], self.exp_avg_sq[lo:hi], lowp[lo:hi],
                             lr, betas, eps, w, self.step_count, self.adamw, inv_scale, self._clip_coef,
                             self.bias_correction)
-        if self.stage >= 1 and self.dp > 1:
+        if self.fused:
+            self._dp_fence()                      # peers' parameter stores have landed; their gradient reads are done
+        elif self.stage >= 1 and self.dp > 1:
             if dist.get_backend(self.dp_group) == "gloo":
                 parts = [torch.empty_like(lowp) for _ in range(self.dp)]
                 dist.all_gather(parts, lowp.contiguous(), group=self.dp_group)
@@ -236,6 +309,22 @@ class ZeroOptimizer:
                 dist.all_gather_into_tensor(self.param_buf, lowp, group=self.dp_group)
         self.zero_grad()
         return True
+
+    def _fused_adam_allgather(self, lo, hi, lr, betas, eps, wd, inv_scale):
+        """Adam on master[lo:hi] with the bf16 result stored into every DP rank's parameter buffer."""
+        from ctypes import c_float, c_int, c_longlong, c_void_p
+        from ..ops import cuda as cu
+        c1 = 1.0 - betas[0] ** self.step_count if self.bias_correction else 1.0
+        c2 = 1.0 - betas[1] ** self.step_count if self.bias_correction else 1.0
+        arr = (c_void_p * self.dp)(*self._param_ptrs)
+        gsh = self._grad_shard()
+        rc = cu.lib().ell_zero_adam_allgather(
+            arr, c_int(self.dp), c_int(self.dp_rank), c_longlong(self.shard_lo + lo), c_longlong(hi - lo),
+            cu._p(self.master[lo:hi]), cu._p(gsh[lo:hi]), cu._p(self.exp_avg[lo:hi]), cu._p(self.exp_avg_sq[lo:hi]),
+            c_float(lr), c_float(betas[0]), c_float(betas[1]), c_float(eps), c_float(wd), c_float(c1), c_float(c2),
+            c_float(inv_scale), c_int(1 if self.adamw else 0), cu._p(self._clip_coef), cu._stream())
+        cu._check(rc, "zero_adam_allgather")
+        cu.LAUNCHES += 1
 
     def refresh_fp32_params(self):
         """Re-derive the fp32 master shard from the (just loaded) low-precision parameters."""

@@ -127,3 +127,29 @@ def test_accumulate_bf16_into_fp32(cu):
     acc = torch.ones(100003, device="cuda")
     cu.accum_bf16_to_f32(x, acc)
     _close(acc, 1 + x.float(), 1e-6, 1e-6)
+
+
+def test_embedding_fwd_bwd(cu):
+    from easyllm_b200 import ops
+    torch.manual_seed(2)
+    rows, h, T, start = 1000, 256, 4096, 3000
+    w = torch.randn(rows, h, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(start - 500, start + rows + 500, (4, T // 4), device="cuda")
+    ids[0, :64] = start + 7                      # many duplicates: exercises the atomics
+    out = ops.embedding(ids, w, start)
+    mine = (ids >= start) & (ids < start + rows)
+    want = torch.where(mine[..., None], w.detach()[(ids - start).clamp(0, rows - 1)], torch.zeros((), device="cuda", dtype=w.dtype))
+    assert torch.equal(out, want)
+    do = torch.randn_like(out)
+    out.backward(do)
+    ref = torch.zeros(rows, h, device="cuda")
+    ref.index_add_(0, (ids - start)[mine], do.float()[mine])
+    torch.testing.assert_close(w.grad.float(), ref, rtol=2e-2, atol=2e-2)
+    # accumulation into an fp32 main_grad
+    w2 = w.detach().clone().requires_grad_()
+    w2.main_grad = torch.ones(rows, h, device="cuda")
+    ops.embedding(ids, w2, start).backward(do)
+    torch.testing.assert_close(w2.main_grad, ref + 1.0, rtol=1e-4, atol=1e-3)
+    assert w2.grad is None
+    torch.cuda.synchronize()
+    cu.check_err_flag()

@@ -3,6 +3,7 @@ composition (run as child processes, one per GPU; plain peer loads/stores, NVLS 
 import os
 import subprocess
 import sys
+import tempfile
 
 import pytest
 import torch
@@ -77,8 +78,7 @@ def _run(nproc):
     if not torch.cuda.is_available() or torch.cuda.device_count() < nproc:
         pytest.skip(f"needs {nproc} GPUs")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    path = os.path.join(root, "gpurun_out", "_fused_tp_worker.py")
-    os.makedirs(os.path.dirname(path), exist_ok=True)
+    path = os.path.join(tempfile.mkdtemp(prefix="ell_fused_tp_"), "worker.py")
     with open(path, "w") as f:
         f.write(WORKER)
     env = dict(os.environ, ELL_ROOT=root, NCCL_NVLS_ENABLE="0")

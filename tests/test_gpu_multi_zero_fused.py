@@ -1,0 +1,81 @@
+"""ZeRO step with the fused reduce-scatter / Adam+all-gather kernels (peer loads and stores over NVLink)
+against the NCCL reduce-scatter + Adam + all-gather path, on 2 GPUs as child processes (NVLS off)."""
+import os
+import subprocess
+import sys
+import tempfile
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["ELL_ROOT"])
+from easyllm_b200.parallel.grid import initialize_distributed, get_grid
+from easyllm_b200.optim.zero import ZeroOptimizer
+import easyllm_b200.ops.cuda as cu
+initialize_distributed(tp=1, pp=1, backend="nccl", launcher="torch", timeout_s=120)
+g = get_grid()
+shapes = [(1024, 512), (512,), (300, 77), (4096, 256), (13,)]
+
+def build(fused):
+    os.environ["EASYLLM_ZERO_FUSED"] = "1" if fused else "0"
+    torch.manual_seed(3)
+    named = []
+    for i, sh in enumerate(shapes):
+        p = torch.nn.Parameter((torch.randn(*sh, device="cuda") * 0.1).to(torch.bfloat16))
+        if len(sh) == 2:
+            p.tensor_model_parallel = True
+        named.append((f"layer{i}.{'weight' if len(sh) == 2 else 'bias'}", p))
+    opt = ZeroOptimizer(named, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1, stage=1, grad_clip=1.0)
+    return named, opt
+
+res = {}
+for fused in (True, False):
+    named, opt = build(fused)
+    assert opt.fused == fused, (opt.fused, fused)
+    norms = []
+    for step in range(3):
+        for i, (_, p) in enumerate(named):
+            gen = torch.Generator(device="cuda").manual_seed(1000 * step + 10 * i + g.dp_rank)
+            p.main_grad.copy_(torch.randn(p.shape, device="cuda", generator=gen) * (0.5 + g.dp_rank))
+        assert opt.step()
+        norms.append(opt.get_global_grad_norm())
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    res[fused] = ([p.detach().float().clone() for _, p in named], norms, opt.master.clone())
+worst = 0.0
+for a, b in zip(res[True][0], res[False][0]):
+    worst = max(worst, (a - b).abs().max().item())
+nerr = max(abs(a - b) / b for a, b in zip(res[True][1], res[False][1]))
+merr = (res[True][2] - res[False][2]).abs().max().item()
+# every rank must hold the same parameters after the fused all-gather
+flat = torch.cat([t.flatten() for t in res[True][0]])
+ref = flat.clone(); dist.broadcast(ref, src=0)
+same = bool((flat == ref).all())
+print(f"RANK{g.rank} param_err={worst:.6f} norm_rel_err={nerr:.2e} master_err={merr:.2e} same={same}", flush=True)
+assert worst < 2e-3 and nerr < 1e-4 and merr < 1e-5 and same
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+def _run(nproc):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.path.join(tempfile.mkdtemp(prefix="ell_zero_fused_"), "worker.py")
+    with open(path, "w") as f:
+        f.write(WORKER)
+    env = dict(os.environ, ELL_ROOT=root, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29613", path]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("param_err") == nproc
+
+
+def test_zero_fused_2gpu():
+    _run(2)
