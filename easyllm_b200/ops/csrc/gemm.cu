@@ -74,6 +74,7 @@ struct FuseArgs {
   float* ce_part;
   long long ce_vocab_start;
   int ce_valid;
+  int no_tail_split;                     // plain launches: 1 disables the half-width tail tiles
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -379,7 +380,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int n_comm = FUSE == kFuseNone ? 0 : fuse.n_comm;
   const int cta0 = (int)blockIdx.x - n_comm;            // index among the GEMM CTAs
   const int cta_stride = (int)gridDim.x - n_comm;
-  const int n_split = split_tail_tiles(num_tiles, cta_stride, FUSE == kFuseNone && BN == 256 && OUT != kOutBf16CE);
+  const int n_split = split_tail_tiles(num_tiles, cta_stride, FUSE == kFuseNone && BN == 256 && OUT != kOutBf16CE &&
+                                                               !fuse.no_tail_split);
   const int num_full = num_tiles - n_split;
   const int num_units = num_tiles + n_split;
 
@@ -803,6 +805,10 @@ static int sm_count() {
 
 using namespace ell;
 
+static int g_no_tail_split = 0;
+// Tuning switch: 0 (default) cuts the tiles of an under-filled last wave in two, 1 keeps whole tiles.
+ELL_API void ell_gemm_set_tail_split(int enabled) { g_no_tail_split = enabled ? 0 : 1; }
+
 // C = op(A)·op(B)^T.  a_mn / b_mn select MN-major storage ([K,M] / [K,N] row-major).
 // out_mode: 0 bf16 C (ldc in elements), 1 fp32 C += result, 2 fp32 C = result.
 // `err` is a device int that receives a non-zero code if a bounded wait inside the kernel expired.
@@ -830,6 +836,7 @@ ELL_API int ell_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   }
   const int ctas = sm_count();
   FuseArgs Cf{};
+  Cf.no_tail_split = g_no_tail_split;
   const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(bias);
   // second B map with a box of BN/2 rows: used by the half-width tiles of a split tail wave
   CUtensorMap tBh = tB;

@@ -2,7 +2,7 @@
 
     python -m easyllm_b200.ops.profile_cases <case> [--iters 6]
 
-Cases: gemm_nt, gemm_dgrad, gemm_wgrad, flash_fwd, rmsnorm_fwd, rmsnorm_bwd, swiglu, rope, adam, ce.
+Cases: gemm_nt, gemm_dgrad, gemm_wgrad, flash_fwd, flash_bwd, rmsnorm_fwd, rmsnorm_bwd, swiglu, rope, adam, ce.
 Inputs are larger than L2 (126 MB) where the op is memory-bound but hold well under a few GB,
 so a full-section profiler capture of 1-3 launches ends by itself in a minute or two.
 """
@@ -38,6 +38,15 @@ def main():
         q, k, v = (qkv[:, i * 4096:(i + 1) * 4096].view(4096, 32, 128) for i in range(3))
         rs = torch.zeros(4096, dtype=torch.int32, device="cuda")
         fn = lambda: cu.flash_attn_fwd(q, k, v, rs, 128 ** -0.5)                      # noqa: E731
+    elif c == "flash_bwd":
+        qkv = torch.randn(4096, 3 * 32 * 128, **bf)
+        q, k, v = (qkv[:, i * 4096:(i + 1) * 4096].view(4096, 32, 128) for i in range(3))
+        rs = torch.zeros(4096, dtype=torch.int32, device="cuda")
+        out, lse = cu.flash_attn_fwd(q, k, v, rs, 128 ** -0.5)
+        do = torch.randn_like(out)
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = (dqkv[:, i * 4096:(i + 1) * 4096].view(4096, 32, 128) for i in range(3))
+        fn = lambda: cu.flash_attn_bwd(do, q, k, v, out, lse, rs, 128 ** -0.5, dq, dk, dv)   # noqa: E731
     elif c in ("rmsnorm_fwd", "rmsnorm_bwd"):
         x = torch.randn(16384, 4096, **bf); r = torch.randn_like(x); w = torch.ones(4096, **bf)
         y, h, rstd = cu.rmsnorm_fwd(x, r, w, 1e-5)
