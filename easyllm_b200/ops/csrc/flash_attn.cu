@@ -39,6 +39,19 @@ struct FaShared {
 
 enum FaErr { kFaErrProducer = 11, kFaErrMma = 12, kFaErrSoftmax = 13 };
 
+// Optional timeline of the first CTA (clock64 stamps per role, step and stage), compiled in with -DELL_FA_TRACE.
+#ifdef ELL_FA_TRACE
+__device__ long long* g_fa_trace = nullptr;   // [3 roles][64 steps][8 stages]
+#define FA_TRACE(role, it, slot)                                                             \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && g_fa_trace && (it) < 64)                       \
+      g_fa_trace[(((role) * 64 + (it)) << 3) + (slot)] = clock64();                          \
+  } while (0)
+#else
+#define FA_TRACE(role, it, slot)
+#endif
+
+// registers are granted per 4 warps: 10 warps count as 12, which caps a thread at 168 registers
 __global__ void __launch_bounds__(kFaThreads, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
@@ -106,13 +119,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tma_load_2d(sQ + t * kFaTileBytes, &tmQ, &sh->q_full, h * kFaD, q0 + t * kFaM);
         tma_load_2d(sQ + t * kFaTileBytes + kFaTileBytes / 2, &tmQ, &sh->q_full, h * kFaD + 64, q0 + t * kFaM);
       }
-      for (int j = 0; j < n_kv_max && ok; ++j) {
+      // K runs one tile ahead of V: K(j+1) is requested as soon as S(j-1) released its stage, before the
+      // loader blocks on the single V stage (free only once PV(j-1) is done)
+      auto load_k = [&](int j) -> bool {
         const int s = j & 1;
-        const int k0 = kv_lo + j * kFaN;
-        if (!mbar_wait(&sh->k_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&sh->k_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) return false;
         mbar_expect_tx(&sh->k_full[s], kFaTileBytes);
-        tma_load_2d(sK + s * kFaTileBytes, &tmK, &sh->k_full[s], kvh * kFaD, k0);
-        tma_load_2d(sK + s * kFaTileBytes + kFaTileBytes / 2, &tmK, &sh->k_full[s], kvh * kFaD + 64, k0);
+        tma_load_2d(sK + s * kFaTileBytes, &tmK, &sh->k_full[s], kvh * kFaD, kv_lo + j * kFaN);
+        tma_load_2d(sK + s * kFaTileBytes + kFaTileBytes / 2, &tmK, &sh->k_full[s], kvh * kFaD + 64, kv_lo + j * kFaN);
+        return true;
+      };
+      if (n_kv_max > 0) ok = load_k(0);
+      for (int j = 0; j < n_kv_max && ok; ++j) {
+        const int k0 = kv_lo + j * kFaN;
+        if (j + 1 < n_kv_max && !load_k(j + 1)) { ok = false; break; }
         if (!mbar_wait(&sh->v_empty, (j & 1) ^ 1, abort_flag)) { ok = false; break; }
         mbar_expect_tx(&sh->v_full, kFaTileBytes);
         tma_load_2d(sV, &tmV, &sh->v_full, kvh * kFaD, k0);
@@ -154,12 +174,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; j < n_kv_max && ok; ++j) {
+        FA_TRACE(0, j, 0);
         if (j + 1 < n_kv_max && !issue_s(j + 1)) { ok = false; break; }
+        FA_TRACE(0, j, 1);
         if (!mbar_wait(&sh->v_full, j & 1, abort_flag)) { ok = false; break; }
+        FA_TRACE(0, j, 2);
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j >= n_kv[t] || !ok) continue;
           if (!mbar_wait(&sh->p_full[t], j & 1, abort_flag)) { ok = false; continue; }
+          FA_TRACE(0, j, 3 + t);
           tc_fence_after();
           const uint32_t p_addr = smem_u32(sP + t * kFaTileBytes);
 #pragma unroll
@@ -171,6 +195,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_commit(&sh->pv_done[t]);
         }
         umma_commit(&sh->v_empty);
+        FA_TRACE(0, j, 5);
       }
       if (!ok) {
         sh->abort_flag = 1;
@@ -201,7 +226,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     };
     const int my_n = n_kv[t];
     for (int j = 0; j < my_n; ++j) {
+      if (threadIdx.x == 64) FA_TRACE(1, j, 0);
       if (!mbar_wait(&sh->s_full[t], j & 1, abort_flag)) fail();
+      if (threadIdx.x == 64) FA_TRACE(1, j, 1);
       tc_fence_after();
       uint32_t s[128];
       tmem_ld_32x32(t_s, s);
@@ -211,6 +238,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&sh->s_free[t]);               // S_t(j+1) may overwrite the columns now
+      if (threadIdx.x == 64) FA_TRACE(1, j, 2);
       const int k0 = kv_lo + j * kFaN;
       const bool need_mask = (k0 + kFaN - 1 > tile_first) || (k0 < max_row_start);
       if (need_mask) {
@@ -237,24 +265,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m_used = m_new;
         l *= alpha;
       }
-      // P = exp2(s*scale - m_used) -> bf16 (kept in registers until the P tile is free)
-      uint32_t pk[64];
-      float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
-      const float neg_m = -m_used;
-#pragma unroll
-      for (int i = 0; i < 128; i += 4) {
-        const float p0 = exp2f(fmaf(__uint_as_float(s[i]), scale_log2, neg_m));
-        const float p1 = exp2f(fmaf(__uint_as_float(s[i + 1]), scale_log2, neg_m));
-        const float p2 = exp2f(fmaf(__uint_as_float(s[i + 2]), scale_log2, neg_m));
-        const float p3 = exp2f(fmaf(__uint_as_float(s[i + 3]), scale_log2, neg_m));
-        ps0 += p0; ps1 += p1; ps2 += p2; ps3 += p3;
-        __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1), b = __floats2bfloat162_rn(p2, p3);
-        pk[i / 2] = *reinterpret_cast<uint32_t*>(&a);
-        pk[i / 2 + 1] = *reinterpret_cast<uint32_t*>(&b);
-      }
-      l += (ps0 + ps1) + (ps2 + ps3);
-      // P(j) overwrites the tile PV(j-1) reads, and a rescale touches O: wait for PV(j-1)
+      // P(j) overwrites the tile PV(j-1) reads, and a rescale touches O: wait for PV(j-1) (issued a whole
+      // softmax period ago, so this rarely blocks)
+      if (threadIdx.x == 64) FA_TRACE(1, j, 3);
       if (j > 0 && !mbar_wait(&sh->pv_done[t], (j - 1) & 1, abort_flag)) fail();
+      if (threadIdx.x == 64) FA_TRACE(1, j, 4);
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
         tc_fence_after();
 #pragma unroll 1
@@ -269,12 +284,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_st_wait();
         tc_fence_before();
       }
+      // P = exp2(s*scale - m_used) -> bf16 -> swizzled smem, 8 columns (one 16-byte chunk) at a time
+      float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
+      const float neg_m = -m_used;
 #pragma unroll
-      for (int c = 0; c < 16; ++c)
-        *reinterpret_cast<uint4*>(p_row + (c >> 3) * (kFaTileBytes / 2) + (((c & 7) ^ sw) << 4)) =
-            make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
+      for (int c = 0; c < 16; ++c) {
+        float p[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) p[i] = exp2f(fmaf(__uint_as_float(s[c * 8 + i]), scale_log2, neg_m));
+        ps0 += p[0] + p[4]; ps1 += p[1] + p[5]; ps2 += p[2] + p[6]; ps3 += p[3] + p[7];
+        *reinterpret_cast<bf16x8*>(p_row + (c >> 3) * (kFaTileBytes / 2) + (((c & 7) ^ sw) << 4)) = pack8(p);
+      }
+      l += (ps0 + ps1) + (ps2 + ps3);
       fence_proxy_async_smem();
       mbar_arrive(&sh->p_full[t]);
+      if (threadIdx.x == 64) FA_TRACE(1, j, 5);
     }
     // ---------------- epilogue: O / l -> bf16 -> global; LSE ----------------
     if (my_n > 0) {
@@ -324,6 +348,12 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_
 }  // namespace ell
 
 using namespace ell;
+
+#ifdef ELL_FA_TRACE
+ELL_API int ell_flash_fwd_set_trace(long long* buf) {
+  return (int)cudaMemcpyToSymbol(ell::g_fa_trace, &buf, sizeof(buf));
+}
+#endif
 
 // q [T, Hq, 128] / k, v [T, Hk, 128] bf16 with row strides (in elements) q_stride / kv_stride (views
 // into the packed QKV GEMM output are fine); out [T, Hq, 128] contiguous; lse [Hq, T] fp32;

@@ -14,7 +14,8 @@
 //               with MN-major descriptors, so nothing is transposed in memory.
 //   warps 2-9   two groups of 128 threads; thread r of a group owns query row r (TMEM lane r) and half of
 //               the 128 columns.  They turn S into P and dP into dS, drain the dQ tile (TMEM -> swizzled
-//               fp32 staging in the P/dS buffers -> cp.reduce.async.bulk add into the fp32 dQ accumulator),
+//               fp32 staging, half in the dS buffer and half in a dedicated tile -> cp.reduce.async.bulk add
+//               into the fp32 dQ accumulator; nothing waits for the adds until the buffers are needed again),
 //               and at the end write dV_j / dK_j.
 // Every wait is bounded; on expiry the CTA records an error code, runs the remaining steps without
 // touching global memory, frees its TMEM and returns.
@@ -31,7 +32,7 @@ constexpr int kFbThreads = 320;
 constexpr int kFbTile = 128, kFbD = 128;
 constexpr int kFbTileBytes = 128 * 128 * 2;   // 32 KiB
 constexpr int kFbHalf = kFbTileBytes / 2;     // 16 KiB: one 64-column half of a tile
-constexpr int kFbSmemBytes = 6 * kFbTileBytes + 1024 + 256;
+constexpr int kFbSmemBytes = 7 * kFbTileBytes + 1024 + 256;   // K, V, Q, dO, P, dS, dQ staging
 
 struct FbShared {
   uint64_t kv_full, q_full, do_full, q_empty, do_empty, s_full, dp_full, p_full, ds_full, dq_full, dq_drained;
@@ -40,6 +41,18 @@ struct FbShared {
 };
 
 enum FbErr { kFbErrProducer = 21, kFbErrMma = 22, kFbErrSoftmax = 23 };
+
+// Optional timeline of the first CTA (clock64 stamps per role, step and stage), compiled in with -DELL_FA_TRACE.
+#ifdef ELL_FA_TRACE
+__device__ long long* g_fb_trace = nullptr;   // [3 roles][64 steps][8 stages]
+#define FB_TRACE(role, it, slot)                                                             \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && g_fb_trace && (it) < 64)                       \
+      g_fb_trace[(((role) * 64 + (it)) << 3) + (slot)] = clock64();                          \
+  } while (0)
+#else
+#define FB_TRACE(role, it, slot)
+#endif
 
 // Index one past the last query tile that can see keys up to k_last: row_start is non-decreasing, so the
 // tiles whose first row starts a document after k_last (and all later tiles) are invisible.  Warp-uniform.
@@ -55,6 +68,7 @@ __device__ __forceinline__ int fb_last_qtile(const int* __restrict__ row_start, 
   return i_end;
 }
 
+// registers are granted per 4 warps: 10 warps count as 12, which caps a thread at 168 registers
 __global__ void __launch_bounds__(kFbThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -71,7 +85,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sdO = smem + 3 * kFbTileBytes;
   uint8_t* sP = smem + 4 * kFbTileBytes;
   uint8_t* sdS = smem + 5 * kFbTileBytes;
-  FbShared* sh = reinterpret_cast<FbShared*>(smem + 6 * kFbTileBytes);
+  uint8_t* sStage = smem + 6 * kFbTileBytes;   // fp32 staging of half of each dQ tile (the other half reuses dS)
+  FbShared* sh = reinterpret_cast<FbShared*>(smem + 7 * kFbTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (T + kFbTile - 1) / kFbTile;
@@ -89,8 +104,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (threadIdx.x == 0) {
     mbar_init(&sh->kv_full, 1);
     mbar_init(&sh->q_full, 1);
-    mbar_init(&sh->do_full, 1);
     mbar_init(&sh->q_empty, 1);
+    mbar_init(&sh->do_full, 1);
     mbar_init(&sh->do_empty, 1);
     mbar_init(&sh->s_full, 1);
     mbar_init(&sh->dp_full, 1);
@@ -132,11 +147,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = j; i < i_end; ++i, ++it) {
           // dO is released by the dV MMA (mid-step), Q by the dK MMA (end of step): the next tiles
           // stream in while the current step computes dS and drains dQ
+          FB_TRACE(2, it, 0);
           if (it > 0 && !mbar_wait(&sh->do_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
+          FB_TRACE(2, it, 1);
           mbar_expect_tx(&sh->do_full, kFbTileBytes);
           tma_load_2d(sdO, &tmdO, &sh->do_full, h * kFbD, i * kFbTile);
           tma_load_2d(sdO + kFbHalf, &tmdO, &sh->do_full, h * kFbD + 64, i * kFbTile);
           if (it > 0 && !mbar_wait(&sh->q_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
+          FB_TRACE(2, it, 2);
           mbar_expect_tx(&sh->q_full, kFbTileBytes);
           tma_load_2d(sQ, &tmQ, &sh->q_full, h * kFbD, i * kFbTile);
           tma_load_2d(sQ + kFbHalf, &tmQ, &sh->q_full, h * kFbD + 64, i * kFbTile);
@@ -158,7 +176,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       bool ok = mbar_wait(&sh->kv_full, 0, abort_flag);
       for (int it = 0; it < n_it && ok; ++it) {
         const uint32_t ph = it & 1;
+        FB_TRACE(0, it, 0);
         if (!mbar_wait(&sh->do_full, ph, abort_flag)) { ok = false; break; }
+        FB_TRACE(0, it, 1);
         tc_fence_after();
         // dP = dO V^T (the dP columns were released when dS of the previous step was published)
 #pragma unroll
@@ -171,6 +191,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // S = Q K^T into the columns the previous dQ tile is drained from
         if (!mbar_wait(&sh->q_full, ph, abort_flag)) { ok = false; break; }
         if (it > 0 && !mbar_wait(&sh->dq_drained, (it - 1) & 1, abort_flag)) { ok = false; break; }
+        FB_TRACE(0, it, 2);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -181,6 +202,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(&sh->s_full);
         // dV += P^T dO
         if (!mbar_wait(&sh->p_full, ph, abort_flag)) { ok = false; break; }
+        FB_TRACE(0, it, 3);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
@@ -189,6 +211,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(&sh->do_empty);
         // dK += dS^T Q ; dQ = dS K
         if (!mbar_wait(&sh->ds_full, ph, abort_flag)) { ok = false; break; }
+        FB_TRACE(0, it, 4);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
@@ -202,6 +225,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         umma_commit(&sh->dq_full);     // also: dV, dK of this step done; P, dS, Q free
         umma_commit(&sh->q_empty);
+        FB_TRACE(0, it, 5);
       }
       if (!ok) {
         sh->abort_flag = 1;
@@ -238,14 +262,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const float dlt = row_valid ? delta[(size_t)h * T + row] : 0.f;
         const bool need_mask = (i == j) || (row_start[min(q0 + kFbTile, T) - 1] > k0) || (q0 + kFbTile > T);
         uint32_t pk[32];                         // P of this thread's 64 columns, packed bf16x2
+        if (threadIdx.x == 64) FB_TRACE(1, it, 0);
         if (!mbar_wait(&sh->s_full, ph, abort_flag)) fail();
+        if (threadIdx.x == 64) FB_TRACE(1, it, 1);
         tc_fence_after();
-        if (it > 0) {
-          // the previous dQ tile was staged in this group's halves of P / dS: the reduce-add must have
-          // read them before they are overwritten
-          if (r == 0) tma_store_wait_read<0>();
-          named_bar_sync(1 + wg, 128);
-        }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
@@ -270,8 +290,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         fence_proxy_async_smem();
         mbar_arrive(&sh->p_full);
+        if (threadIdx.x == 64) FB_TRACE(1, it, 2);
         if (!mbar_wait(&sh->dp_full, ph, abort_flag)) fail();
+        if (threadIdx.x == 64) FB_TRACE(1, it, 3);
         tc_fence_after();
+        if (it > 0) {
+          // half of the previous dQ tile was staged in this group's half of the dS buffer (the older of the
+          // two reduce-add groups): it must have been read before dS overwrites it
+          if (r == 0) tma_store_wait_read<1>();
+          named_bar_sync(1 + wg, 128);
+        }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
@@ -292,15 +320,22 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_before();
         fence_proxy_async_smem();
         mbar_arrive(&sh->ds_full);
+        if (threadIdx.x == 64) FB_TRACE(1, it, 4);
         // ---- dQ tile: TMEM -> fp32 staging (this group's halves of the P and dS buffers) -> reduce-add
         if (!mbar_wait(&sh->dq_full, ph, abort_flag)) fail();
+        if (threadIdx.x == 64) FB_TRACE(1, it, 5);
         tc_fence_after();
+        if (it > 0) {
+          // the dedicated staging half was last read by the newer reduce-add group of the previous step
+          if (r == 0) tma_store_wait_read<0>();
+          named_bar_sync(1 + wg, 128);
+        }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
           tmem_ld_32x32(t_s + lane_off + col_base + c * 32, v);
           tmem_ld_wait();
-          uint8_t* st_row = (c == 0 ? sP : sdS) + wg * kFbHalf + r * 128;
+          uint8_t* st_row = (c == 0 ? sdS : sStage) + wg * kFbHalf + r * 128;
 #pragma unroll
           for (int g4 = 0; g4 < 8; ++g4)
             *reinterpret_cast<uint4*>(st_row + ((g4 ^ sw) << 4)) =
@@ -312,11 +347,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         named_bar_sync(1 + wg, 128);
         if (r == 0) {
           if (!*abort_flag) {
-            tma_reduce_add_2d(&tmDQ, sP + wg * kFbHalf, h * kFbD + col_base, q0);
-            tma_reduce_add_2d(&tmDQ, sdS + wg * kFbHalf, h * kFbD + col_base + 32, q0);
+            tma_reduce_add_2d(&tmDQ, sdS + wg * kFbHalf, h * kFbD + col_base, q0);
+            tma_store_commit();            // older group: the dS buffer is needed again first
+            tma_reduce_add_2d(&tmDQ, sStage + wg * kFbHalf, h * kFbD + col_base + 32, q0);
             tma_store_commit();
           }
         }
+        if (threadIdx.x == 64) FB_TRACE(1, it, 6);
       }
     }
     // ---------------- epilogue: dV (group 0) / dK (group 1) -> bf16 -> global ----------------
@@ -408,6 +445,12 @@ int make_tmap_f32_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t
 }  // namespace ell
 
 using namespace ell;
+
+#ifdef ELL_FA_TRACE
+ELL_API int ell_flash_bwd_set_trace(long long* buf) {
+  return (int)cudaMemcpyToSymbol(ell::g_fb_trace, &buf, sizeof(buf));
+}
+#endif
 
 // q [T, Hq, 128], k / v [T, Hk, 128] (row strides q_stride / kv_stride elements, views into a packed QKV
 // buffer are fine); out, dout [T, Hq, 128] contiguous; lse [Hq, T] from the forward.
