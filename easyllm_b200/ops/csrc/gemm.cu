@@ -899,20 +899,23 @@ static void fill_fuse(FuseArgs& f, int rank, int tp, int n_comm, int rows_per_ra
   f.queue = f.counter + 1;
 }
 
-// All-gather -> GEMM.  out[tp*rows_per_rank, N] = gather(x_local)[.., K] · W[N, K]^T (+ bias).
+// All-gather -> GEMM.  out[tp*rows_per_rank, N] = gather(x_local)[.., K] · W[N, K]^T (+ bias), or with
+// b_mn = 1, gather(x_local) · W[K, N] (W read in place as an MN-major operand).
 // gathered_ptrs[r] is rank r's gathered buffer [tp*rows_per_rank, K] (peer pointers; entry `rank` is local);
 // flag_ptrs[r] / done_ptrs[r] are rank r's flag ([tp][flags_per_src]) and done ([tp]) words.
 ELL_API int ell_gemm_ag(const void* x_local, const void* W, void* out, const void* bias, int rows_per_rank, int N,
-                        int K, int rank, int tp, unsigned int epoch, int n_comm, void* const* gathered_ptrs,
+                        int K, int b_mn, int rank, int tp, unsigned int epoch, int n_comm, void* const* gathered_ptrs,
                         void* const* flag_ptrs, void* const* done_ptrs, void* counter, int flags_per_src, int* err,
                         cudaStream_t stream) {
   if (tp < 1 || tp > kMaxTp || rows_per_rank % kBM || rows_per_rank / kBM > flags_per_src) return -2;
+  if (b_mn && bias) return -2;
   const int M = rows_per_rank * tp;
   const int BN = N >= 256 ? 256 : 128;
   CUtensorMap tA, tB, tC;
   int rc = make_tmap_bf16_2d(&tA, gathered_ptrs[rank], (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBK, kBM);
   if (rc) return rc;
-  rc = make_tmap_bf16_2d(&tB, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, kBK, BN);
+  if (!b_mn) rc = make_tmap_bf16_2d(&tB, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, kBK, BN);
+  else       rc = make_tmap_bf16_2d(&tB, W, (uint64_t)N, (uint64_t)K, (uint64_t)N * 2, 64, kBK);
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tC, out, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 128);
   if (rc) return rc;
@@ -925,6 +928,10 @@ ELL_API int ell_gemm_ag(const void* x_local, const void* W, void* out, const voi
   const int ctas = sm_count();
   if (n_comm < 1 || n_comm >= ctas) return -2;
   const __nv_bfloat16* bp = (const __nv_bfloat16*)bias;
+  if (b_mn) {   // W is [K, N] row-major: the dgrad of a row-parallel linear (gathered dy · W)
+    if (BN == 256) return launch_gemm<256, false, true, kOutBf16, false, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream, &tA2);
+    return launch_gemm<128, false, true, kOutBf16, false, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream, &tA2);
+  }
   if (BN == 256) {
     if (bias) return launch_gemm<256, false, false, kOutBf16, true, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream, &tA2);
     return launch_gemm<256, false, false, kOutBf16, false, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream, &tA2);

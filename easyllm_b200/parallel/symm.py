@@ -3,8 +3,9 @@
 Every rank of the TP group owns, at the same offsets of one symmetric allocation (CUDA VMM
 memory mapped on all peers through ``torch.distributed._symmetric_memory``):
 
-  gathered [T, hidden] bf16   all-gather→GEMM: rank s copies its sequence shard into rows
-                              ``[s·T/tp, (s+1)·T/tp)`` of every rank's buffer
+  gathered [2][T, hidden] bf16  all-gather→GEMM: rank s copies its sequence shard into rows
+                              ``[s·T/tp, (s+1)·T/tp)`` of every rank's buffer; two buffers alternate by
+                              call so a following kernel (wgrad) can still read the previous gather
   staging  [T, hidden] bf16   GEMM→reduce-scatter: this rank's partial product, read by the owners
   flags / done words          epoch counters written by peers (one set per kernel kind)
 
@@ -47,7 +48,7 @@ class FusedTPWorkspace:
         dev = torch.device("cuda", torch.cuda.current_device())
         data_elems = max_tokens * hidden
         flag_words = 2 * (self.tp * _MAX_FLAGS + 64)             # AG set + RS set (flags + done)
-        nbytes = 2 * data_elems * 2 + flag_words * 4
+        nbytes = 3 * data_elems * 2 + flag_words * 4            # gathered x2 (alternating by epoch) + staging
         name = self.group.group_name
         try:
             symm_mem.enable_symm_mem_for_group(name)
@@ -59,10 +60,13 @@ class FusedTPWorkspace:
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
         base = [int(p) for p in self.hdl.buffer_ptrs]
-        off_stage = data_elems * 2
-        off_flags = 2 * data_elems * 2
+        off_stage = 2 * data_elems * 2
+        off_flags = 3 * data_elems * 2
         set_bytes = (self.tp * _MAX_FLAGS + 64) * 4
-        self.gathered_ptrs = base
+        # two gathered buffers used alternately: a later kernel on this stream (the wgrad GEMM) may still read
+        # epoch e's gathered operand while fast peers already push epoch e+1
+        self.gathered_ptrs = [base, [b + data_elems * 2 for b in base]]
+        self._gathered_off = [0, data_elems * 2]
         self.stage_ptrs = [b + off_stage for b in base]
         self.ag_flags = [b + off_flags for b in base]
         self.ag_done = [b + off_flags + self.tp * _MAX_FLAGS * 4 for b in base]
@@ -80,23 +84,33 @@ class FusedTPWorkspace:
         return (rows_per_rank % 128 == 0 and rows_per_rank * self.tp <= self.max_tokens and width <= self.hidden
                 and width % 8 == 0)
 
-    def ag_gemm(self, x_local, w, bias=None):
-        """``gather(x_local) · wᵀ (+bias)``; returns ``[T, N]`` or None when the shape is unsupported."""
+    def ag_gemm(self, x_local, w, bias=None, b_mn=False):
+        """``gather(x_local) · wᵀ (+bias)`` (``w [N, K]``), or with ``b_mn`` ``gather(x_local) · w`` (``w [K, N]``);
+        returns ``[T, N]`` or None when the shape is unsupported."""
         from ..ops import cuda as cu
         rows, K = x_local.shape
-        N = w.shape[0]
-        if not self._ok(rows, K) or rows // 128 > _MAX_FLAGS or N % 8:
+        N = w.shape[1] if b_mn else w.shape[0]
+        if not self._ok(rows, K) or rows // 128 > _MAX_FLAGS or N % 8 or (b_mn and bias is not None):
             return None
         x_local = x_local.contiguous()
         out = torch.empty(rows * self.tp, N, dtype=torch.bfloat16, device=x_local.device)
         self.epoch_ag += 1
         rc = cu.lib().ell_gemm_ag(cu._p(x_local), cu._p(w), cu._p(out), cu._p(bias), c_int(rows), c_int(N), c_int(K),
-                                  c_int(self.rank), c_int(self.tp), c_uint(self.epoch_ag), c_int(self.n_comm_ag),
-                                  self._arr(self.gathered_ptrs), self._arr(self.ag_flags), self._arr(self.ag_done),
+                                  c_int(1 if b_mn else 0), c_int(self.rank), c_int(self.tp), c_uint(self.epoch_ag), c_int(self.n_comm_ag),
+                                  self._arr(self.gathered_ptrs[self.epoch_ag & 1]), self._arr(self.ag_flags), self._arr(self.ag_done),
                                   c_void_p(self.counters.data_ptr()), c_int(_MAX_FLAGS),
                                   cu._p(cu.err_flag(x_local.device)), cu._stream())
         cu._check(rc, "gemm_ag")
+        self._last_ag = (x_local, rows, K, self._gathered_off[self.epoch_ag & 1])
         return out
+
+    def gathered(self):
+        """The all-gathered operand ``[T, K]`` of the last ``ag_gemm`` (a view into the workspace, valid until the
+        next fused call).  Peers' shards were pushed by the kernel; the local shard is copied in here."""
+        x_local, rows, K, off = self._last_ag
+        full = self.buf[off: off + rows * self.tp * K * 2].view(torch.bfloat16).view(rows * self.tp, K)
+        full[self.rank * rows:(self.rank + 1) * rows].copy_(x_local)
+        return full
 
     def gemm_rs(self, x, w, b_mn=False):
         """reduce-scatter over TP of ``x · op(w)``; returns this rank's ``[T/tp, N]`` rows or None."""
@@ -135,9 +149,11 @@ def install(max_tokens, hidden):
         return None
     _WS = FusedTPWorkspace(max_tokens, hidden)
 
-    def ag(x, w, bias):
-        y = _WS.ag_gemm(x, w, bias)
-        return (y, None) if y is not None else None
+    def ag(x, w, bias, b_mn=False, want_gathered=False):
+        y = _WS.ag_gemm(x, w, bias, b_mn)
+        if y is None:
+            return None
+        return (y, _WS.gathered() if want_gathered else None)
 
     def rs(x, w, b_mn=False):
         return _WS.gemm_rs(x, w, b_mn)

@@ -26,8 +26,9 @@ _FUSED = {"ag_gemm": None, "gemm_rs": None}
 
 
 def set_fused_impl(ag_gemm=None, gemm_rs=None):
-    """Install fused kernels: ``ag_gemm(x_local, w, bias) -> (y, x_gathered)`` and
-    ``gemm_rs(x, w) -> y_local``.  ``None`` restores the composition."""
+    """Install fused kernels: ``ag_gemm(x_local, w, bias, b_mn=False, want_gathered=False) -> (y, x_gathered)``
+    and ``gemm_rs(x, w, b_mn=False) -> y_local`` (either may return None for an unsupported shape).
+    ``None`` restores the composition."""
     _FUSED["ag_gemm"], _FUSED["gemm_rs"] = ag_gemm, gemm_rs
 
 
@@ -119,7 +120,15 @@ class _RowSP(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
-        dyg, work = _ag_start(dy.contiguous(), "sp_gather_row_bwd")
+        dy = dy.contiguous()
+        fused = _FUSED["ag_gemm"] if (_use_fused(dy) and ctx.needs_input_grad[0]) else None
+        res = fused(dy, w, None, b_mn=True, want_gathered=ctx.needs_input_grad[1]) if fused is not None else None
+        if res is not None:
+            # dgrad as all-gather -> GEMM in one kernel; the gathered dy it leaves behind feeds the wgrad GEMM
+            dx, dyg = res
+            dw = _wgrad(ctx.wref, dyg, x) if ctx.needs_input_grad[1] else None
+            return dx, dw
+        dyg, work = _ag_start(dy, "sp_gather_row_bwd")
         work.wait()
         dx = ops.matmul_nn(dyg, w) if ctx.needs_input_grad[0] else None
         dw = _wgrad(ctx.wref, dyg, x) if ctx.needs_input_grad[1] else None
