@@ -2,7 +2,7 @@
 
     python -m easyllm_b200.ops.profile_cases <case> [--iters 6]
 
-Cases: gemm_nt, gemm_dgrad, gemm_wgrad, flash_fwd, flash_bwd, rmsnorm_fwd, rmsnorm_bwd, swiglu, rope, adam, ce.
+Cases: gemm_nt, gemm_dgrad, gemm_wgrad, gemm_ag, gemm_rs, flash_fwd, flash_bwd, rmsnorm_fwd, rmsnorm_bwd, swiglu, rope, adam, ce.
 Inputs are larger than L2 (126 MB) where the op is memory-bound but hold well under a few GB,
 so a full-section profiler capture of 1-3 launches ends by itself in a minute or two.
 """
@@ -47,6 +47,23 @@ def main():
         dqkv = torch.empty_like(qkv)
         dq, dk, dv = (dqkv[:, i * 4096:(i + 1) * 4096].view(4096, 32, 128) for i in range(3))
         fn = lambda: cu.flash_attn_bwd(do, q, k, v, out, lse, rs, 128 ** -0.5, dq, dk, dv)   # noqa: E731
+    elif c in ("gemm_ag", "gemm_rs"):
+        # the fused tensor-parallel kernels on a one-rank group: same kernel, flags and staging path, no peers
+        import os
+        import torch.distributed as dist
+        from ..parallel import symm
+        from ..parallel.grid import initialize_distributed
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29655")
+        os.environ.setdefault("RANK", "0"); os.environ.setdefault("WORLD_SIZE", "1"); os.environ.setdefault("LOCAL_RANK", "0")
+        if not dist.is_initialized():
+            initialize_distributed(tp=1, pp=1, backend="nccl", launcher="torch")
+        ws = symm.FusedTPWorkspace(4096, 11008)
+        if c == "gemm_ag":
+            x = torch.randn(4096, 4096, **bf); w = torch.randn(22016, 4096, **bf)
+            fn = lambda: ws.ag_gemm(x, w)                                             # noqa: E731
+        else:
+            x = torch.randn(4096, 11008, **bf); w = torch.randn(4096, 11008, **bf)
+            fn = lambda: ws.gemm_rs(x, w)                                             # noqa: E731
     elif c in ("rmsnorm_fwd", "rmsnorm_bwd"):
         x = torch.randn(16384, 4096, **bf); r = torch.randn_like(x); w = torch.ones(4096, **bf)
         y, h, rstd = cu.rmsnorm_fwd(x, r, w, 1e-5)
