@@ -33,6 +33,7 @@ def timed(fn, iters=20, warmup=3):
     for _ in range(iters):
         flush.zero_()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(300000)   # the device stays busy while the host prepares the launch: no host gap is timed
         a.record()
         fn()
         b.record()

@@ -204,10 +204,17 @@ __device__ void ag_comm_role(const FuseArgs& f, int K, int* err, uint8_t* smem) 
       atomicCAS(err, 0, kErrComm);
       return;
     }
-  uint32_t issued = 0, landed = 0;   // chunk counters across tiles select ring stage and parity
-  for (int t = blockIdx.x; t < tiles; t += f.n_comm) {
+  uint32_t issued = 0, landed = 0;   // chunk counters across items select ring stage and parity
+  // Work item = (row tile, destination): with few row tiles per rank (large tp) every comm CTA still has work,
+  // and each destination's flag is raised as soon as its copy of the tile has landed.
+  const int n_dest = f.tp - 1;
+  const int n_items = tiles * n_dest;
+  for (int item = blockIdx.x; item < n_items; item += f.n_comm) {
+    const int t = item / n_dest;
+    const int dest = (f.rank - 1 - item % n_dest + f.tp) % f.tp;   // the rank that needs this shard soonest first
     const uint8_t* src = reinterpret_cast<const uint8_t*>(f.x_local) + (size_t)t * tile_bytes;
-    const size_t dst_off = ((size_t)f.rank * f.rows_per_rank + (size_t)t * kBM) * K * 2;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(f.data_ptrs[dest]) +
+                   ((size_t)f.rank * f.rows_per_rank + (size_t)t * kBM) * K * 2;
     int next_load = 0;
     auto issue_load = [&](int c) {
       const uint32_t st = issued % kCommStages;
@@ -225,22 +232,17 @@ __device__ void ag_comm_role(const FuseArgs& f, int K, int* err, uint8_t* smem) 
       }
       ++landed;
       const uint32_t bytes = (uint32_t)min((size_t)kCommChunkBytes, tile_bytes - (size_t)c * kCommChunkBytes);
-      for (int i = 1; i < f.tp; ++i) {
-        const int dest = (f.rank - i + f.tp) % f.tp;   // the rank that needs this shard soonest first
-        bulk_store(reinterpret_cast<uint8_t*>(f.data_ptrs[dest]) + dst_off + (size_t)c * kCommChunkBytes,
-                   smem + st * kCommChunkBytes, bytes);
-      }
+      bulk_store(dst + (size_t)c * kCommChunkBytes, smem + st * kCommChunkBytes, bytes);
       tma_store_commit();
       if (next_load < chunks) {
         tma_store_wait_read<1>();   // the stage about to be refilled was last read by the previous group
         issue_load(next_load++);
       }
     }
-    tma_store_wait_all<0>();        // the whole tile has been written on every destination
+    tma_store_wait_all<0>();        // the whole tile has been written on the destination
     fence_proxy_async_all();
     __threadfence_system();
-    for (int d = 0; d < f.tp; ++d)
-      if (d != f.rank) st_release_sys(f.flag_ptrs[d] + (size_t)f.rank * f.flags_per_src + t, f.epoch);
+    st_release_sys(f.flag_ptrs[dest] + (size_t)f.rank * f.flags_per_src + t, f.epoch);
   }
 }
 

@@ -72,6 +72,30 @@ GLU_ACTIVATIONS = {
 }
 
 
+class _BiasGelu(torch.autograd.Function):
+    """tanh-approximated GeLU of ``x + bias`` with its analytic backward (one fused elementwise pass each way).
+    Parity: llm/models/mg_models/base_modules/layers/fused_bias_gelu.py:32-64 (unused by the Llama family)."""
+
+    @staticmethod
+    def forward(ctx, x, bias):
+        ctx.save_for_backward(x, bias)
+        y = (x + bias).float()
+        return (y * 0.5 * (1.0 + torch.tanh(0.79788456 * y * (1 + 0.044715 * y * y)))).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, bias = ctx.saved_tensors
+        y = (x + bias).float()
+        t = torch.tanh(0.79788456 * y * (1 + 0.044715 * y * y))
+        ff = 0.5 * y * ((1 - t * t) * (0.79788456 + 0.1070322243 * y * y)) + 0.5 * (1 + t)
+        gx = (ff * g.float()).to(x.dtype)
+        return gx, gx.reshape(-1, bias.shape[-1]).sum(0).to(bias.dtype) if bias.dim() == 1 else gx
+
+
+def bias_gelu(x, bias):
+    return _BiasGelu.apply(x, bias)
+
+
 def linear(x, w, bias=None):
     return F.linear(x, w, bias)
 

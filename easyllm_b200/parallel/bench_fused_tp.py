@@ -4,7 +4,7 @@
         -m easyllm_b200.parallel.bench_fused_tp [--model 7b] [--iters 20] [--json out.json]
 
 Per shape: median over iterations of the CUDA-event time, maximum over ranks; an L2 flush
-between iterations.  The roofline of a fused kernel is the slower of FLOPs at the measured
+between iterations; a short device-side sleep precedes the first event so host launch work is not timed.  The roofline of a fused kernel is the slower of FLOPs at the measured
 bf16 GEMM peak and the bytes that must cross NVLink at 770 GB/s per direction per GPU.
 """
 from __future__ import annotations
@@ -46,6 +46,9 @@ def timed(fn, iters, group):
         flush.zero_()
         dist.barrier(group=group)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # keep the device busy while the host prepares the launch (tensor maps, allocations), so the interval
+        # between the two events is device time of the kernels only
+        torch.cuda._sleep(400000)
         a.record()
         fn()
         b.record()
