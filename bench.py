@@ -45,7 +45,8 @@ MODELS = {
     # BASELINE config shapes beyond the headline: Qwen-14B (QKV bias, 152k vocabulary) and the Llama-2-70B layer
     # shape truncated to 40 layers (GQA 64/8)
     "qwen_14b": dict(num_layers=40, hidden_size=5120, num_attention_heads=40, num_kv_attention_heads=40,
-                     intermediate_size=13696, vocab_size=152064, attention_qkv_bias=True),
+                     intermediate_size=13696, vocab_size=152064,
+                     transformer_layer_params={"attention_qkv_bias": True}),
     "llama2_70b_40l": dict(num_layers=40, hidden_size=8192, num_attention_heads=64, num_kv_attention_heads=8,
                            intermediate_size=28672),
     "dev_1b": dict(num_layers=8, hidden_size=2048, num_attention_heads=16, num_kv_attention_heads=16,

@@ -72,12 +72,14 @@ def bench_gemm(iters):
             lib = lambda: torch.matmul(a.t(), b)                               # noqa: E731
         fl = 2.0 * M * N * K
         t_m, t_l = timed(mine, iters), timed(lib, iters)
-        if cu.has_symbol("ell_gemm_set_tail_split"):       # A/B of the half-width tail tiles, same process
-            cu.lib().ell_gemm_set_tail_split(0)
-            t_ns = timed(mine, iters)
-            cu.lib().ell_gemm_set_tail_split(1)
-            t_m2 = timed(mine, iters)
-            print(f"    tail split on {t_m:.4f} / {t_m2:.4f} ms, off {t_ns:.4f} ms", flush=True)
+        if os.environ.get("ELL_BENCH_SWEEP") and cu.has_symbol("ell_gemm_set_prefetch"):
+            # same-process sweep of the producer's L2 prefetch distance (k-blocks); the default is restored after
+            res = []
+            for d in (0, 4, 8, 16):
+                cu.lib().ell_gemm_set_prefetch(d)
+                res.append(f"{d}: {timed(mine, iters):.4f}")
+            cu.lib().ell_gemm_set_prefetch(0)
+            print("    L2 prefetch distance -> ms  " + "  ".join(res), flush=True)
         rows.append({"name": name, "M": M, "N": N, "K": K, "layout": lay, "ms": t_m, "tflops": fl / t_m / 1e9,
                      "frac_of_peak": fl / t_m / 1e9 / _PEAKS["bf16_tflops"], "cublas_ms": t_l,
                      "cublas_tflops": fl / t_l / 1e9, "vs_cublas": t_l / t_m})

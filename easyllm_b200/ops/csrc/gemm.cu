@@ -75,6 +75,7 @@ struct FuseArgs {
   long long ce_vocab_start;
   int ce_valid;
   int no_tail_split;                     // plain launches: 1 disables the half-width tail tiles
+  int prefetch_kb;                       // L2 prefetch distance of the producer in k-blocks (0 = off)
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -470,6 +471,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int i = 0; i < BN / 64; ++i)
               if (i * 64 < u.bn) tma_load_2d(b_dst + i * (64 * kBK * 2), &tmB, &sh->full[stage], n0 + i * 64, kb * kBK);
           }
+          // optional L2 prefetch of the k-block `prefetch_kb` ahead (off by default: on B200 it slowed every shape,
+          // the CTAs that share a tile each re-request it)
+          if (FUSE != kFuseAG && fuse.prefetch_kb > 0 && kb + fuse.prefetch_kb < num_kb) {
+            const int kp = (kb + fuse.prefetch_kb) * kBK;
+            if (!A_MN) {
+              tma_prefetch_l2_2d(a_map, kp, a_row);
+            } else {
+#pragma unroll
+              for (int i = 0; i < kBM / 64; ++i) tma_prefetch_l2_2d(&tmA, m0 + i * 64, kp);
+            }
+            if (!B_MN) {
+              tma_prefetch_l2_2d(b_map, kp, n0);
+            } else {
+#pragma unroll
+              for (int i = 0; i < BN / 64; ++i)
+                if (i * 64 < u.bn) tma_prefetch_l2_2d(&tmB, n0 + i * 64, kp);
+            }
+          }
           if (++stage == Cfg::kStages) {
             stage = 0;
             phase ^= 1;
@@ -808,6 +827,10 @@ static int sm_count() {
 using namespace ell;
 
 static int g_no_tail_split = 0;
+static int g_prefetch_kb = 0;   // measured on B200: distances 4-16 cost 15-40 % (every CTA re-requests shared tiles)
+// Tuning switch: L2 prefetch distance of the GEMM producer in 64-element k-blocks (0 disables it).
+ELL_API void ell_gemm_set_prefetch(int k_blocks) { g_prefetch_kb = k_blocks < 0 ? 0 : k_blocks; }
+
 // Tuning switch: 0 (default) cuts the tiles of an under-filled last wave in two, 1 keeps whole tiles.
 ELL_API void ell_gemm_set_tail_split(int enabled) { g_no_tail_split = enabled ? 0 : 1; }
 
@@ -839,6 +862,7 @@ ELL_API int ell_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   const int ctas = sm_count();
   FuseArgs Cf{};
   Cf.no_tail_split = g_no_tail_split;
+  Cf.prefetch_kb = g_prefetch_kb;
   const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(bias);
   // second B map with a box of BN/2 rows: used by the half-width tiles of a split tail wave
   CUtensorMap tBh = tB;
@@ -884,6 +908,7 @@ ELL_API int ell_gemm_ce(const void* X, const void* W, void* logits, const long l
   f.ce_part = part;
   f.ce_vocab_start = vocab_start;
   f.ce_valid = valid_cols < N ? valid_cols : N;
+  f.prefetch_kb = g_prefetch_kb;
   return launch_gemm<256, false, false, kOutBf16CE, false>(tA, tB, tC, f, nullptr, M, N, K, N, err, sm_count(), stream);
 }
 
@@ -899,6 +924,7 @@ static void fill_fuse(FuseArgs& f, int rank, int tp, int n_comm, int rows_per_ra
   }
   f.counter = (unsigned int*)counter;
   f.queue = f.counter + 1;
+  f.prefetch_kb = g_prefetch_kb;
 }
 
 // All-gather -> GEMM.  out[tp*rows_per_rank, N] = gather(x_local)[.., K] · W[N, K]^T (+ bias), or with

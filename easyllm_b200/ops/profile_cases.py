@@ -2,7 +2,7 @@
 
     python -m easyllm_b200.ops.profile_cases <case> [--iters 6]
 
-Cases: gemm_nt, gemm_dgrad, gemm_wgrad, gemm_ag, gemm_rs, flash_fwd, flash_bwd, rmsnorm_fwd, rmsnorm_bwd, swiglu, rope, adam, ce.
+Cases: gemm_nt, gemm_nt_n4096, gemm_dgrad, gemm_wgrad, gemm_ag, gemm_rs, flash_fwd, flash_bwd, rmsnorm_fwd, rmsnorm_bwd, swiglu, rope, adam, ce.
 Inputs are larger than L2 (126 MB) where the op is memory-bound but hold well under a few GB,
 so a full-section profiler capture of 1-3 launches ends by itself in a minute or two.
 """
@@ -25,6 +25,9 @@ def main():
     c = a.case
     if c == "gemm_nt":
         x = torch.randn(4096, 4096, **bf); w = torch.randn(12288, 4096, **bf)
+        fn = lambda: cu.gemm(x, w)                                                   # noqa: E731
+    elif c == "gemm_nt_n4096":      # few output tiles, long K: the o_proj / down_proj forward class
+        x = torch.randn(4096, 11008, **bf); w = torch.randn(4096, 11008, **bf)
         fn = lambda: cu.gemm(x, w)                                                   # noqa: E731
     elif c == "gemm_dgrad":
         x = torch.randn(4096, 11008, **bf); w = torch.randn(11008, 4096, **bf)
