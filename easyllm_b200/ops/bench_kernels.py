@@ -72,7 +72,16 @@ def bench_gemm(iters):
             lib = lambda: torch.matmul(a.t(), b)                               # noqa: E731
         fl = 2.0 * M * N * K
         t_m, t_l = timed(mine, iters), timed(lib, iters)
-        if os.environ.get("ELL_BENCH_SWEEP") and cu.has_symbol("ell_gemm_set_prefetch"):
+        if os.environ.get("ELL_BENCH_SWEEP"):
+            # tile width: 128x256 (default for N >= 256) against 128x128
+            if lay == "nt":
+                t128 = timed(lambda: cu.gemm(a, b, bn=128), iters)
+            elif lay == "nn":
+                t128 = timed(lambda: cu.gemm(a, b, b_mn=True, bn=128), iters)
+            else:
+                t128 = timed(lambda: cu.gemm(a, b, out=acc, a_mn=True, b_mn=True, out_mode=1, bn=128), iters)
+            print(f"    BN=256 {t_m:.4f} ms   BN=128 {t128:.4f} ms", flush=True)
+        if os.environ.get("ELL_BENCH_SWEEP_PREFETCH") and cu.has_symbol("ell_gemm_set_prefetch"):
             # same-process sweep of the producer's L2 prefetch distance (k-blocks); the default is restored after
             res = []
             for d in (0, 4, 8, 16):
