@@ -113,6 +113,8 @@ def main():
     ap.add_argument("--ops", default=None, choices=[None, "b200", "torch"])
     ap.add_argument("--recompute-layers", type=int, default=0, help="leading layers per stage to recompute")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--varlen", action="store_true",
+                    help="packed variable-length documents (lengths uniform in [256, seq]) with cu_seqlens")
     ap.add_argument("--no-fused-tp", action="store_true", help="use the NCCL + GEMM composition for TP linears")
     args = ap.parse_args()
 
@@ -169,15 +171,15 @@ def main():
     tokens_per_step = global_batch * args.seq
     dev = torch.device("cuda", torch.cuda.current_device())
 
-    host_iter = synthetic_batches(vocab, args.seq, 1, seed=0, pin=True)
+    host_iter = synthetic_batches(vocab, args.seq, 1, seed=0, pin=True, packed_varlen=args.varlen)
 
     def device_iter():
         # a fixed pool of device-resident micro-batches (distinct data per micro-batch of a step)
         pool = []
-        src = synthetic_batches(vocab, args.seq, 1, seed=1)
+        src = synthetic_batches(vocab, args.seq, 1, seed=1, packed_varlen=args.varlen)
         for _ in range(min(n_micro, 64)):
-            (tok, pos, _), (lab, msk) = next(src)
-            pool.append(((tok.to(dev), pos.to(dev), None), (lab.to(dev), msk.to(dev))))
+            inp, (lab, msk) = next(src)
+            pool.append((tuple(None if t is None else t.to(dev) for t in inp), (lab.to(dev), msk.to(dev))))
         i = 0
         while True:
             yield pool[i % len(pool)]
@@ -236,6 +238,7 @@ def main():
                "tokens_per_s_per_gpu": value / world, "loss": loss, "impl": "ours",
                "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq,
                           "parallelism": f"tp{g.tp}pp{g.pp}dp{g.dp}-zero{args.zero}" + ("-sp" if g.tp > 1 else ""),
+                          "packing": "variable-length documents, cu_seqlens" if args.varlen else "fixed length",
                           "micro_batch": 1, "grad_accum": n_micro, "optimizer": "fused Adam wd 0.1 clip 1.0",
                           "gemm": ops.get_gemm_backend(), "ops": ops.get_backend(), "fused_tp": fused_tp,
                           "recompute_layers": args.recompute_layers,
