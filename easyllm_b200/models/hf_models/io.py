@@ -1,4 +1,9 @@
-"""Family ↔ canonical (HF Llama names) state-dict and config translation for ``hf_models``."""
+"""Family ↔ canonical (HF Llama names) state-dict and config translation for ``hf_models``.
+
+The reference vendors one modeling file per family with its own parameter names
+(llm/models/hf_models/qwen/modeling_qwen.py ``c_attn`` / ``w1`` / ``w2``, internlm2/modeling_internlm2.py
+interleaved ``wqkv``, baichuan*/modeling_baichuan.py ``W_pack``); here one decoder serves all of them and this
+module maps their checkpoints in and out."""
 from __future__ import annotations
 
 import torch

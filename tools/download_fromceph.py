@@ -1,4 +1,5 @@
-"""Copy a checkpoint directory from remote (s3://, via ``.ceph`` pointer files) to local disk."""
+"""Copy a checkpoint directory from remote (s3://, via ``.ceph`` pointer files) to local disk
+(tools/download_fromceph.py of the reference; pointer-file convention of llm/utils/tools/petrel_helper.py:127-135)."""
 import argparse
 import os
 import sys

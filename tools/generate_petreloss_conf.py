@@ -1,4 +1,5 @@
-"""Write a ``petreloss.conf`` for the Petrel (Ceph) SDK from command-line credentials."""
+"""Write a ``petreloss.conf`` for the Petrel (Ceph) SDK from command-line credentials
+(tools/generate_petreloss_conf.py of the reference)."""
 import argparse
 import os
 
