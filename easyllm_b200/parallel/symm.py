@@ -45,6 +45,9 @@ class FusedTPWorkspace:
         self.max_tokens, self.hidden = max_tokens, hidden
         self.n_comm_ag = int(os.environ.get("ELL_NCOMM_AG", n_comm_ag))
         self.n_comm_rs = int(os.environ.get("ELL_NCOMM_RS", n_comm_rs))
+        if "ELL_RS_ORDER" in os.environ:              # tuning: "interleaved" (default) or "ring"
+            from ..ops import cuda as cu
+            cu.lib().ell_gemm_set_rs_order(c_int(1 if os.environ["ELL_RS_ORDER"] == "ring" else 0))
         dev = torch.device("cuda", torch.cuda.current_device())
         data_elems = max_tokens * hidden
         flag_words = 2 * (self.tp * _MAX_FLAGS + 64)             # AG set + RS set (flags + done)
