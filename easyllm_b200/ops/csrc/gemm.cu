@@ -837,6 +837,32 @@ static int sm_count() {
 
 using namespace ell;
 
+// Self-test of the bounded peer-flag wait used by the fused kernels: one thread waits for *flag >= want exactly as a
+// GEMM CTA waits for a peer's tile; if nothing raises the flag the wait gives up after its limit, the kernel records
+// kErrFlagWait in *err and returns normally (no trap, the context stays usable).  Also covers the mbarrier wait
+// (a barrier nobody arrives on) with the same limit.  *waited_ns receives the time spent in the two waits.
+__global__ void bounded_wait_selftest_kernel(const uint32_t* flag, uint32_t want, int* err,
+                                             unsigned long long* waited_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x != 0) return;
+  abort_flag = 0;
+  mbar_init(&bar, 1);
+  fence_barrier_init();
+  const unsigned long long t0 = globaltimer_ns();
+  const bool got_flag = wait_flag_ge(flag, want, &abort_flag);
+  if (!got_flag) atomicCAS(err, 0, kErrFlagWait);
+  const bool got_bar = got_flag ? true : mbar_wait(&bar, 0, &abort_flag);   // phase 0 never completes
+  if (!got_bar) atomicCAS(err, 0, kErrProducer);
+  *waited_ns = globaltimer_ns() - t0;
+}
+
+ELL_API int ell_bounded_wait_selftest(const void* flag, unsigned int want, int* err, unsigned long long* waited_ns,
+                                      cudaStream_t stream) {
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>((const uint32_t*)flag, want, err, waited_ns);
+  return launch_status();
+}
+
 static int g_no_tail_split = 0;
 static int g_rs_ring = 0;   // measured on 2 x B200: the ring order is not faster (o_proj 0.103 vs 0.101 ms, down 0.183 vs 0.177)
 // Tuning switch: tile order of the GEMM -> reduce-scatter kernel (1 ring order, 0 owners interleaved).

@@ -153,3 +153,33 @@ def test_embedding_fwd_bwd(cu):
     assert w2.grad is None
     torch.cuda.synchronize()
     cu.check_err_flag()
+
+
+def test_bounded_wait_gives_up_and_reports(cu):
+    """A wait on a flag that nothing sets (and on a barrier nobody arrives on) expires after its limit, the kernel
+    returns with an error code the host reads, and the context stays usable."""
+    import ctypes
+    L = cu.lib()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    waited = torch.zeros(1, dtype=torch.int64, device="cuda")
+    err = cu.err_flag()
+    rc = L.ell_bounded_wait_selftest(ctypes.c_void_p(flag.data_ptr()), ctypes.c_uint(1), ctypes.c_void_p(err.data_ptr()),
+                                     ctypes.c_void_p(waited.data_ptr()), cu._stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert 3.5e9 < int(waited) < 9e9, int(waited)          # two waits of 2 s each
+    with pytest.raises(cu.KernelError):
+        cu.check_err_flag()
+    cu.check_err_flag()                                      # the error word was cleared by the read
+    # the context is healthy: a tensor-core GEMM right after gives the right answer
+    a = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
+    torch.testing.assert_close(cu.gemm(a, b).float(), a.float() @ b.float().t(), rtol=2e-2, atol=2e-1)
+    # success path: the flag is already at the wanted epoch, nothing is reported and nothing is waited for
+    flag.fill_(7)
+    rc = L.ell_bounded_wait_selftest(ctypes.c_void_p(flag.data_ptr()), ctypes.c_uint(7), ctypes.c_void_p(err.data_ptr()),
+                                     ctypes.c_void_p(waited.data_ptr()), cu._stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(waited) < 1e8
+    cu.check_err_flag()
