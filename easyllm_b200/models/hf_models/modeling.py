@@ -142,8 +142,17 @@ class Attention(nn.Module):
         w, b = self._packed()
         qkv = ops.linear(x, w, b)
         pos = meta["position_ids"]
+        rope = None
         if self.rotary is not None:
             cos, sin = self.rotary.get(int(meta["max_position"]), x.device)
+            rope = (cos, sin, pos)
+        if cache is None and not (a.use_logn_attn and not self.training):
+            # training / full-sequence path: RoPE + attention on the packed projection, one packed gradient back
+            sl = self.slopes.to(x.device) if self.slopes is not None else None
+            o = ops.flash_attention_packed(qkv, hq, hk, d, meta["cu_seqlens"], meta["max_seqlen"], alibi_slopes=sl,
+                                           rope=rope)
+            return ops.linear(o, self.o_proj.weight, self.o_proj.bias)
+        if rope is not None:
             qkv = ops.rope_packed(qkv, cos, sin, pos, hq, hk, d)
         q = qkv[:, :hq * d].view(T, hq, d)
         k = qkv[:, hq * d:(hq + hk) * d].view(T, hk, d)

@@ -31,19 +31,6 @@ constexpr int kFaTileBytes = 128 * 128 * 2;  // 32 KiB: Q, K, V and P tiles are 
 constexpr int kFaSmemBytes = 7 * kFaTileBytes + 1024 + 512;   // Q x2, K x2, V, P x2
 constexpr float kFaRescaleThreshold = 8.0f;   // log2 units
 
-// 2^x on the FMA / integer pipes (no MUFU): round-to-nearest split x = n + f with the 1.5*2^23 trick, a cubic for
-// 2^f on [-0.5, 0.5] (relative error 6e-4, below bf16 resolution), n added into the exponent field.  Every fourth
-// exponential of a row takes this path, so the 16-per-clock MUFU unit and the FMA pipes work side by side.
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -126.f);
-  const float t = x + 12582912.f;
-  const float f = x - (t - 12582912.f);
-  float p = fmaf(f, 0.0555041f, 0.2402265f);
-  p = fmaf(p, f, 0.6931472f);
-  p = fmaf(p, f, 1.0f);
-  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
-}
-
 struct FaShared {
   uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], s_free[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
@@ -304,10 +291,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int c = 0; c < 16; ++c) {
         float p[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float x = fmaf(__uint_as_float(s[c * 8 + i]), scale_log2, neg_m);
-          p[i] = (i & 3) == 3 ? exp2_poly(x) : exp2f(x);
-        }
+        for (int i = 0; i < 8; ++i) p[i] = exp2f(fmaf(__uint_as_float(s[c * 8 + i]), scale_log2, neg_m));
         ps0 += p[0] + p[4]; ps1 += p[1] + p[5]; ps2 += p[2] + p[6]; ps3 += p[3] + p[7];
         *reinterpret_cast<bf16x8*>(p_row + (c >> 3) * (kFaTileBytes / 2) + (((c & 7) ^ sw) << 4)) = pack8(p);
       }

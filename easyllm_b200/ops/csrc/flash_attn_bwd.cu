@@ -34,18 +34,6 @@ constexpr int kFbTileBytes = 128 * 128 * 2;   // 32 KiB
 constexpr int kFbHalf = kFbTileBytes / 2;     // 16 KiB: one 64-column half of a tile
 constexpr int kFbSmemBytes = 7 * kFbTileBytes + 1024 + 256;   // K, V, Q, dO, P, dS, dQ staging
 
-// 2^x on the FMA / integer pipes (see flash_attn.cu): every fourth exponential of a row takes this path so the
-// 16-per-clock MUFU unit is not the only exponent source.
-__device__ __forceinline__ float fb_exp2_poly(float x) {
-  x = fmaxf(x, -126.f);
-  const float t = x + 12582912.f;
-  const float f = x - (t - 12582912.f);
-  float p = fmaf(f, 0.0555041f, 0.2402265f);
-  p = fmaf(p, f, 0.6931472f);
-  p = fmaf(p, f, 1.0f);
-  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
-}
-
 struct FbShared {
   uint64_t kv_full, q_full, do_full, q_empty, do_empty, s_full, dp_full, p_full, ds_full, dq_full, dq_drained;
   uint32_t tmem_base;
@@ -288,8 +276,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             float p[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-              const float x = fmaf(__uint_as_float(v[g8 * 8 + e]), scale_log2, -lse2);
-              p[e] = (e & 3) == 3 ? fb_exp2_poly(x) : exp2f(x);
+              p[e] = exp2f(fmaf(__uint_as_float(v[g8 * 8 + e]), scale_log2, -lse2));
               if (need_mask) {
                 const int kidx = k0 + col_base + c * 32 + g8 * 8 + e;
                 if (kidx > row || kidx < my_start || !row_valid) p[e] = 0.f;
