@@ -130,17 +130,12 @@ class Attention(nn.Module):
             if a.position == "rope" else None
         self.slopes = torch.tensor(alibi_slopes(hq), dtype=torch.float32) if a.position == "alibi" else None
 
-    def _packed(self):
-        w = torch.cat((self.q_proj.weight, self.k_proj.weight, self.v_proj.weight), 0)
-        b = torch.cat((self.q_proj.bias, self.k_proj.bias, self.v_proj.bias), 0) if self.a.qkv_bias else None
-        return w, b
-
     def forward(self, x, meta, cache=None):
         a = self.a
         d, hq, hk = a.head_dim, a.num_attention_heads, a.kv_heads
         T = x.shape[0]
-        w, b = self._packed()
-        qkv = ops.linear(x, w, b)
+        qkv = ops.linear_parts(x, (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight),
+                               (self.q_proj.bias, self.k_proj.bias, self.v_proj.bias) if a.qkv_bias else None)
         pos = meta["position_ids"]
         rope = None
         if self.rotary is not None:
@@ -214,7 +209,7 @@ class MLP(nn.Module):
         self.down_proj = nn.Linear(a.intermediate_size, a.hidden_size, bias=False, dtype=dtype)
 
     def forward(self, x):
-        gu = ops.linear(x, torch.cat((self.gate_proj.weight, self.up_proj.weight), 0))
+        gu = ops.linear_parts(x, (self.gate_proj.weight, self.up_proj.weight))
         return ops.linear(ops.glu(gu, "silu"), self.down_proj.weight)
 
 

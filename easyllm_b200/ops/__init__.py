@@ -199,6 +199,70 @@ def linear(x, w, bias=None):
     return F.linear(x, w, bias)
 
 
+def _adjacent_alias(tensors):
+    """One ``[sum(rows), cols]`` tensor aliasing ``tensors`` when they sit back to back in one storage (as the
+    parameters of a module do after the optimizer moved them into its flat buffer), else None."""
+    t0 = tensors[0]
+    if not all(t.is_contiguous() and t.dim() == 2 and t.shape[1] == t0.shape[1] and t.dtype == t0.dtype for t in tensors):
+        return None
+    ptr, base = t0.data_ptr(), t0.untyped_storage().data_ptr()
+    for t in tensors:
+        # adjacent addresses are not enough: separate allocations can be neighbours in the caching allocator
+        if t.data_ptr() != ptr or t.untyped_storage().data_ptr() != base:
+            return None
+        ptr += t.numel() * t.element_size()
+    rows = sum(t.shape[0] for t in tensors)
+    return torch.as_strided(t0, (rows, t0.shape[1]), (t0.shape[1], 1))
+
+
+class _LinearParts(torch.autograd.Function):
+    """``x · [W_1; W_2; ...]ᵀ`` for projections stored as separate parameters (q/k/v, gate/up of the HF-named
+    modules).  When the parameters (and their fp32 ``main_grad`` views) are adjacent in memory the fused weight is
+    an alias — nothing is concatenated, and the wgrad GEMM accumulates into the fused ``main_grad`` in one call."""
+
+    @staticmethod
+    def forward(ctx, x, bias, *weights):
+        alias = _adjacent_alias([w.detach() for w in weights])
+        W = alias if alias is not None else torch.cat([w.detach() for w in weights], 0)
+        ctx.save_for_backward(x, W)
+        ctx.wrefs = weights
+        ctx.has_bias = bias is not None
+        return matmul_nt(x, W, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, W = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = matmul_nn(dy, W) if ctx.needs_input_grad[0] else None
+        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias and ctx.needs_input_grad[1] else None
+        ws = ctx.wrefs
+        if not any(ctx.needs_input_grad[2:]):
+            return (dx, db) + (None,) * len(ws)
+        mgs = [getattr(w, "main_grad", None) for w in ws]
+        if all(m is not None for m in mgs):
+            fused = _adjacent_alias(mgs)
+            if fused is not None:
+                matmul_tn_accum(dy, x, fused)
+            else:
+                r0 = 0
+                for w, m in zip(ws, mgs):
+                    matmul_tn_accum(dy[:, r0:r0 + w.shape[0]].contiguous(), x, m)
+                    r0 += w.shape[0]
+            return (dx, db) + (None,) * len(ws)
+        dW = matmul_tn_accum(dy, x).to(W.dtype)
+        return (dx, db) + tuple(dW.split([w.shape[0] for w in ws], 0))
+
+
+def linear_parts(x, weights, biases=None):
+    """``x · concat(weights)ᵀ (+ concat(biases))`` without materialising the concatenation when avoidable."""
+    bias = None
+    if biases is not None and all(b is not None for b in biases):
+        bias = torch.cat(list(biases), 0)
+    if _kern(x) and x.dim() == 2:
+        return _LinearParts.apply(x.contiguous(), bias, *weights)
+    return F.linear(x, torch.cat(list(weights), 0), bias)
+
+
 # ---------------------------------------------------------------------------------------------
 # Vocab-parallel embedding lookup (partial: rows of ids owned by other ranks are zero)
 # ---------------------------------------------------------------------------------------------

@@ -82,3 +82,21 @@ def test_hf_style_model_kernel_path_matches_library_path():
         for n, g_ref in res["torch"][1].items():
             g_k = res["b200"][1][n]
             assert (g_ref - g_k).abs().max().item() / (g_ref.abs().max().item() + 1e-6) < 8e-2, (fam, n)
+        # once the optimizer has moved the parameters into its flat buffer, q/k/v (and gate/up) are adjacent:
+        # the fused projection aliases them and the wgrad GEMM accumulates into the adjacent fp32 main_grad views
+        from easyllm_b200.optim import ZeroOptimizer
+        opt = ZeroOptimizer(m.named_parameters(), lr=1e-4, stage=0)
+        att = m.model.layers[0].self_attn if hasattr(m, "model") else None
+        if att is not None:
+            assert ops._adjacent_alias([att.q_proj.weight.detach(), att.k_proj.weight.detach(),
+                                        att.v_proj.weight.detach()]) is not None
+            assert ops._adjacent_alias([att.q_proj.weight.main_grad, att.k_proj.weight.main_grad,
+                                        att.v_proj.weight.main_grad]) is not None
+        opt.zero_grad()
+        m(input_ids=ids, labels=ids)["loss"].backward()
+        opt.accumulate_grads()
+        torch.cuda.synchronize()
+        cu.check_err_flag()
+        for n, p in m.named_parameters():
+            g_ref = res["torch"][1][n]
+            assert (g_ref - p.main_grad.float()).abs().max().item() / (g_ref.abs().max().item() + 1e-6) < 8e-2, (fam, n)

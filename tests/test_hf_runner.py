@@ -97,3 +97,33 @@ def test_alibi_matches_cached_decode_and_lora_merge():
         before = m(ids)["logits"]
         after = merge_and_unload(m)(ids)["logits"]
     assert torch.allclose(before, after, atol=1e-4)
+
+
+def test_fused_projection_aliases_adjacent_parameters():
+    """q/k/v stored as separate (HF-named) parameters: once the optimizer has packed them into its flat buffer the
+    fused projection aliases them instead of concatenating, and wgrad lands in the adjacent fp32 main_grad views."""
+    from easyllm_b200 import ops
+    from easyllm_b200.models.hf_models import CausalLM, HFArch
+    from easyllm_b200.optim import ZeroOptimizer
+    torch.manual_seed(0)
+    a = HFArch(family="qwen", vocab_size=200, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+               num_attention_heads=4, qkv_bias=True)
+    m = CausalLM(a).train()
+    att = m.model.layers[0].self_attn
+    ws = (att.q_proj.weight, att.k_proj.weight, att.v_proj.weight)
+    assert ops._adjacent_alias([w.detach() for w in ws]) is None          # separately allocated
+    x = torch.randn(8, 64, requires_grad=True)
+    y0 = ops._LinearParts.apply(x, None, *ws)
+    y0.sum().backward()
+    g0 = [w.grad.clone() for w in ws]
+    dx0 = x.grad.clone()
+    opt = ZeroOptimizer(m.named_parameters(), lr=1e-4, stage=0)
+    assert ops._adjacent_alias([w.detach() for w in ws]) is not None
+    assert ops._adjacent_alias([w.main_grad for w in ws]) is not None
+    opt.zero_grad()
+    x.grad = None
+    y1 = ops._LinearParts.apply(x, None, *ws)
+    y1.sum().backward()
+    assert torch.allclose(y0, y1, atol=1e-6) and torch.allclose(dx0, x.grad, atol=1e-6)
+    for w, g in zip(ws, g0):
+        assert w.grad is None and torch.allclose(w.main_grad, g, atol=1e-5)
