@@ -113,6 +113,8 @@ def main():
     ap.add_argument("--ops", default=None, choices=[None, "b200", "torch"])
     ap.add_argument("--recompute-layers", type=int, default=0, help="leading layers per stage to recompute")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--runner", default="megatron", choices=["megatron", "hf"],
+                    help="megatron: 3D-parallel LlamaModelPipe + PipelineEngine; hf: HF-style decoder + ZeRO data-parallel engine")
     ap.add_argument("--varlen", action="store_true",
                     help="packed variable-length documents (lengths uniform in [256, seq]) with cu_seqlens")
     ap.add_argument("--no-fused-tp", action="store_true", help="use the NCCL + GEMM composition for TP linears")
@@ -155,8 +157,21 @@ def main():
     dc = None
     if args.recompute_layers:
         dc = {"enabled": True, "size_map": {1 << 30: args.recompute_layers}}
-    model = llama_custom(vocab_size=vocab, seq_length=args.seq, bf16=True, sequence_parallel=g.tp > 1,
-                         checkpoint_activations=False, dynamic_checkpoint=dc, pp_partition_method="parameters", **shape)
+    if args.runner == "hf":
+        if g.tp > 1 or g.pp > 1:
+            raise SystemExit("--runner hf is data-parallel only: pass --tp 1 --pp 1")
+        from easyllm_b200.models.hf_models import CausalLM, HFArch
+        arch = HFArch(family="qwen" if (shape.get("transformer_layer_params") or {}).get("attention_qkv_bias") else "llama",
+                      vocab_size=vocab, hidden_size=shape["hidden_size"], intermediate_size=shape["intermediate_size"],
+                      num_hidden_layers=shape["num_layers"], num_attention_heads=shape["num_attention_heads"],
+                      num_key_value_heads=shape["num_kv_attention_heads"], max_position_embeddings=args.seq,
+                      qkv_bias=bool((shape.get("transformer_layer_params") or {}).get("attention_qkv_bias")))
+        with torch.device(torch.device("cuda", torch.cuda.current_device())):
+            model = CausalLM(arch, dtype=torch.bfloat16).train()
+    else:
+        model = llama_custom(vocab_size=vocab, seq_length=args.seq, bf16=True, sequence_parallel=g.tp > 1,
+                             checkpoint_activations=False, dynamic_checkpoint=dc, pp_partition_method="parameters",
+                             **shape)
     fused_tp = False
     if g.tp > 1 and not args.no_fused_tp and ops.get_backend() == "b200":
         from easyllm_b200.parallel import symm
@@ -166,10 +181,32 @@ def main():
                         stage=args.zero, grad_clip=1.0)
     n_micro = args.seqs_per_gpu * g.tp * g.pp          # per DP rank: global / dp
     global_batch = args.seqs_per_gpu * world
-    eng = PipelineEngine(model, opt, None, {"train_micro_batch_size_per_gpu": 1,
-                                            "gradient_accumulation_steps": n_micro, "bf16": {"enabled": True}})
     tokens_per_step = global_batch * args.seq
     dev = torch.device("cuda", torch.cuda.current_device())
+    if args.runner == "hf":
+        from easyllm_b200.engine.zero_dp import ZeroDPEngine
+        dp_eng = ZeroDPEngine(model, opt, None, {"gradient_accumulation_steps": n_micro, "bf16": {"enabled": True}})
+
+        class _HFSteps:
+            """One optimizer step of the HF runner's loop (model call, engine.backward, engine.step per micro-batch)."""
+
+            def train_batch(self, it):
+                total = None
+                for _ in range(n_micro):
+                    inp, _ = next(it)
+                    tok = inp[0].to(dev, non_blocking=True)
+                    pos = inp[1].to(dev, non_blocking=True)
+                    cu = inp[3].to(dev, non_blocking=True) if len(inp) > 3 and inp[3] is not None else None
+                    # HF convention: the model shifts the labels itself
+                    out = model(input_ids=tok, labels=tok, position_ids=pos, cu_seqlens=cu)
+                    dp_eng.backward(out["loss"])
+                    dp_eng.step()
+                    total = out["loss"].detach() if total is None else total + out["loss"].detach()
+                return total / n_micro
+        eng = _HFSteps()
+    else:
+        eng = PipelineEngine(model, opt, None, {"train_micro_batch_size_per_gpu": 1,
+                                                "gradient_accumulation_steps": n_micro, "bf16": {"enabled": True}})
 
     host_iter = synthetic_batches(vocab, args.seq, 1, seed=0, pin=True, packed_varlen=args.varlen)
 
@@ -239,6 +276,7 @@ def main():
                "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq,
                           "parallelism": f"tp{g.tp}pp{g.pp}dp{g.dp}-zero{args.zero}" + ("-sp" if g.tp > 1 else ""),
                           "packing": "variable-length documents, cu_seqlens" if args.varlen else "fixed length",
+                          "runner": args.runner,
                           "micro_batch": 1, "grad_accum": n_micro, "optimizer": "fused Adam wd 0.1 clip 1.0",
                           "gemm": ops.get_gemm_backend(), "ops": ops.get_backend(), "fused_tp": fused_tp,
                           "recompute_layers": args.recompute_layers,

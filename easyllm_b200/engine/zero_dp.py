@@ -4,10 +4,9 @@ What the HF runner of the reference gets from ``deepspeed.initialize`` with ZeRO
 DDP + GradScaler without it (llm/runners/hf_runner.py:150-170, 238-278): ``backward(loss)``
 accumulates, ``step()`` acts on accumulation boundaries.  Parameters live in the flat buffers
 of ``ZeroOptimizer`` over the whole world as the DP group: gradients are reduce-scattered,
-the fp32 Adam shard is updated by the fused kernel and parameters are all-gathered.  With
-``stage: 2`` the reduce-scatter is issued bucket by bucket on a side stream while the last
-micro-batch's backward is still running (buckets complete from the end of the buffer, the
-order in which autograd produces gradients).
+the fp32 Adam shard is updated by the fused kernel and parameters are all-gathered (on GPUs by
+the two fused kernels of ``ops/csrc/zero_fused.cu``).  Stages 1 and 2 share this path: gradients
+are accumulated in fp32 over the micro-batches and reduced once per optimizer step.
 """
 from __future__ import annotations
 
