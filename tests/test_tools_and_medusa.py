@@ -99,3 +99,109 @@ def test_medusa_tree_decoding_matches_greedy():
     assert torch.isfinite(mm.compute_loss(logits, labels))
     report = mm.compute_loss(logits, labels, return_dict=True)._d
     assert {"medusa0.loss", "medusa2_top5.accuracy"} <= set(report)
+
+
+def test_convert_colossalai_shards_to_hf(tmp_path):
+    """pp=2 x tp=2 ColossalAI-style shards (stage-local layer numbers, interleaved rotary layout) round-trip to HF."""
+    tool = _tool("convert_colossalai_hf")
+    torch.manual_seed(1)
+    h, ffn, heads, vocab, layers = 32, 48, 4, 40, 2
+    hf = {"model.embed_tokens.weight": torch.randn(vocab, h), "model.norm.weight": torch.randn(h),
+          "lm_head.weight": torch.randn(vocab, h)}
+    for li in range(layers):
+        p = f"model.layers.{li}."
+        for n, shape in (("self_attn.q_proj", (h, h)), ("self_attn.k_proj", (h, h)), ("self_attn.v_proj", (h, h)),
+                         ("self_attn.o_proj", (h, h)), ("mlp.gate_proj", (ffn, h)), ("mlp.up_proj", (ffn, h)),
+                         ("mlp.down_proj", (h, ffn))):
+            hf[p + n + ".weight"] = torch.randn(*shape)
+        hf[p + "input_layernorm.weight"] = torch.randn(h)
+        hf[p + "post_attention_layernorm.weight"] = torch.randn(h)
+
+    def interleave(w):            # HF half-rotation layout -> interleaved pairs (the source layout)
+        return w.view(heads, 2, h // heads // 2, h).transpose(1, 2).reshape(h, h)
+
+    back = {v: k for k, v in tool.NAME.items()}
+    src = tmp_path / "shards"
+    os.makedirs(src)
+    for pp in range(2):               # one layer per stage, numbered from 0 inside the stage
+        full = {}
+        for n, sub in back.items():
+            w = hf[f"model.layers.{pp}.{n}.weight"]
+            if n in ("self_attn.q_proj", "self_attn.k_proj"):
+                w = interleave(w)
+            full[f"model.layers.0.{sub}.weight"] = w
+        if pp == 0:
+            full["model.tok_embeddings.weight"] = hf["model.embed_tokens.weight"]
+        else:
+            full["model.norm.weight"] = hf["model.norm.weight"]
+            full["model.output.weight"] = hf["lm_head.weight"]
+        for tp in range(2):
+            shard = {}
+            for k, w in full.items():
+                if any(c in k for c in tool.COL):
+                    shard[k] = w.chunk(2, 0)[tp].clone()
+                elif any(c in k for c in tool.ROW):
+                    shard[k] = w.chunk(2, 1)[tp].clone()
+                else:
+                    shard[k] = w.clone()
+            torch.save(shard, src / f"model_tp{tp}_pp{pp}.pt")
+    out = tmp_path / "hf"
+    tool.main(["--input_dir", str(src), "--output_dir", str(out), "--n_heads", str(heads), "--dim", str(h)])
+    got = torch.load(out / "pytorch_model.bin")
+    assert set(got) == set(hf)
+    for k in hf:
+        torch.testing.assert_close(got[k], hf[k], msg=k)
+    cfg = json.load(open(out / "config.json"))
+    assert cfg["num_hidden_layers"] == layers and cfg["intermediate_size"] == ffn and cfg["vocab_size"] == vocab
+
+
+def test_generate_petreloss_conf(tmp_path):
+    tool = _tool("generate_petreloss_conf")
+    out = tmp_path / "petreloss.conf"
+    tool.main(["--access_key", "AK", "--secret_key", "SK", "--host_base", "http://ceph:80", "--cluster", "c1",
+               "--out", str(out)])
+    import configparser
+    cp = configparser.ConfigParser()
+    cp.read(out)
+    assert cp["DEFAULT"]["default_cluster"] == "c1" and cp["c1"]["access_key"] == "AK" and cp["c1"]["host_base"].endswith(":80")
+
+
+def test_build_index_mmap_from_config(tmp_path):
+    """The offline cache builder reads the dataset block of a training YAML and leaves a reusable .bin/.idx cache."""
+    tool = _tool("build_index_mmap")
+    lines = [json.dumps({"text": "doc %d " % i + "w" * (5 + i % 7)}) for i in range(40)]
+    jf = tmp_path / "d.jsonl"
+    jf.write_text("\n".join(lines) + "\n")
+    cfg = f"""
+tokenizer:
+  type: SimpleTokenizer
+  kwargs: {{}}
+data:
+  train:
+    dataset:
+      type: mmap_index_json
+      kwargs:
+        data_root: {tmp_path}
+        seed: 1
+        total_samples: 20
+        max_seq_length: 32
+        json_file: {jf}
+        cache_worker: 2
+        transformer:
+          - type: sense_tokenization
+            kwargs: {{max_seq_length: 4096, parser_type: base}}
+"""
+    y = tmp_path / "cfg.yaml"
+    y.write_text(cfg)
+    tool.main(["--config", str(y)])
+    cache = list((tmp_path / "train_data_cache").iterdir())
+    assert any(p.name.endswith(".bin") for p in cache) and any(p.name.endswith(".idx") for p in cache)
+    # a dataset built afterwards finds the cache (no rebuild: the .bin keeps its mtime)
+    from easyllm_b200.config import load_yaml
+    from easyllm_b200.data import build_dataset, build_tokenizer
+    c = load_yaml(str(y))
+    before = {p.name: p.stat().st_mtime_ns for p in cache}
+    ds = build_dataset(c["data"]["train"]["dataset"], build_tokenizer(c["tokenizer"]))
+    assert len(ds) >= 20 and ds[0]["input_ids"].shape[0] == 33
+    after = {p.name: p.stat().st_mtime_ns for p in (tmp_path / "train_data_cache").iterdir()}
+    assert all(after[k] == v for k, v in before.items() if k.endswith(".bin"))
