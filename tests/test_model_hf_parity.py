@@ -69,3 +69,34 @@ def test_gqa_and_packed_documents():
     b = hf(input_ids=tok[:, 40:]).logits
     ref = torch.cat((a, b), dim=1)
     assert torch.allclose(logits, ref, atol=2e-4, rtol=1e-4)
+
+
+def test_fp16_boundary_helpers():
+    from easyllm_b200.models.fp16_module import Float16Module, float16_to_fp32, fp32_to_float16
+    x = (torch.ones(2), [torch.ones(2, dtype=torch.int64), {"a": torch.ones(1)}], "s")
+    y = fp32_to_float16(x)
+    assert y[0].dtype == torch.bfloat16 and y[1][0].dtype == torch.int64 and y[1][1]["a"].dtype == torch.bfloat16 and y[2] == "s"
+    z = float16_to_fp32(y)
+    assert z[0].dtype == torch.float32 and z[1][0].dtype == torch.int64
+    m = Float16Module(torch.nn.Linear(4, 3), bf16=True)
+    out = m(torch.randn(5, 4))
+    assert out.dtype == torch.float32 and m.module.weight.dtype == torch.bfloat16
+    assert set(m.state_dict()) == {"weight", "bias"}
+
+
+def test_scale_mask_softmax_wrapper():
+    from easyllm_b200.models.fused_softmax import FusedScaleMaskSoftmax
+    torch.manual_seed(0)
+    s = torch.randn(2, 3, 5, 5)
+    sm = FusedScaleMaskSoftmax(attn_mask_type="causal", scale=0.5)
+    p = sm(s)
+    assert torch.allclose(p.sum(-1), torch.ones(2, 3, 5), atol=1e-6)
+    assert float(p[0, 0, 1, 2:].abs().max()) == 0.0                      # future positions carry no weight
+    ref = torch.softmax((s * 0.5).masked_fill(torch.ones(5, 5, dtype=torch.bool).triu(1), float("-inf")), -1)
+    assert torch.allclose(p, ref, atol=1e-6)
+    pad = torch.zeros(2, 1, 1, 5, dtype=torch.bool); pad[:, :, :, -1] = True
+    q = FusedScaleMaskSoftmax(attn_mask_type="padding", input_in_bf16=True)(s.bfloat16(), pad)
+    assert q.dtype == torch.bfloat16 and float(q[..., -1].float().max()) < 1e-3
+    # decoding step: one query row against a longer key axis sees every key
+    one = FusedScaleMaskSoftmax(attn_mask_type="causal")(torch.randn(1, 1, 1, 7))
+    assert float(one.min()) > 0
