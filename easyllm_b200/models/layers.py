@@ -288,7 +288,7 @@ class ParallelAttention(nn.Module):
             cos, sin = self.rotary.get(need, qkv.device)
             rope = (cos, sin, pos)
         nq, nk = self.hq * self.D, self.hk * self.D
-        if kv_cache is None:
+        if kv_cache is None and self.args.use_flash_attn:
             slopes = self.alibi.to(qkv.device) if self.alibi is not None else None
             o = ops.flash_attention_packed(qkv, self.hq, self.hk, self.D, meta.get("cu_seqlens"),
                                            meta.get("max_seqlen"), alibi_slopes=slopes, rope=rope)
@@ -309,8 +309,13 @@ class ParallelAttention(nn.Module):
                                       kv_cache.v[:, :p0 + S], p0).reshape(T, nq)
         else:
             slopes = self.alibi.to(q.device) if self.alibi is not None else None
-            o = ops.flash_attention(q, k, v, meta.get("cu_seqlens"), meta.get("max_seqlen"), causal=True,
-                                    alibi_slopes=slopes).reshape(T, nq)
+            if not self.args.use_flash_attn:
+                # ``use_flash_attn: False``: scores, fp32 masked softmax and the value product as separate ops
+                # (the reference's baddbmm + scale-mask-softmax + bmm path, transformer.py:492-592)
+                o = ref.attention_varlen(q, k, v, meta.get("cu_seqlens"), True, None, slopes).reshape(T, nq)
+            else:
+                o = ops.flash_attention(q, k, v, meta.get("cu_seqlens"), meta.get("max_seqlen"), causal=True,
+                                        alibi_slopes=slopes).reshape(T, nq)
         return self.o_proj(o)
 
 
