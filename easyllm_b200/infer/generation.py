@@ -173,7 +173,7 @@ def generate_samples_interactive(args, config, engine, tokenizer, force_eos_id=N
             continue
         ctx_t = torch.tensor(ctx if leader else [0] * n_ctx, dtype=torch.long, device=dev)
         if dist.is_initialized() and g.world > 1:
-            dist.all_reduce(ctx_t) if not leader or True else None   # only the leader holds non-zero ids
+            dist.all_reduce(ctx_t)        # only the leader holds non-zero ids: the sum is a broadcast
         out = gen.generate_once([ctx_t.tolist()], max_new_tokens=args.out_seq_length, temperature=args.temperature,
                                 top_k=args.top_k, top_p=args.top_p, greedy=args.greedy, eos_id=force_eos_id,
                                 recompute=getattr(args, "recompute", False))
