@@ -82,3 +82,41 @@ def test_interactive_loop_commands():
         return s
     gen.generate_samples_interactive(args, cfg, eng, tok, force_eos_id=None, input_fn=fake_input)
     assert seen[-1] == "quit" and len(seen) == 7
+
+
+def test_infer_logp_matches_log_softmax(tmp_path):
+    """``logp`` mode: per-token label log-probabilities written as jsonl equal a plain log-softmax gather."""
+    from easyllm_b200.data import build_tokenizer
+    from easyllm_b200.engine import PipelineEngine
+    from easyllm_b200.infer import generation as gen
+    from easyllm_b200.models import llama_custom
+    torch.manual_seed(0)
+    tok = build_tokenizer({"type": "SimpleTokenizer", "kwargs": {"vocab_size": 300}})
+    model = llama_custom(num_layers=1, hidden_size=32, num_attention_heads=2, intermediate_size=64, vocab_size=300,
+                         seq_length=16)
+    eng = PipelineEngine(model, None, None, {"train_micro_batch_size_per_gpu": 1})
+    g = torch.Generator().manual_seed(3)
+    batches = []
+    for _ in range(2):
+        ids = torch.randint(0, 300, (1, 17), generator=g)
+        labels = ids[:, 1:].clone()
+        labels[0, :3] = -100                                   # prompt tokens are ignored
+        batches.append({"input_ids": ids[:, :-1], "labels": labels})
+
+    def batch_fn(b):
+        t = b["input_ids"]
+        pos = torch.arange(t.shape[1]).unsqueeze(0)
+        return (t, pos, None), (b["labels"], (b["labels"] != -100).long())
+    out = tmp_path / "logp.jsonl"
+    gen.infer_logp(eng, tok, iter(batches), batch_fn, str(out), 2)
+    rows = [json.loads(l) for l in open(out)]
+    assert [r["id"] for r in rows] == [0, 1] and len(rows[0]["logp"]) == 16
+    with torch.no_grad():
+        for r, b in zip(rows, batches):
+            pos = torch.arange(16).unsqueeze(0)
+            logits = eng.forward_tokens(b["input_ids"], pos).float()
+            lp = torch.log_softmax(logits.view(16, -1), -1)
+            lab = b["labels"][0]
+            want = torch.where(lab >= 0, lp.gather(1, lab.clamp(min=0)[:, None]).squeeze(1), torch.zeros(16))
+            assert torch.allclose(torch.tensor(r["logp"]), want, atol=1e-4)
+            assert r["logp"][:3] == [0.0, 0.0, 0.0]
