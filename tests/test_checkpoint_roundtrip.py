@@ -95,3 +95,32 @@ def test_truncated_file_is_reported(tmp_path):
         assert "unreadable" in str(e)
     else:
         raise AssertionError("truncated checkpoint was accepted")
+
+
+def _save_pp2(rank, world, out_dir):
+    from easyllm_b200.data.synthetic import synthetic_batches
+    eng = _make_engine(pp=2, world=world)
+    it = synthetic_batches(32000, 64, 2, seed=0)
+    eng.train_batch(it)
+    eng.save_checkpoint(out_dir, tag="global_step1", client_state={"iteration": 1})
+    tok = torch.arange(0, 48).remainder(32000).view(1, 48) * 7 % 32000
+    with torch.no_grad():
+        out = eng.forward_tokens(tok, torch.arange(48).view(1, 48))      # logits on the last stage, None elsewhere
+    return None if out is None else out.detach().float()
+
+
+def test_checkpoint_written_with_pp2_loads_into_pp1(tmp_path):
+    """Layer files are indexed by the position in the layer list, not by stage: a checkpoint saved by a 2-stage
+    pipeline restores the weights of a single-process model (restart with another pipeline size)."""
+    out = str(tmp_path / "ds")
+    want = [r for r in run_ranks(2, _save_pp2, out) if r is not None][0]
+    names = sorted(os.listdir(os.path.join(out, "global_step1")))
+    assert {"layer_01-model_00-model_states.pt", "layer_03-model_00-model_states.pt", "layer_04-model_00-model_states.pt",
+            "layer_06-model_00-model_states.pt", "layer_07-model_00-model_states.pt"} <= set(names)
+    eng = _make_engine(seed=9)                       # different init: the weights must come from the files
+    _, client = eng.load_checkpoint(out, load_module_only=True)
+    assert client["iteration"] == 1
+    tok = torch.arange(0, 48).remainder(32000).view(1, 48) * 7 % 32000
+    with torch.no_grad():
+        got = eng.module((tok, None, None), return_logits=True).float()
+    assert torch.allclose(got.view(-1), want.view(-1), atol=1e-5), (got.view(-1) - want.view(-1)).abs().max()
