@@ -124,3 +124,45 @@ def test_checkpoint_written_with_pp2_loads_into_pp1(tmp_path):
     with torch.no_grad():
         got = eng.module((tok, None, None), return_logits=True).float()
     assert torch.allclose(got.view(-1), want.view(-1), atol=1e-5), (got.view(-1) - want.view(-1)).abs().max()
+
+
+def _engine_dp(world, grad_accum, seed=0):
+    from easyllm_b200.parallel.grid import initialize_model_parallel
+    from easyllm_b200.parallel.rng import set_random_seed
+    from easyllm_b200.models import llama_custom
+    from easyllm_b200.optim import ZeroOptimizer, IterBaseAnnealingLR
+    from easyllm_b200.engine import PipelineEngine
+    if world > 1:
+        initialize_model_parallel(1, 1)
+    set_random_seed(seed + 1)
+    model = llama_custom(**TINY)
+    opt = ZeroOptimizer(model.named_parameters(), lr=1e-3, stage=1, weight_decay=0.1, grad_clip=1.0)
+    sched = IterBaseAnnealingLR(opt, max_lr=1e-3, min_lr=1e-5, decay_style="cosine", lr_warmup_iters=1,
+                                lr_decay_iters=10, global_batch_size=4)
+    return PipelineEngine(model, opt, sched, {"train_micro_batch_size_per_gpu": 2,
+                                              "gradient_accumulation_steps": grad_accum})
+
+
+def _train_dp2_save(rank, world, out_dir):
+    from easyllm_b200.data.synthetic import synthetic_batches
+    eng = _engine_dp(world, 1)
+    it = synthetic_batches(32000, 64, 2, seed=7)
+    for _ in range(2):
+        eng.train_batch(it)
+    eng.save_checkpoint(out_dir, client_state={"iteration": 2})
+    return float(eng.train_batch(it))
+
+
+def test_zero1_state_saved_with_dp2_resumes_on_one_rank(tmp_path):
+    """The ZeRO-1 optimizer shards of a 2-rank run are re-assembled by parameter name when the data-parallel size
+    changed: one rank with two accumulation steps continues with the same loss as the 2-rank run."""
+    from easyllm_b200.data.synthetic import synthetic_batches
+    out = str(tmp_path / "ds")
+    third = run_ranks(2, _train_dp2_save, out)
+    assert abs(third[0] - third[1]) < 1e-6
+    eng = _engine_dp(1, 2, seed=11)                   # different init: weights and Adam state come from the files
+    _, client = eng.load_checkpoint(out)
+    assert client["iteration"] == 2 and eng.optimizer.step_count == 2
+    it = synthetic_batches(32000, 64, 2, seed=7, start=4)      # 2 steps x 2 micro-batches of the global stream consumed
+    loss = float(eng.train_batch(it))
+    assert abs(loss - third[0]) < 2e-5, (loss, third)
