@@ -15,15 +15,12 @@ own masked mean, averaged over DP and broadcast from the last stage.
 """
 from __future__ import annotations
 
-import time
 from typing import Callable, Optional
 
 import torch
 import torch.distributed as dist
 
-from ..models.llama import StageIO
 from ..parallel.grid import get_grid
-from ..utils.log import default_logger as logger
 from .p2p import StageLink
 
 
@@ -63,8 +60,6 @@ class PipelineEngine:
         self.link = StageLink(self.dtype, dynamic=True) if self.g.pp > 1 else None
         self.total_loss = None
         self.fwd_outputs = []
-        self.timers = {"fwd": 0.0, "bwd": 0.0, "step": 0.0}
-        self.wall_clock_breakdown = bool(cfg.get("wall_clock_breakdown", False))
         self.nvtx = bool(cfg.get("nvtx", False)) and torch.cuda.is_available()
 
     # ---- contract surface -------------------------------------------------------------------

@@ -10,7 +10,6 @@ are accumulated in fp32 over the micro-batches and reduced once per optimizer st
 """
 from __future__ import annotations
 
-import torch
 import torch.distributed as dist
 
 from ..optim.zero import ZeroOptimizer

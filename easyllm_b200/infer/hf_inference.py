@@ -2,7 +2,6 @@
 chat with history, and sharded dataset evaluation with results gathered on rank 0."""
 from __future__ import annotations
 
-import json
 
 import torch
 import torch.distributed as dist

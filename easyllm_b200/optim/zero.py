@@ -22,8 +22,7 @@ the TP gradient all-reduce each act on one contiguous range.
 """
 from __future__ import annotations
 
-import math
-from typing import Iterable, List, Optional
+from typing import Iterable, List
 
 import torch
 import torch.distributed as dist
@@ -71,7 +70,7 @@ class ZeroOptimizer:
                  nan_policy="count"):
         g = get_grid()
         self.grid = g
-        self.stage = stage if g.dp > 1 or stage == 0 else stage
+        self.stage = stage
         self.dp, self.dp_rank, self.dp_group = g.dp, g.dp_rank, g.dp_group
         self.defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
         self.param_groups = [dict(self.defaults, name="all")]   # lr schedulers poke param_groups[i]['lr']

@@ -16,7 +16,7 @@ from __future__ import annotations
 import datetime
 import os
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import List, Optional
 
 import torch
 import torch.distributed as dist

@@ -8,7 +8,6 @@ created **gloo** side group (so no GPU memory or NCCL kernels are used for contr
 from __future__ import annotations
 
 import os
-import pickle
 
 import torch
 import torch.distributed as dist

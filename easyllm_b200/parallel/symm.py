@@ -21,7 +21,6 @@ row_parallel_linear.py:116-117).
 """
 from __future__ import annotations
 
-import ctypes
 import os
 from ctypes import c_int, c_uint, c_void_p
 

@@ -14,8 +14,6 @@ kernels when TP > 1 on GPUs), ``nan_policy`` (count | skip | abort), ``watchdog`
 """
 from __future__ import annotations
 
-import os
-import sys
 import time
 
 import torch
@@ -25,7 +23,7 @@ from ..ckpt.helper import load_checkpoint, save_checkpoint
 from ..config import load_yaml, merge_opts_into_cfg, parse_args
 from ..data import build_batch_pipe_fn, build_data_iterator, build_tokenizer
 from ..engine.pipeline import initialize as engine_initialize
-from ..models import build_model, get_layer_info
+from ..models import build_model
 from ..models.lora import log_trainable_params, set_train_params
 from ..optim import (build_learning_rate_scheduler, build_num_microbatches_calculator, build_optimizer,
                      get_train_iters)

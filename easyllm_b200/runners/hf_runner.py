@@ -24,8 +24,7 @@ from ..engine.zero_dp import ZeroDPEngine
 from ..optim import build_learning_rate_scheduler
 from ..optim.grad_scaler import ShardedGradScaler
 from ..optim.zero import ZeroOptimizer
-from ..parallel.grid import get_grid, initialize_distributed
-from ..utils.log import default_logger as logger
+from ..parallel.grid import initialize_distributed
 from . import hf_hooks  # noqa: F401
 from .hooks import build_hooks
 

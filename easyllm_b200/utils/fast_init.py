@@ -6,7 +6,6 @@ from __future__ import annotations
 
 import contextlib
 
-import torch
 import torch.nn as nn
 
 
