@@ -157,9 +157,12 @@ class QWenTokenizer:
         return ids
 
     def encode(self, text, add_special_tokens=True, allowed_special="all"):
+        """``allowed_special``: "all", or the set of special-token strings that may be recognised in ``text``;
+        markup outside that set is encoded as ordinary characters (an empty set for untrusted user text)."""
+        allowed = self.special if allowed_special == "all" else [t for t in self.special if t in allowed_special]
         ids, rest = [], text
         while rest:
-            hit = min(((rest.find(t), t) for t in self.special if t in rest), default=None)
+            hit = min(((rest.find(t), t) for t in allowed if t in rest), default=None)
             chunk, tok = (rest, None) if hit is None else (rest[:hit[0]], hit[1])
             for m in self.pat.findall(chunk):
                 ids += self._bpe(m.encode("utf-8"))

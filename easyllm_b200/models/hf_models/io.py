@@ -92,6 +92,7 @@ def export_config(arch):
                 "intermediate_size": 2 * a.intermediate_size, "num_hidden_layers": a.num_hidden_layers,
                 "num_attention_heads": a.num_attention_heads, "layer_norm_epsilon": a.rms_norm_eps,
                 "rotary_emb_base": a.rope_theta, "use_logn_attn": a.use_logn_attn, "seq_length": a.seq_length,
+                "use_cache_quantization": a.use_cache_quantization,
                 "use_dynamic_ntk": a.rope_dynamic_ntk_max_pos is not None,
                 "max_position_embeddings": a.max_position_embeddings}
     cfg = {"model_type": a.family, "vocab_size": a.vocab_size, "hidden_size": a.hidden_size,

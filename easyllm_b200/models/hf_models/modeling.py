@@ -48,6 +48,7 @@ class HFArch:
     position: str = "rope"                # rope | alibi
     norm_head: bool = False               # Baichuan2: rows of lm_head are L2-normalised
     use_logn_attn: bool = False           # Qwen inference-time log-n scaling of queries
+    use_cache_quantization: bool = False  # Qwen: keep the decode KV cache in uint8 (per-chunk scale / zero)
     seq_length: int = 2048                # Qwen: training length for log-n / NTK
     tie_word_embeddings: bool = False
     pad_token_id: Optional[int] = None
@@ -75,6 +76,7 @@ def arch_from_hf_config(cfg: dict, family: Optional[str] = None) -> HFArch:
         a.rms_norm_eps = g("layer_norm_epsilon", 1e-6)
         a.rope_theta = g("rotary_emb_base", 10000.0)
         a.qkv_bias, a.use_logn_attn, a.seq_length = True, g("use_logn_attn", False), g("seq_length", 2048)
+        a.use_cache_quantization = bool(g("use_cache_quantization", False))
         a.rope_dynamic_ntk_max_pos = a.seq_length if g("use_dynamic_ntk", False) else None
         a.max_position_embeddings = g("max_position_embeddings", 8192)
         return a
@@ -159,9 +161,16 @@ class Attention(nn.Module):
             B = meta["batch"]
             S = T // B
             p0 = cache["len"]
-            cache["k"][:, p0:p0 + S] = k.reshape(B, S, hk, d)
-            cache["v"][:, p0:p0 + S] = v.reshape(B, S, hk, d)
-            cache["len"] = p0 + S
+            cache_ref = cache
+            if "kq" in cache:                 # 8-bit cache: quantise the new chunk, attend over the dequantised prefix
+                cache["kq"].append(p0, k.reshape(B, S, hk, d))
+                cache["vq"].append(p0, v.reshape(B, S, hk, d))
+                cache = dict(cache, k=cache["kq"].read(p0 + S), v=cache["vq"].read(p0 + S))
+                cache_ref["len"] = p0 + S
+            else:
+                cache["k"][:, p0:p0 + S] = k.reshape(B, S, hk, d)
+                cache["v"][:, p0:p0 + S] = v.reshape(B, S, hk, d)
+                cache["len"] = p0 + S
             if meta.get("tree_mask") is not None:
                 o = _tree_cached(q.reshape(B, S, hq, d), cache["k"][:, :p0 + S], cache["v"][:, :p0 + S], p0,
                                  meta["tree_mask"])
@@ -332,18 +341,29 @@ class CausalLM(nn.Module):
 
     # ---- generation -----------------------------------------------------------------------------
     @torch.no_grad()
-    def generate(self, input_ids, attention_mask=None, max_new_tokens=64, do_sample=False, temperature=1.0, top_k=0,
-                 top_p=0.0, eos_token_id=None, repetition_penalty=1.0, num_beams=1, **_):
+    def _decode_steps(self, input_ids, max_new_tokens=64, do_sample=False, temperature=1.0, top_k=0, top_p=0.0,
+                      eos_token_id=None, repetition_penalty=1.0, stop_words_ids=None, **_):
+        """Greedy / sampled decoding with per-layer KV caches; yields the running ``[b, s]`` token tensor after
+        every new token.  A row ends at ``eos_token_id`` or when its tail equals one of ``stop_words_ids`` (token
+        sequences; the stop sequence stays in the output, later positions are filled with eos)."""
         from ...infer.generation import sample_next
         a = self.arch
         eos = a.eos_token_id if eos_token_id is None else eos_token_id
+        stops = [torch.tensor(w, dtype=torch.long, device=input_ids.device) for w in (stop_words_ids or []) if len(w)]
         b, s = input_ids.shape
         dev, dt = input_ids.device, self.lm_head.weight.dtype
-        caches = [{"k": torch.zeros(b, s + max_new_tokens, a.kv_heads, a.head_dim, dtype=dt, device=dev),
-                   "v": torch.zeros(b, s + max_new_tokens, a.kv_heads, a.head_dim, dtype=dt, device=dev), "len": 0}
-                  for _ in range(a.num_hidden_layers)]
+        if a.use_cache_quantization:
+            from .kv_quant import QuantizedKV
+            caches = [{"kq": QuantizedKV(b, s + max_new_tokens, a.kv_heads, a.head_dim, dev, dt),
+                       "vq": QuantizedKV(b, s + max_new_tokens, a.kv_heads, a.head_dim, dev, dt), "len": 0}
+                      for _ in range(a.num_hidden_layers)]
+        else:
+            caches = [{"k": torch.zeros(b, s + max_new_tokens, a.kv_heads, a.head_dim, dtype=dt, device=dev),
+                       "v": torch.zeros(b, s + max_new_tokens, a.kv_heads, a.head_dim, dtype=dt, device=dev), "len": 0}
+                      for _ in range(a.num_hidden_layers)]
         toks = input_ids
         done = torch.zeros(b, dtype=torch.bool, device=dev)
+        fill = eos if eos is not None else 0
         for step in range(max_new_tokens):
             inp = toks if step == 0 else toks[:, -1:]
             p0 = 0 if step == 0 else toks.shape[1] - 1
@@ -355,13 +375,29 @@ class CausalLM(nn.Module):
                 seen = torch.gather(logits, 1, toks)
                 logits.scatter_(1, toks, torch.where(seen > 0, seen / repetition_penalty, seen * repetition_penalty))
             nxt = sample_next(logits, temperature, top_k, top_p, greedy=not do_sample)
-            if eos is not None:
-                nxt = torch.where(done, torch.full_like(nxt, eos), nxt)
-                done |= nxt == eos
+            if eos is not None or stops:
+                nxt = torch.where(done, torch.full_like(nxt, fill), nxt)
             toks = torch.cat((toks, nxt.unsqueeze(1)), 1)
-            if eos is not None and bool(done.all()):
+            if eos is not None:
+                done |= nxt == eos
+            new_len = toks.shape[1] - s
+            for w in stops:
+                if new_len >= len(w):
+                    done |= (toks[:, -len(w):] == w).all(dim=1)
+            yield toks
+            if (eos is not None or stops) and bool(done.all()):
                 break
+
+    def generate(self, input_ids, attention_mask=None, max_new_tokens=64, num_beams=1, **kw):
+        toks = input_ids
+        for toks in self._decode_steps(input_ids, max_new_tokens=max_new_tokens, **kw):
+            pass
         return toks
+
+    def generate_stream(self, input_ids, max_new_tokens=64, **kw):
+        """Yields the newest token of every row (``[b]``) as soon as it is decoded."""
+        for toks in self._decode_steps(input_ids, max_new_tokens=max_new_tokens, **kw):
+            yield toks[:, -1]
 
     # ---- checkpoint IO --------------------------------------------------------------------------------
     def canonical_state(self):
