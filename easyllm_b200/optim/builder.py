@@ -2,7 +2,8 @@
 
 Parity: llm/utils/model/optimizer_helper.py:19-98.  ``FusedAdam`` / ``AdamW`` / ``Adam`` map
 to the native fused Adam on ZeRO-sharded flat buffers (decay / no-decay split: biases and
-1-D parameters are not decayed; frozen parameters are left out).  ``SophiaG`` and any
+1-D parameters are not decayed; frozen parameters are left out).  ``FusedSGD`` maps to
+``torch.optim.SGD``, ``FusedNovoGrad`` to ``optim.novograd.NovoGrad``; ``SophiaG`` and any
 ``torch.optim.*`` class are available for the single-axis runners; ``Adam8bit``
 (bitsandbytes) is not provided and raises a clear error.
 """
@@ -39,6 +40,14 @@ def build_optimizer(cfg_optim, model, zero_stage=0, grad_clip=0.0, fp16=False, n
     if kind == "SophiaG":
         from .sophia import SophiaG
         return SophiaG(groups, **kw)
+    if kind in ("FusedNovoGrad", "NovoGrad"):
+        from .novograd import NovoGrad
+        return NovoGrad(groups, **kw)
+    if kind == "FusedSGD":
+        kw.pop("wd_after_momentum", None)
+        kw.pop("materialize_master_grads", None)
+        kw.pop("set_grad_none", None)
+        return torch.optim.SGD(groups, **kw)
     if hasattr(torch.optim, kind):
         return getattr(torch.optim, kind)(groups, **kw)
     raise KeyError(f"unknown optimizer type {kind}")

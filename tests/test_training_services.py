@@ -103,6 +103,37 @@ def test_sophia_g_is_clipped_sign_momentum():
     assert torch.allclose(p.detach(), torch.tensor([0.9, -1.9, 3.0]), atol=1e-6)
 
 
+def test_novograd_update_rule_and_builder_names():
+    """Two hand-computed steps of the per-tensor second-moment rule; the builder resolves the apex names."""
+    from easyllm_b200.optim import NovoGrad, build_optimizer
+    p = torch.nn.Parameter(torch.tensor([3.0, 4.0]))
+    opt = NovoGrad([p], lr=0.1, betas=(0.5, 0.5), eps=0.0, weight_decay=0.1, bias_correction=False)
+    p.grad = torch.tensor([3.0, 4.0])
+    opt.step()
+    # v = |g|^2 = 25, u = g/5 + 0.1*w = [0.9, 1.2], m = 0.5*u, w -= 0.1*m
+    w1 = torch.tensor([3.0 - 0.1 * 0.45, 4.0 - 0.1 * 0.6])
+    assert torch.allclose(p.detach(), w1, atol=1e-6)
+    p.grad = torch.tensor([0.0, 5.0])
+    opt.step()
+    # v = 0.5*25 + 0.5*25 = 25, u = [0, 1] + 0.1*w1, m = 0.5*[0.45, 0.6] + 0.5*u
+    u2 = torch.tensor([0.0, 1.0]) + 0.1 * w1
+    m2 = 0.5 * torch.tensor([0.45, 0.6]) + 0.5 * u2
+    assert torch.allclose(p.detach(), w1 - 0.1 * m2, atol=1e-6)
+    # bias correction divides the (un-decayed) first norm as well: denom = |g| / sqrt(1 - beta2) = 50
+    q = torch.nn.Parameter(torch.tensor([3.0, 4.0]))
+    o2 = NovoGrad([q], lr=0.1, betas=(0.9, 0.99), eps=0.0)
+    q.grad = torch.tensor([3.0, 4.0])
+    o2.step()
+    # u = g/50; m = 0.1*u; m/c1 = u
+    assert torch.allclose(q.detach(), torch.tensor([3.0 - 0.006, 4.0 - 0.008]), atol=1e-6)
+    lin = torch.nn.Linear(4, 4)
+    assert type(build_optimizer({"type": "FusedNovoGrad", "kwargs": {"lr": 0.1}}, lin)).__name__ == "NovoGrad"
+    sgd = build_optimizer({"type": "FusedSGD", "kwargs": {"lr": 0.1, "momentum": 0.9, "weight_decay": 0.01}}, lin)
+    assert isinstance(sgd, torch.optim.SGD) and sgd.param_groups[1]["weight_decay"] == 0.0
+    with pytest.raises(RuntimeError):
+        NovoGrad([q], amsgrad=True)
+
+
 def test_dynamic_checkpoint_manager_selection():
     from easyllm_b200.utils.dc_manager import DynamicCheckpointManager, bfs_candidates
 
