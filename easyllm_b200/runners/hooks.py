@@ -238,3 +238,55 @@ class WatchdogHook(Hook):
     def after_train(self):
         if self.wd is not None:
             self.wd.leave()
+
+
+@HOOK_REGISTRY.register("torch_profiler")
+class TorchProfilerHook(Hook):
+    """Optional ``torch.profiler`` window over a few training iterations (the reference has no profiler
+    integration; its only timers are the wall-clock ``Timers`` of the logger hook).
+
+    Skips ``wait`` iterations, warms the profiler for ``warmup``, records ``active`` iterations, then writes a Chrome
+    trace ``<out_dir>/trace_rank<r>_iter<i>.json`` and a text table of the top operators; ``ranks`` limits which
+    global ranks profile (default rank 0 only).  CUDA activity is recorded when a GPU is present.
+    """
+
+    def __init__(self, runner, out_dir="profiler", wait=2, warmup=1, active=2, repeat=1, ranks=(0,),
+                 record_shapes=False, with_stack=False, profile_memory=False, row_limit=30):
+        super().__init__(runner)
+        self.out_dir, self.ranks, self.row_limit = out_dir, tuple(ranks), row_limit
+        self.sched = dict(wait=wait, warmup=warmup, active=active, repeat=repeat)
+        self.opts = dict(record_shapes=record_shapes, with_stack=with_stack, profile_memory=profile_memory)
+        self.prof = None
+        self.written = []
+
+    def _on_ready(self, prof):
+        import os
+        os.makedirs(self.out_dir, exist_ok=True)
+        rank = get_grid().rank if torch.distributed.is_initialized() else 0
+        base = os.path.join(self.out_dir, f"trace_rank{rank}_iter{self._iter}")
+        prof.export_chrome_trace(base + ".json")
+        key = "cuda_time_total" if torch.cuda.is_available() else "cpu_time_total"
+        with open(base + ".txt", "w") as f:
+            f.write(prof.key_averages().table(sort_by=key, row_limit=self.row_limit))
+        self.written.append(base + ".json")
+        logger.info(f"torch.profiler trace written to {base}.json")
+
+    def before_train(self):
+        from torch.profiler import ProfilerActivity, profile, schedule
+        rank = get_grid().rank if torch.distributed.is_initialized() else 0
+        if rank not in self.ranks:
+            return
+        acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+        self._iter = 0
+        self.prof = profile(activities=acts, schedule=schedule(**self.sched), on_trace_ready=self._on_ready, **self.opts)
+        self.prof.__enter__()
+
+    def after_train_iter(self, cur_iter, output=None):
+        if self.prof is not None:
+            self._iter = cur_iter
+            self.prof.step()
+
+    def after_train(self):
+        if self.prof is not None:
+            self.prof.__exit__(None, None, None)
+            self.prof = None

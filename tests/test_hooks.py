@@ -63,3 +63,27 @@ def test_early_exit_saves_then_exits():
     with pytest.raises(SystemExit):
         EarlyExitHook(r2, exit_duration_in_mins=30).after_train_iter(6)
     assert r2.saved == [7]
+
+
+def test_torch_profiler_hook_writes_a_trace_for_the_active_window(tmp_path):
+    import json
+    from easyllm_b200.runners.hooks import TorchProfilerHook, build_hooks
+    r = _StubRunner()
+    hooks = build_hooks(r, [{"type": "torch_profiler", "kwargs": {"out_dir": str(tmp_path), "wait": 1, "warmup": 1,
+                                                                   "active": 2, "row_limit": 5}}],
+                        add_log_if_not_exists=False)
+    h = next(x for x in hooks._hooks if isinstance(x, TorchProfilerHook))
+    hooks("before_train")
+    a = torch.randn(64, 64)
+    for it in range(5):
+        (a @ a).sum().item()
+        hooks("after_train_iter", it, {})
+    hooks("after_train")
+    assert len(h.written) == 1 and h.written[0].endswith("trace_rank0_iter3.json")     # iterations 2 and 3 recorded
+    trace = json.load(open(h.written[0]))
+    assert any("mm" in str(e.get("name", "")) for e in trace["traceEvents"])
+    assert (tmp_path / "trace_rank0_iter3.txt").read_text().strip()
+    # a rank outside `ranks` does nothing
+    idle = TorchProfilerHook(r, out_dir=str(tmp_path / "x"), ranks=(3,))
+    idle.before_train(); idle.after_train_iter(0); idle.after_train()
+    assert idle.written == [] and not (tmp_path / "x").exists()
