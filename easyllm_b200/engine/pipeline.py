@@ -60,6 +60,7 @@ class PipelineEngine:
         self.link = StageLink(self.dtype, dynamic=True) if self.g.pp > 1 else None
         self.total_loss = None
         self.fwd_outputs = []
+        self._compute_loss = True        # set False by generation code that wants logits from eval_batch
         self.nvtx = bool(cfg.get("nvtx", False)) and torch.cuda.is_available()
 
     # ---- contract surface -------------------------------------------------------------------
@@ -235,6 +236,7 @@ class PipelineEngine:
         """Forward-only pipeline pass.  With ``compute_loss`` returns the mean loss on every
         stage; otherwise the last stage returns its logits ``[b, s, V(/tp)]`` (others None)."""
         self.module.eval()
+        compute_loss = compute_loss and self._compute_loss
         g, P = self.g, self.g.pp
         M = num_micro_batches or (self.micro_batches if compute_loss else 1)
         if self.link is not None:

@@ -61,6 +61,16 @@ def _block_params(a: ModelArgs):
     return n
 
 
+class _TorchCheckpointEngine:
+    """``save`` / ``load`` with ``torch.save`` semantics (the engine object DeepSpeed exposes on a pipeline module)."""
+
+    def save(self, state_dict, path):
+        torch.save(state_dict, path)
+
+    def load(self, path, map_location="cpu"):
+        return torch.load(path, map_location=map_location, weights_only=False)
+
+
 class LlamaModelPipe(nn.Module):
     def __init__(self, args: ModelArgs):
         super().__init__()
@@ -118,6 +128,26 @@ class LlamaModelPipe(nn.Module):
 
     def layer_index_of(self, module_name: str) -> int:
         return int(module_name.split(".")[1])
+
+    # ---- names the reference's checkpoint helpers reach for on a DeepSpeed PipelineModule -------------------
+    # (llm/models/mg_models/llama/utils.py:485-548 walks ``forward_funcs`` and saves through ``checkpoint_engine``)
+    checkpoint_parallel_write_pipeline = False            # the first DP rank writes every layer file of its stage
+
+    @property
+    def forward_funcs(self):
+        """This stage's entries of the layer list in order: the module for parameter-bearing specs, the spec's
+        type name for the parameter-free ones (casts / transposes)."""
+        return [self.layers[str(s.index)] if str(s.index) in self.layers else s.typename
+                for s in self.specs[self.lo:self.hi]]
+
+    def ckpt_layer_path(self, ckpt_dir, local_layer_idx):
+        """Layer file of entry ``local_layer_idx`` of this stage for this TP rank."""
+        from ..ckpt.layer_files import layer_file
+        return layer_file(ckpt_dir, self.lo + local_layer_idx, get_grid().tp_rank)
+
+    @property
+    def checkpoint_engine(self):
+        return _TorchCheckpointEngine()
 
     # ---- Dynamic Checkpoint ---------------------------------------------------------------
     def get_checkpoint_range(self, seq_len: int) -> int:

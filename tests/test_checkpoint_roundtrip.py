@@ -166,3 +166,28 @@ def test_zero1_state_saved_with_dp2_resumes_on_one_rank(tmp_path):
     it = synthetic_batches(32000, 64, 2, seed=7, start=4)      # 2 steps x 2 micro-batches of the global stream consumed
     loss = float(eng.train_batch(it))
     assert abs(loss - third[0]) < 2e-5, (loss, third)
+
+
+def test_pipeline_module_names_used_by_checkpoint_helpers(tmp_path):
+    """The DeepSpeed PipelineModule attribute names the reference's LoRA saver walks: the stage's layer list in
+    order, the per-layer file path, the checkpoint engine; and the engine's ``_compute_loss`` switch."""
+    from easyllm_b200.data.synthetic import synthetic_batches
+    eng = _make_engine()
+    m = eng.module
+    funcs = m.forward_funcs
+    assert len(funcs) == TINY["num_layers"] + 7 and funcs[0] == "to_float16" and funcs[2] == "transpose"
+    assert funcs[1] is m.layers["1"] and funcs[3] is m.layers["3"] and funcs[-2] is m.layers[str(TINY["num_layers"] + 5)]
+    assert m.checkpoint_parallel_write_pipeline is False
+    path = m.ckpt_layer_path(str(tmp_path), 3)
+    assert os.path.basename(path) == "layer_03-model_00-model_states.pt"
+    m.checkpoint_engine.save({k: v.clone() for k, v in funcs[3].state_dict().items()}, path)
+    eng.save_checkpoint(str(tmp_path / "full"), tag="t")
+    ours = m.checkpoint_engine.load(path)
+    full = torch.load(m.ckpt_layer_path(str(tmp_path / "full" / "t"), 3), weights_only=False)
+    assert set(ours) == set(full) and all(torch.equal(ours[k], full[k]) for k in ours)
+    # generation code of the reference flips _compute_loss and reads fwd_outputs
+    eng._compute_loss = False
+    out = eng.eval_batch(synthetic_batches(32000, 16, 2, seed=3))
+    assert out.shape[:2] == (2, 16) and eng.fwd_outputs[0] is out
+    eng._compute_loss = True
+    assert eng.eval_batch(synthetic_batches(32000, 16, 2, seed=3)).dim() == 0
