@@ -4,9 +4,11 @@ or LoRA on llama-family models, reusing this package's datasets and ``batch_alig
 
     python -m easyllm_b200.runners.open_hf_runner --model_name_or_path hf_dir --data_path d.jsonl \
         --output_dir out [--use_lora --lora_r 8 --lora_alpha 16] [--num_train_steps 100] [--bf16]
+        [--tuning prompt|prefix --num_virtual_tokens 20 [--prompt_init_text "..."]]
 
-Prefix / prompt tuning of the reference script depend on peft and are not provided; LoRA and full
-fine-tuning are.  Multi-GPU: launch with torchrun (data parallel, ZeRO-1).
+Tuning modes: full fine-tuning (default), LoRA (``--use_lora``), prompt tuning and prefix tuning
+(``models/hf_models/soft_prompt.py``); the adapters are written in peft's file layout.
+Multi-GPU: launch with torchrun (data parallel, ZeRO-1).
 """
 from __future__ import annotations
 
@@ -47,6 +49,9 @@ def main(argv=None):
     p.add_argument("--lora_dropout", type=float, default=0.05)
     p.add_argument("--lora_target", default="q_proj,v_proj")
     p.add_argument("--gradient_checkpointing", action="store_true")
+    p.add_argument("--tuning", choices=["none", "prompt", "prefix"], default="none")
+    p.add_argument("--num_virtual_tokens", type=int, default=20)
+    p.add_argument("--prompt_init_text", default=None)
     a = p.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
@@ -63,6 +68,15 @@ def main(argv=None):
                          "target_modules": a.lora_target.split(",")})
     if a.gradient_checkpointing:
         model.gradient_checkpointing_enable()
+    soft = None
+    if a.tuning != "none":
+        from ..models.hf_models import soft_prompt
+        if a.tuning == "prompt":
+            init = tok.encode(a.prompt_init_text) if a.prompt_init_text else None
+            soft = soft_prompt.PromptTuning(model, a.num_virtual_tokens, init_token_ids=init)
+        else:
+            soft = soft_prompt.PrefixTuning(model, a.num_virtual_tokens)
+        model = soft.to(dev)
     tr = [{"type": "sense_tokenization", "kwargs": {"max_seq_length": a.model_max_length, "parser_type": a.parser_type}}]
     ds = build_dataset({"type": "base_nlp_json", "kwargs": {"json_file": a.data_path, "json_type": "line", "transformer": tr}}, tok)
     coll = BatchAlignCollector(tok, alignment=8, max_seq_length=a.model_max_length, offset_label=False)
@@ -85,7 +99,13 @@ def main(argv=None):
             if step >= a.num_train_steps * a.gradient_accumulation_steps:
                 break
     if rank == 0:
-        save_adapter(model, a.output_dir) if a.use_lora else model.save_pretrained(a.output_dir)
+        if soft is not None:
+            from ..models.hf_models.soft_prompt import save_adapter as save_soft
+            save_soft(soft, a.output_dir)
+        elif a.use_lora:
+            save_adapter(model, a.output_dir)
+        else:
+            model.save_pretrained(a.output_dir)
 
 
 if __name__ == "__main__":
