@@ -342,34 +342,54 @@ class CausalLM(nn.Module):
     # ---- generation -----------------------------------------------------------------------------
     @torch.no_grad()
     def _decode_steps(self, input_ids, max_new_tokens=64, do_sample=False, temperature=1.0, top_k=0, top_p=0.0,
-                      eos_token_id=None, repetition_penalty=1.0, stop_words_ids=None, **_):
+                      eos_token_id=None, repetition_penalty=1.0, stop_words_ids=None, soft_prefix=None, **_):
         """Greedy / sampled decoding with per-layer KV caches; yields the running ``[b, s]`` token tensor after
         every new token.  A row ends at ``eos_token_id`` or when its tail equals one of ``stop_words_ids`` (token
-        sequences; the stop sequence stays in the output, later positions are filled with eos)."""
+        sequences; the stop sequence stays in the output, later positions are filled with eos).
+        ``soft_prefix``: ``{"embeds": [P, hidden]}`` (prompt tuning: virtual input embeddings in front of the
+        prompt) or ``{"kv": [layers, 2, P, kv_heads, head_dim]}`` (prefix tuning: pre-filled cache entries)."""
         from ...infer.generation import sample_next
         a = self.arch
         eos = a.eos_token_id if eos_token_id is None else eos_token_id
         stops = [torch.tensor(w, dtype=torch.long, device=input_ids.device) for w in (stop_words_ids or []) if len(w)]
         b, s = input_ids.shape
         dev, dt = input_ids.device, self.lm_head.weight.dtype
+        soft = soft_prefix or {}
+        pre_kv = soft.get("kv")
+        pre_emb = soft.get("embeds")
+        n_kv = 0 if pre_kv is None else pre_kv.shape[2]
+        n_emb = 0 if pre_emb is None else pre_emb.shape[0]
+        room = s + max_new_tokens + n_kv + n_emb
         if a.use_cache_quantization:
             from .kv_quant import QuantizedKV
-            caches = [{"kq": QuantizedKV(b, s + max_new_tokens, a.kv_heads, a.head_dim, dev, dt),
-                       "vq": QuantizedKV(b, s + max_new_tokens, a.kv_heads, a.head_dim, dev, dt), "len": 0}
+            caches = [{"kq": QuantizedKV(b, room, a.kv_heads, a.head_dim, dev, dt),
+                       "vq": QuantizedKV(b, room, a.kv_heads, a.head_dim, dev, dt), "len": 0}
                       for _ in range(a.num_hidden_layers)]
         else:
-            caches = [{"k": torch.zeros(b, s + max_new_tokens, a.kv_heads, a.head_dim, dtype=dt, device=dev),
-                       "v": torch.zeros(b, s + max_new_tokens, a.kv_heads, a.head_dim, dtype=dt, device=dev), "len": 0}
+            caches = [{"k": torch.zeros(b, room, a.kv_heads, a.head_dim, dtype=dt, device=dev),
+                       "v": torch.zeros(b, room, a.kv_heads, a.head_dim, dtype=dt, device=dev), "len": 0}
                       for _ in range(a.num_hidden_layers)]
+        if n_kv:
+            for l, c in enumerate(caches):
+                k0, v0 = (pre_kv[l, i].to(dt).unsqueeze(0).expand(b, -1, -1, -1) for i in (0, 1))
+                if "kq" in c:
+                    c["kq"].append(0, k0); c["vq"].append(0, v0)
+                else:
+                    c["k"][:, :n_kv], c["v"][:, :n_kv] = k0, v0
+                c["len"] = n_kv
         toks = input_ids
         done = torch.zeros(b, dtype=torch.bool, device=dev)
         fill = eos if eos is not None else 0
         for step in range(max_new_tokens):
             inp = toks if step == 0 else toks[:, -1:]
-            p0 = 0 if step == 0 else toks.shape[1] - 1
+            p0 = n_kv if step == 0 else n_kv + n_emb + toks.shape[1] - 1
+            embeds = None
+            if step == 0 and n_emb:
+                embeds = torch.cat((pre_emb.to(dt).unsqueeze(0).expand(b, -1, -1), self.model.embed_tokens(inp)), 1)
+                inp = torch.cat((inp.new_zeros(b, n_emb), inp), 1)          # shapes only: the embeddings are given
             pos = torch.arange(inp.shape[1], device=dev).unsqueeze(0).expand(b, -1) + p0
             meta = build_meta(inp, None, pos)
-            h = self.hidden_states(inp, meta, caches)
+            h = self.hidden_states(inp, meta, caches, inputs_embeds=embeds)
             logits = ops.linear(h.view(b, inp.shape[1], -1)[:, -1], self.head_weight()).float()
             if repetition_penalty != 1.0:
                 seen = torch.gather(logits, 1, toks)

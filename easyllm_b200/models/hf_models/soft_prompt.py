@@ -58,6 +58,12 @@ class PromptTuning(nn.Module):
             out["logits"] = out["logits"][:, self.n:]
         return out
 
+    def generate(self, input_ids, **kw):
+        return self.base.generate(input_ids, soft_prefix={"embeds": self.prompt_embeddings.detach()}, **kw)
+
+    def generate_stream(self, input_ids, **kw):
+        return self.base.generate_stream(input_ids, soft_prefix={"embeds": self.prompt_embeddings.detach()}, **kw)
+
     def adapter_state(self):
         return {"prompt_embeddings": self.prompt_embeddings.detach().cpu()}
 
@@ -109,6 +115,12 @@ class PrefixTuning(nn.Module):
         else:
             out["logits"] = ops.linear(h, base.head_weight()).view(b, s, -1)
         return out
+
+    def generate(self, input_ids, **kw):
+        return self.base.generate(input_ids, soft_prefix={"kv": self.prefix.detach()}, **kw)
+
+    def generate_stream(self, input_ids, **kw):
+        return self.base.generate_stream(input_ids, soft_prefix={"kv": self.prefix.detach()}, **kw)
 
     def adapter_state(self):
         L, _, P, hk, d = self.prefix.shape

@@ -101,3 +101,23 @@ def test_stand_alone_finetune_script_modes(tmp_path):
     assert os.path.exists(tmp_path / "lora" / "adapter_model.bin") and os.path.exists(tmp_path / "lora" / "adapter_config.json")
     full = CausalLM.from_pretrained(str(tmp_path / "full"), family="llama")
     assert not torch.allclose(full(ids)["logits"], CausalLM.from_pretrained(str(tmp_path / "base"), family="llama")(ids)["logits"])
+
+
+def test_soft_prompt_generation_agrees_with_full_recompute():
+    """Decoding with the KV cache (virtual tokens in front) picks the same greedy tokens as re-running the whole
+    wrapped model on the growing sequence."""
+    from easyllm_b200.models.hf_models.soft_prompt import PrefixTuning, PromptTuning
+    base = _base().eval()
+    ids = torch.randint(0, 97, (2, 5))
+    for m in (PromptTuning(base, 4), PrefixTuning(base, 3)):
+        with torch.no_grad():
+            (m.prompt_embeddings if hasattr(m, "prompt_embeddings") else m.prefix).mul_(20)   # make the prefix matter
+        out = m.generate(ids, max_new_tokens=4, eos_token_id=None)
+        assert out.shape == (2, 9) and torch.equal(out[:, :5], ids)
+        cur = ids
+        for t in range(4):
+            nxt = m(cur)["logits"][:, -1].argmax(-1)
+            assert torch.equal(nxt, out[:, 5 + t]), (type(m).__name__, t)
+            cur = torch.cat((cur, nxt.unsqueeze(1)), 1)
+        streamed = torch.stack(list(m.generate_stream(ids, max_new_tokens=4, eos_token_id=None)), 1)
+        assert torch.equal(streamed, out[:, 5:])

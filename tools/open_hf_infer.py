@@ -1,4 +1,4 @@
-"""Stand-alone inference with an HF-format checkpoint (+ optional LoRA adapter), interactive or
+"""Stand-alone inference with an HF-format checkpoint (+ optional LoRA / prompt / prefix adapter), interactive or
 over a question file (tools/open_hf_infer.py:27-211 of the reference).
 
     python tools/open_hf_infer.py --model_path hf_dir [--lora_path adapter] [--family llama] \
@@ -36,14 +36,21 @@ def main(argv=None):
     dev = torch.device("cuda" if torch.cuda.is_available() else "cpu")
     tok = build_tokenizer({"type": a.tokenizer_type, "kwargs": {"tokenizer_name_or_path": a.tokenizer_path or a.model_path}})
     model = CausalLM.from_pretrained(a.model_path, family=a.family, torch_dtype=a.dtype if dev.type == "cuda" else "float32")
+    soft_dir = None
     if a.lora_path:
         from easyllm_b200.models.lora import merge_lora_into_hf_state
         with open(os.path.join(a.lora_path, "adapter_config.json")) as f:
             c = json.load(f)
+        if c.get("peft_type") in ("PROMPT_TUNING", "PREFIX_TUNING"):
+            soft_dir, a.lora_path = a.lora_path, None
+    if a.lora_path:
         sd = merge_lora_into_hf_state(model.state_dict(), torch.load(os.path.join(a.lora_path, "adapter_model.bin"),
                                                                     map_location="cpu"), c["lora_alpha"] / c["r"])
         model.load_state_dict(sd)
     model = model.to(dev).eval()
+    if soft_dir:
+        from easyllm_b200.models.hf_models.soft_prompt import load_adapter
+        model = load_adapter(model, soft_dir).to(dev).eval()
     gen = dict(max_new_tokens=a.max_new_tokens, temperature=a.temperature, top_k=a.top_k, top_p=a.top_p, do_sample=a.do_sample)
     if a.question_file:
         with open(a.question_file) as f, open(a.result_file, "w") as out:
