@@ -441,7 +441,10 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tA, tB, tC, bias, M, N, K, err);
-  if (e != cudaSuccess) return (int)e;
+  if (e != cudaSuccess) {
+    cudaGetLastError();   // a refused launch is reported to the caller, not left behind for the next launch
+    return (int)e;
+  }
   return launch_status();
 }
 

@@ -245,6 +245,11 @@ def set_gemm_pair(enabled):
     _GEMM_PAIR = bool(enabled)
 
 
+# launch-time refusals of a cluster launch (nothing ran, the error is not sticky): cannot co-schedule (-20), invalid
+# configuration (9), launch out of resources (701), invalid cluster size (912)
+_PAIR_LAUNCH_REFUSED = (-20, 9, 701, 912)
+
+
 def _use_pair(M, N, bn):
     return _GEMM_PAIR and bn == 0 and M >= 256 and N >= 256 and (M % 256 == 0 or M >= 2048)
 
@@ -275,8 +280,14 @@ def gemm(a, b, out=None, bias=None, a_mn=False, b_mn=False, out_mode=0, bn=0, pa
         rc = lib().ell_gemm_bf16_pair(_p(a), _p(b), _p(out), _p(bias), c_int(M), c_int(N), c_int(K), c_int(a.shape[1]),
                                       c_int(b.shape[1]), c_int(N), c_int(1 if a_mn else 0), c_int(1 if b_mn else 0),
                                       c_int(out_mode), _p(err_flag(a.device)), _stream())
-        _check(rc, "gemm_bf16_pair")
-        return out
+        if rc not in _PAIR_LAUNCH_REFUSED:
+            _check(rc, "gemm_bf16_pair")
+            return out
+        # the launch itself was refused (no device work was issued): this device cannot co-schedule the two-CTA
+        # cluster with the kernel's shared memory.  Use the single-CTA kernel from here on.
+        import warnings
+        warnings.warn(f"CTA-pair GEMM launch refused (code {rc}); using the single-CTA tcgen05 kernel")
+        set_gemm_pair(False)
     rc = lib().ell_gemm_bf16(_p(a), _p(b), _p(out), _p(bias), c_int(M), c_int(N), c_int(K), c_int(a.shape[1]),
                              c_int(b.shape[1]), c_int(N), c_int(1 if a_mn else 0), c_int(1 if b_mn else 0),
                              c_int(out_mode), c_int(bn), _p(err_flag(a.device)), _stream())
