@@ -96,6 +96,14 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def _pair_on(ops):
+    """Whether plain GEMMs run on the CTA-pair (tcgen05.mma.cta_group::2) kernel in this run."""
+    if ops.get_backend() != "b200" or ops.get_gemm_backend() != "tcgen05":
+        return False
+    import easyllm_b200.ops.cuda as cu
+    return bool(cu._GEMM_PAIR)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -277,7 +285,7 @@ def main():
                           "packing": "variable-length documents, cu_seqlens" if args.varlen else "fixed length",
                           "runner": args.runner,
                           "micro_batch": 1, "grad_accum": n_micro, "optimizer": "fused Adam wd 0.1 clip 1.0",
-                          "gemm": ops.get_gemm_backend(), "ops": ops.get_backend(), "fused_tp": fused_tp,
+                          "gemm": ops.get_gemm_backend(), "gemm_cta_pair": _pair_on(ops), "ops": ops.get_backend(), "fused_tp": fused_tp,
                           "recompute_layers": args.recompute_layers,
                           "l2": "inputs (weights+activations) far larger than L2; no flush",
                           "vs_baseline_note": "per-GPU tokens/s over the published 4304 tok/s/GPU "
