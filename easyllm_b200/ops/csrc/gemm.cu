@@ -103,17 +103,19 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want
   return true;
 }
 
-__device__ __forceinline__ void swizzle_tile(int idx, int tiles_m, int tiles_n, int& mt, int& nt) {
+// The tile-order functions below are __host__ __device__: ell_gemm_enumerate_units runs the very same code on the
+// host so a CPU test can check that every launch covers each output tile exactly once, in the intended order.
+__host__ __device__ __forceinline__ void swizzle_tile(int idx, int tiles_m, int tiles_n, int& mt, int& nt) {
   const int width = kGroupM * tiles_n;
   const int group = idx / width, rem = idx % width;
   const int first_m = group * kGroupM;
-  const int gsz = min(tiles_m - first_m, kGroupM);
+  const int gsz = (tiles_m - first_m) < kGroupM ? (tiles_m - first_m) : kGroupM;
   mt = first_m + rem % gsz;
   nt = rem / gsz;
 }
 
 template <int FUSE>
-__device__ __forceinline__ void map_tile(int idx, int tiles_m, int tiles_n, const FuseArgs& f, int& mt, int& nt) {
+__host__ __device__ __forceinline__ void map_tile(int idx, int tiles_m, int tiles_n, const FuseArgs& f, int& mt, int& nt) {
   if (FUSE == kFuseAG) {
     const int tpr = tiles_m / f.tp, per_phase = tpr * tiles_n;
     const int phase = idx / per_phase;
@@ -152,7 +154,7 @@ __host__ __device__ inline int split_tail_tiles(int num_tiles, int ctas, bool al
 }
 
 template <int BN, int FUSE>
-__device__ __forceinline__ TileUnit decode_unit(int unit, int tiles_m, int tiles_n, int num_full, const FuseArgs& f) {
+__host__ __device__ __forceinline__ TileUnit decode_unit(int unit, int tiles_m, int tiles_n, int num_full, const FuseArgs& f) {
   TileUnit u;
   int tile = unit, half = -1;
   if (FUSE == kFuseNone && unit >= num_full) {
@@ -873,6 +875,42 @@ ELL_API void ell_gemm_set_prefetch(int k_blocks) { g_prefetch_kb = k_blocks < 0 
 
 // Tuning switch: 0 (default) cuts the tiles of an under-filled last wave in two, 1 keeps whole tiles.
 ELL_API void ell_gemm_set_tail_split(int enabled) { g_no_tail_split = enabled ? 0 : 1; }
+
+template <int BN, int FUSE>
+static int enumerate_units(int M, int N, const FuseArgs& f, int ctas, bool allow_split, int* out, int max_units) {
+  const int tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int n_split = split_tail_tiles(num_tiles, ctas, FUSE == kFuseNone && BN == 256 && allow_split);
+  const int num_full = num_tiles - n_split, num_units = num_tiles + n_split;
+  if (num_units > max_units) return -1;
+  for (int u = 0; u < num_units; ++u) {
+    const TileUnit t = decode_unit<BN, FUSE>(u, tiles_m, tiles_n, num_full, f);
+    out[4 * u + 0] = t.mt;
+    out[4 * u + 1] = t.nt;
+    out[4 * u + 2] = t.n0;
+    out[4 * u + 3] = t.bn;
+  }
+  return num_units;
+}
+
+// Host-only: the work units of a launch in the order the kernel walks them (unit u goes to GEMM CTA u % ctas as its
+// (u / ctas)-th item), computed by the kernel's own tile-order code.  out[u] = {row tile, column tile, first column,
+// width}.  fuse: 0 plain, 1 all-gather -> GEMM, 2 GEMM -> reduce-scatter.  Returns the unit count, -1 if out is too
+// small, -3 for an unsupported bn / fuse.  Touches no GPU.
+ELL_API int ell_gemm_enumerate_units(int M, int N, int bn, int fuse, int tp, int rank, int rs_ring, int ctas,
+                                     int allow_split, int* out, int max_units) {
+  FuseArgs f{};
+  f.tp = tp;
+  f.rank = rank;
+  f.rs_ring = rs_ring;
+  if (bn == 256 && fuse == kFuseNone) return enumerate_units<256, kFuseNone>(M, N, f, ctas, allow_split != 0, out, max_units);
+  if (bn == 128 && fuse == kFuseNone) return enumerate_units<128, kFuseNone>(M, N, f, ctas, allow_split != 0, out, max_units);
+  if (bn == 256 && fuse == kFuseAG) return enumerate_units<256, kFuseAG>(M, N, f, ctas, false, out, max_units);
+  if (bn == 128 && fuse == kFuseAG) return enumerate_units<128, kFuseAG>(M, N, f, ctas, false, out, max_units);
+  if (bn == 256 && fuse == kFuseRS) return enumerate_units<256, kFuseRS>(M, N, f, ctas, false, out, max_units);
+  if (bn == 128 && fuse == kFuseRS) return enumerate_units<128, kFuseRS>(M, N, f, ctas, false, out, max_units);
+  return -3;
+}
 
 // C = op(A)·op(B)^T.  a_mn / b_mn select MN-major storage ([K,M] / [K,N] row-major).
 // out_mode: 0 bf16 C (ldc in elements), 1 fp32 C += result, 2 fp32 C = result.

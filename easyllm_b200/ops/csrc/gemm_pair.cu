@@ -123,11 +123,12 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                : "memory");
 }
 
-__device__ __forceinline__ void raster(int idx, int tiles_m, int tiles_n, int& mt, int& nt) {
+// __host__ __device__ so that ell_gemm_pair_enumerate_tiles can run the same code for a CPU coverage test
+__host__ __device__ __forceinline__ void raster(int idx, int tiles_m, int tiles_n, int& mt, int& nt) {
   const int width = kGroupM * tiles_n;
   const int group = idx / width, rem = idx % width;
   const int first_m = group * kGroupM;
-  const int gsz = min(tiles_m - first_m, kGroupM);
+  const int gsz = (tiles_m - first_m) < kGroupM ? (tiles_m - first_m) : kGroupM;
   mt = first_m + rem % gsz;
   nt = rem / gsz;
 }
@@ -452,6 +453,16 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
 }  // namespace ell
 
 using namespace ell;
+
+// Host-only: the 256 x 256 tiles of a launch in the order the clusters walk them (tile t goes to cluster
+// t % clusters), from the kernel's own raster code.  out[t] = {row tile, column tile}.  Returns the tile count or -1.
+ELL_API int ell_gemm_pair_enumerate_tiles(int M, int N, int* out, int max_tiles) {
+  using namespace ell::pair;
+  const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + kTileN - 1) / kTileN;
+  if (tiles_m * tiles_n > max_tiles) return -1;
+  for (int t = 0; t < tiles_m * tiles_n; ++t) raster(t, tiles_m, tiles_n, out[2 * t], out[2 * t + 1]);
+  return tiles_m * tiles_n;
+}
 
 // Same contract as ell_gemm_bf16 (without a tile-width hint): C = op(A)·op(B)^T, a_mn / b_mn select MN-major
 // storage, out_mode 0 bf16 C, 1 fp32 C += result, 2 fp32 C = result; bias only with out_mode 0.

@@ -295,6 +295,30 @@ def gemm(a, b, out=None, bias=None, a_mn=False, b_mn=False, out_mode=0, bn=0, pa
     return out
 
 
+def gemm_work_units(M, N, bn=256, fuse=0, tp=1, rank=0, rs_ring=False, ctas=148, allow_split=True):
+    """Host-only: the (row tile, column tile, first column, width) work units of a single-CTA GEMM launch in the
+    order the kernel walks them, produced by the kernel's own tile-order code (no GPU is touched).
+    ``fuse``: 0 plain, 1 all-gather→GEMM, 2 GEMM→reduce-scatter."""
+    cap = 2 * ((M + 127) // 128) * ((N + bn - 1) // bn) + 8
+    buf = (c_int * (4 * cap))()
+    n = lib().ell_gemm_enumerate_units(c_int(M), c_int(N), c_int(bn), c_int(fuse), c_int(tp), c_int(rank),
+                                       c_int(1 if rs_ring else 0), c_int(ctas), c_int(1 if allow_split else 0), buf,
+                                       c_int(cap))
+    if n < 0:
+        raise KernelError(f"gemm_work_units failed with code {n}")
+    return [tuple(buf[4 * i:4 * i + 4]) for i in range(n)]
+
+
+def gemm_pair_tiles(M, N):
+    """Host-only: the (row tile, column tile) order of the CTA-pair GEMM's 256 x 256 tiles."""
+    cap = ((M + 255) // 256) * ((N + 255) // 256)
+    buf = (c_int * (2 * max(cap, 1)))()
+    n = lib().ell_gemm_pair_enumerate_tiles(c_int(M), c_int(N), buf, c_int(cap))
+    if n < 0:
+        raise KernelError(f"gemm_pair_tiles failed with code {n}")
+    return [tuple(buf[2 * i:2 * i + 2]) for i in range(n)]
+
+
 def gemm_ce(x, w, target, vocab_start, valid_cols):
     """LM-head GEMM with the cross-entropy statistics fused into its epilogue.
 

@@ -1,0 +1,82 @@
+"""Tile order of the GEMM kernels, checked on the host with the kernels' own scheduling code (no GPU):
+every output element is produced exactly once, the tail wave is halved only when that pays, the fused forms visit
+the row shards in the order their protocols rely on."""
+import itertools
+
+import pytest
+
+
+@pytest.fixture(scope="module")
+def cu():
+    import easyllm_b200.ops.cuda as cu
+    if not cu.available():
+        pytest.skip("kernel library not built")
+    cu.lib()
+    return cu
+
+
+def _coverage(units, M, N, bn):
+    seen = {}
+    for mt, nt, n0, w in units:
+        assert 0 <= mt < (M + 127) // 128 and w in (bn, bn // 2) and n0 >= nt * bn and n0 + w <= (nt + 1) * bn
+        for c in range(n0, n0 + w, 64 if w >= 64 else w):
+            key = (mt, c)
+            assert key not in seen, f"column block {key} produced twice"
+            seen[key] = 1
+    step = 64
+    want = {(mt, c) for mt in range((M + 127) // 128) for nt in range((N + bn - 1) // bn)
+            for c in range(nt * bn, (nt + 1) * bn, step)}
+    assert set(seen) == want
+
+
+@pytest.mark.parametrize("M,N,ctas", [(128, 256, 148), (4096, 12288, 148), (4096, 4096, 148), (4096, 11008, 148),
+                                      (1000, 520, 148), (8192, 8192, 148), (2176, 768, 148), (4096, 32000, 148),
+                                      (384, 320, 7), (4096, 4096, 140)])
+def test_plain_launch_covers_every_tile_once(cu, M, N, ctas):
+    for bn in (256, 128):
+        for split in (True, False):
+            units = cu.gemm_work_units(M, N, bn=bn, ctas=ctas, allow_split=split)
+            _coverage(units, M, N, bn)
+            tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
+            tail = tiles % ctas
+            halved = split and bn == 256 and 0 < tail and 2 * tail <= ctas
+            assert len(units) == tiles + (tail if halved else 0)
+            assert all(w == bn for *_, w in units[:tiles - (tail if halved else 0)])
+            if halved:                          # the two halves of a tail tile are neighbours in the unit order
+                rest = units[tiles - tail:]
+                assert all(a[:2] == b[:2] and a[3] == b[3] == bn // 2 and b[2] == a[2] + bn // 2
+                           for a, b in zip(rest[0::2], rest[1::2]))
+    # grouped rasterisation: 16 row tiles share a column tile before the next column tile starts (B stays in L2)
+    u = cu.gemm_work_units(4096, 12288, allow_split=False)
+    assert [x[0] for x in u[:16]] == list(range(16)) and {x[1] for x in u[:16]} == {0} and u[16][:2] == (0, 1)
+
+
+@pytest.mark.parametrize("tp,rank", [(2, 0), (2, 1), (4, 0), (4, 3), (8, 5)])
+def test_fused_launch_orders(cu, tp, rank):
+    M, N = 128 * 8 * tp, 2048
+    rows_per_rank_tiles = 8
+    for bn in (256, 128):
+        tiles_n = N // bn
+        ag = cu.gemm_work_units(M, N, bn=bn, fuse=1, tp=tp, rank=rank)
+        _coverage(ag, M, N, bn)
+        per_phase = rows_per_rank_tiles * tiles_n
+        for phase in range(tp):                 # all-gather: own shard first, then the shards in ring order
+            owners = {mt // rows_per_rank_tiles for mt, *_ in ag[phase * per_phase:(phase + 1) * per_phase]}
+            assert owners == {(rank + phase) % tp}
+        rs = cu.gemm_work_units(M, N, bn=bn, fuse=2, tp=tp, rank=rank)
+        _coverage(rs, M, N, bn)
+        first = [mt // rows_per_rank_tiles for mt, *_ in rs[:tp]]
+        assert sorted(first) == list(range(tp))           # reduce-scatter: consecutive tiles feed different owners
+        ring = cu.gemm_work_units(M, N, bn=bn, fuse=2, tp=tp, rank=rank, rs_ring=True)
+        _coverage(ring, M, N, bn)
+        assert {mt // rows_per_rank_tiles for mt, *_ in ring[:per_phase]} == {(rank + 1) % tp}
+        assert {mt // rows_per_rank_tiles for mt, *_ in ring[-per_phase:]} == {rank}
+
+
+@pytest.mark.parametrize("M,N", [(256, 256), (4096, 12288), (1000, 520), (384, 320), (22016, 4096), (4352, 1280)])
+def test_pair_kernel_tile_order(cu, M, N):
+    tiles = cu.gemm_pair_tiles(M, N)
+    tm, tn = (M + 255) // 256, (N + 255) // 256
+    assert sorted(tiles) == sorted(itertools.product(range(tm), range(tn)))
+    g = min(8, tm)
+    assert [t[0] for t in tiles[:g]] == list(range(g)) and {t[1] for t in tiles[:g]} == {0}
