@@ -52,6 +52,20 @@ __device__ long long* g_fa_trace = nullptr;   // [3 roles][64 steps][8 stages]
 #endif
 
 // registers are granted per 4 warps: 10 warps count as 12, which caps a thread at 168 registers
+// Tile plan of the forward kernel, __host__ __device__ so that ell_flash_fwd_plan can run the same arithmetic on the
+// host for a CPU test.  A query tile starting at row `first` walks key tiles of kFaN keys from kv_lo (the document
+// start of the first row of the CTA's tile pair) up to the tile's last row.
+__host__ __device__ __forceinline__ int fa_num_kv_tiles(int first, int T, int kv_lo) {
+  const int last = (first + kFaM < T ? first + kFaM : T) - 1;
+  return first < T ? (last + 1 - kv_lo + kFaN - 1) / kFaN : 0;
+}
+
+// A key tile starting at k0 needs no per-element mask when every key in it precedes (or is) the tile's first query
+// row and no row of the query tile starts its document after k0.
+__host__ __device__ __forceinline__ bool fa_tile_needs_mask(int k0, int tile_first, int max_row_start) {
+  return (k0 + kFaN - 1 > tile_first) || (k0 < max_row_start);
+}
+
 __global__ void __launch_bounds__(kFaThreads, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
@@ -75,11 +89,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   // key tiles each query tile walks: tile t covers keys kv_lo .. last row of the tile
   int n_kv[2];
 #pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int first = q0 + t * kFaM;
-    const int last = min(first + kFaM, T) - 1;
-    n_kv[t] = first < T ? (last + 1 - kv_lo + kFaN - 1) / kFaN : 0;
-  }
+  for (int t = 0; t < 2; ++t) n_kv[t] = fa_num_kv_tiles(q0 + t * kFaM, T, kv_lo);
   const int n_kv_max = max(n_kv[0], n_kv[1]);
 
   if (threadIdx.x == 0) {
@@ -240,7 +250,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_arrive(&sh->s_free[t]);               // S_t(j+1) may overwrite the columns now
       if (threadIdx.x == 64) FA_TRACE(1, j, 2);
       const int k0 = kv_lo + j * kFaN;
-      const bool need_mask = (k0 + kFaN - 1 > tile_first) || (k0 < max_row_start);
+      const bool need_mask = fa_tile_needs_mask(k0, tile_first, max_row_start);
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 128; ++i) {
@@ -354,6 +364,30 @@ ELL_API int ell_flash_fwd_set_trace(long long* buf) {
   return (int)cudaMemcpyToSymbol(ell::g_fa_trace, &buf, sizeof(buf));
 }
 #endif
+
+// Host-only: the forward kernel's plan for host-resident row_start [T], from the kernel's own arithmetic.  For every
+// CTA tile pair p (query rows 256p ..) and tile t in {0, 1}: out[(2p + t) * 3 + {0, 1, 2}] = first key row, number of
+// key tiles, and a bit mask (bit j set = key tile j is masked element-wise; only the first 31 tiles are recorded).
+ELL_API int ell_flash_fwd_plan(const int* row_start, int T, int* out) {
+  const int n_pairs = (T + 2 * kFaM - 1) / (2 * kFaM);
+  for (int p = 0; p < n_pairs; ++p) {
+    const int q0 = p * 2 * kFaM, kv_lo = row_start[q0];
+    for (int t = 0; t < 2; ++t) {
+      const int tile_first = q0 + t * kFaM;
+      const int n = fa_num_kv_tiles(tile_first, T, kv_lo);
+      const int last_row = (tile_first + kFaM < T ? tile_first + kFaM : T) - 1;
+      const int max_row_start = n > 0 ? row_start[last_row] : 0;
+      int bits = 0;
+      for (int j = 0; j < n && j < 31; ++j)
+        if (fa_tile_needs_mask(kv_lo + j * kFaN, tile_first, max_row_start)) bits |= 1 << j;
+      int* o = out + (2 * p + t) * 3;
+      o[0] = kv_lo;
+      o[1] = n;
+      o[2] = bits;
+    }
+  }
+  return n_pairs;
+}
 
 // q [T, Hq, 128] / k, v [T, Hk, 128] bf16 with row strides (in elements) q_stride / kv_stride (views
 // into the packed QKV GEMM output are fine); out [T, Hq, 128] contiguous; lse [Hq, T] fp32;

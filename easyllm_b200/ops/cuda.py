@@ -295,6 +295,19 @@ def gemm(a, b, out=None, bias=None, a_mn=False, b_mn=False, out_mode=0, bn=0, pa
     return out
 
 
+def flash_fwd_plan(row_start):
+    """Host-only: per (tile pair, tile) of the attention forward the first key row, the number of 128-key tiles it
+    walks and which of them are masked element-wise, from the kernel's own arithmetic (``row_start``: a list or CPU
+    int32 tensor with the document start of every token).  Returns ``[(kv_lo, n_tiles, mask_bits), ...]``."""
+    rs = [int(x) for x in row_start]
+    T = len(rs)
+    arr = (c_int * T)(*rs)
+    n_pairs = (T + 255) // 256
+    out = (c_int * (6 * n_pairs))()
+    lib().ell_flash_fwd_plan(arr, c_int(T), out)
+    return [tuple(out[3 * i:3 * i + 3]) for i in range(2 * n_pairs)]
+
+
 def gemm_work_units(M, N, bn=256, fuse=0, tp=1, rank=0, rs_ring=False, ctas=148, allow_split=True):
     """Host-only: the (row tile, column tile, first column, width) work units of a single-CTA GEMM launch in the
     order the kernel walks them, produced by the kernel's own tile-order code (no GPU is touched).

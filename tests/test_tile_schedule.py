@@ -80,3 +80,37 @@ def test_pair_kernel_tile_order(cu, M, N):
     assert sorted(tiles) == sorted(itertools.product(range(tm), range(tn)))
     g = min(8, tm)
     assert [t[0] for t in tiles[:g]] == list(range(g)) and {t[1] for t in tiles[:g]} == {0}
+
+
+def _row_starts(T, doc_lens):
+    rs, start = [], 0
+    for n in doc_lens:
+        rs += [start] * n
+        start += n
+    assert len(rs) == T
+    return rs
+
+
+@pytest.mark.parametrize("T,docs", [(512, [512]), (1000, [1000]), (1024, [100, 28, 128, 256, 1, 511]),
+                                    (777, [255, 2, 520]), (640, [129, 127, 128, 256]), (300, [300]),
+                                    (2048, [5] * 409 + [3]), (1536, [1, 1535])])
+def test_attention_forward_plan_covers_visible_keys_and_skips_masks_only_when_safe(cu, T, docs):
+    rs = _row_starts(T, docs)
+    plan = cu.flash_fwd_plan(rs)
+    assert len(plan) == 2 * ((T + 255) // 256)
+    for idx, (kv_lo, n, bits) in enumerate(plan):
+        first = (idx // 2) * 256 + (idx % 2) * 128
+        rows = range(first, min(first + 128, T))
+        if not rows:
+            assert n == 0
+            continue
+        assert kv_lo == rs[(idx // 2) * 256]
+        # every key a row may see lies inside the walked range, and the last walked tile is not wasted
+        assert all(kv_lo <= rs[i] and i < kv_lo + n * 128 for i in rows)
+        assert rows[-1] >= kv_lo + (n - 1) * 128
+        for j in range(min(n, 31)):
+            if bits >> j & 1:
+                continue
+            k0 = kv_lo + j * 128                # an unmasked tile: every (row, key) pair in it must be visible
+            assert k0 + 127 < T
+            assert all(rs[i] <= k0 and k0 + 127 <= i for i in rows), (idx, j)
