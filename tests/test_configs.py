@@ -6,7 +6,8 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 MEGATRON = sorted(glob.glob(os.path.join(ROOT, "configs", "megatron", "*.yaml")))
-HF = sorted(glob.glob(os.path.join(ROOT, "configs", "huggingface", "*.yaml")))
+HF = sorted(glob.glob(os.path.join(ROOT, "configs", "huggingface", "*.yaml"))
+            + glob.glob(os.path.join(ROOT, "configs", "huggingface", "inference", "*.yaml")))
 
 
 def _registered(registry, cfg, what, path):
