@@ -176,3 +176,72 @@ def test_batch_fn_masks_and_documents():
     fn = build_batch_pipe_fn({"type": "flash_batch_pipe"}, TOK)
     (t, p, m), (lab, lm) = fn({"input_ids": tok, "labels": tok})
     assert torch.equal(m, tok.ne(eod)) and torch.equal(lm, m)
+
+
+def test_preprocess_reward_mini_rlhf_parsers():
+    pre = build_parser("preprocess", dict(tokenizer=TOK, max_seq_length=64))
+    out = pre({"inputs": "question: ", "outputs": "answer"})
+    n_in = len(TOK.encode("question: "))
+    assert out["labels"][:n_in].tolist() == [-100] * n_in and out["labels"][-1] == TOK.eos_token_id
+    assert TOK.decode(out["input_ids"].tolist()) == "question: answer"
+    keep = build_parser("preprocess", dict(tokenizer=TOK, max_seq_length=64, keep_all_keys=True))({"inputs": "a", "outputs": "b"})
+    assert (keep["labels"] != -100).all()
+
+    rw = build_parser("reward", dict(tokenizer=TOK, max_seq_length=32))
+    good, bad = rw({"input_text": "prompt ", "choice": "nice", "bad_answer": "awful"})["input_ids"]
+    n_q = len(TOK.encode("prompt "))
+    assert good[:n_q].tolist() == bad[:n_q].tolist() and good[-1] == bad[-1] == TOK.eos_token_id
+    assert TOK.decode(good.tolist()) == "prompt nice" and TOK.decode(bad.tolist()) == "prompt awful"
+    rw_inf = build_parser("reward", dict(tokenizer=TOK, max_seq_length=8, inference_mode=True))
+    inf = rw_inf({"input_text": "a long prompt that is cut from the left", "choice": "ok"})
+    assert len(inf["input_ids"]) == 8 and TOK.decode(inf["input_ids"].tolist()).endswith("ok")
+    assert (inf["labels"][-2:] != -100).all() and (inf["labels"][:-2] == -100).all()
+
+    rl = build_parser("mini_rlhf", dict(tokenizer=TOK, max_seq_length=64))
+    out = rl({"question": "q? ", "answers": ["first", "second one"], "scores": [0.9, 0.1]})
+    assert len(out["input_ids"]) == 2 and torch.allclose(out["scores"], torch.tensor([0.9, 0.1]))
+    for ids, lab in zip(out["input_ids"], out["labels"]):
+        assert ids[-1] == TOK.eos_token_id and (lab[:len(TOK.encode("q? "))] == -100).all() and lab[-1] == TOK.eos_token_id
+    assert build_parser("mini_rlhf", dict(tokenizer=TOK, max_seq_length=64, inference_mode=True))({"question": "q"}) == "q"
+
+
+def test_intern_tools_and_combined_chat_parsers():
+    meta = {"messages": [{"role": "system", "content": "be useful"}, {"role": "user", "content": "plot x"},
+                         {"role": "assistant", "content": "running",
+                          "tool_calls": [{"function": {"name": "python_interpreter", "arguments": {"code": "print(1)"}}}]},
+                         {"role": "tool", "name": "python_interpreter", "content": "1"},
+                         {"role": "assistant", "content": "done"}],
+            "tools": [{"function": {"name": "search", "description": "web"}},
+                      {"function": {"name": "python_interpreter", "description": "py"}}],
+            "interpreter": [{"name": "python_interpreter", "description": "runs python"}]}
+    p = build_parser("intern_tools", dict(tokenizer=TOK, max_seq_length=2048))
+    out = p(meta)
+    text = TOK.decode(out["input_ids"].tolist())
+    assert text.startswith("<|im_start|>system\nbe useful<|im_end|>\n")
+    assert "system name=<|interpreter|>\nruns python" in text and 'system name=<|plugin|>\n[{"name": "search"' in text
+    assert "python_interpreter" not in text.split("<|plugin|>")[1].split("<|im_end|>")[0]     # not listed as a plugin
+    assert "<|action_start|><|interpreter|>\nprint(1)\n<|action_end|>" in text
+    assert "environment name=<|interpreter|>\n1<|im_end|>" in text and text.rstrip().endswith("done<|im_end|>")
+    learned = TOK.decode(out["input_ids"][out["labels"] != -100].tolist())
+    assert "running" in learned and "done" in learned and "plot x" not in learned and "be useful" not in learned
+    toks, labels = build_parser("intern_tools", dict(tokenizer=TOK, max_seq_length=2048, inference_mode=True))(meta["messages"][:2])
+    assert TOK.decode(toks).endswith("<|im_start|>assistant\n") and labels == []
+    try:
+        p({"messages": [], "interpreter": [{"name": "bash", "description": ""}]})
+        raise AssertionError("a non-python interpreter must be rejected")
+    except ValueError:
+        pass
+
+    conv = [{"role": "user", "content": "one"}, {"role": "assistant", "content": "first"},
+            {"role": "user", "content": "two"}, {"role": "assistant", "content": "second"}]
+    comb = build_parser("combine_general_chat", dict(tokenizer=TOK, max_seq_length=512))
+    plain = build_parser("general_chat", dict(tokenizer=TOK, max_seq_length=512))
+
+    def learned_text(o):
+        return TOK.decode(o["input_ids"][o["labels"] != -100].tolist())
+    assert torch.equal(comb(conv)["labels"], plain(conv)["labels"])                      # no per-record switch
+    last = comb({"only_last_answer": True, "convs": conv})
+    assert "second" in learned_text(last) and "first" not in learned_text(last)
+    everything = comb({"keep_all_keys": True, "convs": conv})
+    assert (everything["labels"] != -100).sum() > (plain(conv)["labels"] != -100).sum()
+    assert "one" in learned_text(everything)
