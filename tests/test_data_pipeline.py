@@ -245,3 +245,95 @@ def test_intern_tools_and_combined_chat_parsers():
     everything = comb({"keep_all_keys": True, "convs": conv})
     assert (everything["labels"] != -100).sum() > (plain(conv)["labels"] != -100).sum()
     assert "one" in learned_text(everything)
+
+
+def test_reward_and_mini_rlhf_collators_and_batch_fns():
+    from easyllm_b200.config.registry import BATCH_COLLECTOR_REGISTRY
+    pad = len(TOK) - 1
+    rw = build_parser("reward", dict(tokenizer=TOK, max_seq_length=32))
+    items = [rw({"input_text": "p ", "choice": "good answer", "bad_answer": "bad"}),
+             rw({"input_text": "another prompt ", "choice": "y", "bad_answer": "nope nope"})]
+    coll = BATCH_COLLECTOR_REGISTRY.build({"type": "reward_batch", "kwargs": {"tokenizer": TOK, "max_seq_length": 32}})
+    b = coll(items)
+    # chosen sequences first, rejected second, one common width
+    assert b["input_ids"].shape[0] == 4 and b["input_ids"].shape == b["labels"].shape
+    assert b["input_ids"][0, :len(items[0]["input_ids"][0])].tolist() == items[0]["input_ids"][0].tolist()
+    assert b["input_ids"][2, :len(items[0]["input_ids"][1])].tolist() == items[0]["input_ids"][1].tolist()
+    assert torch.equal(b["attention_mask"], b["input_ids"].ne(pad)) and (b["labels"][b["input_ids"] == pad] == -100).all()
+
+    rl = build_parser("mini_rlhf", dict(tokenizer=TOK, max_seq_length=64))
+    ritems = [rl({"question": "q1 ", "answers": ["a", "bb"], "scores": [1.0, 0.0]}),
+              rl({"question": "q2 is longer ", "answers": ["ccc", "d"], "scores": [0.3, 0.7]})]
+    rcoll = BATCH_COLLECTOR_REGISTRY.build({"type": "mini_rlhf_batch", "kwargs": {"tokenizer": TOK, "alignment": 8,
+                                                                                  "max_seq_length": 64}})
+    rb = rcoll(ritems)
+    assert rb["input_ids"].shape[0] == 4 and rb["input_ids"].shape[1] % 8 == 0
+    assert torch.allclose(rb["scores"], torch.tensor([1.0, 0.0, 0.3, 0.7]))
+    fn = build_batch_pipe_fn({"type": "mini_rlhf_json_batch_pipe"}, TOK)
+    (tokens, pos, mask), (labels, loss_mask, scores) = fn(rb)
+    assert torch.equal(tokens, rb["input_ids"]) and torch.allclose(scores, rb["scores"])
+    assert pos[0].tolist() == list(range(tokens.shape[1])) and loss_mask.shape == tokens.shape
+    assert (loss_mask[tokens == pad] == 0).all()
+
+    jf = build_batch_pipe_fn({"type": "json_batch_pipe", "kwargs": {"dense_mask": True}}, TOK)
+    ids = torch.tensor([[5, 6, 7, pad]])
+    (t, p, m), (lab, lm) = jf({"input_ids": ids, "labels": ids})
+    assert m.shape == (1, 1, 4, 4) and bool(m[0, 0, 0, 1]) and not bool(m[0, 0, 2, 1])        # True = masked, causal
+    assert lm.tolist() == [[1.0, 1.0, 1.0, 0.0]]
+    hf = build_batch_pipe_fn({"type": "json_batch_pipe", "kwargs": {"dense_mask": True, "hf_atten_mask": True}}, TOK)
+    (_, _, mh), _ = hf({"input_ids": ids, "labels": ids})
+    assert bool(mh[0, 0, 3, 3]) and not bool(mh[0, 0, 2, 2])                                  # the padded key is masked
+
+    tf = build_batch_pipe_fn({"type": "token_batch_pipe", "kwargs": {"micro_batch_size": 2}}, TOK)
+    flat = torch.arange(10, 18)
+    (t, p, _), (lab, lm) = tf(flat)
+    t, lab = t.cpu(), lab.cpu()
+    assert t.tolist() == [[10, 11, 12, 13], [14, 15, 16, 17]]
+    assert lab.tolist() == [[11, 12, 13, TOK.eos_token_id], [15, 16, 17, TOK.eos_token_id]]
+
+
+def test_dist_samplers_and_infinite_batches():
+    from easyllm_b200.data.samplers import DistributedSampler, InfiniteBatchSampler, TestDistributedSampler
+    # evaluation sampler: a strided split without padding
+    parts = [list(TestDistributedSampler(10, r, 3)) for r in range(3)]
+    assert parts == [[0, 3, 6, 9], [1, 4, 7], [2, 5, 8]]
+    # training sampler: the ranks see disjoint slices of one seeded permutation, padded to equal length
+    full = [list(DistributedSampler(10, r, 4)) for r in range(4)]
+    assert all(len(p) == 3 for p in full) and len({i for p in full for i in p}) == 10
+    # resume inside an epoch: rank 1 continues where 4 globally consumed samples left it
+    s = DistributedSampler(10, 1, 4)
+    s.set_consumed_samples(4)
+    assert list(s) == full[1][1:]
+    # next epoch uses another permutation
+    s.set_consumed_samples(12)
+    nxt = list(s)
+    assert len(nxt) == 3 and s.epoch == 1 and nxt != full[1]
+    bs = build_batch_sampler({"type": "base", "kwargs": {"sampler": {"type": "dist"}, "total_samples": 10,
+                                                         "data_parallel_rank": 0, "data_parallel_size": 2,
+                                                         "micro_batch_size": 2}})
+    assert isinstance(bs, InfiniteBatchSampler)
+    it = iter(bs)
+    got = [next(it) for _ in range(5)]                  # 5 samples per rank and epoch: batches of 2, 2, 1, then epoch 2
+    assert [len(b) for b in got] == [2, 2, 1, 2, 2] and bs.consumed_samples == 18
+    again = build_batch_sampler({"type": "base", "kwargs": {"sampler": {"type": "dist"}, "total_samples": 10,
+                                                            "data_parallel_rank": 0, "data_parallel_size": 2,
+                                                            "micro_batch_size": 2}})
+    again.set_consumed_samples(4)
+    assert next(iter(again)) == got[1]
+
+
+def test_rampup_batch_size_calculator():
+    from easyllm_b200.config.registry import BATCH_CALCULATOR_REGISTRY
+    import easyllm_b200.optim  # noqa: F401
+    calc = BATCH_CALCULATOR_REGISTRY.build({"type": "rampup_batch_size_num", "kwargs": {
+        "start_batch_size": 4, "batch_size_increment": 4, "ramup_samples": 40, "global_batch_size": 16,
+        "micro_batch_size": 2}})
+    seen = []
+    for consumed in (0, 9, 14, 27, 28, 41, 1000):
+        calc.update(consumed, False)
+        seen.append((calc.get_current_global_batch_size(), calc.get()))
+    # three increments over 40 samples: a step every 40/3 samples; micro-batches = global / (micro * dp), dp = 1 here
+    assert seen == [(4, 2), (4, 2), (8, 4), (12, 6), (12, 6), (16, 8), (16, 8)]
+    from easyllm_b200.optim.microbatches import get_train_iters
+    # 4 + 4 + 4 + 4 (consumed 16 -> 8) + 8 + 8 (32 -> 12) + 12 (44 > 40) then 16 per step
+    assert get_train_iters(calc, train_samples=44 + 5 * 16) == 7 + 5
