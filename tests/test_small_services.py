@@ -1,0 +1,137 @@
+"""Small services without a test of their own: sharded grad scaler, fast_init, named scratch buffers, timers,
+TP input broadcast, padded data gather over DP, pickled-object collectives (CPU / gloo)."""
+import time
+
+import torch
+
+from dist_utils import run_ranks
+
+
+def test_sharded_grad_scaler_skips_and_backs_off():
+    from easyllm_b200.optim.grad_scaler import ShardedGradScaler
+    p = torch.nn.Parameter(torch.tensor([1.0, 2.0]))
+    opt = torch.optim.SGD([p], lr=0.5)
+    sc = ShardedGradScaler(init_scale=8.0, growth_interval=2)
+    sc.scale((p * torch.tensor([1.0, 3.0])).sum()).backward()
+    assert p.grad.tolist() == [8.0, 24.0]
+    sc.unscale_(opt)
+    sc.unscale_(opt)                                   # second call in the same step is a no-op
+    assert p.grad.tolist() == [1.0, 3.0]
+    sc.step(opt); sc.update()
+    assert p.detach().tolist() == [0.5, 0.5] and sc.get_scale() == 8.0
+    opt.zero_grad()
+    p.grad = torch.tensor([float("inf"), 1.0])
+    before = p.detach().clone()
+    assert sc.step(opt) is None                        # step skipped on overflow
+    sc.update()
+    assert torch.equal(p.detach(), before) and sc.get_scale() == 4.0
+    for _ in range(2):                                 # two clean steps grow the scale again
+        p.grad = torch.tensor([4.0, 4.0])
+        sc.step(opt); sc.update()
+    assert sc.get_scale() == 8.0
+    other = ShardedGradScaler()
+    other.load_state_dict(sc.state_dict())
+    assert other.get_scale() == 8.0
+    off = ShardedGradScaler(enabled=False)
+    assert off.get_scale() == 1.0 and off.scale(torch.tensor(3.0)).item() == 3.0 and off.state_dict() == {}
+
+
+def _scaler_rank(rank, world):
+    from easyllm_b200.optim.grad_scaler import ShardedGradScaler
+    p = torch.nn.Parameter(torch.ones(2))
+    opt = torch.optim.SGD([p], lr=1.0)
+    sc = ShardedGradScaler(init_scale=2.0)
+    p.grad = torch.tensor([float("nan") if rank == 1 else 2.0, 2.0])
+    out = sc.step(opt)
+    sc.update()
+    return out is None, p.detach().tolist(), sc.get_scale()
+
+
+def test_sharded_grad_scaler_agrees_across_ranks():
+    res = run_ranks(2, _scaler_rank)
+    # only rank 1 overflowed, both ranks skip the step and halve the scale
+    assert all(skipped and w == [1.0, 1.0] and s == 1.0 for skipped, w, s in res)
+
+
+def test_fast_init_skips_allocation_and_random_init():
+    from easyllm_b200.utils.fast_init import fast_init, materialize
+    with fast_init():
+        m = torch.nn.Sequential(torch.nn.Embedding(1000, 64), torch.nn.Linear(64, 64), torch.nn.LayerNorm(64))
+    assert all(p.is_meta for p in m.parameters())
+    m = materialize(m, "cpu")
+    assert not any(p.is_meta for p in m.parameters()) and m[1].weight.shape == (64, 64)
+    after = torch.nn.Linear(4, 4)                       # the patch is gone after the context
+    assert not after.weight.is_meta and after.weight.abs().sum() > 0
+    with fast_init(device="cpu"):
+        t0 = time.time()
+        big = torch.nn.Linear(2048, 2048)
+        assert time.time() - t0 < 1.0 and not big.weight.is_meta
+
+
+def test_global_memory_buffer_reuses_and_grows():
+    from easyllm_b200.parallel.buffers import GlobalMemoryBuffer
+    buf = GlobalMemoryBuffer()
+    a = buf.get_tensor((4, 8), torch.float32, "ag", device="cpu")
+    b = buf.get_tensor((2, 8), torch.float32, "ag", device="cpu")
+    assert a.data_ptr() == b.data_ptr() and b.shape == (2, 8)
+    c = buf.get_tensor((8, 8), torch.float32, "ag", device="cpu")
+    assert c.numel() == 64
+    d = buf.get_tensor((4, 8), torch.bfloat16, "ag", device="cpu")
+    assert d.dtype == torch.bfloat16 and d.data_ptr() != c.data_ptr()
+    buf.clear()
+    assert buf._bufs == {}
+
+
+def test_timers_and_memory_report():
+    from easyllm_b200.utils.timers import Timers, report_memory
+    t = Timers()
+    t("step").start(); time.sleep(0.02); t("step").stop()
+    t("step").start(); time.sleep(0.02); t("step").stop()
+    e = t("step").elapsed(reset=False)
+    assert 0.03 < e < 0.5
+    assert t("step").elapsed() == e and t("step").elapsed() == 0.0       # reset by the second read
+    lines = []
+    report_memory("after step", printer=lines.append)
+    assert len(lines) <= 1                              # one line on a GPU, nothing on a CPU-only host
+
+
+def _tp_broadcast(rank, world):
+    from easyllm_b200.parallel.data import broadcast_data
+    from easyllm_b200.parallel.grid import get_grid, initialize_model_parallel
+    from easyllm_b200.parallel.mappings import data_gather
+    initialize_model_parallel(2, 1)                    # tp 2, dp 2
+    g = get_grid()
+    data = None
+    if g.tp_rank == 0:
+        data = {"input_ids": torch.arange(12).view(2, 6) + 100 * g.dp_rank, "labels": torch.arange(6).view(1, 6)}
+    out = broadcast_data(["input_ids", "labels"], data, torch.int64)
+    x = torch.full((g.dp_rank + 1, 3), float(g.dp_rank))
+    parts = data_gather(x, dst=0)
+    return (g.tp_rank, g.dp_rank, out["input_ids"].tolist(), out["labels"].tolist(),
+            None if parts is None else [p.tolist() for p in parts])
+
+
+def test_tp_input_broadcast_and_dp_padded_gather():
+    res = run_ranks(4, _tp_broadcast)
+    for tp_rank, dp_rank, ids, labels, parts in res:
+        assert ids == (torch.arange(12).view(2, 6) + 100 * dp_rank).tolist() and labels == [list(range(6))]
+        if dp_rank == 0:
+            assert parts == [[[0.0] * 3], [[1.0] * 3, [1.0] * 3]]      # unpadded per-rank tensors on the destination
+        else:
+            assert parts is None
+
+
+def _objects(rank, world):
+    from easyllm_b200.parallel import hf_dist
+    everyone = hf_dist.all_gather_object({"rank": rank, "payload": list(range(rank))})
+    only0 = hf_dist.gather_pk(("r", rank))
+    b = hf_dist.broadcast_object({"cfg": rank} if rank == 0 else None)
+    return everyone, only0, b, hf_dist.get_rank(), hf_dist.get_world_size()
+
+
+def test_pickled_object_collectives():
+    res = run_ranks(3, _objects)
+    for rank, (everyone, only0, b, r, w) in enumerate(res):
+        assert [e["rank"] for e in everyone] == [0, 1, 2] and everyone[2]["payload"] == [0, 1]
+        assert (only0 == [("r", 0), ("r", 1), ("r", 2)]) if rank == 0 else only0 is None
+        assert b == {"cfg": 0} and r == rank and w == 3
