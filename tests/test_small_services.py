@@ -135,3 +135,58 @@ def test_pickled_object_collectives():
         assert [e["rank"] for e in everyone] == [0, 1, 2] and everyone[2]["payload"] == [0, 1]
         assert (only0 == [("r", 0), ("r", 1), ("r", 2)]) if rank == 0 else only0 is None
         assert b == {"cfg": 0} and r == rank and w == 3
+
+
+def test_storage_helper_local_paths_pointer_files_and_fake_remote(tmp_path, monkeypatch):
+    import json
+    import pytest
+    from easyllm_b200.utils.petrel_helper import PetrelHelper, get_ceph_path
+    # local paths: save creates folders, load / exists / listdir / open / load_json work on files
+    target = tmp_path / "a" / "b" / "w.pt"
+    PetrelHelper.save({"w": torch.arange(3)}, str(target))
+    assert PetrelHelper.exists(str(target)) and PetrelHelper.listdir(str(tmp_path / "a" / "b")) == ["w.pt"]
+    assert PetrelHelper.load(str(target))["w"].tolist() == [0, 1, 2]
+    (tmp_path / "c.json").write_text(json.dumps({"k": 1}))
+    assert PetrelHelper.load_json(str(tmp_path / "c.json")) == {"k": 1}
+    # pointer files: `<path>.ceph` / `<path>.ini` name the real location on their first line
+    (tmp_path / "ckpt.ceph").write_text(str(target) + "\nsecond line ignored\n")
+    assert PetrelHelper.resolve(str(tmp_path / "ckpt")) == str(target)
+    assert PetrelHelper.load(str(tmp_path / "ckpt"))["w"].tolist() == [0, 1, 2]
+    (tmp_path / "link.ini").write_text(str(tmp_path / "c.json"))
+    assert PetrelHelper.load_json(str(tmp_path / "link.ini")) == {"k": 1}
+    assert PetrelHelper.resolve(str(tmp_path / "plain")) == str(tmp_path / "plain")
+    # bucket prefixing
+    assert get_ceph_path("./ckpt/step1", "s3://bucket/run/") == "s3://bucket/run/ckpt/step1"
+    assert get_ceph_path("ckpt/step1", "") == "ckpt/step1"
+    monkeypatch.setenv("CEPHBUCKET", "s3://b")
+    assert get_ceph_path("/x/y") == "s3://b/x/y"
+    # s3:// without the SDK is a clear error; with a client (a fake here) every call goes through it
+    assert PetrelHelper.is_remote("s3://bucket/x") and not PetrelHelper.is_remote(str(target))
+    monkeypatch.setattr(PetrelHelper, "_client", None)
+    with pytest.raises(RuntimeError, match="petrel_client"):
+        PetrelHelper.load("s3://bucket/x.pt")
+
+    class FakeClient:
+        def __init__(self):
+            self.store = {}
+
+        def put(self, k, v):
+            self.store[k] = v
+
+        def get(self, k):
+            return self.store[k]
+
+        def contains(self, k):
+            return k in self.store
+
+        def list(self, prefix):
+            return [k[len(prefix):] for k in self.store if k.startswith(prefix)]
+    fake = FakeClient()
+    monkeypatch.setattr(PetrelHelper, "_client", fake)
+    PetrelHelper.save({"w": torch.ones(2)}, "s3://bucket/run/w.pt")
+    assert PetrelHelper.exists("s3://bucket/run/w.pt") and PetrelHelper.listdir("s3://bucket/run/") == ["w.pt"]
+    assert PetrelHelper.load("s3://bucket/run/w.pt")["w"].tolist() == [1.0, 1.0]
+    fake.put("s3://bucket/c.json", b'{"r": 2}')
+    assert PetrelHelper.load_json("s3://bucket/c.json") == {"r": 2}
+    (tmp_path / "remote.ceph").write_text("s3://bucket/run/w.pt")
+    assert PetrelHelper.load(str(tmp_path / "remote"))["w"].tolist() == [1.0, 1.0]
