@@ -205,3 +205,50 @@ data:
     assert len(ds) >= 20 and ds[0]["input_ids"].shape[0] == 33
     after = {p.name: p.stat().st_mtime_ns for p in (tmp_path / "train_data_cache").iterdir()}
     assert all(after[k] == v for k, v in before.items() if k.endswith(".bin"))
+
+
+def test_medusa_runner_trains_heads_only_and_answers_questions(tmp_path):
+    """MedusaRunner end to end on CPU: only the extra heads train, the checkpoint is ``medusa_lm_head.pth``, and
+    inference over a question file writes one result per question with acceptance statistics."""
+    import copy
+    import json
+    import os
+    from easyllm_b200.config import load_yaml, parse_args
+    from easyllm_b200.runners.medusa_runner import MedusaRunner
+    cfg_path = os.path.join(os.path.dirname(__file__), "..", "configs", "huggingface", "tiny_llama_cpu.yaml")
+    cfg = load_yaml(cfg_path)
+    with open(tmp_path / "d.jsonl", "w") as f:
+        for i in range(32):
+            f.write(json.dumps({"instruction": f"question number {i}", "input": "", "output": f"answer {i % 5}"}) + "\n")
+    cfg["data"]["train"]["dataset"]["kwargs"]["json_file"] = str(tmp_path / "d.jsonl")
+    cfg["saver"] = {"enabled": True, "save_path": str(tmp_path / "ck"), "save_interval": 3, "save_mode": "huggingface"}
+    cfg["trainer"]["train_iters"] = 3
+    cfg["hooks"] = [h for h in cfg.get("hooks", []) if h["type"] != "dynamic_checkpoint"]
+    cfg["model"] = {"type": "medusa", "kwargs": {"base_model": copy.deepcopy(cfg["model"]), "medusa_num_heads": 2,
+                                                  "medusa_num_layers": 1}}
+    r = MedusaRunner(parse_args(["--config", cfg_path]), cfg, training=True)
+    trainable = [n for n, p in r.model.named_parameters() if p.requires_grad]
+    assert trainable and all(n.startswith("medusa_head") for n in trainable)
+    base_before = {n: p.detach().clone() for n, p in r.model.base_model.named_parameters()}
+    head_before = {n: p.detach().clone() for n, p in r.model.medusa_head.named_parameters()}
+    r.train()
+    assert all(torch.equal(p.detach().float(), base_before[n].float()) for n, p in r.model.base_model.named_parameters())
+    assert any(not torch.equal(p.detach().float(), head_before[n].float()) for n, p in r.model.medusa_head.named_parameters())
+    saved = tmp_path / "ck" / "checkpoint-3" / "medusa_lm_head.pth"
+    assert saved.exists() and set(torch.load(saved)) == set(r.model.medusa_head.state_dict())
+
+    with open(tmp_path / "q.jsonl", "w") as f:
+        f.write(json.dumps({"instruction": "question number 1", "input": "", "output": "answer 1"}) + "\n")
+        f.write(json.dumps({"instruction": "another", "input": " one", "output": "x"}) + "\n")
+    cfg2 = copy.deepcopy(cfg)
+    cfg2["infer_cfg"] = {"question_file": str(tmp_path / "q.jsonl"), "result_file": str(tmp_path / "res.jsonl")}
+    cfg2["model"]["kwargs"]["medusa_head_name_or_path"] = str(saved)
+    cfg2["infer_tokenization"] = {"type": "sense_tokenization", "kwargs": {
+        "max_seq_length": 128, "parser_type": "simple_chat", "parser_kwargs": {"inference_mode": True}}}
+    args = parse_args(["--config", cfg_path, "--inference", "--medusa-generate", "--medusa-max-steps", "4",
+                       "--medusa-choices", "mc_sim_7b_3_head_top5"])
+    r2 = MedusaRunner(args, cfg2, training=False)
+    res = r2.infer()
+    lines = [json.loads(l) for l in open(tmp_path / "res.jsonl")]
+    assert len(res) == len(lines) == 2 and lines[1]["input"] == "another one" and lines[0]["answer"] == "answer 1"
+    assert all(l["infos"]["count"] >= 1 and l["infos"]["accept_length"] >= l["infos"]["count"] for l in lines)
