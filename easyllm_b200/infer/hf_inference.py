@@ -56,7 +56,9 @@ def hf_inference(infer_cfg, model, tokenizer, cfg_tokenization, device, args=Non
         results = []
         for i in range(rank, len(ds), world):
             item = ds[i]
-            results.append(dict(item["meta"], id=i, answer=generate_text(model, tokenizer, item["tokens"], device, gen_cfg)))
+            # `answer` becomes the model's reply; the reference answer of the question file is kept as `gold`
+            results.append(dict(item["meta"], id=i, gold=item["meta"].get("answer", ""),
+                                answer=generate_text(model, tokenizer, item["tokens"], device, gen_cfg)))
         if world > 1:
             from ..parallel.hf_dist import all_gather_object
             results = [r for part in all_gather_object(results) for r in part]

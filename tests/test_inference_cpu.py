@@ -120,3 +120,41 @@ def test_infer_logp_matches_log_softmax(tmp_path):
             want = torch.where(lab >= 0, lp.gather(1, lab.clamp(min=0)[:, None]).squeeze(1), torch.zeros(16))
             assert torch.allclose(torch.tensor(r["logp"]), want, atol=1e-4)
             assert r["logp"][:3] == [0.0, 0.0, 0.0]
+
+
+def test_hf_inference_interactive_and_question_file(tmp_path):
+    """The HF runner's inference loops on a tiny model: the interactive loop keeps / clears history and stops at
+    ``quit``; the evaluation loop writes one line per question and keeps the reference answer next to the reply."""
+    import json
+    import torch
+    from easyllm_b200.data import SimpleTokenizer
+    from easyllm_b200.infer.hf_inference import hf_inference
+    from easyllm_b200.models.hf_models import CausalLM, HFArch
+    torch.manual_seed(0)
+    tok = SimpleTokenizer(vocab_size=300)
+    model = CausalLM(HFArch(family="llama", vocab_size=300, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                            num_attention_heads=4)).eval()
+    cfg_tok = {"type": "sense_tokenization", "kwargs": {"max_seq_length": 256, "parser_type": "simple_chat",
+                                                       "parser_kwargs": {"inference_mode": True}}}
+    seen = []
+    orig = model.generate
+
+    def spy(ids, **kw):
+        seen.append(ids.shape[1])
+        return orig(ids, **kw)
+    model.generate = spy
+    script = iter(["first question", "second question", "clean", "third", "quit"])
+    hf_inference({"generation_cfg": {"max_new_tokens": 3}}, model, tok, cfg_tok, torch.device("cpu"),
+                 input_fn=lambda: next(script))
+    # the second prompt carries the first exchange as history, the one after `clean` does not
+    assert len(seen) == 3 and seen[1] > seen[0] and seen[2] < seen[1]
+
+    with open(tmp_path / "q.jsonl", "w") as f:
+        f.write(json.dumps({"instruction": "what is 1+1", "input": "", "output": "2"}) + "\n")
+        f.write(json.dumps({"instruction": "capital of", "input": " France", "output": "Paris"}) + "\n")
+    icfg = {"infer_type": "eval", "eval_task": "base", "question_file": str(tmp_path / "q.jsonl"),
+            "result_file": str(tmp_path / "out.jsonl"), "generation_cfg": {"max_new_tokens": 2}}
+    hf_inference(icfg, model, tok, cfg_tok, torch.device("cpu"))
+    rows = [json.loads(l) for l in open(tmp_path / "out.jsonl")]
+    assert [r["id"] for r in rows] == [0, 1] and rows[1]["input"] == "capital of France"
+    assert [r["gold"] for r in rows] == ["2", "Paris"] and all(isinstance(r["answer"], str) for r in rows)
