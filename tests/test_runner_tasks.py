@@ -1,0 +1,94 @@
+"""Megatron runner on CPU through the task-specific data paths: SFT from json chat records, offline DPO pairs with
+reference log-probabilities, mini-RLHF ranked answers (parser → collator → batch function → loss, from YAML)."""
+import copy
+import json
+import os
+
+from dist_utils import run_ranks
+
+CFG = os.path.join(os.path.dirname(__file__), "..", "configs", "megatron", "tiny_llama_cpu.yaml")
+
+
+def _run(rank, world, cfg, iters):
+    from easyllm_b200.config import parse_args
+    from easyllm_b200.runners.base_llm_runner import BaseRunner
+    cfg = copy.deepcopy(cfg)
+    cfg["trainer"]["train_iters"] = iters
+    args = parse_args(["--config", CFG, "--launcher", "torch", "--distributed-backend", "gloo"])
+    r = BaseRunner(args, cfg, training=True, base_type="train")
+    seen = []
+    orig = r.forward_step
+
+    def rec(it):
+        out = orig(it)
+        seen.append({k: float(v) for k, v in out.items()})
+        return out
+    r.forward_step = rec
+    r.train()
+    return seen
+
+
+def _base_cfg(tmp_path, parser_type, parser_kwargs=None):
+    from easyllm_b200.config import load_yaml
+    cfg = load_yaml(CFG)
+    tok = {"type": "sense_tokenization", "kwargs": {"max_seq_length": 128, "parser_type": parser_type,
+                                                    "parser_kwargs": parser_kwargs or {}}}
+    cfg["data"]["train"]["dataset"] = {"type": "base_nlp_json", "kwargs": {
+        "json_file": str(tmp_path / "d.jsonl"), "transformer": [tok], "json_type": "line"}}
+    cfg["saver"]["save_path"] = str(tmp_path / "ck")
+    cfg["saver"]["save_interval"] = 1000
+    cfg["loader"]["load_path"] = None
+    return cfg
+
+
+def test_sft_from_chat_records(tmp_path):
+    with open(tmp_path / "d.jsonl", "w") as f:
+        for i in range(64):
+            f.write(json.dumps({"messages": [{"role": "user", "content": f"say the number {i % 4}"},
+                                             {"role": "assistant", "content": f"the number is {i % 4}"}]}) + "\n")
+    cfg = _base_cfg(tmp_path, "simple_chat")
+    cfg["data"]["train"]["batch_pipe"] = {"type": "json_batch_pipe", "kwargs": {}}
+    seen = run_ranks(1, _run, cfg, 6)[0]
+    assert len(seen) == 6 and all("lm_loss" in s for s in seen) and seen[-1]["lm_loss"] < seen[0]["lm_loss"]
+
+
+def test_offline_dpo_pairs(tmp_path):
+    good = [{"role": "user", "content": "pick a colour"}, {"role": "assistant", "content": "blue is calm"}]
+    bad = [{"role": "user", "content": "pick a colour"}, {"role": "assistant", "content": "no"}]
+    # per-token reference log-probabilities as `infer_logp` writes them: one value per token after the first
+    from easyllm_b200.data import SimpleTokenizer, build_parser
+    chat = build_parser("general_chat", dict(tokenizer=SimpleTokenizer(vocab_size=32000), max_seq_length=128))
+    n_w, n_l = len(chat(good)["input_ids"]), len(chat(bad)["input_ids"])
+    with open(tmp_path / "d.jsonl", "w") as f:
+        for i in range(64):
+            f.write(json.dumps({"yw": good, "yl": bad, "yw_logp": [-2.0] * (n_w - 1), "yl_logp": [-2.5] * (n_l - 1)}) + "\n")
+    cfg = _base_cfg(tmp_path, "combine_dpo_general_chat")
+    cfg["data"]["train"]["batch_pipe"] = {"type": "mini_rlhf_json_batch_pipe", "kwargs": {}}
+    cfg["data"]["train"]["batch_collector"] = {"type": "mini_rlhf_batch", "kwargs": {"alignment": 4, "max_seq_length": 128}}
+    cfg["data"]["train"]["micro_batch_size"] = 1
+    cfg["data"]["train"]["batch_sampler"]["kwargs"]["micro_batch_size"] = 1
+    cfg["data"]["train"]["batch_calculator"]["kwargs"].update(micro_batch_size=1, global_batch_size=2)
+    cfg["data"]["train"]["global_batch_size"] = 2
+    cfg["model"]["kwargs"]["loss_params"] = {"type": "dpo_loss", "kwargs": {"beta": 0.1}}
+    seen = run_ranks(1, _run, cfg, 4)[0]
+    assert len(seen) == 4
+    keys = set(seen[0])
+    assert any("loss" in k for k in keys), keys
+    assert all(v == v for s in seen for v in s.values())                    # finite
+
+
+def test_mini_rlhf_ranked_answers(tmp_path):
+    with open(tmp_path / "d.jsonl", "w") as f:
+        for i in range(64):
+            f.write(json.dumps({"question": f"question {i % 3}? ", "answers": ["a good answer", "bad"],
+                                "scores": [0.9, 0.1]}) + "\n")
+    cfg = _base_cfg(tmp_path, "mini_rlhf")
+    cfg["data"]["train"]["batch_pipe"] = {"type": "mini_rlhf_json_batch_pipe", "kwargs": {}}
+    cfg["data"]["train"]["batch_collector"] = {"type": "mini_rlhf_batch", "kwargs": {"alignment": 8, "max_seq_length": 128}}
+    cfg["data"]["train"]["micro_batch_size"] = 1
+    cfg["data"]["train"]["batch_sampler"]["kwargs"]["micro_batch_size"] = 1
+    cfg["data"]["train"]["batch_calculator"]["kwargs"].update(micro_batch_size=1, global_batch_size=2)
+    cfg["data"]["train"]["global_batch_size"] = 2
+    cfg["model"]["kwargs"]["loss_params"] = {"type": "mini_rlhf_entropy", "kwargs": {"sentense_pairs": 2}}
+    seen = run_ranks(1, _run, cfg, 4)[0]
+    assert len(seen) == 4 and all(v == v for s in seen for v in s.values())
