@@ -55,9 +55,26 @@ class BaseRunner:
         self.build_data_engine()
 
     # ---- configuration ------------------------------------------------------------------------
+    def _default_infer_data(self):
+        """``data.infer`` of a config written for training only: interactive generation, one prompt per batch,
+        the token batch function (what the reference's SFT configs spell out in their ``infer`` block)."""
+        data = self.config["data"]
+        train = data.get("train") or {}
+        data["infer"] = {"seq_length": train.get("seq_length", 2048), "global_batch_size": 1, "micro_batch_size": 1,
+                         "infer_type": "interactive",
+                         "batch_pipe": {"type": "token_batch_pipe",
+                                        "kwargs": {"reset_position_ids": False, "reset_attention_mask": False,
+                                                   "eod_mask_loss": False, "loss_on_targets_only": False}}}
+        logger.info("config has no data.infer section: using interactive generation with token_batch_pipe")
+
     def set_param_components(self):
         self.start_iteration = self.consumed_train_samples = self.consumed_train_tokens = 0
         rt = self.config["runtime"]
+        if self.base_type == "infer":
+            if "infer" not in self.config["data"]:
+                self._default_infer_data()
+            # inference never touches the training data: build only the infer entry
+            self.config["data"]["data_types"] = ["infer"]
         self.deepspeed = rt.get("deepspeed", True)
         cfg_ds = self.config.get("deepspeed") or {"config": {}}
         cfg_ds.setdefault("config", {})

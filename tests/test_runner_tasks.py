@@ -92,3 +92,36 @@ def test_mini_rlhf_ranked_answers(tmp_path):
     cfg["model"]["kwargs"]["loss_params"] = {"type": "mini_rlhf_entropy", "kwargs": {"sentense_pairs": 2}}
     seen = run_ranks(1, _run, cfg, 4)[0]
     assert len(seen) == 4 and all(v == v for s in seen for v in s.values())
+
+
+def _interactive(rank, world, cfg):
+    import builtins
+    from easyllm_b200.config import parse_args
+    from easyllm_b200.runners.base_llm_runner import BaseRunner
+    from easyllm_b200.utils.log import default_logger
+    cfg = copy.deepcopy(cfg)
+    args = parse_args(["--config", CFG, "--launcher", "torch", "--distributed-backend", "gloo", "--inference",
+                       "--generate-mode", "interactive", "--out-seq-length", "4", "--greedy"])
+    r = BaseRunner(args, cfg, training=False, base_type="infer")
+    script = iter(["hello there", "quit"])
+    builtins.input = lambda *a: next(script)
+    lines = []
+    orig = default_logger.info
+    default_logger.info = lambda m, *a, **k: (lines.append(str(m)), orig(m, *a, **k))
+    try:
+        r.generate()
+    finally:
+        default_logger.info = orig
+    return r.config["data"]["data_types"], sorted(r.data_iterators), [l for l in lines if "EasyLLM:" in l]
+
+
+def test_interactive_generation_from_a_training_config():
+    """A config written for training (no ``data.infer`` block) still serves ``--inference``: the runner fills in the
+    interactive defaults and does not build the training data."""
+    from easyllm_b200.config import load_yaml
+    cfg = load_yaml(CFG)
+    cfg["loader"]["load_path"] = None
+    cfg["infer_tokenization"] = {"type": "sense_tokenization", "kwargs": {
+        "max_seq_length": 64, "parser_type": "simple_chat", "parser_kwargs": {"inference_mode": True}}}
+    types, iters, replies = run_ranks(1, _interactive, cfg)[0]
+    assert types == ["infer"] and iters == [] and len(replies) == 1
