@@ -155,25 +155,32 @@ def convert(input_dir, output_dir, tp_size=None, n_heads=None, num_key_value_hea
 
 
 def convert_lora(input_dir, output_dir, tp_size=None):
-    """peft adapter: ``adapter_model.bin`` with ``base_model.model.…lora_{A,B}.weight`` keys."""
+    """peft adapter: ``adapter_model.bin`` with ``base_model.model.…lora_{A,B}.weight`` keys.
+
+    An adapter directory holds files only for the layers that carry adapter tensors (the embedding and head files
+    exist only when they are in ``modules_to_save``), so the highest file index says nothing about the depth of the
+    model.  A file's role is therefore read from its tensor names: ``word_embeddings.*`` in file 1 is the input
+    embedding, in any other file the LM head; everything else is transformer block ``index − 3``."""
     if os.path.abspath(output_dir) == os.path.abspath(input_dir):
         output_dir = os.path.join(output_dir, "convert_hf")
     os.makedirs(output_dir, exist_ok=True)
-    table, n_layer = index_layer_files(input_dir)
+    table, _ = index_layer_files(input_dir)
     tp_size = tp_size or len(next(iter(table.values())))
     state = {}
     for lid in sorted(table):
-        if lid == n_layer + 4:
-            continue
         shards = _read_shards(table[lid], tp_size, lid)
-        for name in shards[0]:
+        names = list(shards[0])
+        if not names or names == ["weight"]:               # the final norm has no adapter
+            continue
+        embedding_like = all(n.startswith("word_embeddings") for n in names)
+        for name in names:
             merged = merge_tensor(name, [s[name] for s in shards])
             for k, v in merged.items():
-                if lid == 1:
+                if embedding_like and lid == 1:
                     key = k.replace("word_embeddings", "base_model.model.model.embed_tokens")
                     key = key.replace("lora_embedding_A_weight", "lora_embedding_A").replace(
                         "lora_embedding_B_weight", "lora_embedding_B")
-                elif lid == n_layer + 5:
+                elif embedding_like:
                     key = k.replace("word_embeddings", "base_model.model.lm_head")
                     key = key.replace("lora_embedding_A_weight", "lora_A.weight").replace(
                         "lora_embedding_B_weight", "lora_B.weight")

@@ -125,3 +125,59 @@ def test_interactive_generation_from_a_training_config():
         "max_seq_length": 64, "parser_type": "simple_chat", "parser_kwargs": {"inference_mode": True}}}
     types, iters, replies = run_ranks(1, _interactive, cfg)[0]
     assert types == ["infer"] and iters == [] and len(replies) == 1
+
+
+def _lora_train_and_logits(rank, world, save_dir):
+    import torch
+    from easyllm_b200.config import load_yaml, parse_args
+    from easyllm_b200.runners.base_llm_runner import BaseRunner
+    cfg = load_yaml(CFG)
+    cfg["runtime"].update(tensor_model_parallel_size=2, pipeline_model_parallel_size=1, lora_mode=True)
+    cfg["saver"]["save_path"] = save_dir
+    cfg["trainer"]["train_iters"] = 3
+    cfg["trainer"]["optimizer"]["kwargs"]["lr"] = 5.e-3          # large steps so the adapters clearly matter
+    cfg["loader"]["load_path"] = None
+    cfg["lora"] = {"lora_rank": 4, "lora_alpha": 8, "lora_dropout": 0.0,
+                   "target_modules": ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"],
+                   # the full layer files are written too: they are the base model of this test
+                   "saver": {"save_path": os.path.join(save_dir, "lora"), "only_save_trainable": False, "modules_to_save": []}}
+    args = parse_args(["--config", CFG, "--launcher", "torch", "--distributed-backend", "gloo"])
+    r = BaseRunner(args, cfg, training=True, base_type="train")
+    r.train()
+    r.model.eval()
+    tok = (torch.arange(0, 40) * 13 % 32000).view(1, 40)
+    with torch.no_grad():
+        return r.model((tok, None, None), return_logits=True).detach()      # this rank's vocabulary shard
+
+
+def test_lora_train_convert_merge_matches_the_trained_model(tmp_path):
+    """The LoRA flow end to end at TP=2: train adapters with the Megatron runner, convert the base layer files and
+    the adapter layer files to HF / peft format, merge them with the CLI tool, and get the trained model's logits back
+    from a plain HuggingFace Llama."""
+    import importlib.util
+    import torch
+    d = str(tmp_path / "ck")
+    shards = run_ranks(2, _lora_train_and_logits, d)
+    ours = torch.cat(shards, dim=-1)
+
+    def tool(name):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(os.path.dirname(__file__), "..", "tools", name + ".py"))
+        m = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(m)
+        return m
+    conv = tool("convert_ds_weight_to_hf_fast")
+    geometry = ["--tp_size", "2", "--n_heads", "4", "--num_key_value_heads", "4", "--norm_eps", "1e-5"]
+    conv.main(["--input_dir", os.path.join(d, "global_step3"), "--output_dir", str(tmp_path / "hf_base")] + geometry)
+    conv.main(["--input_dir", os.path.join(d, "lora", "global_step3"), "--output_dir", str(tmp_path / "adapter"),
+               "--lora_mode"] + geometry)
+    assert os.path.exists(tmp_path / "adapter" / "adapter_model.bin")
+    tool("merge_base_model_with_lora").main(["--base_model", str(tmp_path / "hf_base"), "--lora_model",
+                                             str(tmp_path / "adapter"), "--output_dir", str(tmp_path / "merged")])
+    from transformers import LlamaForCausalLM
+    tok = (torch.arange(0, 40) * 13 % 32000).view(1, 40)
+    merged = LlamaForCausalLM.from_pretrained(str(tmp_path / "merged"), torch_dtype=torch.float32,
+                                              attn_implementation="eager")(input_ids=tok).logits
+    base = LlamaForCausalLM.from_pretrained(str(tmp_path / "hf_base"), torch_dtype=torch.float32,
+                                            attn_implementation="eager")(input_ids=tok).logits
+    assert torch.allclose(ours, merged, atol=5e-4, rtol=1e-3), (ours - merged).abs().max()
+    assert (ours - base).abs().max() > 10 * (ours - merged).abs().max()      # the adapters are what closes the gap
