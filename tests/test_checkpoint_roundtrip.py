@@ -191,3 +191,43 @@ def test_pipeline_module_names_used_by_checkpoint_helpers(tmp_path):
     assert out.shape[:2] == (2, 16) and eng.fwd_outputs[0] is out
     eng._compute_loss = True
     assert eng.eval_batch(synthetic_batches(32000, 16, 2, seed=3)).dim() == 0
+
+
+def _import_family(rank, world, path, pretrain_type, model_kw):
+    from easyllm_b200.ckpt.hf_import import load_llama_from_hf_format
+    from easyllm_b200.models import llama_custom
+    from easyllm_b200.parallel.grid import initialize_model_parallel
+    if world > 1:
+        initialize_model_parallel(world, 1)
+    m = llama_custom(**model_kw).eval()
+    load_llama_from_hf_format(m, path, pretrain_type, worker=2)
+    tok = (torch.arange(0, 24) * 5 % 300).view(1, 24)
+    with torch.no_grad():
+        return m((tok, None, None), return_logits=True)
+
+
+def test_family_checkpoints_import_into_the_megatron_model(tmp_path):
+    """Qwen (fused c_attn with bias, w2 → gate, w1 → up), InternLM2 (GQA-interleaved wqkv, w1/w3/w2) and Baichuan
+    (W_pack) checkpoints, written in each family's own key names, load into the 3D-parallel Llama model at TP 1 and
+    TP 2 and reproduce the logits of the HF-style decoder they came from."""
+    from easyllm_b200.models.hf_models import CausalLM, HFArch
+    tok = (torch.arange(0, 24) * 5 % 300).view(1, 24)
+    common = dict(vocab_size=304, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4)
+    cases = [("qwen", "qwen", {"qkv_bias": True}, dict(transformer_layer_params={"attention_qkv_bias": True}), 4),
+             ("internlm2", "internlm2", {"num_key_value_heads": 2}, {}, 2),
+             ("baichuan", "baichuan", {}, {}, 4),
+             ("llama", "llama", {"num_key_value_heads": 2}, {}, 2)]
+    for family, pretrain_type, arch_kw, model_extra, kv in cases:
+        torch.manual_seed(1)
+        src = CausalLM(HFArch(family=family, rms_norm_eps=1e-5, **common, **arch_kw)).eval()
+        d = str(tmp_path / family)
+        src.save_pretrained(d)
+        with torch.no_grad():
+            ref = src(tok)["logits"]
+        model_kw = dict(num_layers=2, hidden_size=64, num_attention_heads=4, num_kv_attention_heads=kv,
+                        intermediate_size=96, vocab_size=304, layer_norm_params={"kwargs": {"eps": 1e-5}},
+                        checkpoint_activations=False, **model_extra)
+        one = run_ranks(1, _import_family, d, pretrain_type, model_kw)[0]
+        assert torch.allclose(one, ref, atol=2e-4, rtol=1e-4), (family, (one - ref).abs().max())
+        two = torch.cat(run_ranks(2, _import_family, d, pretrain_type, model_kw), dim=-1)
+        assert torch.allclose(two, ref, atol=2e-4, rtol=1e-4), (family, "tp2", (two - ref).abs().max())
