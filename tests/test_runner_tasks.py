@@ -181,3 +181,65 @@ def test_lora_train_convert_merge_matches_the_trained_model(tmp_path):
                                             attn_implementation="eager")(input_ids=tok).logits
     assert torch.allclose(ours, merged, atol=5e-4, rtol=1e-3), (ours - merged).abs().max()
     assert (ours - base).abs().max() > 10 * (ours - merged).abs().max()      # the adapters are what closes the gap
+
+
+def _pretrain_bin(rank, world, cfg, iters):
+    from easyllm_b200.config import parse_args
+    from easyllm_b200.runners.base_llm_runner import BaseRunner
+    cfg = copy.deepcopy(cfg)
+    cfg["runtime"].update(tensor_model_parallel_size=1, pipeline_model_parallel_size=world)
+    cfg["trainer"]["train_iters"] = iters
+    args = parse_args(["--config", CFG, "--launcher", "torch", "--distributed-backend", "gloo"])
+    r = BaseRunner(args, cfg, training=True, base_type="train")
+    seen, batches = [], []
+    orig_fn = r.batch_pipe_func["train"]
+
+    def spy(data):
+        out = orig_fn(data)
+        batches.append([tuple(t.shape) if hasattr(t, "shape") else None for t in out[0]])
+        return out
+    r.batch_pipe_func["train"] = spy
+    r.engine.set_batch_fn(spy)
+    orig = r.forward_step
+
+    def rec(it):
+        out = orig(it)
+        seen.append(float(out["lm_loss"]))
+        return out
+    r.forward_step = rec
+    r.train()
+    return seen, batches
+
+
+def test_packed_pretraining_from_token_bins_over_two_pipeline_stages(tmp_path):
+    """jsonl → token bins (the offline tool) → pretrain_bin dataset → packed batches with per-document position
+    ids and cu_seqlens → two pipeline stages; the loss is finite and falls on a repetitive corpus."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bpb", os.path.join(os.path.dirname(__file__), "..", "tools",
+                                                                      "build_pretrain_bin.py"))
+    tool = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(tool)
+    src = tmp_path / "docs.jsonl"
+    src.write_text("\n".join(json.dumps({"content": "the quick brown fox jumps over the lazy dog. " * (1 + i % 3)})
+                             for i in range(400)))
+    tool.main(["--tokenizer_type", "SimpleTokenizer", "--jsonl", str(src), "--out_dir", str(tmp_path / "bins"),
+               "--bin_size", "8192", "--workers", "1"])
+    from easyllm_b200.config import load_yaml
+    cfg = load_yaml(CFG)
+    tok = {"type": "sense_tokenization", "kwargs": {"max_seq_length": 128, "parser_type": "pretrain_bin", "parser_kwargs": {}}}
+    tr = cfg["data"]["train"]
+    tr["dataset"] = {"type": "pretrain_bin", "kwargs": {"folders": str(tmp_path / "bins"), "seq_length": 128,
+                                                         "bin_size": 8192, "transformer": [tok]}}
+    tr["batch_collector"] = {"type": "batch_align", "kwargs": {"alignment": 8, "max_seq_length": 128, "pretrain": True,
+                                                               "offset_label": True}}
+    tr["batch_pipe"] = {"type": "flash_batch_pipe", "kwargs": {"eod_mask_loss": True, "pretrain": True}}
+    cfg["saver"]["save_path"] = str(tmp_path / "ck")
+    cfg["saver"]["save_interval"] = 1000
+    cfg["loader"]["load_path"] = None
+    cfg["trainer"]["optimizer"]["kwargs"]["lr"] = 2.e-3
+    res = run_ranks(2, _pretrain_bin, cfg, 8)
+    losses = res[1][0] or res[0][0]                     # the last stage records the loss
+    assert len(losses) == 8 and all(l == l for l in losses) and losses[-1] < losses[0]
+    first_stage_batches = res[0][1]
+    # (tokens, position_ids, mask, cu_seqlens): documents are packed, so cu_seqlens has more than two entries
+    assert first_stage_batches and len(first_stage_batches[0]) == 4 and first_stage_batches[0][3][0] > 2
