@@ -176,7 +176,12 @@ class HFRunner:
         if cfg.get("save_mode", "deepspeed") == "huggingface":
             if self.rank == 0:
                 out = os.path.join(path, f"checkpoint-{global_step}")
-                self.model.save_pretrained(out)
+                if getattr(self.model, "peft_config", None):
+                    # a LoRA run saves what peft's save_pretrained saves: the adapter tensors and their config
+                    from ..models.hf_models.lora import save_adapter
+                    save_adapter(self.model, out)
+                else:
+                    self.model.save_pretrained(out)
                 if hasattr(self.tokenizer, "save_pretrained"):
                     self.tokenizer.save_pretrained(out)
         else:

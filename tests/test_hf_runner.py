@@ -127,3 +127,51 @@ def test_fused_projection_aliases_adjacent_parameters():
     assert torch.allclose(y0, y1, atol=1e-6) and torch.allclose(dx0, x.grad, atol=1e-6)
     for w, g in zip(ws, g0):
         assert w.grad is None and torch.allclose(w.main_grad, g, atol=1e-5)
+
+
+def _train_lora(rank, world, workdir):
+    from easyllm_b200.config import load_yaml, parse_args
+    from easyllm_b200.parallel.grid import initialize_model_parallel
+    from easyllm_b200.runners.hf_runner import HFRunner
+    initialize_model_parallel(1, 1)
+    cfg = load_yaml(CFG)
+    cfg["data"]["train"]["dataset"]["kwargs"]["json_file"] = os.path.join(workdir, "d.jsonl")
+    cfg["saver"] = {"enabled": True, "save_path": os.path.join(workdir, "ck"), "save_mode": "huggingface", "save_interval": 3}
+    cfg["trainer"]["train_iters"] = 3
+    cfg["trainer"]["optimizer"]["kwargs"]["lr"] = 1.e-2
+    cfg["hooks"] = [h for h in cfg.get("hooks", []) if h["type"] != "dynamic_checkpoint"]
+    cfg["model"]["peft_model_cfg"] = {"r": 4, "lora_alpha": 8, "lora_dropout": 0.0, "target_modules": ["q_proj", "v_proj", "down_proj"]}
+    r = HFRunner(parse_args(["--config", CFG]), cfg, training=True)
+    base = {n: p.detach().clone() for n, p in r.model.named_parameters() if "lora_" not in n}
+    trainable = [n for n, p in r.model.named_parameters() if p.requires_grad]
+    r.train()
+    frozen_ok = all(torch.equal(p.detach(), base[n]) for n, p in r.model.named_parameters() if "lora_" not in n)
+    r.model.eval()
+    ids = torch.arange(3, 19).view(1, 16)
+    with torch.no_grad():
+        logits = r.model(ids)["logits"].float()
+    return trainable, frozen_ok, logits, {n.replace(".base.", "."): v for n, v in base.items()}
+
+
+def test_hf_runner_lora_saves_an_adapter_that_merges_back(tmp_path):
+    """LoRA through the HF runner's YAML (``model.peft_model_cfg``): only adapters train, the checkpoint is a peft
+    adapter folder, and merging it into the untouched base weights reproduces the trained model."""
+    from easyllm_b200.models.lora import merge_lora_into_hf_state
+    _write_data(str(tmp_path / "d.jsonl"))
+    trainable, frozen_ok, logits, base = run_ranks(1, _train_lora, str(tmp_path))[0]
+    assert trainable and all("lora_" in n for n in trainable) and frozen_ok
+    out = tmp_path / "ck" / "checkpoint-3"
+    assert (out / "adapter_model.bin").exists() and (out / "adapter_config.json").exists()
+    cfg = json.load(open(out / "adapter_config.json"))
+    assert cfg["r"] == 4 and cfg["lora_alpha"] == 8 and sorted(cfg["target_modules"]) == ["down_proj", "q_proj", "v_proj"]
+    adapter = torch.load(out / "adapter_model.bin")
+    assert len(adapter) == 2 * 3 * 2                     # A and B for three projections in two layers
+    merged = merge_lora_into_hf_state(base, adapter, cfg["lora_alpha"] / cfg["r"])
+    from easyllm_b200.config import load_yaml
+    from easyllm_b200.runners.hf_runner import build_hf_model
+    model_cfg = load_yaml(CFG)["model"]
+    plain = build_hf_model(model_cfg).float().eval()
+    plain.load_state_dict({k: v.float() for k, v in merged.items()})
+    with torch.no_grad():
+        again = plain(torch.arange(3, 19).view(1, 16))["logits"]
+    assert torch.allclose(again, logits, atol=1e-4, rtol=1e-4), (again - logits).abs().max()
