@@ -85,6 +85,31 @@ def save_adapter(model, path):
                    "lora_dropout": c["lora_dropout"], "target_modules": c["target_modules"], "bias": "none"}, f, indent=2)
 
 
+def load_adapter(model, path):
+    """Wrap ``model`` with the LoRA layout recorded in ``path/adapter_config.json`` and load ``adapter_model.bin``
+    (what ``PeftModel.from_pretrained`` does for the reference's ``peft_model_cfg.peft_path``)."""
+    with open(os.path.join(path, "adapter_config.json")) as f:
+        cfg = json.load(f)
+    add_lora(model, {"r": cfg["r"], "lora_alpha": cfg["lora_alpha"], "lora_dropout": cfg.get("lora_dropout", 0.0),
+                     "target_modules": cfg["target_modules"], "modules_to_save": cfg.get("modules_to_save")})
+    sd = torch.load(os.path.join(path, "adapter_model.bin"), map_location="cpu")
+    mods = dict(model.named_modules())
+    loaded = 0
+    for key, val in sd.items():
+        name = key[len("base_model.model."):] if key.startswith("base_model.model.") else key
+        for suffix, attr in ((".lora_A.weight", "lora_A"), (".lora_B.weight", "lora_B")):
+            if name.endswith(suffix):
+                mod = mods.get(name[:-len(suffix)])
+                if not isinstance(mod, LoraLinear):
+                    raise KeyError(f"{path}: adapter tensor {key} has no LoRA layer in the model")
+                getattr(mod, attr).data.copy_(val.to(getattr(mod, attr)))
+                loaded += 1
+    expected = 2 * sum(isinstance(m, LoraLinear) for m in mods.values())
+    if loaded != expected:
+        raise KeyError(f"{path}: loaded {loaded} adapter tensors, the model has {expected}")
+    return model
+
+
 def merge_and_unload(model):
     for parent in list(model.modules()):
         for name, child in list(parent.named_children()):

@@ -25,6 +25,7 @@ from ..optim import build_learning_rate_scheduler
 from ..optim.grad_scaler import ShardedGradScaler
 from ..optim.zero import ZeroOptimizer
 from ..parallel.grid import initialize_distributed
+from ..utils.log import default_logger as logger
 from . import hf_hooks  # noqa: F401
 from .hooks import build_hooks
 
@@ -42,8 +43,12 @@ def build_hf_model(cfg_model):
     model = MODULE_ZOO_REGISTRY.build({"type": cfg_model["type"], "kwargs": dict(cfg_model.get("kwargs") or {})})
     peft = cfg_model.get("peft_model_cfg")
     if peft:
-        from ..models.hf_models.lora import add_lora
-        add_lora(model, peft)
+        from ..models.hf_models.lora import add_lora, load_adapter
+        if peft.get("peft_path"):                      # continue from / serve a saved adapter
+            load_adapter(model, peft["peft_path"])
+            logger.info(f"load peft model from : {peft['peft_path']}")
+        else:
+            add_lora(model, peft)
     return model
 
 

@@ -175,3 +175,10 @@ def test_hf_runner_lora_saves_an_adapter_that_merges_back(tmp_path):
     with torch.no_grad():
         again = plain(torch.arange(3, 19).view(1, 16))["logits"]
     assert torch.allclose(again, logits, atol=1e-4, rtol=1e-4), (again - logits).abs().max()
+    # `peft_model_cfg.peft_path` rebuilds the adapted model from the saved folder (for resuming or serving)
+    served_cfg = dict(model_cfg, peft_model_cfg={"peft_path": str(out)})
+    served = build_hf_model(served_cfg).float().eval()
+    served.load_state_dict({(k if k in dict(served.named_parameters()) else k.replace(".weight", ".base.weight")): v.float()
+                            for k, v in base.items()}, strict=False)
+    with torch.no_grad():
+        assert torch.allclose(served(torch.arange(3, 19).view(1, 16))["logits"], logits, atol=1e-4, rtol=1e-4)
