@@ -244,12 +244,98 @@ def save_lora_ckpt_pretrained(cfg_lora, model, iteration=None):
     return path
 
 
+def _reshard(name, full, tp, rank):
+    """This rank's slice of a merged (TP-free) adapter tensor, by the same rules that merge it."""
+    from ..ckpt.ds_to_hf import LORA_COL, LORA_ROW
+    if tp == 1:
+        return full
+    if LORA_COL.search(name):
+        n = full.shape[0] // tp
+        return full[rank * n:(rank + 1) * n].clone()
+    if LORA_ROW.search(name):
+        n = full.shape[1] // tp
+        return full[:, rank * n:(rank + 1) * n].clone()
+    return full                                            # replicated halves
+
+
+def load_lora_from_ds_format(load_dir, model):
+    """Adapter layer files written at any TP size: same size → this rank's files as they are; another size → the
+    shards of every tensor are merged and re-cut for this rank (llm/models/mg_models/llama/utils.py:353-439)."""
+    from ..ckpt.ds_to_hf import index_layer_files, merge_tensor
+    from ..ckpt.layer_files import load_layer_states, safe_load
+    g = get_grid()
+    try:
+        table, _ = index_layer_files(load_dir)
+    except FileNotFoundError:
+        return False
+    saved_tp = max(len(v) for v in table.values())
+    if saved_tp == g.tp:
+        load_layer_states(model, load_dir, strict=False)
+        return True
+    for key, mod in model.layers.items():
+        files = table.get(int(key))
+        if not files:
+            continue
+        shards = [safe_load(files[r]) for r in sorted(files)]
+        sd = {}
+        for name in shards[0]:
+            if "lora_" not in name:
+                continue
+            full = list(merge_tensor(name, [sh[name] for sh in shards]).values())[0]
+            sd[name] = _reshard(name, full, g.tp, g.tp_rank)
+        mod.load_state_dict(sd, strict=False)
+    return True
+
+
+def load_lora_from_hf_format(load_dir, model):
+    """A peft adapter folder (``adapter_model.bin``, keys ``base_model.model.model.layers.N.….lora_A.weight``) into
+    the TP-sharded adapter modules of this rank."""
+    path = os.path.join(load_dir, "adapter_model.bin")
+    if not os.path.exists(path):
+        return False
+    g = get_grid()
+    sd = torch.load(path, map_location="cpu")
+    per_layer = {}
+    for k, v in sd.items():
+        k = k.replace("base_model.model.", "", 1)
+        if k.startswith("model.layers."):
+            _, _, idx, rest = k.split(".", 3)
+            lid, name = int(idx) + 3, rest.replace("lora_A.weight", "lora_A_weight").replace("lora_B.weight", "lora_B_weight")
+        elif k.startswith("model.embed_tokens."):
+            lid = 1
+            name = "word_embeddings." + k.split(".", 2)[2].replace("lora_embedding_A", "lora_embedding_A_weight").replace(
+                "lora_embedding_B", "lora_embedding_B_weight")
+        elif k.startswith("lm_head."):
+            lid = model.num_layers + 5
+            name = "word_embeddings." + k.split(".", 1)[1].replace("lora_A.weight", "lora_embedding_A_weight").replace(
+                "lora_B.weight", "lora_embedding_B_weight")
+        else:
+            continue
+        per_layer.setdefault(lid, {})[name] = _reshard(name, v, g.tp, g.tp_rank)
+    for key, mod in model.layers.items():
+        if int(key) in per_layer:
+            mod.load_state_dict(per_layer[int(key)], strict=False)
+    return bool(per_layer)
+
+
 def load_lora_ckpt_pretrained(cfg_lora, model, optimizer=None):
-    from ..ckpt.layer_files import load_layer_states
     loader = cfg_lora["loader"]
-    load_layer_states(model, loader["load_path"], strict=False)
-    if optimizer is not None and hasattr(optimizer, "refresh_fp32_params"):
-        optimizer.refresh_fp32_params()
+    if loader.get("debug", False):
+        logger.info("skip loaded checkpoint for debug")
+        return
+    mode = loader.get("load_mode", "deepspeed")
+    if mode == "deepspeed":
+        ok = load_lora_from_ds_format(loader["load_path"], model)
+    elif mode == "huggingface":
+        ok = load_lora_from_hf_format(loader["load_path"], model)
+    else:
+        raise NotImplementedError(f"lora load mode {mode} is not support")
+    if ok:
+        logger.info(f"Successfully loaded lora checkpoint from {loader['load_path']}.")
+        if optimizer is not None and hasattr(optimizer, "refresh_fp32_params"):
+            optimizer.refresh_fp32_params()
+    else:
+        logger.info("Fail to load any lora checkpoints and will start from random.")
 
 
 def merge_lora_into_hf_state(base_state, adapter_state, scaling):

@@ -150,6 +150,25 @@ def _lora_train_and_logits(rank, world, save_dir):
         return r.model((tok, None, None), return_logits=True).detach()      # this rank's vocabulary shard
 
 
+def _load_lora_tp1(rank, world, hf_base, mode, lora_path):
+    import torch
+    from easyllm_b200.ckpt.hf_import import load_llama_from_hf_format
+    from easyllm_b200.config import load_yaml
+    from easyllm_b200.models import build_model
+    from easyllm_b200.models.lora import load_lora_ckpt_pretrained
+    from easyllm_b200.data import build_tokenizer
+    cfg = load_yaml(CFG)
+    cfg_lora = {"lora_rank": 4, "lora_alpha": 8, "lora_dropout": 0.0,
+                "target_modules": ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"],
+                "loader": {"load_path": lora_path, "load_mode": mode}}
+    model = build_model(build_tokenizer(cfg["tokenizer"]), cfg, True, cfg_lora, base_type="train").eval()
+    load_llama_from_hf_format(model, hf_base, "llama", worker=2)
+    load_lora_ckpt_pretrained(cfg_lora, model)
+    tok = (torch.arange(0, 40) * 13 % 32000).view(1, 40)
+    with torch.no_grad():
+        return model((tok, None, None), return_logits=True)
+
+
 def test_lora_train_convert_merge_matches_the_trained_model(tmp_path):
     """The LoRA flow end to end at TP=2: train adapters with the Megatron runner, convert the base layer files and
     the adapter layer files to HF / peft format, merge them with the CLI tool, and get the trained model's logits back
@@ -181,6 +200,10 @@ def test_lora_train_convert_merge_matches_the_trained_model(tmp_path):
                                             attn_implementation="eager")(input_ids=tok).logits
     assert torch.allclose(ours, merged, atol=5e-4, rtol=1e-3), (ours - merged).abs().max()
     assert (ours - base).abs().max() > 10 * (ours - merged).abs().max()      # the adapters are what closes the gap
+    # the adapters trained at TP 2 load into a TP 1 model, from the layer files (re-sharded) and from the peft folder
+    for mode, path in (("deepspeed", os.path.join(d, "lora", "global_step3")), ("huggingface", str(tmp_path / "adapter"))):
+        again = run_ranks(1, _load_lora_tp1, str(tmp_path / "hf_base"), mode, path)[0]
+        assert torch.allclose(again, ours, atol=5e-4, rtol=1e-3), (mode, (again - ours).abs().max())
 
 
 def _pretrain_bin(rank, world, cfg, iters):
