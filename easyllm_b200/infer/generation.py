@@ -197,15 +197,21 @@ def generate_samples_eval(args, context_tokens, engine, tokenizer, force_eos_id=
 
 
 def infer_logp(engine, tokenizer, data_iter, batch_fn, out_file, num_samples):
-    """Per-token label log-probs of every sample → jsonl (offline reference log-probs for DPO)."""
+    """Per-token label log-probs of every sample → jsonl (offline reference log-probs for DPO).
+
+    One value per input position that holds a real token, i.e. per token of the sample after the first (the
+    collator feeds ``ids[:-1]`` and asks for ``ids[1:]``); positions whose label is ignored give 0.  This is the
+    ``yw_logp`` / ``yl_logp`` list the ``combine_dpo_general_chat`` parser multiplies with its label mask."""
     g = get_grid()
     gen = Generator(engine, tokenizer)
+    pad = len(tokenizer) - 1
     f = open(out_file, "w") if g.rank == 0 else None
     for i in range(num_samples):
         batch = next(data_iter)
         (tokens, _pos, *_), (labels, _mask, *_) = batch_fn(batch)
         lp = gen.token_logps(tokens.to(gen.dev), labels.to(gen.dev))
         if f is not None:
-            f.write(json.dumps({"id": i, "logp": lp[0].tolist()}) + "\n")
+            n_real = int((tokens[0] != pad).sum())          # alignment padding is not part of the sample
+            f.write(json.dumps({"id": i, "logp": lp[0][:n_real].tolist()}) + "\n")
     if f is not None:
         f.close()

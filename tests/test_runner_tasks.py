@@ -266,3 +266,61 @@ def test_packed_pretraining_from_token_bins_over_two_pipeline_stages(tmp_path):
     first_stage_batches = res[0][1]
     # (tokens, position_ids, mask, cu_seqlens): documents are packed, so cu_seqlens has more than two entries
     assert first_stage_batches and len(first_stage_batches[0]) == 4 and first_stage_batches[0][3][0] > 2
+
+
+def _infer_modes(rank, world, cfg, mode, extra):
+    from easyllm_b200.config import parse_args
+    from easyllm_b200.runners.base_llm_runner import BaseRunner
+    cfg = copy.deepcopy(cfg)
+    args = parse_args(["--config", CFG, "--launcher", "torch", "--distributed-backend", "gloo", "--inference",
+                       "--generate-mode", mode, "--out-seq-length", "4", "--greedy"] + extra)
+    r = BaseRunner(args, cfg, training=False, base_type="infer")
+    r.generate()
+    return True
+
+
+def test_runner_eval_and_logp_modes_feed_offline_dpo(tmp_path):
+    """``--generate-mode eval`` answers a question file; ``--generate-mode logp`` writes per-token label log-probs of a
+    dataset, in the form the offline-DPO parser consumes as reference scores."""
+    from easyllm_b200.config import load_yaml
+    from easyllm_b200.data import SimpleTokenizer, build_parser
+    cfg = load_yaml(CFG)
+    cfg["loader"]["load_path"] = None
+    cfg["infer_tokenization"] = {"type": "sense_tokenization", "kwargs": {
+        "max_seq_length": 64, "parser_type": "simple_chat", "parser_kwargs": {"inference_mode": True}}}
+    with open(tmp_path / "q.jsonl", "w") as f:
+        f.write(json.dumps({"instruction": "name a colour", "input": "", "output": "blue"}) + "\n")
+        f.write(json.dumps({"instruction": "name a", "input": " fruit", "output": "pear"}) + "\n")
+    cfg["infer_cfg"] = {"eval_task": "base", "question_file": str(tmp_path / "q.jsonl"), "result_file": str(tmp_path / "r.jsonl")}
+    assert run_ranks(1, _infer_modes, cfg, "eval", [])[0]
+    rows = [json.loads(l) for l in open(tmp_path / "r.jsonl")]
+    assert len(rows) == 2 and rows[1]["input"] == "name a fruit" and rows[0]["gold"] == "blue" and "raw_output" in rows[0]
+
+    # logp over a chat dataset
+    conv = [{"role": "user", "content": "pick a colour"}, {"role": "assistant", "content": "blue is calm"}]
+    with open(tmp_path / "d.jsonl", "w") as f:
+        for _ in range(4):
+            f.write(json.dumps(conv) + "\n")
+    tok = {"type": "sense_tokenization", "kwargs": {"max_seq_length": 128, "parser_type": "general_chat",
+                                                    "parser_kwargs": {"only_last_answer": True}}}
+    cfg2 = copy.deepcopy(cfg)
+    train = cfg2["data"]["train"]
+    cfg2["data"] = {"data_types": ["infer"], "infer": dict(
+        train, infer_type="logp", micro_batch_size=1, global_batch_size=1,
+        dataset={"type": "base_nlp_json", "kwargs": {"json_file": str(tmp_path / "d.jsonl"), "transformer": [tok],
+                                                      "json_type": "line"}},
+        batch_sampler={"type": "megatron_pretrain", "kwargs": {"micro_batch_size": 1, "drop_last": True}},
+        batch_collector={"type": "batch_align", "kwargs": {"alignment": 1, "max_seq_length": 128}},
+        batch_pipe={"type": "json_batch_pipe", "kwargs": {}},
+        batch_calculator={"type": "constant_num", "kwargs": {"global_batch_size": 1, "micro_batch_size": 1}})}
+    assert run_ranks(1, _infer_modes, cfg2, "logp", ["--logp-file", str(tmp_path / "logp.jsonl")])[0]
+    lines = [json.loads(l) for l in open(tmp_path / "logp.jsonl")]
+    chat = build_parser("general_chat", dict(tokenizer=SimpleTokenizer(vocab_size=32000), max_seq_length=128,
+                                             only_last_answer=True))
+    n = len(chat(conv)["input_ids"])
+    assert len(lines) == 4 and all(len(l["logp"]) == n - 1 for l in lines)     # one value per token after the first
+    assert all(v <= 0 for v in lines[0]["logp"]) and lines[0]["logp"] == lines[1]["logp"]
+    # and those lists are exactly what the DPO parser takes as yw_logp / yl_logp
+    dpo = build_parser("combine_dpo_general_chat", dict(tokenizer=SimpleTokenizer(vocab_size=32000), max_seq_length=128))
+    pair = dpo({"yw": conv, "yl": conv, "yw_logp": lines[0]["logp"], "yl_logp": lines[1]["logp"]})
+    assert pair["scores"][0] == pair["scores"][1] < 0
