@@ -168,7 +168,15 @@ class HFRunner:
             from ..ckpt.hf_import import load_hf_state
             from ..models.hf_models.io import import_state
             sd = import_state(load_hf_state(cfg["load_path"]), self.model.arch)
-            self.model.load_state_dict({k: v.to(self.dtype) for k, v in sd.items()}, strict=False)
+            own = set(self.model.state_dict())
+            # a LoRA-wrapped projection keeps its frozen weight one level down (`q_proj.base.weight`)
+            sd = {(k if k in own else k.replace(".weight", ".base.weight").replace(".bias", ".base.bias")): v.to(self.dtype)
+                  for k, v in sd.items()}
+            missing, unexpected = self.model.load_state_dict(sd, strict=False)
+            tied = getattr(self.model.arch, "tie_word_embeddings", False)
+            missing = [m for m in missing if "lora_" not in m and not (tied and m == "lm_head.weight")]
+            if missing or unexpected:
+                raise RuntimeError(f"{cfg['load_path']}: missing {missing[:8]}, unexpected {unexpected[:8]}")
             if self.training:
                 self.optimizer.refresh_fp32_params()
         else:

@@ -182,3 +182,36 @@ def test_hf_runner_lora_saves_an_adapter_that_merges_back(tmp_path):
                             for k, v in base.items()}, strict=False)
     with torch.no_grad():
         assert torch.allclose(served(torch.arange(3, 19).view(1, 16))["logits"], logits, atol=1e-4, rtol=1e-4)
+
+
+def _hf_mode_roundtrip(rank, world, workdir, phase):
+    from easyllm_b200.config import load_yaml, parse_args
+    from easyllm_b200.parallel.grid import initialize_model_parallel
+    from easyllm_b200.runners.hf_runner import HFRunner
+    initialize_model_parallel(1, 1)
+    cfg = load_yaml(CFG)
+    cfg["data"]["train"]["dataset"]["kwargs"]["json_file"] = os.path.join(workdir, "d.jsonl")
+    cfg["saver"] = {"enabled": True, "save_path": os.path.join(workdir, "ck"), "save_mode": "huggingface", "save_interval": 2}
+    cfg["trainer"]["train_iters"] = 2
+    cfg["hooks"] = [h for h in cfg.get("hooks", []) if h["type"] != "dynamic_checkpoint"]
+    if phase != "train":
+        cfg["loader"] = {"enabled": True, "load_path": os.path.join(workdir, "ck", "checkpoint-2"), "load_mode": "huggingface"}
+    if phase == "lora":
+        cfg["model"]["peft_model_cfg"] = {"r": 2, "lora_alpha": 4, "target_modules": ["q_proj", "o_proj"]}
+    r = HFRunner(parse_args(["--config", CFG]), cfg, training=True)
+    if phase == "train":
+        r.train()
+    r.model.eval()
+    with torch.no_grad():
+        return r.model(torch.arange(5, 21).view(1, 16))["logits"].float()
+
+
+def test_hf_mode_checkpoint_loads_back_also_under_lora_wrappers(tmp_path):
+    """``save_mode: huggingface`` → ``loader.load_mode: huggingface``: the weights come back exactly, and they also
+    reach the frozen projections of a model that has been wrapped for LoRA (fresh adapters start as a no-op)."""
+    _write_data(str(tmp_path / "d.jsonl"))
+    trained = run_ranks(1, _hf_mode_roundtrip, str(tmp_path), "train")[0]
+    loaded = run_ranks(1, _hf_mode_roundtrip, str(tmp_path), "load")[0]
+    assert torch.allclose(trained, loaded, atol=1e-5)
+    wrapped = run_ranks(1, _hf_mode_roundtrip, str(tmp_path), "lora")[0]
+    assert torch.allclose(trained, wrapped, atol=1e-5)
