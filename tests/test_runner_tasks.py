@@ -324,3 +324,27 @@ def test_runner_eval_and_logp_modes_feed_offline_dpo(tmp_path):
     dpo = build_parser("combine_dpo_general_chat", dict(tokenizer=SimpleTokenizer(vocab_size=32000), max_seq_length=128))
     pair = dpo({"yw": conv, "yl": conv, "yw_logp": lines[0]["logp"], "yl_logp": lines[1]["logp"]})
     assert pair["scores"][0] == pair["scores"][1] < 0
+
+
+def test_sft_from_the_mmap_index_dataset(tmp_path):
+    """The Megatron-style indexed dataset (tokenise once into .bin/.idx, sample fixed-length windows through the
+    native location index) feeding the runner, as in the mmap SFT config."""
+    with open(tmp_path / "d.jsonl", "w") as f:
+        for i in range(200):
+            f.write(json.dumps({"messages": [{"role": "user", "content": f"count to {i % 5}"},
+                                             {"role": "assistant", "content": " ".join(str(k) for k in range(i % 5 + 1))}]}) + "\n")
+    from easyllm_b200.config import load_yaml
+    cfg = load_yaml(CFG)
+    tok = {"type": "sense_tokenization", "kwargs": {"max_seq_length": 4096, "parser_type": "simple_chat",
+                                                    "parser_kwargs": {"keep_all_keys": False}}}
+    cfg["data"]["train"]["dataset"] = {"type": "mmap_index_json", "kwargs": {
+        "data_root": str(tmp_path), "seed": 7, "total_samples": 64, "max_seq_length": 128,
+        "json_file": str(tmp_path / "d.jsonl"), "transformer": [tok], "cache_location_builder": "cpp"}}
+    cfg["saver"]["save_path"] = str(tmp_path / "ck")
+    cfg["saver"]["save_interval"] = 1000
+    cfg["loader"]["load_path"] = None
+    cfg["trainer"]["optimizer"]["kwargs"]["lr"] = 2.e-3
+    seen = run_ranks(1, _run, cfg, 6)[0]
+    assert len(seen) == 6 and all(s["lm_loss"] == s["lm_loss"] for s in seen) and seen[-1]["lm_loss"] < seen[0]["lm_loss"]
+    cache = os.listdir(tmp_path / "train_data_cache")
+    assert any(n.endswith(".bin") for n in cache) and any(n.endswith(".idx") for n in cache)
