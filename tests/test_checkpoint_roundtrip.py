@@ -206,6 +206,13 @@ def _import_family(rank, world, path, pretrain_type, model_kw):
         return m((tok, None, None), return_logits=True)
 
 
+def _import_families(rank, world, jobs):
+    from easyllm_b200.parallel.grid import initialize_model_parallel
+    if world > 1:
+        initialize_model_parallel(world, 1)
+    return [_import_family(rank, 1, *job) for job in jobs]      # the grid is set once for all of them
+
+
 def test_family_checkpoints_import_into_the_megatron_model(tmp_path):
     """Qwen (fused c_attn with bias, w2 → gate, w1 → up), InternLM2 (GQA-interleaved wqkv, w1/w3/w2) and Baichuan
     (W_pack) checkpoints, written in each family's own key names, load into the 3D-parallel Llama model at TP 1 and
@@ -217,6 +224,7 @@ def test_family_checkpoints_import_into_the_megatron_model(tmp_path):
              ("internlm2", "internlm2", {"num_key_value_heads": 2}, {}, 2),
              ("baichuan", "baichuan", {}, {}, 4),
              ("llama", "llama", {"num_key_value_heads": 2}, {}, 2)]
+    jobs = []
     for family, pretrain_type, arch_kw, model_extra, kv in cases:
         torch.manual_seed(1)
         src = CausalLM(HFArch(family=family, rms_norm_eps=1e-5, **common, **arch_kw)).eval()
@@ -227,7 +235,12 @@ def test_family_checkpoints_import_into_the_megatron_model(tmp_path):
         model_kw = dict(num_layers=2, hidden_size=64, num_attention_heads=4, num_kv_attention_heads=kv,
                         intermediate_size=96, vocab_size=304, layer_norm_params={"kwargs": {"eps": 1e-5}},
                         checkpoint_activations=False, **model_extra)
-        one = run_ranks(1, _import_family, d, pretrain_type, model_kw)[0]
+        jobs.append((family, d, pretrain_type, model_kw, ref))
+    ones = run_ranks(1, _import_families, [j[1:4] for j in jobs])[0]
+    for (family, *_, ref), one in zip(jobs, ones):
         assert torch.allclose(one, ref, atol=2e-4, rtol=1e-4), (family, (one - ref).abs().max())
-        two = torch.cat(run_ranks(2, _import_family, d, pretrain_type, model_kw), dim=-1)
+    sharded = [j for j in jobs if j[0] in ("qwen", "internlm2")]      # the fused / interleaved layouts, cut over TP
+    twos = run_ranks(2, _import_families, [j[1:4] for j in sharded])
+    for i, (family, *_, ref) in enumerate(sharded):
+        two = torch.cat([twos[0][i], twos[1][i]], dim=-1)
         assert torch.allclose(two, ref, atol=2e-4, rtol=1e-4), (family, "tp2", (two - ref).abs().max())

@@ -206,14 +206,16 @@ def _hf_mode_roundtrip(rank, world, workdir, phase):
         return r.model(torch.arange(5, 21).view(1, 16))["logits"].float()
 
 
+def _hf_mode_all_phases(rank, world, workdir):
+    return tuple(_hf_mode_roundtrip(rank, world, workdir, phase) for phase in ("train", "load", "lora"))
+
+
 def test_hf_mode_checkpoint_loads_back_also_under_lora_wrappers(tmp_path):
     """``save_mode: huggingface`` → ``loader.load_mode: huggingface``: the weights come back exactly, and they also
     reach the frozen projections of a model that has been wrapped for LoRA (fresh adapters start as a no-op)."""
     _write_data(str(tmp_path / "d.jsonl"))
-    trained = run_ranks(1, _hf_mode_roundtrip, str(tmp_path), "train")[0]
-    loaded = run_ranks(1, _hf_mode_roundtrip, str(tmp_path), "load")[0]
+    trained, loaded, wrapped = run_ranks(1, _hf_mode_all_phases, str(tmp_path))[0]
     assert torch.allclose(trained, loaded, atol=1e-5)
-    wrapped = run_ranks(1, _hf_mode_roundtrip, str(tmp_path), "lora")[0]
     assert torch.allclose(trained, wrapped, atol=1e-5)
 
 
