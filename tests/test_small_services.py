@@ -190,3 +190,33 @@ def test_storage_helper_local_paths_pointer_files_and_fake_remote(tmp_path, monk
     assert PetrelHelper.load_json("s3://bucket/c.json") == {"r": 2}
     (tmp_path / "remote.ceph").write_text("s3://bucket/run/w.pt")
     assert PetrelHelper.load(str(tmp_path / "remote"))["w"].tolist() == [1.0, 1.0]
+
+
+def test_download_tool_follows_pointer_files(tmp_path, monkeypatch):
+    """``tools/download_fromceph.py`` on a folder of ``.ceph`` pointer files and plain files, with a fake remote."""
+    import importlib.util
+    import os
+    from easyllm_b200.utils.petrel_helper import PetrelHelper
+
+    class Fake:
+        store = {"s3://b/run/layer_01.pt": b"REMOTE-BYTES"}
+
+        def get(self, k):
+            return self.store[k]
+
+        def list(self, prefix):
+            return [k[len(prefix):] for k in self.store if k.startswith(prefix)]
+    monkeypatch.setattr(PetrelHelper, "_client", Fake())
+    src = tmp_path / "ck"
+    src.mkdir()
+    (src / "layer_01.pt.ceph").write_text("s3://b/run/layer_01.pt\n")
+    (src / "latest").write_text("global_step1")
+    spec = importlib.util.spec_from_file_location("dl", os.path.join(os.path.dirname(__file__), "..", "tools",
+                                                                     "download_fromceph.py"))
+    tool = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(tool)
+    tool.main(["--src", str(src), "--dst", str(tmp_path / "out")])
+    assert (tmp_path / "out" / "layer_01.pt").read_bytes() == b"REMOTE-BYTES"
+    assert (tmp_path / "out" / "latest").read_text() == "global_step1"
+    tool.main(["--src", "s3://b/run/", "--dst", str(tmp_path / "out2")])
+    assert (tmp_path / "out2" / "layer_01.pt").read_bytes() == b"REMOTE-BYTES"
