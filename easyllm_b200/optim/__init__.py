@@ -4,3 +4,4 @@ from .lr import build_learning_rate_scheduler, IterBaseAnnealingLR, SampleBaseAn
 from .microbatches import build_num_microbatches_calculator, get_train_iters  # noqa
 from .sophia import SophiaG  # noqa
 from .novograd import NovoGrad  # noqa
+from .adam8bit import Adam8bit  # noqa

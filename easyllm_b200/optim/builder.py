@@ -4,8 +4,8 @@ Parity: llm/utils/model/optimizer_helper.py:19-98.  ``FusedAdam`` / ``AdamW`` / 
 to the native fused Adam on ZeRO-sharded flat buffers (decay / no-decay split: biases and
 1-D parameters are not decayed; frozen parameters are left out).  ``FusedSGD`` maps to
 ``torch.optim.SGD``, ``FusedNovoGrad`` to ``optim.novograd.NovoGrad``; ``SophiaG`` and any
-``torch.optim.*`` class are available for the single-axis runners; ``Adam8bit``
-(bitsandbytes) is not provided and raises a clear error.
+``torch.optim.*`` class are available for the single-axis runners; ``Adam8bit`` /
+``AdamW8bit`` map to ``optim.adam8bit.Adam8bit`` (block-wise 8-bit optimizer state).
 """
 from __future__ import annotations
 
@@ -34,8 +34,10 @@ def build_optimizer(cfg_optim, model, zero_stage=0, grad_clip=0.0, fp16=False, n
                              eps=kw.get("eps", 1e-8), weight_decay=kw.get("weight_decay", 0.0), adamw=adamw,
                              stage=zero_stage, grad_clip=grad_clip, fp16=fp16,
                              bias_correction=kw.get("bias_correction", True), nan_policy=nan_policy)
-    if kind == "Adam8bit":
-        raise NotImplementedError("Adam8bit (bitsandbytes) is not available in this build; use FusedAdam")
+    if kind in ("Adam8bit", "AdamW8bit"):
+        from .adam8bit import Adam8bit
+        groups = param_groups_weight_decay(model, kw.pop("weight_decay", 0.0))
+        return Adam8bit(groups, adamw=(kind == "AdamW8bit"), **kw)
     groups = param_groups_weight_decay(model, kw.pop("weight_decay", 0.0))
     if kind == "SophiaG":
         from .sophia import SophiaG

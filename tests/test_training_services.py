@@ -134,6 +134,45 @@ def test_novograd_update_rule_and_builder_names():
         NovoGrad([q], amsgrad=True)
 
 
+def test_adam8bit_tracks_fp32_adam_with_a_quarter_of_the_state():
+    from easyllm_b200.optim import Adam8bit, build_optimizer
+    from easyllm_b200.optim.adam8bit import (dequantize_signed, dequantize_unsigned, quantize_signed,
+                                             quantize_unsigned)
+    torch.manual_seed(0)
+    x = torch.randn(5000) * torch.logspace(-4, 0, 5000)                 # four decades of magnitudes
+    q, s = quantize_signed(x, 256)
+    back = dequantize_signed(q, s, x.numel(), x.shape)
+    assert q.dtype == torch.int8 and (back - x).abs().max() <= 0.02 * x.abs().max()
+    big_enough = x.abs() > 1e-2
+    assert torch.equal(torch.sign(back[big_enough]), torch.sign(x[big_enough]))
+    v = x * x
+    qv, sv = quantize_unsigned(v, 256)
+    backv = dequantize_unsigned(qv, sv, v.numel(), v.shape)
+    assert qv.dtype == torch.uint8 and (backv.sqrt() - v.sqrt()).abs().max() <= 0.02 * v.sqrt().max()
+
+    def fit(make_opt):
+        torch.manual_seed(1)
+        net = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.Tanh(), torch.nn.Linear(128, 64))
+        opt = make_opt(net)
+        data = torch.randn(256, 64)
+        target = data.roll(1, dims=1) * 0.5
+        losses = []
+        for _ in range(60):
+            loss = ((net(data) - target) ** 2).mean()
+            opt.zero_grad(); loss.backward(); opt.step()
+            losses.append(loss.item())
+        return losses, opt
+    ref, _ = fit(lambda n: torch.optim.Adam(n.parameters(), lr=3e-3))
+    got, opt8 = fit(lambda n: Adam8bit(n.parameters(), lr=3e-3, min_8bit_size=1024, block_size=256))
+    assert got[-1] < 0.5 * got[0] and abs(got[-1] - ref[-1]) < 0.15 * ref[-1]
+    # the two weight matrices (8192 elements each) hold 1 byte per moment, the biases keep fp32 state
+    big = 2 * 8192
+    assert opt8.state_bytes() < 2.3 * big + 8 * (128 + 64) + 4096
+    lin = torch.nn.Linear(8, 8)
+    assert type(build_optimizer({"type": "Adam8bit", "kwargs": {"lr": 1e-3}}, lin)).__name__ == "Adam8bit"
+    assert build_optimizer({"type": "AdamW8bit", "kwargs": {"lr": 1e-3, "weight_decay": 0.1}}, lin).param_groups[0]["adamw"]
+
+
 def test_dynamic_checkpoint_manager_selection():
     from easyllm_b200.utils.dc_manager import DynamicCheckpointManager, bfs_candidates
 
