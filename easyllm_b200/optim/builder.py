@@ -25,7 +25,10 @@ def param_groups_weight_decay(model, weight_decay):
     return [{"params": decay, "weight_decay": weight_decay}, {"params": no_decay, "weight_decay": 0.0}]
 
 
-def build_optimizer(cfg_optim, model, zero_stage=0, grad_clip=0.0, fp16=False, nan_policy="count"):
+def build_optimizer(cfg_optim, model, zero_stage=0, grad_clip=0.0, fp16=False, nan_policy="count",
+                    engine_contract=False):
+    """``engine_contract``: wrap optimizers other than the native fused Adam so that the training engines can drive
+    them (accumulation into ``main_grad``, DP / TP gradient reduction, clipping); the runners pass True."""
     kind = cfg_optim["type"]
     kw = dict(cfg_optim.get("kwargs") or {})
     if kind in _NATIVE:
@@ -34,22 +37,26 @@ def build_optimizer(cfg_optim, model, zero_stage=0, grad_clip=0.0, fp16=False, n
                              eps=kw.get("eps", 1e-8), weight_decay=kw.get("weight_decay", 0.0), adamw=adamw,
                              stage=zero_stage, grad_clip=grad_clip, fp16=fp16,
                              bias_correction=kw.get("bias_correction", True), nan_policy=nan_policy)
+    groups = param_groups_weight_decay(model, kw.pop("weight_decay", 0.0))
     if kind in ("Adam8bit", "AdamW8bit"):
         from .adam8bit import Adam8bit
-        groups = param_groups_weight_decay(model, kw.pop("weight_decay", 0.0))
-        return Adam8bit(groups, adamw=(kind == "AdamW8bit"), **kw)
-    groups = param_groups_weight_decay(model, kw.pop("weight_decay", 0.0))
-    if kind == "SophiaG":
+        inner = Adam8bit(groups, adamw=(kind == "AdamW8bit"), **kw)
+    elif kind == "SophiaG":
         from .sophia import SophiaG
-        return SophiaG(groups, **kw)
-    if kind in ("FusedNovoGrad", "NovoGrad"):
+        inner = SophiaG(groups, **kw)
+    elif kind in ("FusedNovoGrad", "NovoGrad"):
         from .novograd import NovoGrad
-        return NovoGrad(groups, **kw)
-    if kind == "FusedSGD":
-        kw.pop("wd_after_momentum", None)
-        kw.pop("materialize_master_grads", None)
-        kw.pop("set_grad_none", None)
-        return torch.optim.SGD(groups, **kw)
-    if hasattr(torch.optim, kind):
-        return getattr(torch.optim, kind)(groups, **kw)
-    raise KeyError(f"unknown optimizer type {kind}")
+        inner = NovoGrad(groups, **kw)
+    elif kind == "FusedSGD":
+        for extra in ("wd_after_momentum", "materialize_master_grads", "set_grad_none"):
+            kw.pop(extra, None)
+        inner = torch.optim.SGD(groups, **kw)
+    elif hasattr(torch.optim, kind):
+        inner = getattr(torch.optim, kind)(groups, **kw)
+    else:
+        raise KeyError(f"unknown optimizer type {kind}")
+    if not engine_contract:
+        return inner
+    # the engines drive every optimizer through the ZeroOptimizer surface
+    from .torch_adapter import TorchOptimizerAdapter
+    return TorchOptimizerAdapter(inner, model.named_parameters(), grad_clip=grad_clip, nan_policy=nan_policy)

@@ -153,7 +153,8 @@ class BaseRunner:
                                          zero_stage=(ds.get("zero_optimization") or {}).get("stage", 0),
                                          grad_clip=ds.get("gradient_clipping", 0.0),
                                          fp16=self.config["runtime"].get("fp16", False),
-                                         nan_policy=self.config["runtime"].get("nan_policy", "count"))
+                                         nan_policy=self.config["runtime"].get("nan_policy", "count"),
+                                         engine_contract=True)
         cfg_lr = self.config["trainer"]["lr_scheduler"]
         cfg_lr.setdefault("kwargs", {})["max_lr"] = cfg_optim["kwargs"]["lr"]
         if cfg_lr["type"] == "iter_base_annealing":

@@ -21,9 +21,8 @@ from ..data import build_dataset, build_tokenizer
 from ..data.loader import build_batch_collator, build_data_loader
 from ..data.samplers import build_batch_sampler
 from ..engine.zero_dp import ZeroDPEngine
-from ..optim import build_learning_rate_scheduler
+from ..optim import build_learning_rate_scheduler, build_optimizer
 from ..optim.grad_scaler import ShardedGradScaler
-from ..optim.zero import ZeroOptimizer
 from ..parallel.grid import initialize_distributed
 from ..utils.log import default_logger as logger
 from . import hf_hooks  # noqa: F401
@@ -131,13 +130,13 @@ class HFRunner:
         self.mirco_train_batch_size = loader.batch_sampler.batch_size
         self.train_epoch_size = max(1, loader.get_epoch_size() // self.gradient_accumulation_steps)
         self.global_train_batch_size = self.mirco_train_batch_size * self.world * self.gradient_accumulation_steps
-        ok = tr["optimizer"]["kwargs"]
         stage = (self.ds_config.get("zero_optimization") or {}).get("stage", 1) if self.deepspeed else 0
-        self.optimizer = ZeroOptimizer(self.model.named_parameters(), lr=ok.get("lr", 1e-4),
-                                       betas=tuple(ok.get("betas", (0.9, 0.999))), eps=ok.get("eps", 1e-8),
-                                       weight_decay=ok.get("weight_decay", 0.0), stage=stage,
-                                       grad_clip=self.ds_config.get("gradient_clipping", 0.0),
-                                       fp16=self.dtype == torch.float16 and self.deepspeed)
+        # `trainer.optimizer.type`: Adam / AdamW / FusedAdam run on the native ZeRO optimizer, every other type
+        # (SophiaG, Adam8bit, SGD, torch.optim.*) on the wrapped torch optimizer with plain data parallelism
+        cfg_optim = {"type": tr["optimizer"].get("type", "AdamW"), "kwargs": dict(tr["optimizer"].get("kwargs") or {})}
+        self.optimizer = build_optimizer(cfg_optim, self.model, zero_stage=stage,
+                                         grad_clip=self.ds_config.get("gradient_clipping", 0.0),
+                                         fp16=self.dtype == torch.float16 and self.deepspeed, engine_contract=True)
         lr_cfg = {"type": tr["lr_scheduler"]["type"], "kwargs": dict(tr["lr_scheduler"].get("kwargs") or {})}
         self.lr_scheduler = build_learning_rate_scheduler(lr_cfg, self.optimizer)
         self.engine = ZeroDPEngine(self.model, self.optimizer, self.lr_scheduler,

@@ -267,3 +267,36 @@ def test_hf_runner_packed_pretraining_from_token_bins(tmp_path):
     losses, shapes = run_ranks(1, _hf_pretrain_bin, str(tmp_path))[0]
     assert len(losses) >= 6 and losses[-1] < losses[0]
     assert shapes and all(s is not None and s > 2 for s in shapes)
+
+
+def _hf_other_optimizer(rank, world, workdir):
+    from easyllm_b200.config import load_yaml, parse_args
+    from easyllm_b200.parallel.grid import initialize_model_parallel
+    from easyllm_b200.runners.hf_runner import HFRunner
+    initialize_model_parallel(1, 1)
+    cfg = load_yaml(CFG)
+    cfg["data"]["train"]["dataset"]["kwargs"]["json_file"] = os.path.join(workdir, "d.jsonl")
+    cfg["saver"] = {"enabled": False}
+    cfg["trainer"]["train_iters"] = 6
+    cfg["trainer"]["optimizer"] = {"type": "Adam8bit", "kwargs": {"lr": 3e-3, "min_8bit_size": 1024, "block_size": 256}}
+    cfg["hooks"] = [h for h in cfg.get("hooks", []) if h["type"] != "dynamic_checkpoint"]
+    r = HFRunner(parse_args(["--config", CFG]), cfg, training=True)
+    losses = []
+    orig = r.engine.backward
+
+    def rec(loss):
+        losses.append(float(loss))
+        return orig(loss)
+    r.engine.backward = rec
+    r.train()
+    return type(r.optimizer.inner).__name__, losses
+
+
+def test_hf_runner_uses_the_optimizer_type_of_its_yaml(tmp_path):
+    """Two data-parallel ranks with ``trainer.optimizer.type: Adam8bit``: the wrapped optimizer is driven through
+    the engine (gradient averaging over DP included) and the chat data is learnt."""
+    _write_data(str(tmp_path / "d.jsonl"))
+    res = run_ranks(2, _hf_other_optimizer, str(tmp_path))
+    assert all(name == "Adam8bit" for name, _ in res)
+    losses = res[0][1]
+    assert len(losses) >= 6 and losses[-1] < losses[0]

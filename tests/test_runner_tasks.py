@@ -352,3 +352,50 @@ def test_sft_from_the_mmap_index_dataset(tmp_path):
     assert len(seen) == 6 and all(s["lm_loss"] == s["lm_loss"] for s in seen) and seen[-1]["lm_loss"] < seen[0]["lm_loss"]
     cache = os.listdir(tmp_path / "train_data_cache")
     assert any(n.endswith(".bin") for n in cache) and any(n.endswith(".idx") for n in cache)
+
+
+def _other_optimizers(rank, world, kinds):
+    """Both runners with optimizer types other than the native fused Adam, from their YAML."""
+    import torch
+    from easyllm_b200.config import load_yaml, parse_args
+    from easyllm_b200.parallel.grid import initialize_model_parallel
+    from easyllm_b200.runners.base_llm_runner import BaseRunner
+    from easyllm_b200.runners.hf_runner import HFRunner
+    hf_cfg_path = os.path.join(os.path.dirname(CFG), "..", "huggingface", "tiny_llama_cpu.yaml")
+    out = {}
+    for kind, kwargs in kinds:
+        cfg = load_yaml(CFG)
+        cfg["runtime"].update(tensor_model_parallel_size=1, pipeline_model_parallel_size=world)
+        cfg["trainer"]["train_iters"] = 5
+        cfg["trainer"]["optimizer"] = {"type": kind, "kwargs": dict(kwargs)}
+        cfg["saver"]["save_path"] = None
+        cfg["loader"]["load_path"] = None
+        args = parse_args(["--config", CFG, "--launcher", "torch", "--distributed-backend", "gloo"])
+        r = BaseRunner(args, cfg, training=True, base_type="train")
+        before = [p.detach().clone() for p in r.model.parameters()]
+        losses = []
+        orig = r.forward_step
+
+        def rec(it, _orig=orig, _l=losses):
+            o = _orig(it)
+            _l.append(float(o["lm_loss"]))
+            return o
+        r.forward_step = rec
+        r.train()
+        moved = max(float((p.detach() - b).abs().max()) for p, b in zip(r.model.parameters(), before))
+        out[kind] = (type(r.optimizer).__name__, type(getattr(r.optimizer, "inner", None)).__name__, losses,
+                     r.engine.get_global_grad_norm(), moved)
+    return out
+
+
+def test_runner_drives_non_native_optimizers_over_two_pipeline_stages():
+    kinds = [("SophiaG", {"lr": 2e-4, "betas": [0.9, 0.99], "rho": 0.04, "weight_decay": 0.0}),
+             ("Adam8bit", {"lr": 1e-3, "min_8bit_size": 1024, "block_size": 256}),
+             ("SGD", {"lr": 0.05, "momentum": 0.9})]
+    res = run_ranks(2, _other_optimizers, kinds)
+    last = res[1]                                       # the last stage records the loss
+    for kind, inner in (("SophiaG", "SophiaG"), ("Adam8bit", "Adam8bit"), ("SGD", "SGD")):
+        wrapper, inner_name, losses, norm, moved = last[kind]
+        assert wrapper == "TorchOptimizerAdapter" and inner_name == inner
+        assert len(losses) == 5 and all(l == l and l < 12 for l in losses), (kind, losses)
+        assert norm is not None and norm > 0 and moved > 0 and res[0][kind][4] > 0       # both stages were updated
