@@ -80,3 +80,42 @@ def test_four_ranks_tp2_pp2_recompute(baseline):
     outs = run_ranks(4, _train, 2, 2, 0, True, full, True)
     for losses in outs:
         assert max(abs(a - b) for a, b in zip(losses, ref)) < 2e-5, (losses, ref)
+
+
+def _train_adapter(rank, world, tp, pp, sp, full, native):
+    """Adam with clipping at 0.5: natively on one process, or torch.optim.Adam through the adapter on a layout."""
+    from easyllm_b200.parallel.grid import get_grid, initialize_model_parallel
+    from easyllm_b200.models import llama_custom
+    from easyllm_b200.optim import ZeroOptimizer
+    from easyllm_b200.optim.torch_adapter import TorchOptimizerAdapter
+    from easyllm_b200.engine import PipelineEngine
+    from easyllm_b200.data.synthetic import synthetic_batches
+    if world > 1:
+        initialize_model_parallel(tp, pp)
+    g = get_grid()
+    model = llama_custom(**dict(TINY, sequence_parallel=sp))
+    _load_sliced(model, full)
+    if native:
+        opt = ZeroOptimizer(model.named_parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
+                            adamw=False, stage=0, grad_clip=0.5)
+    else:
+        inner = torch.optim.Adam([p for p in model.parameters() if p.requires_grad], lr=1e-3, betas=(0.9, 0.999), eps=1e-8)
+        opt = TorchOptimizerAdapter(inner, model.named_parameters(), grad_clip=0.5)
+    eng = PipelineEngine(model, opt, None, {"train_micro_batch_size_per_gpu": MBS,
+                                            "gradient_accumulation_steps": GBS // (MBS * g.dp)})
+    it = synthetic_batches(32000, SEQ, MBS, seed=0)
+    losses = [float(eng.train_batch(it)) for _ in range(3)]
+    return losses, eng.get_global_grad_norm()
+
+
+def test_optimizer_adapter_matches_the_native_path_on_every_layout(baseline):
+    """The adapter's gradient plumbing (fp32 accumulation, DP averaging, TP sum of sequence-parallel norm weights,
+    global norm with replicated parameters counted once, clipping) reproduces the native optimizer's trajectory."""
+    full, _ = baseline
+    ref_losses, ref_norm = _train_adapter(0, 1, 1, 1, False, full, True)
+    one_losses, one_norm = _train_adapter(0, 1, 1, 1, False, full, False)
+    assert max(abs(a - b) for a, b in zip(one_losses, ref_losses)) < 2e-5 and abs(one_norm - ref_norm) < 1e-4 * ref_norm
+    for tp, pp, sp in ((2, 1, True), (1, 2, False), (1, 1, False)):
+        for losses, norm in run_ranks(2, _train_adapter, tp, pp, sp, full, False):
+            assert max(abs(a - b) for a, b in zip(losses, ref_losses)) < 5e-5, (tp, pp, sp, losses, ref_losses)
+            assert abs(norm - ref_norm) < 1e-3 * ref_norm, (tp, pp, sp, norm, ref_norm)
