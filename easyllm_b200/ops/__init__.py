@@ -26,6 +26,36 @@ from . import reference as ref
 _BACKEND = os.environ.get("EASYLLM_OPS", "b200")          # b200 | torch
 _GEMM = os.environ.get("EASYLLM_GEMM", "tcgen05")         # tcgen05 | cublas
 _ATTN = os.environ.get("EASYLLM_ATTN", "auto")            # auto | kernel | library
+_STRICT = os.environ.get("EASYLLM_STRICT", "0") == "1"    # 1: a shape the kernels cannot take raises instead of falling back
+_FALLBACKS = {}                                           # (op, reason) -> count, for reports and tests
+
+
+def set_strict(flag):
+    """With strict mode on, a CUDA bf16 call that cannot run on the sm_100a kernels raises instead of taking the
+    PyTorch / library path (benchmarks run strict, so a lost product path cannot go unnoticed)."""
+    global _STRICT
+    _STRICT = bool(flag)
+
+
+def fallbacks():
+    """``{(op, reason): count}`` of the calls that left the kernel path since the process started."""
+    return dict(_FALLBACKS)
+
+
+def note_fallback(op, t, reason):
+    """Record that a CUDA bf16 call of ``op`` takes the PyTorch / library path.  Logged once per (op, reason)
+    with the offending shape; raises under strict mode.  CPU tensors, other dtypes and an explicitly selected
+    ``torch`` / ``cublas`` backend are deliberate choices and are not reported."""
+    if not (torch.is_tensor(t) and t.is_cuda and t.dtype == torch.bfloat16 and _BACKEND == "b200"):
+        return
+    msg = f"{op}: {reason} (shape {tuple(t.shape)}); taking the PyTorch / library path instead of the sm_100a kernel"
+    if _STRICT:
+        raise RuntimeError(msg + " [EASYLLM_STRICT=1]")
+    key = (op, reason)
+    if key not in _FALLBACKS:
+        from ..utils.log import default_logger
+        default_logger.warning(msg)
+    _FALLBACKS[key] = _FALLBACKS.get(key, 0) + 1
 
 
 def set_backend(name):
@@ -121,43 +151,61 @@ class _AddRMSNorm(torch.autograd.Function):
         return dh, dh, dw.to(w.dtype), None
 
 
+def _norm_ok(x, op):
+    if not _kern(x):
+        return False
+    if x.shape[-1] % 8 or x.shape[-1] > 8192:
+        note_fallback(op, x, "the row length must be a multiple of 8 and at most 8192")
+        return False
+    return True
+
+
 def rmsnorm(x, weight, eps=1e-6):
-    if _kern(x) and x.dim() == 2 and x.shape[1] % 8 == 0 and x.shape[1] <= 8192:
-        return _RMSNorm.apply(x.contiguous(), weight, eps)
+    if _norm_ok(x, "rmsnorm"):
+        return _RMSNorm.apply(x.reshape(-1, x.shape[-1]).contiguous(), weight, eps).view(x.shape)
     return ref.rmsnorm(x, weight, eps)
 
 
 def add_rmsnorm(x, residual, weight, eps=1e-6):
     """Returns (norm(x + residual), x + residual)."""
-    if _kern(x) and x.dim() == 2 and x.shape[1] % 8 == 0 and x.shape[1] <= 8192:
-        return _AddRMSNorm.apply(x.contiguous(), residual.contiguous(), weight, eps)
+    if _norm_ok(x, "add_rmsnorm"):
+        H = x.shape[-1]
+        y, h = _AddRMSNorm.apply(x.reshape(-1, H).contiguous(), residual.reshape(-1, H).contiguous(), weight, eps)
+        return y.view(x.shape), h.view(x.shape)
     return ref.add_rmsnorm(x, residual, weight, eps)
 
 
 # ---------------------------------------------------------------------------------------------
 # Linear:  y = x · Wᵀ (+ b)
 # ---------------------------------------------------------------------------------------------
-def _gemm_ok(*ts):
-    return _GEMM == "tcgen05" and all(t.shape[-1] % 8 == 0 for t in ts)
+def _gemm_ok(op, a, *dims):
+    """tcgen05 GEMM eligibility: every row length and the output width must be a multiple of 8 elements (TMA
+    strides are multiples of 16 bytes)."""
+    if not _kern(a) or _GEMM != "tcgen05":
+        return False
+    if any(d % 8 for d in dims):
+        note_fallback(op, a, f"dimensions {dims} must all be multiples of 8")
+        return False
+    return True
 
 
 def matmul_nt(a, b, bias=None):
     """a [M,K] · b [N,K]ᵀ → [M,N] (bf16)."""
-    if _kern(a) and _gemm_ok(a, b) and b.shape[0] % 8 == 0:
+    if _gemm_ok("matmul_nt", a, a.shape[-1], b.shape[-1], b.shape[0]):
         return _cu().gemm(a, b, bias=bias)
     return F.linear(a, b, bias)
 
 
 def matmul_nn(a, b):
     """a [M,K] · b [K,N] → [M,N]; b is read in place as an MN-major operand."""
-    if _kern(a) and _gemm_ok(a, b):
+    if _gemm_ok("matmul_nn", a, a.shape[-1], b.shape[-1]):
         return _cu().gemm(a, b, b_mn=True)
     return a @ b
 
 
 def matmul_tn_accum(a, b, out32=None):
     """aᵀ [K,M]ᵀ·b [K,N] → [M,N] fp32, accumulated into ``out32`` when given."""
-    if _kern(a) and _gemm_ok(a, b) and a.shape[1] % 8 == 0:
+    if _gemm_ok("matmul_tn", a, a.shape[-1], b.shape[-1]):
         if out32 is None:
             return _cu().gemm(a, b, a_mn=True, b_mn=True, out_mode=2)
         return _cu().gemm(a, b, out=out32, a_mn=True, b_mn=True, out_mode=1)
@@ -194,8 +242,9 @@ class _Linear(torch.autograd.Function):
 
 
 def linear(x, w, bias=None):
-    if _kern(x) and x.dim() == 2:
-        return _Linear.apply(x.contiguous(), w, bias)
+    if _kern(x):
+        y = _Linear.apply(x.reshape(-1, x.shape[-1]).contiguous(), w, bias)
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], w.shape[0])
     return F.linear(x, w, bias)
 
 
@@ -258,8 +307,9 @@ def linear_parts(x, weights, biases=None):
     bias = None
     if biases is not None and all(b is not None for b in biases):
         bias = torch.cat(list(biases), 0)
-    if _kern(x) and x.dim() == 2:
-        return _LinearParts.apply(x.contiguous(), bias, *weights)
+    if _kern(x):
+        y = _LinearParts.apply(x.reshape(-1, x.shape[-1]).contiguous(), bias, *weights)
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], y.shape[-1])
     return F.linear(x, torch.cat(list(weights), 0), bias)
 
 
@@ -290,8 +340,10 @@ class _Embedding(torch.autograd.Function):
 
 def embedding(ids, weight, vocab_start=0):
     """``weight[ids - vocab_start]`` with zero rows for ids outside this rank's vocabulary range."""
-    if _kern(weight) and weight.shape[1] % 8 == 0 and weight.is_contiguous():
-        return _Embedding.apply(ids, weight, vocab_start)
+    if _kern(weight):
+        if weight.shape[1] % 8 == 0 and weight.is_contiguous():
+            return _Embedding.apply(ids, weight, vocab_start)
+        note_fallback("embedding", weight, "the table must be contiguous with a row length that is a multiple of 8")
     rows = weight.shape[0]
     mask = (ids < vocab_start) | (ids >= vocab_start + rows)
     out = F.embedding((ids - vocab_start).masked_fill(mask, 0), weight)
@@ -320,9 +372,11 @@ class _RopePacked(torch.autograd.Function):
 
 def rope_packed(qkv, cos, sin, pos, n_q_heads, n_kv_heads, head_dim):
     """Rotate the q and k heads of ``qkv [T, (Hq+2Hk)·D]`` (layout q|k|v) at positions ``pos``."""
-    if _kern(qkv) and head_dim % 16 == 0:
-        pos32 = pos if pos.dtype == torch.int32 else pos.to(torch.int32)
-        return _RopePacked.apply(qkv, cos, sin, pos32, n_q_heads + n_kv_heads, head_dim)
+    if _kern(qkv):
+        if head_dim % 16 == 0:
+            pos32 = pos if pos.dtype == torch.int32 else pos.to(torch.int32)
+            return _RopePacked.apply(qkv, cos, sin, pos32, n_q_heads + n_kv_heads, head_dim)
+        note_fallback("rope", qkv, f"head_dim {head_dim} must be a multiple of 16")
     T = qkv.shape[0]
     nq, nk = n_q_heads * head_dim, n_kv_heads * head_dim
     q = qkv[:, :nq].reshape(T, n_q_heads, head_dim)
@@ -345,8 +399,11 @@ class _SwiGLU(torch.autograd.Function):
 
 def glu(gate_up, activation="silu"):
     """``act(gate) * up`` on fused rows ``[T, 2F]`` (gate columns first)."""
-    if _kern(gate_up) and activation in ("silu", "swiglu") and gate_up.dim() == 2 and gate_up.shape[1] % 16 == 0:
-        return _SwiGLU.apply(gate_up.contiguous())
+    if _kern(gate_up):
+        if activation in ("silu", "swiglu") and gate_up.shape[-1] % 16 == 0:
+            W = gate_up.shape[-1]
+            return _SwiGLU.apply(gate_up.reshape(-1, W).contiguous()).view(*gate_up.shape[:-1], W // 2)
+        note_fallback("glu", gate_up, f"activation {activation!r} / width must be silu and a multiple of 16")
     F_ = gate_up.shape[-1] // 2
     return ref.GLU_ACTIVATIONS[activation](gate_up[..., :F_], gate_up[..., F_:])
 
@@ -373,20 +430,38 @@ def _library_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale):
         return flash_attn_varlen_func(q, k, v, cs, cs, max_seqlen, max_seqlen, softmax_scale=scale, causal=causal)
 
 
+def _attn_kernel_reason(dtype, head_dim, alibi_slopes, dropout_p=0.0):
+    """None when the sm_100a attention kernels take the call, else why not."""
+    if _BACKEND != "b200" or _ATTN not in ("auto", "kernel"):
+        return "backend"
+    if dtype != torch.bfloat16:
+        return "dtype"
+    if head_dim != 128:
+        return f"head_dim {head_dim} (the kernels are built for 128)"
+    if alibi_slopes is not None:
+        return "ALiBi bias"
+    if dropout_p:
+        return "attention dropout"
+    return None
+
+
 def flash_attention(q, k, v, cu_seqlens=None, max_seqlen=None, causal=True, scale=None, alibi_slopes=None):
-    """Attention over packed documents: q ``[T,Hq,D]``, k/v ``[T,Hk,D]`` → ``[T,Hq,D]``."""
+    """Attention over packed documents: q ``[T,Hq,D]``, k/v ``[T,Hk,D]`` → ``[T,Hq,D]``.
+    Pass ``max_seqlen`` (a Python int) with ``cu_seqlens``: deriving it here costs a device→host sync."""
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
-    if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and alibi_slopes is None:
+    if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16):
         if max_seqlen is None:
             max_seqlen = q.shape[0] if cu_seqlens is None else int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
-        if _BACKEND == "b200" and _ATTN in ("auto", "kernel"):
-            from . import attention
-            if attention.supported(q, k, v):
-                return attention.flash_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale)
-            if _ATTN == "kernel":
-                raise RuntimeError("attention kernel does not support this shape")
-        return _library_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+        why = _attn_kernel_reason(q.dtype, q.shape[-1], alibi_slopes) or (None if causal else "non-causal")
+        if why is None:
+            return _cu().flash_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+        if _ATTN == "kernel":
+            raise RuntimeError(f"attention kernel does not support this call: {why}")
+        if why not in ("backend", "dtype"):
+            note_fallback("flash_attention", q, why)
+        if alibi_slopes is None:
+            return _library_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale)
     return ref.attention_varlen(q, k, v, cu_seqlens, causal, scale, alibi_slopes)
 
 
@@ -400,8 +475,8 @@ def flash_attention_packed(qkv, n_q_heads, n_kv_heads, head_dim, cu_seqlens=None
     nq, nk = n_q_heads * head_dim, n_kv_heads * head_dim
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
-    if (_kern(qkv) and alibi_slopes is None and head_dim == 128 and _ATTN in ("auto", "kernel") and qkv.dim() == 2
-            and qkv.is_contiguous()):
+    if _kern(qkv) and qkv.dim() == 2 and _attn_kernel_reason(qkv.dtype, head_dim, alibi_slopes) is None:
+        qkv = qkv.contiguous()
         if max_seqlen is None:
             max_seqlen = T if cu_seqlens is None else int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
         if rope is not None:
@@ -525,8 +600,7 @@ class _LMHeadCE(torch.autograd.Function):
 def lm_head_cross_entropy(hidden, weight, target, cut_size=None):
     """LM head GEMM + vocab-parallel CE → per-token losses (fp32, shape of ``target``).  The bf16 logits
     live only between forward and backward; their buffer is overwritten by dlogits in backward."""
-    if (_kern(hidden) and hidden.dim() == 2 and _GEMM == "tcgen05" and hidden.shape[1] % 8 == 0
-            and weight.shape[0] % 8 == 0):
+    if hidden.dim() == 2 and _gemm_ok("lm_head_cross_entropy", hidden, hidden.shape[1], weight.shape[0]):
         return _LMHeadCE.apply(hidden.contiguous(), weight, target, cut_size)
     logits = linear(hidden, weight)
     return vocab_parallel_cross_entropy(logits, target, cut_size, inplace_backward=True)

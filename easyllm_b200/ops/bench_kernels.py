@@ -56,6 +56,7 @@ GEMM_SHAPES = [
 
 def bench_gemm(iters):
     rows = []
+    print(f"# CTA-pair kernel: {cu.lib().ell_gemm_pair_resident_clusters()} two-CTA clusters resident", flush=True)
     for name, M, N, K, lay in GEMM_SHAPES:
         if lay == "nt":
             a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16); b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
@@ -75,23 +76,6 @@ def bench_gemm(iters):
         cu.set_gemm_pair(False)                      # the same call through the single-CTA kernel
         t_one = timed(mine, iters)
         cu.set_gemm_pair(True)
-        if os.environ.get("ELL_BENCH_SWEEP"):
-            # tile width: 128x256 (default for N >= 256) against 128x128
-            if lay == "nt":
-                t128 = timed(lambda: cu.gemm(a, b, bn=128), iters)
-            elif lay == "nn":
-                t128 = timed(lambda: cu.gemm(a, b, b_mn=True, bn=128), iters)
-            else:
-                t128 = timed(lambda: cu.gemm(a, b, out=acc, a_mn=True, b_mn=True, out_mode=1, bn=128), iters)
-            print(f"    BN=256 {t_m:.4f} ms   BN=128 {t128:.4f} ms", flush=True)
-        if os.environ.get("ELL_BENCH_SWEEP_PREFETCH") and cu.has_symbol("ell_gemm_set_prefetch"):
-            # same-process sweep of the producer's L2 prefetch distance (k-blocks); the default is restored after
-            res = []
-            for d in (0, 4, 8, 16):
-                cu.lib().ell_gemm_set_prefetch(d)
-                res.append(f"{d}: {timed(mine, iters):.4f}")
-            cu.lib().ell_gemm_set_prefetch(0)
-            print("    L2 prefetch distance -> ms  " + "  ".join(res), flush=True)
         rows.append({"name": name, "M": M, "N": N, "K": K, "layout": lay, "ms": t_m, "tflops": fl / t_m / 1e9,
                      "frac_of_peak": fl / t_m / 1e9 / _PEAKS["bf16_tflops"], "cublas_ms": t_l,
                      "cublas_tflops": fl / t_l / 1e9, "vs_cublas": t_l / t_m, "single_cta_ms": t_one})

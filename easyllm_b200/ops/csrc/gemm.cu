@@ -865,7 +865,9 @@ ELL_API int ell_bounded_wait_selftest(const void* flag, unsigned int want, int* 
   return launch_status();
 }
 
-static int g_no_tail_split = 0;
+namespace ell {
+int g_no_tail_split = 0;   // shared with gemm_pair.cu
+}
 static int g_rs_ring = 0;   // measured on 2 x B200: the ring order is not faster (o_proj 0.103 vs 0.101 ms, down 0.183 vs 0.177)
 // Tuning switch: tile order of the GEMM -> reduce-scatter kernel (1 ring order, 0 owners interleaved).
 ELL_API void ell_gemm_set_rs_order(int ring) { g_rs_ring = ring ? 1 : 0; }

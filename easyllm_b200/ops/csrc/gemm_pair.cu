@@ -32,6 +32,8 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_
 int make_tmap_f32_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                      uint32_t box_inner, uint32_t box_outer);
 
+extern int g_no_tail_split;   // gemm.cu: 1 keeps whole tiles in an under-filled last wave (ell_gemm_set_tail_split)
+
 namespace pair {
 
 constexpr int kTileM = 256, kTileN = 256;   // per cluster
@@ -133,11 +135,36 @@ __host__ __device__ __forceinline__ void raster(int idx, int tiles_m, int tiles_
   nt = rem / gsz;
 }
 
+// Work units of a launch.  When the last wave would leave at least half of the clusters idle, each of its tiles is
+// cut into two half-width units (128 columns, tcgen05.mma with N = 128), so the tail costs half a wave:
+// units [0, num_full) are whole tiles, unit num_full + 2i + h is half h of tile num_full + i.
+struct Unit {
+  int mt, nt, n0, bn;
+};
+
+__host__ __device__ inline int split_tail(int num_tiles, int clusters, bool allowed) {
+  const int tail = num_tiles % clusters;
+  return (allowed && tail > 0 && 2 * tail <= clusters) ? tail : 0;
+}
+
+__host__ __device__ __forceinline__ Unit decode_unit(int unit, int tiles_m, int tiles_n, int num_full) {
+  Unit u;
+  int tile = unit, half = -1;
+  if (unit >= num_full) {
+    tile = num_full + ((unit - num_full) >> 1);
+    half = (unit - num_full) & 1;
+  }
+  raster(tile, tiles_m, tiles_n, u.mt, u.nt);
+  u.bn = half >= 0 ? kTileN / 2 : kTileN;
+  u.n0 = u.nt * kTileN + (half > 0 ? kTileN / 2 : 0);
+  return u;
+}
+
 template <bool A_MN, bool B_MN, int OUT, bool HAS_BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
-                 int* __restrict__ err) {
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmBh,
+                 const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int tail_split, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
@@ -152,6 +179,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + kTileN - 1) / kTileN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + kBK - 1) / kBK;
+  const int n_split = split_tail(num_tiles, n_clusters, tail_split != 0);
+  const int num_full = num_tiles - n_split, num_units = num_tiles + n_split;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -184,17 +213,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
-        int mt, nt;
-        raster(tile, tiles_m, tiles_n, mt, nt);
-        const int m0 = mt * kTileM + (int)cta_rank * kHalfM;     // A rows of this CTA
-        const int nb0 = nt * kTileN + (int)cta_rank * kHalfN;    // B rows of this CTA
+      for (int unit = cluster_id; unit < num_units && ok; unit += n_clusters) {
+        const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full);
+        const int b_rows = u.bn / 2;                                // B rows staged by one CTA (128, or 64 in a half unit)
+        const int m0 = u.mt * kTileM + (int)cta_rank * kHalfM;     // A rows of this CTA
+        const int nb0 = u.n0 + (int)cta_rank * b_rows;             // B rows of this CTA
+        const CUtensorMap* b_map = (u.bn == kTileN) ? &tmB : &tmBh; // half units: box of 64 B rows
+        const uint32_t stage_tx = 2u * (kABytes + (uint32_t)b_rows * kBK * 2);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) {
             ok = false;
             break;
           }
-          if (is_leader) mbar_expect_tx(&sh->full[stage], 2u * kStageBytes);
+          if (is_leader) mbar_expect_tx(&sh->full[stage], stage_tx);
           const uint32_t bar = map_to_cta(smem_u32(&sh->full[stage]), 0);
           uint8_t* a_dst = sA + stage * kABytes;
           uint8_t* b_dst = sB + stage * kBBytes;
@@ -206,11 +237,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tma_load_2d_pair(a_dst + i * (64 * kBK * 2), &tmA, bar, m0 + i * 64, kb * kBK);
           }
           if (!B_MN) {
-            tma_load_2d_pair(b_dst, &tmB, bar, kb * kBK, nb0);
+            tma_load_2d_pair(b_dst, b_map, bar, kb * kBK, nb0);
           } else {
 #pragma unroll
             for (int i = 0; i < kHalfN / 64; ++i)
-              tma_load_2d_pair(b_dst + i * (64 * kBK * 2), &tmB, bar, nb0 + i * 64, kb * kBK);
+              if (i * 64 < b_rows) tma_load_2d_pair(b_dst + i * (64 * kBK * 2), &tmB, bar, nb0 + i * 64, kb * kBK);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -234,14 +265,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) --------------------------
     if (lane == 0 && is_leader) {
-      constexpr uint32_t idesc = make_idesc_bf16(kTileM, kTileN, A_MN, B_MN);
+      constexpr uint32_t idesc_full = make_idesc_bf16(kTileM, kTileN, A_MN, B_MN);
+      constexpr uint32_t idesc_half = make_idesc_bf16(kTileM, kTileN / 2, A_MN, B_MN);
       constexpr uint32_t a_lbo = A_MN ? 64 * kBK * 2 : 16, a_sbo = 1024, a_kstep = A_MN ? 2048 : 32;
       constexpr uint32_t b_lbo = B_MN ? 64 * kBK * 2 : 16, b_sbo = 1024, b_kstep = B_MN ? 2048 : 32;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters, ++it) {
+      for (int unit = cluster_id; unit < num_units && ok; unit += n_clusters, ++it) {
+        const uint32_t idesc = unit >= num_full ? idesc_half : idesc_full;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&sh->tmem_empty[acc], acc_phase ^ 1, abort_flag)) {
@@ -286,10 +319,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t empty_bar1 = map_to_cta(smem_u32(&sh->tmem_empty[1]), 0);
     int it = 0;
     uint32_t store_count = 0;
-    for (int tile = cluster_id; tile < num_tiles; tile += n_clusters, ++it) {
-      int mt, nt;
-      raster(tile, tiles_m, tiles_n, mt, nt);
-      const int m0 = mt * kTileM + (int)cta_rank * kHalfM, n0 = nt * kTileN;
+    for (int unit = cluster_id; unit < num_units; unit += n_clusters, ++it) {
+      const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full);
+      const int m0 = u.mt * kTileM + (int)cta_rank * kHalfM, n0 = u.n0;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&sh->tmem_full[acc], acc_phase, abort_flag)) sh->epi_abort = 1;
@@ -299,7 +331,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * kTileN;
       if (OUT == kOutBf16) {
 #pragma unroll 1
-        for (int j = 0; j < kTileN / 64; ++j) {
+        for (int j = 0; j < u.bn / 64; ++j) {
           uint8_t* buf = sC + (store_count & 1) * kEpiBufBytes;
           if (store_thread) tma_store_wait_read<1>();
           named_bar_sync(1, kEpiThreads);
@@ -340,7 +372,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       } else {
         // fp32 output: 128 x 32 sub-tiles, stored or added into C at L2 by the TMA unit
 #pragma unroll 1
-        for (int j = 0; j < kTileN / 32; ++j) {
+        for (int j = 0; j < u.bn / 32; ++j) {
           uint8_t* buf = sC + (store_count & 1) * kEpiBufBytes;
           if (store_thread) tma_store_wait_read<1>();
           named_bar_sync(1, kEpiThreads);
@@ -391,6 +423,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// Clusters of a launch: every resident cluster when there is at least a wave of tiles; with less than half a wave,
+// twice the tile count, so that every tile runs as two half-width units on two clusters.
+__host__ inline int launch_clusters(int tiles, int resident) {
+  if (tiles >= resident) return resident;
+  if (!g_no_tail_split && 2 * tiles <= resident) return 2 * tiles;
+  return tiles;
+}
+
 static int max_clusters(const void* kern) {
   static int n = 0;
   if (!n) {
@@ -416,8 +456,8 @@ static int max_clusters(const void* kern) {
 }
 
 template <bool A_MN, bool B_MN, int OUT, bool HAS_BIAS>
-static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, const __nv_bfloat16* bias, int M,
-                  int N, int K, int* err, cudaStream_t stream) {
+static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, const CUtensorMap& tBh,
+                  const __nv_bfloat16* bias, int M, int N, int K, int* err, cudaStream_t stream) {
   auto kern = gemm_pair_kernel<A_MN, B_MN, OUT, HAS_BIAS>;
   static bool configured = false;
   if (!configured) {
@@ -428,7 +468,7 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   const int resident = max_clusters(reinterpret_cast<const void*>(kern));
   if (resident <= 0) return -20;                 // the device cannot co-schedule a pair with this much shared memory
   const int tiles = ((M + kTileM - 1) / kTileM) * ((N + kTileN - 1) / kTileN);
-  const int clusters = tiles < resident ? tiles : resident;
+  const int clusters = launch_clusters(tiles, resident);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * clusters, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
@@ -441,7 +481,7 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tA, tB, tC, bias, M, N, K, err);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tA, tB, tC, tBh, bias, M, N, K, g_no_tail_split ? 0 : 1, err);
   if (e != cudaSuccess) {
     cudaGetLastError();   // a refused launch is reported to the caller, not left behind for the next launch
     return (int)e;
@@ -464,6 +504,40 @@ ELL_API int ell_gemm_pair_enumerate_tiles(int M, int N, int* out, int max_tiles)
   return tiles_m * tiles_n;
 }
 
+// Host-only: the work units of a launch on `clusters` clusters in the order the kernel walks them (unit u goes to
+// cluster u % clusters), tail halving included.  out[u] = {row tile, column tile, first column, width}.  Returns the
+// unit count or -1 when out is too small.
+ELL_API int ell_gemm_pair_enumerate_units(int M, int N, int clusters, int allow_split, int* out, int max_units) {
+  using namespace ell::pair;
+  const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + kTileN - 1) / kTileN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int n_split = split_tail(num_tiles, clusters, allow_split != 0);
+  const int num_full = num_tiles - n_split, num_units = num_tiles + n_split;
+  if (num_units > max_units) return -1;
+  for (int u = 0; u < num_units; ++u) {
+    const Unit t = decode_unit(u, tiles_m, tiles_n, num_full);
+    out[4 * u + 0] = t.mt;
+    out[4 * u + 1] = t.nt;
+    out[4 * u + 2] = t.n0;
+    out[4 * u + 3] = t.bn;
+  }
+  return num_units;
+}
+
+// Two-CTA clusters of the pair kernel that fit on the current device at once (needs a GPU; <= 0 if it cannot run).
+ELL_API int ell_gemm_pair_resident_clusters() {
+  using namespace ell::pair;
+  auto kern = gemm_pair_kernel<false, false, kOutBf16, false>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return max_clusters(reinterpret_cast<const void*>(kern));
+}
+
+// Clusters the kernel would launch for `tiles` tiles when `resident` clusters fit on the device.
+ELL_API int ell_gemm_pair_launch_clusters(int tiles, int resident) { return ell::pair::launch_clusters(tiles, resident); }
+
 // Same contract as ell_gemm_bf16 (without a tile-width hint): C = op(A)·op(B)^T, a_mn / b_mn select MN-major
 // storage, out_mode 0 bf16 C, 1 fp32 C += result, 2 fp32 C = result; bias only with out_mode 0.
 ELL_API int ell_gemm_bf16_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
@@ -483,10 +557,16 @@ ELL_API int ell_gemm_bf16_pair(const void* A, const void* B, void* C, const void
   if (out_mode == kOutBf16) rc = make_tmap_bf16_2d(&tC, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64, 128);
   else                      rc = make_tmap_f32_2d(&tC, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 4, 32, 128);
   if (rc) return rc;
+  // B map with a box of 64 rows: the half-width units of a split tail wave stage 64 B rows per CTA
+  CUtensorMap tBh = tB;
+  if (!b_mn) {
+    rc = make_tmap_bf16_2d(&tBh, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kBK, kHalfN / 2);
+    if (rc) return rc;
+  }
   const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(bias);
 #define ELL_PAIR_CASE(AM_, BM_, OUT_, BIAS_)                                                   \
   if ((bool)a_mn == AM_ && (bool)b_mn == BM_ && out_mode == OUT_ && (bias != nullptr) == BIAS_) \
-    return launch<AM_, BM_, OUT_, BIAS_>(tA, tB, tC, bp, M, N, K, err, stream);
+    return launch<AM_, BM_, OUT_, BIAS_>(tA, tB, tC, tBh, bp, M, N, K, err, stream);
   ELL_PAIR_CASE(false, false, kOutBf16, false)
   ELL_PAIR_CASE(false, false, kOutBf16, true)
   ELL_PAIR_CASE(false, true, kOutBf16, false)

@@ -332,6 +332,25 @@ def gemm_pair_tiles(M, N):
     return [tuple(buf[2 * i:2 * i + 2]) for i in range(n)]
 
 
+def gemm_pair_units(M, N, resident=74, allow_split=True):
+    """Host-only: the (row tile, column tile, first column, width) work units of a CTA-pair GEMM launch on a device
+    where ``resident`` two-CTA clusters fit, in the order the kernel walks them (unit ``u`` runs on cluster
+    ``u % clusters``).  Returns ``(clusters, units)``; an under-filled last wave shows up as 128-wide units."""
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    lib().ell_gemm_set_tail_split(c_int(1 if allow_split else 0))
+    try:
+        clusters = lib().ell_gemm_pair_launch_clusters(c_int(tiles), c_int(resident))
+    finally:
+        lib().ell_gemm_set_tail_split(c_int(1))
+    cap = 2 * tiles + 2
+    buf = (c_int * (4 * cap))()
+    n = lib().ell_gemm_pair_enumerate_units(c_int(M), c_int(N), c_int(clusters), c_int(1 if allow_split else 0), buf,
+                                            c_int(cap))
+    if n < 0:
+        raise KernelError(f"gemm_pair_units failed with code {n}")
+    return clusters, [tuple(buf[4 * i:4 * i + 4]) for i in range(n)]
+
+
 def gemm_ce(x, w, target, vocab_start, valid_cols):
     """LM-head GEMM with the cross-entropy statistics fused into its epilogue.
 

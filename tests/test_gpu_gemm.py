@@ -15,9 +15,13 @@ def cu():
 
 
 def _check(out, ref, K):
+    """Two bounds: the largest element error (catches a single bad element) and the relative Frobenius error (a
+    dropped k-slice or a misplaced tile moves it far above bf16 rounding noise, which sits near 1e-3)."""
     err = (out.float() - ref).abs().max().item()
     tol = 2e-2 * max(1.0, ref.abs().max().item()) if out.dtype == torch.bfloat16 else 1e-3 * (K ** 0.5)
     assert err <= tol, (err, tol)
+    rel = ((out.float() - ref).norm() / ref.norm().clamp_min(1e-12)).item()
+    assert rel <= (4e-3 if out.dtype == torch.bfloat16 else 1e-4), rel
 
 
 SHAPES = [(128, 256, 64), (128, 128, 128), (200, 136, 72), (512, 768, 512), (1000, 520, 264), (4096, 4096, 1024)]
@@ -74,7 +78,10 @@ def test_gemm_tn_wgrad_layout(cu, M, N, K):
     cu.check_err_flag()
 
 
-PAIR_SHAPES = [(256, 256, 64), (384, 320, 192), (1000, 520, 264), (2304, 1280, 328), (4096, 4096, 1024)]
+# (256,256), (384,320), (1000,520): under half a wave of tiles, every tile runs as two half-width units;
+# (2304,1280): 45 whole tiles; (4096,4096): 256 tiles, the last 34 of them cut in two; (4096,9472): 592 whole tiles
+PAIR_SHAPES = [(256, 256, 64), (384, 320, 192), (1000, 520, 264), (2304, 1280, 328), (4096, 4096, 1024),
+               (4096, 9472, 256)]
 
 
 @pytest.mark.parametrize("M,N,K", PAIR_SHAPES)
@@ -102,6 +109,17 @@ def test_gemm_pair_kernel_all_layouts(cu, M, N, K):
     # and the two kernels agree with each other much more closely than either does with the rounding bound
     one, two = cu.gemm(a, b, out_mode=2, pair=False), cu.gemm(a, b, out_mode=2, pair=True)
     assert (one - two).abs().max().item() <= 1e-4 * (K ** 0.5)
+    # whole tiles in the last wave (tail halving off) give the same numbers as the half-width units
+    cu.lib().ell_gemm_set_tail_split(0)
+    try:
+        whole = cu.gemm(a, b, out_mode=2, pair=True)
+        whole_t = cu.gemm(at, bt, a_mn=True, b_mn=True, out_mode=2, pair=True)
+    finally:
+        cu.lib().ell_gemm_set_tail_split(1)
+    assert (whole - two).abs().max().item() <= 1e-4 * (K ** 0.5)
+    _check(whole_t, ref, K)
+    torch.cuda.synchronize()
+    cu.check_err_flag()
 
 
 def test_linear_autograd_matches_torch(cu):

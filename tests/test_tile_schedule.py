@@ -82,6 +82,31 @@ def test_pair_kernel_tile_order(cu, M, N):
     assert [t[0] for t in tiles[:g]] == list(range(g)) and {t[1] for t in tiles[:g]} == {0}
 
 
+@pytest.mark.parametrize("M,N", [(256, 256), (4096, 4096), (4096, 12288), (1000, 520), (4096, 11008), (22016, 4096),
+                                 (4096, 32000), (2304, 1280)])
+@pytest.mark.parametrize("split", [True, False])
+def test_pair_kernel_units_cover_the_output_once_and_halve_only_the_tail(cu, M, N, split):
+    clusters, units = cu.gemm_pair_units(M, N, resident=74, allow_split=split)
+    tm, tn = (M + 255) // 256, (N + 255) // 256
+    cover = {}
+    for mt, nt, n0, bn in units:
+        assert bn in (128, 256) and n0 == nt * 256 + (0 if bn == 256 or (n0 % 256) == 0 else 128)
+        for c in range(n0, n0 + bn, 128):
+            assert (mt, c) not in cover
+            cover[(mt, c)] = 1
+    assert sorted(cover) == sorted((m, c) for m in range(tm) for c in range(0, tn * 256, 128))
+    halves = [u for u in units if u[3] == 128]
+    if not split:
+        assert not halves
+    else:
+        tail = (tm * tn) % clusters
+        want = 2 * tail if (tail and 2 * tail <= clusters) else 0
+        assert len(halves) == want
+        assert all(u[3] == 256 for u in units[:len(units) - want])     # only the last wave is cut
+        if want:                                                        # and it now fits half a wave's worth of clusters
+            assert want <= clusters
+
+
 def _row_starts(T, doc_lens):
     rs, start = [], 0
     for n in doc_lens:
