@@ -168,6 +168,14 @@ def load_engine_checkpoint(engine, load_dir, tag=None, load_optimizer_states=Tru
                 opt.load_resharded(shards)
             else:
                 logger.warning("optimizer shards not found or pipeline layout changed: optimizer state starts fresh")
+    elif opt is not None and load_optimizer_states and load_zero and hasattr(opt, "load_state_dict"):
+        # optimizers driven through the adapter (SophiaG, Adam8bit, NovoGrad, SGD, torch.optim.*): replicated over
+        # DP, saved once by the first DP rank
+        path = zero_file(ckpt_dir, 0, g.pp_rank * g.tp + g.tp_rank, engine.bfloat16_enabled())
+        if os.path.exists(path):
+            opt.load_state_dict(safe_load(path)["optimizer_state_dict"])
+        else:
+            logger.warning(f"no optimizer state at {path}: the optimizer starts with fresh moments and step count")
     client = {k: v for k, v in state.items() if k not in ("lr_scheduler", "ds_config", "module")}
     _barrier()
     return ckpt_dir, client

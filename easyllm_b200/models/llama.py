@@ -150,11 +150,12 @@ class LlamaModelPipe(nn.Module):
         return _TorchCheckpointEngine()
 
     # ---- Dynamic Checkpoint ---------------------------------------------------------------
-    def get_checkpoint_range(self, seq_len: int) -> int:
-        """Number of leading layers of this stage to recompute for a micro-batch of ``seq_len``
-        tokens: the value of the first ``size_map`` key ≥ seq_len; −1 (all) when none is."""
+    def get_checkpoint_range(self, n_tokens: int) -> int:
+        """Number of leading layers of this stage to recompute for a micro-batch of ``n_tokens``
+        tokens (micro-batch size x sequence length, or the packed length): the value of the first
+        ``size_map`` key ≥ n_tokens; −1 (all) when none is."""
         for key in sorted(self.size_map):
-            if seq_len <= key:
+            if n_tokens <= key:
                 return self.size_map[key]
         return -1
 
@@ -219,7 +220,7 @@ class LlamaModelPipe(nn.Module):
         else:
             delta, residual = io.hidden, None
         meta = io.meta()
-        plan = self.recompute_plan(io.seq * (1 if True else g.tp))
+        plan = self.recompute_plan(io.batch * io.seq)      # Dynamic Checkpoint: keyed on the micro-batch's token count
         self.last_recompute_count = sum(plan)
         for bid, rc in zip(self.block_ids, plan):
             cache = self.kv_caches.get(bid) if self.kv_caches is not None else None
@@ -243,9 +244,12 @@ class LlamaModelPipe(nn.Module):
         fused = (self.args.fused_lm_head_loss and type(self.loss_fn).__name__ == "CrossEntropy"
                  and not getattr(head, "lora_head", False))
         if fused:
-            xin = head.gathered_input(x)
+            # under sequence parallelism the gather of the hidden rows is part of the fused op
+            sp = bool(self.args.sequence_parallel) and get_grid().tp > 1
+            xin = x if sp else head.gathered_input(x)
             safe = lab.reshape(-1).masked_fill(lab.reshape(-1) == -100, 0)
-            tok = ops.lm_head_cross_entropy(xin, head.word_embeddings.weight, safe, self.loss_fn.cut_size)
+            tok = ops.lm_head_cross_entropy(xin, head.word_embeddings.weight, safe, self.loss_fn.cut_size,
+                                            gather_sp=sp)
             return self.loss_fn.from_token_losses(tok, lab, labels[1])
         logits = head(x).float().view(io.batch, io.seq, -1)
         return self.loss_fn(logits, labels)

@@ -216,6 +216,14 @@ def matmul_tn_accum(a, b, out32=None):
     return out32
 
 
+def column_sum(x):
+    """fp32 column sums ``x.sum(0)`` of a 2-D tensor (the bias gradient of a linear layer)."""
+    if _kern(x) and x.dim() == 2 and x.shape[1] % 8 == 0:
+        out = torch.zeros(x.shape[1], dtype=torch.float32, device=x.device)
+        return _cu().colsum_(x.contiguous(), out)
+    return x.float().sum(0)
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias):
@@ -237,7 +245,7 @@ class _Linear(torch.autograd.Function):
                 dw = matmul_tn_accum(dy, x).to(w.dtype)
         db = None
         if ctx.bref is not None and ctx.needs_input_grad[2]:
-            db = _grad_to(ctx.bref, dy.float().sum(0))
+            db = _grad_to(ctx.bref, column_sum(dy))
         return dx, dw, db
 
 
@@ -283,7 +291,7 @@ class _LinearParts(torch.autograd.Function):
         x, W = ctx.saved_tensors
         dy = dy.contiguous()
         dx = matmul_nn(dy, W) if ctx.needs_input_grad[0] else None
-        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias and ctx.needs_input_grad[1] else None
+        db = column_sum(dy).to(dy.dtype) if ctx.has_bias and ctx.needs_input_grad[1] else None
         ws = ctx.wrefs
         if not any(ctx.needs_input_grad[2:]):
             return (dx, db) + (None,) * len(ws)
@@ -500,9 +508,22 @@ def _tp_info():
     return g.tp_group, g.tp, g.tp_rank
 
 
-def _combine_parts(mx, se, tl, group, tp):
-    """Cross-rank combine of (max, sumexp, target-logit): returns (lse, target_logit)."""
+def _tp_workspace():
+    from ..parallel import symm
+    return symm.workspace()
+
+
+def _combine_parts(parts, group, tp):
+    """Cross-rank combine of per-token ``parts [T, 3]`` = (max, sum-exp, target logit): returns (lse, target_logit).
+    With the fused-TP workspace installed the exchange is one kernel over peer memory (3 floats per token and rank);
+    otherwise a MAX and a SUM all-reduce."""
+    mx, se, tl = parts[:, 0], parts[:, 1], parts[:, 2]
     if tp > 1:
+        ws = _tp_workspace() if parts.is_cuda and _BACKEND == "b200" else None
+        if ws is not None:
+            res = ws.ce_combine(parts)
+            if res is not None:
+                return res
         gmx = mx.clone()
         dist.all_reduce(gmx, op=dist.ReduceOp.MAX, group=group)
         pair = torch.stack((se * torch.exp(mx - gmx), tl), dim=0)
@@ -527,10 +548,9 @@ class _VocabParallelCE(torch.autograd.Function):
         if _kern(flat):
             flat = flat.contiguous()
             parts = _cu().ce_fwd(flat, tflat.contiguous(), start, valid)
-            mx, se, tl = parts[:, 0].contiguous(), parts[:, 1].contiguous(), parts[:, 2].contiguous()
         else:
-            mx, se, tl = ref.cross_entropy_parts(flat, tflat, start, valid)
-        lse, tl = _combine_parts(mx, se, tl, group, tp)
+            parts = torch.stack(ref.cross_entropy_parts(flat, tflat, start, valid), dim=1)
+        lse, tl = _combine_parts(parts, group, tp)
         ctx.save_for_backward(flat, tflat, lse)
         ctx.meta = (start, valid, logits.shape, inplace_backward)
         return (lse - tl).view(target.shape)
@@ -574,8 +594,7 @@ class _LMHeadCE(torch.autograd.Function):
         start = rank * Vp
         tflat = target.reshape(-1).contiguous()
         logits, parts = _cu().gemm_ce(hidden, weight, tflat, start, valid)
-        lse, tl = _combine_parts(parts[:, 0].contiguous(), parts[:, 1].contiguous(), parts[:, 2].contiguous(),
-                                 group, tp)
+        lse, tl = _combine_parts(parts, group, tp)
         ctx.save_for_backward(hidden, weight, logits, tflat, lse)
         ctx.wref = weight
         ctx.meta = (start, valid)
@@ -597,9 +616,66 @@ class _LMHeadCE(torch.autograd.Function):
         return dx, dw, None, None
 
 
-def lm_head_cross_entropy(hidden, weight, target, cut_size=None):
+class _LMHeadCESP(torch.autograd.Function):
+    """The LM head of a sequence-parallel model in three fused kernels: all-gather of the hidden rows → GEMM →
+    cross-entropy statistics (forward), dlogits·W → reduce-scatter (input gradient) and all-gather → dlogitsᵀ·x
+    (weight gradient).  Nothing is gathered by a separate collective (lm_head.py:53-57 of the reference gathers
+    with ``gather_from_sequence_parallel_region`` first)."""
+
+    @staticmethod
+    def forward(ctx, x_local, weight, target, cut_size):
+        group, tp, rank = _tp_info()
+        ws = _tp_workspace()
+        Vp = weight.shape[0]
+        valid = Vp - cut_size if (cut_size and rank == tp - 1) else Vp
+        start = rank * Vp
+        tflat = target.reshape(-1).contiguous()
+        logits, parts = ws.ag_gemm_ce(x_local, weight, tflat, start, valid)
+        lse, tl = _combine_parts(parts, group, tp)
+        ctx.save_for_backward(x_local, weight, logits, tflat, lse)
+        ctx.wref = weight
+        ctx.meta = (start, valid)
+        return (lse - tl).view(target.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..parallel import mappings as mp
+        x_local, weight, logits, tflat, lse = ctx.saved_tensors
+        start, valid = ctx.meta
+        ws = _tp_workspace()
+        dlogits = _cu().ce_bwd_(logits, tflat, lse, g.reshape(-1).float().contiguous(), start, valid)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = ws.gemm_rs(dlogits, weight, b_mn=True)
+            if dx is None:
+                dx = mp.reduce_scatter_first_dim(matmul_nn(dlogits, weight))
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(ctx.wref, "main_grad", None)
+            if mg is None or ws.agk_wgrad(dlogits, x_local, mg) is None:
+                xg = mp.gather_first_dim(x_local)
+                if mg is not None:
+                    matmul_tn_accum(dlogits, xg, mg)
+                else:
+                    dw = matmul_tn_accum(dlogits, xg).to(weight.dtype)
+        return dx, dw, None, None
+
+
+def lm_head_cross_entropy(hidden, weight, target, cut_size=None, gather_sp=False):
     """LM head GEMM + vocab-parallel CE → per-token losses (fp32, shape of ``target``).  The bf16 logits
-    live only between forward and backward; their buffer is overwritten by dlogits in backward."""
+    live only between forward and backward; their buffer is overwritten by dlogits in backward.
+    ``gather_sp``: ``hidden`` is this rank's sequence shard ``[T/tp, h]``; the gather over the TP group is part
+    of the op (fused into the GEMM kernel when the fused-TP workspace is installed)."""
+    if gather_sp:
+        ws = _tp_workspace() if _kern(hidden) and _GEMM == "tcgen05" else None
+        if ws is not None and hidden.dim() == 2 and ws._pair(hidden.shape[0], weight.shape[0]) \
+                and hidden.shape[0] * ws.tp <= ws.max_tokens and hidden.shape[1] <= ws.hidden and weight.shape[0] % 8 == 0:
+            return _LMHeadCESP.apply(hidden.contiguous(), weight, target, cut_size)
+        if ws is not None:
+            note_fallback("lm_head_cross_entropy", hidden, "the fused gather needs rows per rank in multiples of 256 "
+                                                           "within the workspace")
+        from ..parallel import mappings as mp
+        hidden = mp.gather_from_sequence_parallel_region(hidden, True)
     if hidden.dim() == 2 and _gemm_ok("lm_head_cross_entropy", hidden, hidden.shape[1], weight.shape[0]):
         return _LMHeadCE.apply(hidden.contiguous(), weight, target, cut_size)
     logits = linear(hidden, weight)

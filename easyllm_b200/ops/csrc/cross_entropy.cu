@@ -140,3 +140,94 @@ ELL_API int ell_ce_combine(const float* part, float* parts, int tiles, int T, cu
   ell::ce_combine_kernel<<<(T + 255) / 256, 256, 0, stream>>>(part, parts, tiles, T);
   return ell::launch_status();
 }
+
+#include "gemm_fuse.cuh"
+
+namespace ell {
+constexpr int kCeTpThreads = 256;
+constexpr int kErrCeExchange = 21;
+
+// Cross-rank combine of the vocab-parallel cross-entropy statistics in one kernel, over peer memory.
+// Every rank holds parts[T][3] = (max, sum exp(x - max), target logit) of its vocabulary shard.  A CTA pushes the
+// triples of its 256 tokens into slot [parity][rank] of every peer's exchange buffer (plain stores over NVLink),
+// raises a per-(source, CTA) epoch flag on the peer, waits (bounded) for the peers' flags of the same token block
+// and merges the tp triples in rank order: out[0][t] = log-sum-exp over the whole vocabulary, out[1][t] = target logit.
+// Two buffers alternate by epoch: a peer can only be one call ahead, because a call needs every rank's push.
+__global__ void __launch_bounds__(kCeTpThreads)
+ce_combine_tp_kernel(const float* __restrict__ parts, float* __restrict__ out, int T, int max_tokens, int rank, int tp,
+                     uint32_t epoch, FuseArgs ptrs, int flags_per_src, int* __restrict__ err) {
+  __shared__ int failed;
+  const int t = blockIdx.x * kCeTpThreads + threadIdx.x;
+  const size_t slot = (size_t)max_tokens * 3;
+  const size_t par = (size_t)(epoch & 1) * tp * slot;
+  float m = -INFINITY, s = 0.f, tl = 0.f;
+  if (threadIdx.x == 0) failed = 0;
+  if (t < T) {
+    m = parts[(size_t)t * 3];
+    s = parts[(size_t)t * 3 + 1];
+    tl = parts[(size_t)t * 3 + 2];
+    for (int p = 0; p < tp; ++p) {
+      if (p == rank) continue;
+      float* dst = reinterpret_cast<float*>(ptrs.data_ptrs[p]) + par + (size_t)rank * slot + (size_t)t * 3;
+      dst[0] = m;
+      dst[1] = s;
+      dst[2] = tl;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int p = 0; p < tp; ++p)
+      if (p != rank) st_release_sys(ptrs.flag_ptrs[p] + (size_t)rank * flags_per_src + blockIdx.x, epoch);
+  }
+  if ((int)threadIdx.x < tp && (int)threadIdx.x != rank) {
+    volatile int never = 0;
+    if (!wait_flag_ge(ptrs.flag_ptrs[rank] + (size_t)threadIdx.x * flags_per_src + blockIdx.x, epoch, &never)) {
+      failed = 1;
+      atomicCAS(err, 0, kErrCeExchange);
+    }
+  }
+  __syncthreads();
+  if (t >= T || failed) return;
+  const float* mine = reinterpret_cast<const float*>(ptrs.data_ptrs[rank]) + par;
+  float gm = -INFINITY, gs = 0.f, gt = 0.f;
+  for (int p = 0; p < tp; ++p) {
+    float pm = m, ps = s, pt = tl;
+    if (p != rank) {
+      const float* src = mine + (size_t)p * slot + (size_t)t * 3;
+      pm = src[0];
+      ps = src[1];
+      pt = src[2];
+    }
+    gt += pt;
+    if (pm > -INFINITY) {
+      const float nm = fmaxf(gm, pm);
+      gs = gs * __expf(gm - nm) + ps * __expf(pm - nm);
+      gm = nm;
+    }
+  }
+  out[t] = __logf(gs) + gm;
+  out[(size_t)T + t] = gt;
+}
+}  // namespace ell
+
+// parts [T, 3] of this rank -> out [2][T] = (lse, target logit) over all tp ranks.  bufs[r] / flags[r]: rank r's
+// exchange buffer ([2][tp][max_tokens][3] floats) and flag words ([tp][flags_per_src]) as peer pointers.
+ELL_API int ell_ce_combine_tp(const float* parts, float* out, int T, int max_tokens, int rank, int tp,
+                              unsigned int epoch, void* const* bufs, void* const* flags, int* err,
+                              cudaStream_t stream) {
+  using namespace ell;
+  if (T == 0) return 0;
+  if (tp < 1 || tp > kMaxTp || T > max_tokens) return -2;
+  const int blocks = (T + kCeTpThreads - 1) / kCeTpThreads;
+  const int flags_per_src = 8192;
+  if (blocks > flags_per_src) return -2;
+  FuseArgs a{};
+  for (int i = 0; i < tp; ++i) {
+    a.data_ptrs[i] = (__nv_bfloat16*)bufs[i];
+    a.flag_ptrs[i] = (uint32_t*)flags[i];
+  }
+  ce_combine_tp_kernel<<<blocks, kCeTpThreads, 0, stream>>>(parts, out, T, max_tokens, rank, tp, epoch, a, flags_per_src,
+                                                           err);
+  return launch_status();
+}

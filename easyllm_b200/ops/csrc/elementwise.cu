@@ -207,3 +207,50 @@ ELL_API int ell_embedding_bwd(const long long* ids, const void* dout, float* gra
                                                        rows);
   return ell::launch_status();
 }
+
+namespace ell {
+// Column sums of a bf16 matrix added into fp32: out[c] += sum_r x[r, c].  The bias gradient of a linear layer
+// (db = sum over tokens of dy) without materialising an fp32 copy of dy.  A block covers 256 columns (32 threads x 8
+// columns, 16-byte loads) and a slice of the rows (8 row lanes); lanes meet in shared memory, one atomic per column
+// and block.
+__global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out,
+                                                     int rows, int cols) {
+  __shared__ float red[8][256];
+  const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * 256 + cg * 8;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  if (c0 < cols) {
+    for (int r = blockIdx.y * 8 + rl; r < rows; r += gridDim.y * 8) {
+      float t[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(x + (size_t)r * cols + c0), t);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += t[e];
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) red[rl][cg * 8 + e] = acc[e];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < cols) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += red[i][threadIdx.x];
+    atomicAdd(out + c, s);
+  }
+}
+}  // namespace ell
+
+// out[cols] (fp32) += column sums of x[rows, cols] (bf16, cols a multiple of 8).
+ELL_API int ell_colsum_bf16(const void* x, float* out, int rows, int cols, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (cols % 8) return -1;
+  const int bx = (cols + 255) / 256;
+  int by = (rows + 63) / 64;
+  const int cap = (ell::kNumSMs * 8 + bx - 1) / bx;
+  if (by > cap) by = cap;
+  if (by < 1) by = 1;
+  ell::colsum_kernel<<<dim3(bx, by), 256, 0, stream>>>((const __nv_bfloat16*)x, out, rows, cols);
+  return ell::launch_status();
+}

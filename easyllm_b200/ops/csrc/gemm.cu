@@ -22,86 +22,12 @@
 // This replaces the cuBLAS calls behind torch.matmul / F.linear in the reference
 // (llm/models/mg_models/base_modules/layers/column_parallel_linear.py:42,68,99,
 //  row_parallel_linear.py:113, llama/lm_head.py:62-66).
-#include "common.cuh"
-#include "sm100.cuh"
+#include "gemm_fuse.cuh"
 
 namespace ell {
-using namespace sm100;
 
-constexpr int kBM = 128;
-constexpr int kBK = 64;                    // 64 bf16 = one 128-byte swizzle row
-constexpr int kGemmThreads = 192;
-constexpr int kEpiThreads = 128;
 constexpr int kABytes = kBM * kBK * 2;     // 16 KiB
-constexpr int kEpiBufBytes = 128 * 64 * 2; // one 128x64 bf16 store box
-
-// kOutBf16CE: bf16 C plus, per row and column tile, the cross-entropy statistics (max, sum-exp, target logit)
-// of the rounded logits, computed in the epilogue while the tile is in registers.
-enum GemmOut { kOutBf16 = 0, kOutF32Accum = 1, kOutF32 = 2, kOutBf16CE = 3 };
-enum GemmErr { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3, kErrComm = 4, kErrFlagWait = 5 };
-
-// ---- fusion with the tensor-parallel collective (sequence parallelism) ------------------------------
-//  kFuseAG  all-gather -> GEMM: the A operand is the concatenation over ranks of row shards.  CTAs
-//           [0, n_comm) copy this rank's shard into every rank's gathered buffer through peer pointers
-//           (plain 16-byte loads/stores over NVLink), one 128-row tile at a time, and publish a flag per
-//           tile; the GEMM CTAs start on the local shard and take remote shards in ring order, waiting
-//           on a tile's flag only before its first TMA load (always a load of local memory into one CTA).
-//  kFuseRS  GEMM -> reduce-scatter: every rank computes the full partial product; finished bf16 tiles
-//           go to a local staging buffer (TMA store) and a flag is raised on the tile's owner rank; CTAs
-//           [0, n_comm) of the owner sum the tp staged copies (peer loads, fp32 add, fixed order so the
-//           result is deterministic) into the local output shard while the main loop is still running,
-//           and every GEMM CTA joins that reduction as soon as its own tiles are done.
-// Flags are epoch counters that only grow; a per-peer `done` word tells a producer that the consumer
-// has finished the previous epoch before a buffer is overwritten.  Every wait is bounded.
-enum GemmFuse { kFuseNone = 0, kFuseAG = 1, kFuseRS = 2 };
-constexpr int kMaxTp = 8;
 constexpr int kGroupM = 16;   // tiles are walked in groups of 16 M-tiles x all N-tiles for L2 reuse
-
-struct FuseArgs {
-  int rank, tp, n_comm, rows_per_rank, flags_per_src;
-  uint32_t epoch;
-  const __nv_bfloat16* x_local;          // AG: this rank's shard [rows_per_rank, K]
-  __nv_bfloat16* data_ptrs[kMaxTp];      // AG: gathered buffers [M, K]; RS: staging buffers [M, N]
-  uint32_t* flag_ptrs[kMaxTp];           // [tp][flags_per_src] on every rank
-  uint32_t* done_ptrs[kMaxTp];           // [tp] on every rank
-  unsigned int* counter;                 // local, monotonic: finished CTAs
-  unsigned int* queue;                   // RS: local, monotonic: next owned tile to reduce
-  unsigned int queue_base;               // RS: value of *queue when this launch starts (tracked by the host)
-  __nv_bfloat16* y_local;                // RS: output shard [rows_per_rank, N]
-  // kOutBf16CE: targets [M] (global vocab ids), partials [tiles_n][3][M], first vocab id of column 0,
-  // number of leading columns that are real vocabulary (the padded tail is excluded)
-  const long long* ce_target;
-  float* ce_part;
-  long long ce_vocab_start;
-  int ce_valid;
-  int no_tail_split;                     // plain launches: 1 disables the half-width tail tiles
-  int prefetch_kb;                       // L2 prefetch distance of the producer in k-blocks (0 = off)
-  int rs_ring;                           // RS: 1 = ring tile order (own tiles last), 0 = owners interleaved
-};
-
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
-
-// Bounded spin until *flag >= want.  False on timeout / abort.
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, volatile int* abort_flag) {
-  if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  while ((int32_t)(ld_acquire_sys(flag) - want) < 0) {
-    if ((++spins & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitTimeoutNs) return false;
-    }
-  }
-  return true;
-}
 
 // The tile-order functions below are __host__ __device__: ell_gemm_enumerate_units runs the very same code on the
 // host so a CPU test can check that every launch covers each output tile exactly once, in the intended order.
@@ -122,20 +48,10 @@ __host__ __device__ __forceinline__ void map_tile(int idx, int tiles_m, int tile
     int mi;
     swizzle_tile(idx % per_phase, tpr, tiles_n, mi, nt);
     mt = ((f.rank + phase) % f.tp) * tpr + mi;
-  } else if (FUSE == kFuseRS) {
-    if (f.rs_ring) {
-      // ring order: the tiles owned by rank+1 first, ..., this rank's own tiles last.  Partials for remote owners
-      // cross NVLink early, and the tiles a rank reduces at the very end only wait for its own (local) partial.
-      const int tpr = tiles_m / f.tp, per_phase = tpr * tiles_n;
-      const int phase = idx / per_phase;
-      int mi;
-      swizzle_tile(idx % per_phase, tpr, tiles_n, mi, nt);
-      mt = ((f.rank + 1 + phase) % f.tp) * tpr + mi;
-    } else {
-      int mp;
-      swizzle_tile(idx, tiles_m, tiles_n, mp, nt);
-      mt = (mp % f.tp) * (tiles_m / f.tp) + mp / f.tp;   // interleave owners so every owner is fed evenly
-    }
+  } else if (FUSE == kFuseRS || FUSE == kFuseAR) {
+    int mp;
+    swizzle_tile(idx, tiles_m, tiles_n, mp, nt);
+    mt = (mp % f.tp) * (tiles_m / f.tp) + mp / f.tp;   // interleave owners so every owner is fed evenly
   } else {
     swizzle_tile(idx, tiles_m, tiles_n, mt, nt);
   }
@@ -186,195 +102,6 @@ struct GemmShared {
   int epi_abort;
 };
 
-
-// ---- communication roles (CTAs [0, n_comm) of a fused launch) ---------------------------------------
-// Both roles move data with the bulk-copy engine (cp.async.bulk through a shared-memory ring), driven by
-// one thread, so a CTA keeps ~190 KB in flight: NVLink latency is hidden without many threads or SMs.
-constexpr int kCommStages = 6;
-constexpr int kCommChunkBytes = 32768;
-
-struct CommShared {
-  uint64_t full[kCommStages];
-  uint64_t empty[kCommStages];
-  int meta[kCommStages];
-  int abort_flag;
-};
-
-// All-gather side: copy the local shard, tile by tile, into the gathered buffer of every other rank.
-// (The local GEMM reads its own shard in place; nothing is copied to self.)
-__device__ void ag_comm_role(const FuseArgs& f, int K, int* err, uint8_t* smem) {
-  CommShared* cs = reinterpret_cast<CommShared*>(smem + kCommStages * kCommChunkBytes);
-  if (threadIdx.x != 0) return;
-  for (int s = 0; s < kCommStages; ++s) mbar_init(&cs->full[s], 1);
-  cs->abort_flag = 0;
-  fence_barrier_init();
-  volatile int* abort_flag = &cs->abort_flag;
-  const int tiles = f.rows_per_rank / kBM;
-  const size_t tile_bytes = (size_t)kBM * K * 2;
-  const int chunks = (int)((tile_bytes + kCommChunkBytes - 1) / kCommChunkBytes);
-  // destinations must have consumed the previous epoch before their buffers are overwritten
-  for (int d = 0; d < f.tp; ++d)
-    if (d != f.rank && !wait_flag_ge(f.done_ptrs[f.rank] + d, f.epoch - 1, abort_flag)) {
-      atomicCAS(err, 0, kErrComm);
-      return;
-    }
-  uint32_t issued = 0, landed = 0;   // chunk counters across items select ring stage and parity
-  // Work item = (row tile, destination): with few row tiles per rank (large tp) every comm CTA still has work,
-  // and each destination's flag is raised as soon as its copy of the tile has landed.
-  const int n_dest = f.tp - 1;
-  const int n_items = tiles * n_dest;
-  for (int item = blockIdx.x; item < n_items; item += f.n_comm) {
-    const int t = item / n_dest;
-    const int dest = (f.rank - 1 - item % n_dest + f.tp) % f.tp;   // the rank that needs this shard soonest first
-    const uint8_t* src = reinterpret_cast<const uint8_t*>(f.x_local) + (size_t)t * tile_bytes;
-    uint8_t* dst = reinterpret_cast<uint8_t*>(f.data_ptrs[dest]) +
-                   ((size_t)f.rank * f.rows_per_rank + (size_t)t * kBM) * K * 2;
-    int next_load = 0;
-    auto issue_load = [&](int c) {
-      const uint32_t st = issued % kCommStages;
-      const uint32_t bytes = (uint32_t)min((size_t)kCommChunkBytes, tile_bytes - (size_t)c * kCommChunkBytes);
-      mbar_expect_tx(&cs->full[st], bytes);
-      bulk_load(smem + st * kCommChunkBytes, src + (size_t)c * kCommChunkBytes, bytes, &cs->full[st]);
-      ++issued;
-    };
-    for (; next_load < chunks && next_load < kCommStages - 1; ++next_load) issue_load(next_load);
-    for (int c = 0; c < chunks; ++c) {
-      const uint32_t st = landed % kCommStages;
-      if (!mbar_wait(&cs->full[st], (landed / kCommStages) & 1, abort_flag)) {
-        atomicCAS(err, 0, kErrComm);
-        return;
-      }
-      ++landed;
-      const uint32_t bytes = (uint32_t)min((size_t)kCommChunkBytes, tile_bytes - (size_t)c * kCommChunkBytes);
-      bulk_store(dst + (size_t)c * kCommChunkBytes, smem + st * kCommChunkBytes, bytes);
-      tma_store_commit();
-      if (next_load < chunks) {
-        tma_store_wait_read<1>();   // the stage about to be refilled was last read by the previous group
-        issue_load(next_load++);
-      }
-    }
-    tma_store_wait_all<0>();        // the whole tile has been written on the destination
-    fence_proxy_async_all();
-    __threadfence_system();
-    st_release_sys(f.flag_ptrs[dest] + (size_t)f.rank * f.flags_per_src + t, f.epoch);
-  }
-}
-
-// Staged tile layout of GEMM->reduce-scatter: every 128x64 bf16 sub-tile is one contiguous 16 KiB block
-// (rows of 128 B, 16-byte chunks XOR-swizzled by row & 7, exactly as the epilogue wrote them to smem).
-template <int BN>
-__device__ __forceinline__ size_t stage_block(int mt, int nt, int j, int tiles_n) {
-  return ((size_t)(mt * tiles_n + nt) * (BN / 64) + j) * kEpiBufBytes;
-}
-
-// Reduce-scatter side: sum the tp staged copies of every tile this rank owns into y_local.
-// Owned tiles are handed out through a global queue in the order producers emit them, so the dedicated
-// CTAs keep pace with the main loop and the GEMM CTAs only pick up what is left when they finish.
-template <int BN>
-__device__ void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int* err, uint8_t* smem, int nparts) {
-  CommShared* cs = reinterpret_cast<CommShared*>(smem + kCommStages * kCommChunkBytes);
-  constexpr int kConsumers = kGemmThreads - 32;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kCommStages; ++s) {
-      mbar_init(&cs->full[s], 1);
-      mbar_init(&cs->empty[s], kConsumers);
-    }
-    cs->abort_flag = 0;
-    fence_barrier_init();
-  }
-  __syncthreads();
-  volatile int* abort_flag = &cs->abort_flag;
-  const int tpr = f.rows_per_rank / kBM;
-  const int owned = tpr * tiles_n;
-  const int gm = f.rs_ring ? kGroupM : max(1, kGroupM / f.tp);   // the order in which producers emit owned tiles
-  const int R = 256 / f.tp;                   // rows per ring stage: tp sources x R rows x 128 B = 32 KiB
-  const int parts = kBM / R;
-  const uint32_t src_bytes = (uint32_t)R * 128;
-  const unsigned int queue_base = f.queue_base;
-  if (threadIdx.x == 0) {
-    uint32_t item = 0;
-    bool ok = true;
-    while (ok) {
-      const int j = (int)(atomicAdd(f.queue, 1u) - queue_base);
-      if (j >= owned) break;
-      const int width = gm * tiles_n, g = j / width, rem = j % width;
-      const int first = g * gm, gsz = min(tpr - first, gm);
-      const int mi = first + rem % gsz, nt = rem / gsz;
-      for (int s = 0; s < f.tp && ok; ++s) {
-        const uint32_t* fl = f.flag_ptrs[f.rank] + (size_t)s * f.flags_per_src + mi * tiles_n + nt;
-        ok = wait_flag_ge(fl, f.epoch, abort_flag);
-      }
-      if (!ok) break;
-      fence_proxy_async_all();
-      const int mt = f.rank * tpr + mi;
-      for (int sub = 0; sub < BN / 64 && ok; ++sub) {
-        const size_t blk = stage_block<BN>(mt, nt, sub, tiles_n);
-        for (int p = 0; p < parts; ++p, ++item) {
-          const uint32_t st = item % kCommStages;
-          if (!mbar_wait(&cs->empty[st], ((item / kCommStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
-          cs->meta[st] = ((mi * tiles_n + nt) * (BN / 64) + sub) * parts + p;
-          mbar_expect_tx(&cs->full[st], src_bytes * f.tp);
-          for (int s = 0; s < f.tp; ++s)
-            bulk_load(smem + st * kCommChunkBytes + s * src_bytes,
-                      reinterpret_cast<const uint8_t*>(f.data_ptrs[s]) + blk + (size_t)p * src_bytes, src_bytes,
-                      &cs->full[st]);
-        }
-      }
-    }
-    if (ok) {
-      // end marker for the consumers
-      const uint32_t st = item % kCommStages;
-      if (mbar_wait(&cs->empty[st], ((item / kCommStages) & 1) ^ 1, abort_flag)) {
-        cs->meta[st] = -1;
-        mbar_arrive(&cs->full[st]);
-      } else {
-        ok = false;
-      }
-    }
-    if (!ok) {
-      cs->abort_flag = 1;
-      atomicCAS(err, 0, kErrComm);
-    }
-  } else if (threadIdx.x >= 32) {
-    const int ct = threadIdx.x - 32;
-    for (uint32_t item = 0;; ++item) {
-      const uint32_t st = item % kCommStages;
-      if (!mbar_wait(&cs->full[st], (item / kCommStages) & 1, abort_flag)) break;
-      int code = cs->meta[st];
-      if (code < 0) break;
-      const int p = code % parts; code /= parts;
-      const int sub = code % (BN / 64); code /= (BN / 64);
-      const int nt = code % tiles_n, mi = code / tiles_n;
-      const uint8_t* base = smem + st * kCommChunkBytes;
-      for (int q = ct; q < R * 8; q += kConsumers) {
-        const int rl = q >> 3, cphys = q & 7;
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-        for (int s = 0; s < f.tp; ++s) {
-          float t[8];
-          unpack8(*reinterpret_cast<const bf16x8*>(base + s * src_bytes + q * 16), t);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] += t[e];
-        }
-        const int row = p * R + rl;
-        const int col = nt * BN + sub * 64 + ((cphys ^ (row & 7)) << 3);
-        if (col < N) *reinterpret_cast<bf16x8*>(f.y_local + ((size_t)mi * kBM + row) * N + col) = pack8(acc);
-      }
-      mbar_arrive(&cs->empty[st]);
-    }
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const unsigned int old = atomicAdd(f.counter, 1u);
-    if ((old + 1) % (unsigned int)nparts == 0) {
-      for (int p = 0; p < f.tp; ++p)
-        if (p != f.rank) st_release_sys(f.done_ptrs[p] + f.rank, f.epoch);
-    }
-  }
-}
-
 template <int BN, bool A_MN, bool B_MN, int OUT, bool HAS_BIAS, int FUSE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -403,7 +130,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (FUSE != kFuseNone && (int)blockIdx.x < n_comm) {
     if (FUSE == kFuseAG) ag_comm_role(fuse, K, err, smem);
-    else rs_reduce_role<BN>(fuse, N, tiles_n, err, smem, (int)gridDim.x);
+    else rs_reduce_role<BN>(fuse, N, tiles_n, err, smem, (int)gridDim.x, false, FUSE == kFuseAR);
     return;
   }
 
@@ -484,24 +211,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int i = 0; i < BN / 64; ++i)
               if (i * 64 < u.bn) tma_load_2d(b_dst + i * (64 * kBK * 2), &tmB, &sh->full[stage], n0 + i * 64, kb * kBK);
           }
-          // optional L2 prefetch of the k-block `prefetch_kb` ahead (off by default: on B200 it slowed every shape,
-          // the CTAs that share a tile each re-request it)
-          if (FUSE != kFuseAG && fuse.prefetch_kb > 0 && kb + fuse.prefetch_kb < num_kb) {
-            const int kp = (kb + fuse.prefetch_kb) * kBK;
-            if (!A_MN) {
-              tma_prefetch_l2_2d(a_map, kp, a_row);
-            } else {
-#pragma unroll
-              for (int i = 0; i < kBM / 64; ++i) tma_prefetch_l2_2d(&tmA, m0 + i * 64, kp);
-            }
-            if (!B_MN) {
-              tma_prefetch_l2_2d(b_map, kp, n0);
-            } else {
-#pragma unroll
-              for (int i = 0; i < BN / 64; ++i)
-                if (i * 64 < u.bn) tma_prefetch_l2_2d(&tmB, n0 + i * 64, kp);
-            }
-          }
           if (++stage == Cfg::kStages) {
             stage = 0;
             phase ^= 1;
@@ -572,7 +281,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int it = 0;
     uint32_t store_count = 0;
     uint32_t* pending_flag = nullptr;   // RS: flag of the last staged tile, raised once its stores completed
-    if (FUSE == kFuseRS && leader) {
+    if ((FUSE == kFuseRS || FUSE == kFuseAR) && leader) {
       // peers must have finished reading last epoch's staged tiles before they are overwritten
       for (int p = 0; p < fuse.tp; ++p)
         if (p != fuse.rank && !wait_flag_ge(fuse.done_ptrs[fuse.rank] + p, fuse.epoch - 1, abort_flag)) {
@@ -655,7 +364,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           fence_proxy_async_smem();
           named_bar_sync(1, kEpiThreads);
           if (leader) {
-            if (FUSE == kFuseRS) {
+            if (FUSE == kFuseRS || FUSE == kFuseAR) {
               bulk_store(reinterpret_cast<uint8_t*>(fuse.data_ptrs[fuse.rank]) + stage_block<BN>(mt, nt, j, tiles_n),
                          buf, kEpiBufBytes);
             } else if (n0 + j * 64 < N) {
@@ -674,7 +383,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             part[(size_t)2 * M] = ce_t;
           }
         }
-        if (FUSE == kFuseRS && leader) {
+        if ((FUSE == kFuseRS || FUSE == kFuseAR) && leader) {
           // Publish the flag of the PREVIOUS tile: its bulk stores were committed BN/64 groups ago, so
           // waiting until at most BN/64 groups are pending does not stall behind this tile's stores.
           if (pending_flag != nullptr) {
@@ -724,7 +433,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     if (leader) {
       tma_store_wait_all<0>();
-      if (FUSE == kFuseRS && pending_flag != nullptr) {
+      if ((FUSE == kFuseRS || FUSE == kFuseAR) && pending_flag != nullptr) {
         fence_proxy_async_all();
         st_release_sys(pending_flag, fuse.epoch);
       }
@@ -743,17 +452,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc<Cfg::kTmemCols>(tmem_base);
   }
-  if (FUSE == kFuseRS) {
+  if (FUSE == kFuseRS || FUSE == kFuseAR) {
     // the main loop is done: this CTA now helps summing the staged tiles its rank owns (the
     // dedicated CTAs [0, n_comm) have been doing so since launch)
     __syncthreads();
-    rs_reduce_role<BN>(fuse, N, tiles_n, err, smem, (int)gridDim.x);
+    rs_reduce_role<BN>(fuse, N, tiles_n, err, smem, (int)gridDim.x, false, FUSE == kFuseAR);
   }
   if (FUSE == kFuseAG && threadIdx.x == 0) {
     // last GEMM CTA of this rank: tell every peer that its pushes of this epoch were consumed
     __threadfence();
     const unsigned int old = atomicAdd(fuse.counter, 1u);
-    if ((old + 1) % (unsigned int)cta_stride == 0) {
+    if (old + 1 - fuse.counter_base == (unsigned int)cta_stride) {
       for (int p = 0; p < fuse.tp; ++p)
         if (p != fuse.rank) st_release_sys(fuse.done_ptrs[p] + fuse.rank, fuse.epoch);
     }
@@ -868,13 +577,6 @@ ELL_API int ell_bounded_wait_selftest(const void* flag, unsigned int want, int* 
 namespace ell {
 int g_no_tail_split = 0;   // shared with gemm_pair.cu
 }
-static int g_rs_ring = 0;   // measured on 2 x B200: the ring order is not faster (o_proj 0.103 vs 0.101 ms, down 0.183 vs 0.177)
-// Tuning switch: tile order of the GEMM -> reduce-scatter kernel (1 ring order, 0 owners interleaved).
-ELL_API void ell_gemm_set_rs_order(int ring) { g_rs_ring = ring ? 1 : 0; }
-static int g_prefetch_kb = 0;   // measured on B200: distances 4-16 cost 15-40 % (every CTA re-requests shared tiles)
-// Tuning switch: L2 prefetch distance of the GEMM producer in 64-element k-blocks (0 disables it).
-ELL_API void ell_gemm_set_prefetch(int k_blocks) { g_prefetch_kb = k_blocks < 0 ? 0 : k_blocks; }
-
 // Tuning switch: 0 (default) cuts the tiles of an under-filled last wave in two, 1 keeps whole tiles.
 ELL_API void ell_gemm_set_tail_split(int enabled) { g_no_tail_split = enabled ? 0 : 1; }
 
@@ -899,12 +601,11 @@ static int enumerate_units(int M, int N, const FuseArgs& f, int ctas, bool allow
 // (u / ctas)-th item), computed by the kernel's own tile-order code.  out[u] = {row tile, column tile, first column,
 // width}.  fuse: 0 plain, 1 all-gather -> GEMM, 2 GEMM -> reduce-scatter.  Returns the unit count, -1 if out is too
 // small, -3 for an unsupported bn / fuse.  Touches no GPU.
-ELL_API int ell_gemm_enumerate_units(int M, int N, int bn, int fuse, int tp, int rank, int rs_ring, int ctas,
-                                     int allow_split, int* out, int max_units) {
+ELL_API int ell_gemm_enumerate_units(int M, int N, int bn, int fuse, int tp, int rank, int ctas, int allow_split,
+                                     int* out, int max_units) {
   FuseArgs f{};
   f.tp = tp;
   f.rank = rank;
-  f.rs_ring = rs_ring;
   if (bn == 256 && fuse == kFuseNone) return enumerate_units<256, kFuseNone>(M, N, f, ctas, allow_split != 0, out, max_units);
   if (bn == 128 && fuse == kFuseNone) return enumerate_units<128, kFuseNone>(M, N, f, ctas, allow_split != 0, out, max_units);
   if (bn == 256 && fuse == kFuseAG) return enumerate_units<256, kFuseAG>(M, N, f, ctas, false, out, max_units);
@@ -942,7 +643,6 @@ ELL_API int ell_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   const int ctas = sm_count();
   FuseArgs Cf{};
   Cf.no_tail_split = g_no_tail_split;
-  Cf.prefetch_kb = g_prefetch_kb;
   const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(bias);
   // second B map with a box of BN/2 rows: used by the half-width tiles of a split tail wave
   CUtensorMap tBh = tB;
@@ -988,34 +688,38 @@ ELL_API int ell_gemm_ce(const void* X, const void* W, void* logits, const long l
   f.ce_part = part;
   f.ce_vocab_start = vocab_start;
   f.ce_valid = valid_cols < N ? valid_cols : N;
-  f.prefetch_kb = g_prefetch_kb;
   return launch_gemm<256, false, false, kOutBf16CE, false>(tA, tB, tC, f, nullptr, M, N, K, N, err, sm_count(), stream);
 }
 
 static void fill_fuse(FuseArgs& f, int rank, int tp, int n_comm, int rows_per_rank, int flags_per_src,
-                      unsigned int epoch, void* const* data_ptrs, void* const* flag_ptrs, void* const* done_ptrs,
-                      void* counter) {
+                      unsigned int epoch, void* const* data_ptrs, void* const* flag_ptrs, void* const* red_ptrs,
+                      void* const* done_ptrs, void* counter, unsigned int counter_base) {
   f.rank = rank; f.tp = tp; f.n_comm = n_comm; f.rows_per_rank = rows_per_rank; f.flags_per_src = flags_per_src;
   f.epoch = epoch;
   for (int i = 0; i < tp; ++i) {
     f.data_ptrs[i] = (__nv_bfloat16*)data_ptrs[i];
     f.flag_ptrs[i] = (uint32_t*)flag_ptrs[i];
+    f.red_ptrs[i] = red_ptrs ? (uint32_t*)red_ptrs[i] : nullptr;
     f.done_ptrs[i] = (uint32_t*)done_ptrs[i];
   }
   f.counter = (unsigned int*)counter;
+  f.counter_base = counter_base;
   f.queue = f.counter + 1;
-  f.prefetch_kb = g_prefetch_kb;
-  f.rs_ring = g_rs_ring;
 }
+
+// Total CTAs of a fused single-CTA launch (communication CTAs included): the host advances its copy of the CTA
+// counter by this (reduce forms) or by this minus n_comm (gather forms) per launch.
+ELL_API int ell_gemm_fused_grid() { return sm_count(); }
 
 // All-gather -> GEMM.  out[tp*rows_per_rank, N] = gather(x_local)[.., K] · W[N, K]^T (+ bias), or with
 // b_mn = 1, gather(x_local) · W[K, N] (W read in place as an MN-major operand).
 // gathered_ptrs[r] is rank r's gathered buffer [tp*rows_per_rank, K] (peer pointers; entry `rank` is local);
-// flag_ptrs[r] / done_ptrs[r] are rank r's flag ([tp][flags_per_src]) and done ([tp]) words.
+// flag_ptrs[r] / done_ptrs[r] are rank r's flag ([tp][flags_per_src]) and done ([tp]) words.  `counter_base` is the
+// running value of the CTA counter: every launch advances it by (ell_gemm_fused_grid() - n_comm).
 ELL_API int ell_gemm_ag(const void* x_local, const void* W, void* out, const void* bias, int rows_per_rank, int N,
                         int K, int b_mn, int rank, int tp, unsigned int epoch, int n_comm, void* const* gathered_ptrs,
-                        void* const* flag_ptrs, void* const* done_ptrs, void* counter, int flags_per_src, int* err,
-                        cudaStream_t stream) {
+                        void* const* flag_ptrs, void* const* done_ptrs, void* counter, unsigned int counter_base,
+                        int flags_per_src, int* err, cudaStream_t stream) {
   if (tp < 1 || tp > kMaxTp || rows_per_rank % kBM || rows_per_rank / kBM > flags_per_src) return -2;
   if (b_mn && bias) return -2;
   const int M = rows_per_rank * tp;
@@ -1032,7 +736,8 @@ ELL_API int ell_gemm_ag(const void* x_local, const void* W, void* out, const voi
   rc = make_tmap_bf16_2d(&tA2, x_local, (uint64_t)K, (uint64_t)rows_per_rank, (uint64_t)K * 2, kBK, kBM);
   if (rc) return rc;
   FuseArgs f{};
-  fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, gathered_ptrs, flag_ptrs, done_ptrs, counter);
+  fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, gathered_ptrs, flag_ptrs, nullptr, done_ptrs,
+            counter, counter_base);
   f.x_local = (const __nv_bfloat16*)x_local;
   const int ctas = sm_count();
   if (n_comm < 1 || n_comm >= ctas) return -2;
@@ -1049,16 +754,20 @@ ELL_API int ell_gemm_ag(const void* x_local, const void* W, void* out, const voi
   return launch_gemm<128, false, false, kOutBf16, false, kFuseAG>(tA, tB, tC, f, bp, M, N, K, N, err, ctas, stream, &tA2);
 }
 
-// GEMM -> reduce-scatter.  y_local[rows_per_rank, N] = sum over ranks of (x[M, K] · op(W))[own rows].
+// GEMM -> reduce-scatter.  y_local[rows_per_rank, N] = sum over ranks of (x[M, K] · op(W))[own rows]; with
+// all_reduce = 1, GEMM -> all-reduce: y is the full [M, N] sum on every rank and red_ptrs[r] rank r's "tile reduced"
+// flags ([tp][flags_per_src]).
 // b_mn = 0: W is [N, K] (forward of a row-parallel linear); b_mn = 1: W is [K, N] (its use as dgrad of a
 // column-parallel linear).  stage_ptrs[r] is rank r's staging buffer [M, N].  `queue_base` is the running value
-// of the tile queue: every launch advances it by (owned tiles + number of CTAs); ell_gemm_rs_queue_advance
-// returns that amount.
+// of the tile queue: every launch advances it by ell_gemm_rs_queue_advance(...); `counter_base` that of the CTA
+// counter, advanced by ell_gemm_fused_grid() per launch.
 ELL_API int ell_gemm_rs(const void* x, const void* W, void* y_local, int rows_per_rank, int N, int K, int b_mn,
                         int rank, int tp, unsigned int epoch, int n_comm, void* const* stage_ptrs,
-                        void* const* flag_ptrs, void* const* done_ptrs, void* counter, int flags_per_src,
-                        unsigned int queue_base, int* err, cudaStream_t stream) {
+                        void* const* flag_ptrs, void* const* red_ptrs, void* const* done_ptrs, void* counter,
+                        unsigned int counter_base, int flags_per_src, unsigned int queue_base, int all_reduce, int* err,
+                        cudaStream_t stream) {
   if (tp < 1 || tp > kMaxTp || rows_per_rank % kBM || N % 8) return -2;
+  if (all_reduce && !red_ptrs) return -2;
   const int M = rows_per_rank * tp;
   const int BN = N >= 256 ? 256 : 128;
   const int tiles_n = (N + BN - 1) / BN;
@@ -1072,20 +781,31 @@ ELL_API int ell_gemm_rs(const void* x, const void* W, void* y_local, int rows_pe
   rc = make_tmap_bf16_2d(&tC, stage_ptrs[rank], (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 128);
   if (rc) return rc;
   FuseArgs f{};
-  fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, stage_ptrs, flag_ptrs, done_ptrs, counter);
+  fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, stage_ptrs, flag_ptrs, red_ptrs, done_ptrs,
+            counter, counter_base);
   f.y_local = (__nv_bfloat16*)y_local;
   f.queue_base = queue_base;
   const int ctas = sm_count();
   if (n_comm < 0 || n_comm >= ctas) return -2;
-  if (BN == 256) {
-    if (b_mn) return launch_gemm<256, false, true, kOutBf16, false, kFuseRS>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);
-    return launch_gemm<256, false, false, kOutBf16, false, kFuseRS>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);
-  }
-  if (b_mn) return launch_gemm<128, false, true, kOutBf16, false, kFuseRS>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);
-  return launch_gemm<128, false, false, kOutBf16, false, kFuseRS>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);
+#define ELL_RS_CASE(BN_, BM_, FUSE_)                                                                        \
+  if (BN == BN_ && (bool)b_mn == BM_ && (all_reduce ? kFuseAR : kFuseRS) == FUSE_)                          \
+    return launch_gemm<BN_, false, BM_, kOutBf16, false, FUSE_>(tA, tB, tC, f, nullptr, M, N, K, N, err, ctas, stream);
+  ELL_RS_CASE(256, false, kFuseRS)
+  ELL_RS_CASE(256, true, kFuseRS)
+  ELL_RS_CASE(128, false, kFuseRS)
+  ELL_RS_CASE(128, true, kFuseRS)
+  ELL_RS_CASE(256, false, kFuseAR)
+  ELL_RS_CASE(256, true, kFuseAR)
+  ELL_RS_CASE(128, false, kFuseAR)
+  ELL_RS_CASE(128, true, kFuseAR)
+#undef ELL_RS_CASE
+  return -3;
 }
 
-ELL_API int ell_gemm_rs_queue_advance(int rows_per_rank, int N) {
+// Queue positions one reduce launch consumes: the tiles it hands out (the owned ones; with all_reduce every tile of
+// the output) plus one overshoot per CTA.  grid: ell_gemm_fused_grid() or ell_gemm_pair_fused_grid().
+ELL_API int ell_gemm_rs_queue_advance(int rows_per_rank, int N, int tp, int all_reduce, int grid) {
   const int BN = N >= 256 ? 256 : 128;
-  return (rows_per_rank / kBM) * ((N + BN - 1) / BN) + sm_count();
+  const int owned = (rows_per_rank / kBM) * ((N + BN - 1) / BN);
+  return owned * (all_reduce ? tp : 1) + grid;
 }

@@ -19,38 +19,28 @@
 // Before a CTA leaves, its producer waits until the last commits on its own empty barriers have landed and
 // the cluster meets at a cluster barrier, so nothing signals into the shared memory of a CTA that has exited.
 //
-// Restrictions: plain launches only (no collective fusion, no cross-entropy epilogue); any M, N, K that the
-// single-CTA kernel accepts (out-of-range parts of a tile are zero-filled on load and clipped on store).
-#include "common.cuh"
-#include "sm100.cuh"
+// The same kernel carries the tensor-parallel fusions of gemm_fuse.cuh (all-gather -> GEMM on the A rows or on
+// the reduction rows, GEMM -> reduce-scatter / all-reduce) and the cross-entropy epilogue of the LM head.  In a
+// fused launch CTAs [0, n_comm) (whole clusters: n_comm is even) run the communication role; each CTA of a GEMM
+// pair waits for the flag of its own 128 A rows, stages and flags its own 128 x 256 block of partial sums, and
+// joins the reduction when the main loop is done.  Any M, N, K that the single-CTA kernel accepts (out-of-range
+// parts of a tile are zero-filled on load and clipped on store); fused launches need rows_per_rank % 256 == 0.
+#include "gemm_fuse.cuh"
 
 namespace ell {
-using namespace sm100;
-
-int make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
-                      uint32_t box_inner, uint32_t box_outer);
-int make_tmap_f32_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
-                     uint32_t box_inner, uint32_t box_outer);
-
-extern int g_no_tail_split;   // gemm.cu: 1 keeps whole tiles in an under-filled last wave (ell_gemm_set_tail_split)
-
 namespace pair {
 
 constexpr int kTileM = 256, kTileN = 256;   // per cluster
 constexpr int kHalfM = 128, kHalfN = 128;   // rows of A / rows of B staged by one CTA
-constexpr int kBK = 64;
-constexpr int kThreads = 192;               // warp 0 producer, warp 1 MMA issuer + TMEM owner, warps 2-5 epilogue
-constexpr int kEpiThreads = 128;
+constexpr int kThreads = kGemmThreads;      // warp 0 producer, warp 1 MMA issuer + TMEM owner, warps 2-5 epilogue
 constexpr int kStages = 6;
 constexpr int kABytes = kHalfM * kBK * 2;   // 16 KiB
 constexpr int kBBytes = kHalfN * kBK * 2;   // 16 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kEpiBufBytes = 128 * 64 * 2;
 constexpr int kTmemCols = 2 * kTileN;       // two accumulator buffers
 constexpr int kSmemBytes = kStages * kStageBytes + 2 * kEpiBufBytes + 1024 + 256;
 constexpr int kGroupM = 8;                  // rasterisation: 8 M-tiles x all N-tiles per group
-enum Out { kOutBf16 = 0, kOutF32Accum = 1, kOutF32 = 2 };
-enum Err { kErrProducer = 11, kErrMma = 12, kErrEpilogue = 13 };
+enum Err { kErrPairProducer = 11, kErrPairMma = 12, kErrPairEpilogue = 13, kErrPairFlagWait = 15 };
 
 struct Shared {
   uint64_t full[8];
@@ -125,7 +115,7 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                : "memory");
 }
 
-// __host__ __device__ so that ell_gemm_pair_enumerate_tiles can run the same code for a CPU coverage test
+// __host__ __device__ so that the enumerate functions below can run the same code for a CPU coverage test
 __host__ __device__ __forceinline__ void raster(int idx, int tiles_m, int tiles_n, int& mt, int& nt) {
   const int width = kGroupM * tiles_n;
   const int group = idx / width, rem = idx % width;
@@ -147,26 +137,56 @@ __host__ __device__ inline int split_tail(int num_tiles, int clusters, bool allo
   return (allowed && tail > 0 && 2 * tail <= clusters) ? tail : 0;
 }
 
-__host__ __device__ __forceinline__ Unit decode_unit(int unit, int tiles_m, int tiles_n, int num_full) {
+// Tile order of the fused forms (256-row tiles): all-gather -> GEMM walks the local shard's row tiles first and the
+// other shards in ring order; GEMM -> reduce-scatter / all-reduce interleaves the owners so each is fed evenly.
+__host__ __device__ __forceinline__ Unit decode_unit(int unit, int tiles_m, int tiles_n, int num_full, int fuse, int rank,
+                                                     int tp) {
   Unit u;
   int tile = unit, half = -1;
   if (unit >= num_full) {
     tile = num_full + ((unit - num_full) >> 1);
     half = (unit - num_full) & 1;
   }
-  raster(tile, tiles_m, tiles_n, u.mt, u.nt);
+  if (fuse == kFuseAG) {
+    const int tpr = tiles_m / tp, per_phase = tpr * tiles_n;
+    const int phase = tile / per_phase;
+    int mi;
+    raster(tile % per_phase, tpr, tiles_n, mi, u.nt);
+    u.mt = ((rank + phase) % tp) * tpr + mi;
+  } else if (fuse == kFuseRS || fuse == kFuseAR) {
+    int mp;
+    raster(tile, tiles_m, tiles_n, mp, u.nt);
+    u.mt = (mp % tp) * (tiles_m / tp) + mp / tp;
+  } else {
+    raster(tile, tiles_m, tiles_n, u.mt, u.nt);
+  }
   u.bn = half >= 0 ? kTileN / 2 : kTileN;
   u.n0 = u.nt * kTileN + (half > 0 ? kTileN / 2 : 0);
   return u;
 }
 
-template <bool A_MN, bool B_MN, int OUT, bool HAS_BIAS>
+// tmX: the local shard of the gathered operand (kFuseAG: A rows, box 128 x 64; kFuseAGK: reduction rows of B,
+// box 64 x 64); tmBh: B with a box of 64 rows for the half-width units.
+template <bool A_MN, bool B_MN, int OUT, bool HAS_BIAS, int FUSE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmBh,
-                 const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int tail_split, int* __restrict__ err) {
+                 const __grid_constant__ CUtensorMap tmX, const __grid_constant__ FuseArgs fuse,
+                 const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr bool kReduce = (FUSE == kFuseRS || FUSE == kFuseAR);
+  constexpr bool kGather = (FUSE == kFuseAG || FUSE == kFuseAGK);
+  const int n_comm = FUSE == kFuseNone ? 0 : fuse.n_comm;
+  const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + kTileN - 1) / kTileN;
+
+  if (FUSE != kFuseNone && (int)blockIdx.x < n_comm) {
+    // communication role; both CTAs of such a cluster take it, neither touches TMEM or the cluster barrier
+    if (kGather) ag_comm_role(fuse, FUSE == kFuseAG ? K : N, err, smem);
+    else rs_reduce_role<kTileN>(fuse, N, tiles_n, err, smem, (int)gridDim.x, true, FUSE == kFuseAR);
+    return;
+  }
+
   uint8_t* sA = smem;
   uint8_t* sB = smem + kStages * kABytes;
   uint8_t* sC = smem + kStages * kStageBytes;
@@ -175,11 +195,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta_rank = cluster_cta_rank();       // 0: leader, 1: peer
   const bool is_leader = cta_rank == 0;
-  const int cluster_id = (int)blockIdx.x >> 1, n_clusters = (int)gridDim.x >> 1;
-  const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + kTileN - 1) / kTileN;
+  const int cluster_id = ((int)blockIdx.x - n_comm) >> 1, n_clusters = ((int)gridDim.x - n_comm) >> 1;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + kBK - 1) / kBK;
-  const int n_split = split_tail(num_tiles, n_clusters, tail_split != 0);
+  const int n_split = split_tail(num_tiles, n_clusters, !kReduce && !fuse.no_tail_split);
   const int num_full = num_tiles - n_split, num_units = num_tiles + n_split;
 
   if (threadIdx.x == 0) {
@@ -213,14 +232,61 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // kFuseAGK: leading row tiles of every source rank already seen flagged (the k-loop revisits them per unit)
+      int seen[kMaxTp];
+#pragma unroll
+      for (int i = 0; i < kMaxTp; ++i) seen[i] = 0;
+      const int kb_rot = FUSE == kFuseAGK ? fuse.rank * (fuse.rows_per_rank / kBK) : 0;
       for (int unit = cluster_id; unit < num_units && ok; unit += n_clusters) {
-        const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full);
+        const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp);
         const int b_rows = u.bn / 2;                                // B rows staged by one CTA (128, or 64 in a half unit)
         const int m0 = u.mt * kTileM + (int)cta_rank * kHalfM;     // A rows of this CTA
         const int nb0 = u.n0 + (int)cta_rank * b_rows;             // B rows of this CTA
         const CUtensorMap* b_map = (u.bn == kTileN) ? &tmB : &tmBh; // half units: box of 64 B rows
         const uint32_t stage_tx = 2u * (kABytes + (uint32_t)b_rows * kBK * 2);
+        const CUtensorMap* a_map = &tmA;
+        int a_row = m0;
+        if (FUSE == kFuseAG) {
+          // the 128 A rows of this CTA come from rank `src`: the local shard is read in place, a remote shard
+          // from the local gathered buffer once the peer's copy of this row tile is flagged
+          const int src = m0 / fuse.rows_per_rank;
+          if (src == fuse.rank) {
+            a_map = &tmX;
+            a_row = m0 - src * fuse.rows_per_rank;
+          } else if (m0 < M) {
+            const uint32_t* fl = fuse.flag_ptrs[fuse.rank] + (size_t)src * fuse.flags_per_src +
+                                 (m0 - src * fuse.rows_per_rank) / kBM;
+            if (!wait_flag_ge(fl, fuse.epoch, abort_flag)) {
+              ok = false;
+              atomicCAS(err, 0, kErrPairFlagWait);
+              break;
+            }
+            fence_proxy_async_all();   // peer writes -> TMA reads (async proxy)
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
+          int kk = kb;                       // k-block actually loaded
+          const CUtensorMap* bk_map = &tmB;  // kFuseAGK: map of the B k-block
+          int bk_row = 0;
+          if (FUSE == kFuseAGK) {
+            kk = kb + kb_rot;
+            if (kk >= num_kb) kk -= num_kb;
+            const int t0 = kk * kBK, src = t0 / fuse.rows_per_rank, loc = t0 - src * fuse.rows_per_rank;
+            bk_row = t0;
+            if (src == fuse.rank) {
+              bk_map = &tmX;
+              bk_row = loc;
+            } else if (loc / kBM >= seen[src]) {
+              const uint32_t* fl = fuse.flag_ptrs[fuse.rank] + (size_t)src * fuse.flags_per_src + loc / kBM;
+              if (!wait_flag_ge(fl, fuse.epoch, abort_flag)) {
+                ok = false;
+                atomicCAS(err, 0, kErrPairFlagWait);
+                break;
+              }
+              fence_proxy_async_all();
+              seen[src] = loc / kBM + 1;
+            }
+          }
           if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) {
             ok = false;
             break;
@@ -230,18 +296,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* a_dst = sA + stage * kABytes;
           uint8_t* b_dst = sB + stage * kBBytes;
           if (!A_MN) {
-            tma_load_2d_pair(a_dst, &tmA, bar, kb * kBK, m0);
+            tma_load_2d_pair(a_dst, a_map, bar, kk * kBK, a_row);
           } else {
 #pragma unroll
             for (int i = 0; i < kHalfM / 64; ++i)
-              tma_load_2d_pair(a_dst + i * (64 * kBK * 2), &tmA, bar, m0 + i * 64, kb * kBK);
+              tma_load_2d_pair(a_dst + i * (64 * kBK * 2), &tmA, bar, m0 + i * 64, kk * kBK);
           }
           if (!B_MN) {
-            tma_load_2d_pair(b_dst, b_map, bar, kb * kBK, nb0);
+            tma_load_2d_pair(b_dst, b_map, bar, kk * kBK, nb0);
           } else {
 #pragma unroll
             for (int i = 0; i < kHalfN / 64; ++i)
-              if (i * 64 < b_rows) tma_load_2d_pair(b_dst + i * (64 * kBK * 2), &tmB, bar, nb0 + i * 64, kb * kBK);
+              if (i * 64 < b_rows)
+                tma_load_2d_pair(b_dst + i * (64 * kBK * 2), FUSE == kFuseAGK ? bk_map : &tmB, bar, nb0 + i * 64,
+                                 FUSE == kFuseAGK ? bk_row : kk * kBK);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -259,7 +327,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!ok) {
         sh->abort_flag = 1;
-        atomicCAS(err, 0, kErrProducer);
+        atomicCAS(err, 0, kErrPairProducer);
       }
     }
   } else if (warp == 1) {
@@ -307,7 +375,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!ok) {
         sh->abort_flag = 1;
-        atomicCAS(err, 0, kErrMma);
+        atomicCAS(err, 0, kErrPairMma);
       }
     }
   } else {
@@ -319,8 +387,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t empty_bar1 = map_to_cta(smem_u32(&sh->tmem_empty[1]), 0);
     int it = 0;
     uint32_t store_count = 0;
+    uint32_t* pending_flag = nullptr;   // reduce forms: flag of the last staged block, raised once its stores completed
+    if (kReduce && store_thread) {
+      // peers must have finished reading last epoch's staged tiles before they are overwritten
+      for (int p = 0; p < fuse.tp; ++p)
+        if (p != fuse.rank && !wait_flag_ge(fuse.done_ptrs[fuse.rank] + p, fuse.epoch - 1, abort_flag)) {
+          sh->epi_abort = 1;
+          atomicCAS(err, 0, kErrPairFlagWait);
+        }
+    }
     for (int unit = cluster_id; unit < num_units; unit += n_clusters, ++it) {
-      const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full);
+      const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp);
       const int m0 = u.mt * kTileM + (int)cta_rank * kHalfM, n0 = u.n0;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -329,7 +406,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (*(volatile int*)&sh->epi_abort) break;   // uniform across the 128 epilogue threads
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * kTileN;
-      if (OUT == kOutBf16) {
+      float ce_m = -INFINITY, ce_s = 0.f, ce_t = 0.f;
+      int ce_tcol = -1;                          // target column inside this unit, if any
+      if (OUT == kOutBf16CE) {
+        const int row = m0 + row_in_tile;
+        if (row < M) {
+          const long long tc = fuse.ce_target[row] - fuse.ce_vocab_start - n0;
+          if (tc >= 0 && tc < u.bn && tc + n0 < fuse.ce_valid) ce_tcol = (int)tc;
+        }
+      }
+      if (OUT == kOutBf16 || OUT == kOutBf16CE) {
 #pragma unroll 1
         for (int j = 0; j < u.bn / 64; ++j) {
           uint8_t* buf = sC + (store_count & 1) * kEpiBufBytes;
@@ -345,6 +431,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               const int col = n0 + j * 64 + c;
               const float b = col < N ? __bfloat162float(bias[col]) : 0.f;
               r[c] = __float_as_uint(__uint_as_float(r[c]) + b);
+            }
+          }
+          if (OUT == kOutBf16CE) {
+            // statistics of the logits as stored (rounded to bf16), so that backward's exp(logit - lse) sums to 1
+            const int cbase = n0 + j * 64;
+            float cm = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+              const float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[c])));
+              r[c] = __float_as_uint(x);
+              if (cbase + c < fuse.ce_valid) cm = fmaxf(cm, x);
+              if (j * 64 + c == ce_tcol) ce_t = x;
+            }
+            if (cm > -INFINITY) {
+              const float nm = fmaxf(ce_m, cm);
+              float acc_s = ce_s * __expf(ce_m - nm);
+#pragma unroll
+              for (int c = 0; c < 64; ++c)
+                if (cbase + c < fuse.ce_valid) acc_s += __expf(__uint_as_float(r[c]) - nm);
+              ce_s = acc_s;
+              ce_m = nm;
             }
           }
           uint8_t* row_ptr = buf + row_in_tile * 128;
@@ -364,10 +471,44 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           fence_proxy_async_smem();
           named_bar_sync(1, kEpiThreads);
           if (store_thread) {
-            if (n0 + j * 64 < N && m0 < M) tma_store_2d(&tmC, buf, n0 + j * 64, m0);
+            if (kReduce) {
+              bulk_store(reinterpret_cast<uint8_t*>(fuse.data_ptrs[fuse.rank]) +
+                             stage_block<kTileN>(m0 / kBM, u.nt, j, tiles_n),
+                         buf, kEpiBufBytes);
+            } else if (n0 + j * 64 < N && m0 < M) {
+              tma_store_2d(&tmC, buf, n0 + j * 64, m0);
+            }
             tma_store_commit();
           }
           ++store_count;
+        }
+        if (OUT == kOutBf16CE) {
+          // one slot of partials per 128 columns: a whole unit fills its first slot and neutralises the second
+          const int row = m0 + row_in_tile;
+          if (row < M) {
+            float* part = fuse.ce_part + (size_t)(n0 / (kTileN / 2)) * 3 * M + row;
+            part[0] = ce_m;
+            part[(size_t)M] = ce_s;
+            part[(size_t)2 * M] = ce_t;
+            if (u.bn == kTileN) {
+              part += (size_t)3 * M;
+              part[0] = -INFINITY;
+              part[(size_t)M] = 0.f;
+              part[(size_t)2 * M] = 0.f;
+            }
+          }
+        }
+        if (kReduce && store_thread) {
+          // Publish the flag of the PREVIOUS block: its bulk stores were committed 4 groups ago, so waiting until
+          // at most 4 groups are pending does not stall behind this block's stores.
+          if (pending_flag != nullptr) {
+            tma_store_wait_all<kTileN / 64>();
+            fence_proxy_async_all();
+            st_release_sys(pending_flag, fuse.epoch);
+          }
+          const int owner = m0 / fuse.rows_per_rank;
+          const int mi = (m0 - owner * fuse.rows_per_rank) / kBM;
+          pending_flag = fuse.flag_ptrs[owner] + (size_t)fuse.rank * fuse.flags_per_src + mi * tiles_n + u.nt;
         }
       } else {
         // fp32 output: 128 x 32 sub-tiles, stored or added into C at L2 by the TMA unit
@@ -402,9 +543,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     if (*(volatile int*)&sh->epi_abort && store_thread) {
       sh->abort_flag = 1;
-      atomicCAS(err, 0, kErrEpilogue);
+      atomicCAS(err, 0, kErrPairEpilogue);
     }
-    if (store_thread) tma_store_wait_all<0>();
+    if (store_thread) {
+      tma_store_wait_all<0>();
+      if (kReduce && pending_flag != nullptr) {
+        fence_proxy_async_all();
+        st_release_sys(pending_flag, fuse.epoch);
+      }
+    }
   }
 
   __syncthreads();
@@ -421,10 +568,25 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc_pair(tmem_base);
   }
+  if (kReduce) {
+    // the main loop is done: this CTA now helps summing the staged tiles its rank owns (the dedicated CTAs
+    // [0, n_comm) have been doing so since launch)
+    __syncthreads();
+    rs_reduce_role<kTileN>(fuse, N, tiles_n, err, smem, (int)gridDim.x, true, FUSE == kFuseAR);
+  }
+  if (kGather && threadIdx.x == 0) {
+    // last GEMM CTA of this rank: tell every peer that its pushes of this epoch were consumed
+    __threadfence();
+    const unsigned int old = atomicAdd(fuse.counter, 1u);
+    if (old + 1 - fuse.counter_base == gridDim.x - (unsigned int)n_comm) {
+      for (int p = 0; p < fuse.tp; ++p)
+        if (p != fuse.rank) st_release_sys(fuse.done_ptrs[p] + fuse.rank, fuse.epoch);
+    }
+  }
 }
 
-// Clusters of a launch: every resident cluster when there is at least a wave of tiles; with less than half a wave,
-// twice the tile count, so that every tile runs as two half-width units on two clusters.
+// Clusters of a plain launch: every resident cluster when there is at least a wave of tiles; with less than half a
+// wave, twice the tile count, so that every tile runs as two half-width units on two clusters.
 __host__ inline int launch_clusters(int tiles, int resident) {
   if (tiles >= resident) return resident;
   if (!g_no_tail_split && 2 * tiles <= resident) return 2 * tiles;
@@ -455,10 +617,12 @@ static int max_clusters(const void* kern) {
   return n;
 }
 
-template <bool A_MN, bool B_MN, int OUT, bool HAS_BIAS>
+// Fused launches keep a fixed grid (every resident cluster): the counters of the flag protocol count CTAs.
+template <bool A_MN, bool B_MN, int OUT, bool HAS_BIAS, int FUSE = kFuseNone>
 static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, const CUtensorMap& tBh,
-                  const __nv_bfloat16* bias, int M, int N, int K, int* err, cudaStream_t stream) {
-  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT, HAS_BIAS>;
+                  const CUtensorMap& tX, const FuseArgs& fuse, const __nv_bfloat16* bias, int M, int N, int K, int* err,
+                  cudaStream_t stream) {
+  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT, HAS_BIAS, FUSE>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
@@ -468,9 +632,15 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   const int resident = max_clusters(reinterpret_cast<const void*>(kern));
   if (resident <= 0) return -20;                 // the device cannot co-schedule a pair with this much shared memory
   const int tiles = ((M + kTileM - 1) / kTileM) * ((N + kTileN - 1) / kTileN);
-  const int clusters = launch_clusters(tiles, resident);
+  int grid;
+  if (FUSE == kFuseNone) {
+    grid = 2 * launch_clusters(tiles, resident);
+  } else {
+    if ((fuse.n_comm & 1) || fuse.n_comm >= 2 * resident) return -2;
+    grid = 2 * resident;
+  }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
@@ -481,12 +651,67 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tA, tB, tC, tBh, bias, M, N, K, g_no_tail_split ? 0 : 1, err);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tA, tB, tC, tBh, tX, fuse, bias, M, N, K, err);
   if (e != cudaSuccess) {
     cudaGetLastError();   // a refused launch is reported to the caller, not left behind for the next launch
     return (int)e;
   }
   return launch_status();
+}
+
+static int resident_clusters() {
+  auto kern = gemm_pair_kernel<false, false, kOutBf16, false, kFuseNone>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return max_clusters(reinterpret_cast<const void*>(kern));
+}
+
+static void fill_fuse(FuseArgs& f, int rank, int tp, int n_comm, int rows_per_rank, int flags_per_src,
+                      unsigned int epoch, void* const* data_ptrs, void* const* flag_ptrs, void* const* red_ptrs,
+                      void* const* done_ptrs, void* counter, unsigned int counter_base) {
+  f.rank = rank; f.tp = tp; f.n_comm = n_comm; f.rows_per_rank = rows_per_rank; f.flags_per_src = flags_per_src;
+  f.epoch = epoch;
+  for (int i = 0; i < tp; ++i) {
+    f.data_ptrs[i] = (__nv_bfloat16*)data_ptrs[i];
+    f.flag_ptrs[i] = (uint32_t*)flag_ptrs[i];
+    f.red_ptrs[i] = red_ptrs ? (uint32_t*)red_ptrs[i] : nullptr;
+    f.done_ptrs[i] = (uint32_t*)done_ptrs[i];
+  }
+  f.counter = (unsigned int*)counter;
+  f.counter_base = counter_base;
+  f.queue = f.counter + 1;
+  f.no_tail_split = g_no_tail_split;
+}
+
+// LM-head form: logits + cross-entropy partials, optionally behind the all-gather of the hidden rows.
+static int gemm_ce(const void* X, const void* W, void* logits, const long long* target, float* part, int M, int N,
+                   int K, long long vocab_start, int valid_cols, const FuseArgs* ag, const void* x_local, int* err,
+                   cudaStream_t stream) {
+  CUtensorMap tA, tB, tC, tBh, tX;
+  int rc = make_tmap_bf16_2d(&tA, X, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBK, kHalfM);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tB, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, kBK, kHalfN);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tBh, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, kBK, kHalfN / 2);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tC, logits, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 128);
+  if (rc) return rc;
+  tX = tA;
+  FuseArgs f{};
+  if (ag) {
+    f = *ag;
+    rc = make_tmap_bf16_2d(&tX, x_local, (uint64_t)K, (uint64_t)f.rows_per_rank, (uint64_t)K * 2, kBK, kHalfM);
+    if (rc) return rc;
+  }
+  f.no_tail_split = g_no_tail_split;
+  f.ce_target = target;
+  f.ce_part = part;
+  f.ce_vocab_start = vocab_start;
+  f.ce_valid = valid_cols < N ? valid_cols : N;
+  if (ag) return launch<false, false, kOutBf16CE, false, kFuseAG>(tA, tB, tC, tBh, tX, f, nullptr, M, N, K, err, stream);
+  return launch<false, false, kOutBf16CE, false, kFuseNone>(tA, tB, tC, tBh, tX, f, nullptr, M, N, K, err, stream);
 }
 
 }  // namespace pair
@@ -504,18 +729,21 @@ ELL_API int ell_gemm_pair_enumerate_tiles(int M, int N, int* out, int max_tiles)
   return tiles_m * tiles_n;
 }
 
-// Host-only: the work units of a launch on `clusters` clusters in the order the kernel walks them (unit u goes to
-// cluster u % clusters), tail halving included.  out[u] = {row tile, column tile, first column, width}.  Returns the
-// unit count or -1 when out is too small.
-ELL_API int ell_gemm_pair_enumerate_units(int M, int N, int clusters, int allow_split, int* out, int max_units) {
+// Host-only: the work units of a launch on `clusters` GEMM clusters in the order the kernel walks them (unit u goes to
+// cluster u % clusters), tail halving included.  fuse: 0 plain, 1 all-gather -> GEMM, 2 GEMM -> reduce-scatter,
+// 3 GEMM -> all-reduce, 4 all-gather of the reduction rows.  out[u] = {row tile, column tile, first column, width}.
+// Returns the unit count or -1 when out is too small.
+ELL_API int ell_gemm_pair_enumerate_units(int M, int N, int clusters, int allow_split, int fuse, int tp, int rank,
+                                          int* out, int max_units) {
   using namespace ell::pair;
   const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + kTileN - 1) / kTileN;
   const int num_tiles = tiles_m * tiles_n;
-  const int n_split = split_tail(num_tiles, clusters, allow_split != 0);
+  const bool reduce = fuse == kFuseRS || fuse == kFuseAR;
+  const int n_split = split_tail(num_tiles, clusters, allow_split != 0 && !reduce);
   const int num_full = num_tiles - n_split, num_units = num_tiles + n_split;
   if (num_units > max_units) return -1;
   for (int u = 0; u < num_units; ++u) {
-    const Unit t = decode_unit(u, tiles_m, tiles_n, num_full);
+    const Unit t = decode_unit(u, tiles_m, tiles_n, num_full, fuse, rank, tp < 1 ? 1 : tp);
     out[4 * u + 0] = t.mt;
     out[4 * u + 1] = t.nt;
     out[4 * u + 2] = t.n0;
@@ -524,16 +752,17 @@ ELL_API int ell_gemm_pair_enumerate_units(int M, int N, int clusters, int allow_
   return num_units;
 }
 
-// Two-CTA clusters of the pair kernel that fit on the current device at once (needs a GPU; <= 0 if it cannot run).
-ELL_API int ell_gemm_pair_resident_clusters() {
-  using namespace ell::pair;
-  auto kern = gemm_pair_kernel<false, false, kOutBf16, false>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
-    cudaGetLastError();
-    return -1;
-  }
-  return max_clusters(reinterpret_cast<const void*>(kern));
+// Host-only: the order in which the reduce role takes the 128-row tiles a rank owns (queue position -> {row tile
+// inside the shard, column tile}).  pair = 1: tiles staged by the CTA-pair kernel, 0: by the single-CTA kernel.
+ELL_API int ell_gemm_owned_tile_order(int rows_per_rank, int tiles_n, int tp, int pair, int* out, int max_tiles) {
+  const int tpr = rows_per_rank / kBM;
+  if (tpr * tiles_n > max_tiles) return -1;
+  for (int j = 0; j < tpr * tiles_n; ++j) owned_tile_of(j, tpr, tiles_n, tp, pair != 0, out[2 * j], out[2 * j + 1]);
+  return tpr * tiles_n;
 }
+
+// Two-CTA clusters of the pair kernel that fit on the current device at once (needs a GPU; <= 0 if it cannot run).
+ELL_API int ell_gemm_pair_resident_clusters() { return ell::pair::resident_clusters(); }
 
 // Clusters the kernel would launch for `tiles` tiles when `resident` clusters fit on the device.
 ELL_API int ell_gemm_pair_launch_clusters(int tiles, int resident) { return ell::pair::launch_clusters(tiles, resident); }
@@ -563,10 +792,12 @@ ELL_API int ell_gemm_bf16_pair(const void* A, const void* B, void* C, const void
     rc = make_tmap_bf16_2d(&tBh, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kBK, kHalfN / 2);
     if (rc) return rc;
   }
+  FuseArgs f{};
+  f.no_tail_split = g_no_tail_split;
   const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(bias);
 #define ELL_PAIR_CASE(AM_, BM_, OUT_, BIAS_)                                                   \
   if ((bool)a_mn == AM_ && (bool)b_mn == BM_ && out_mode == OUT_ && (bias != nullptr) == BIAS_) \
-    return launch<AM_, BM_, OUT_, BIAS_>(tA, tB, tC, tBh, bp, M, N, K, err, stream);
+    return launch<AM_, BM_, OUT_, BIAS_>(tA, tB, tC, tBh, tA, f, bp, M, N, K, err, stream);
   ELL_PAIR_CASE(false, false, kOutBf16, false)
   ELL_PAIR_CASE(false, false, kOutBf16, true)
   ELL_PAIR_CASE(false, true, kOutBf16, false)
@@ -577,4 +808,129 @@ ELL_API int ell_gemm_bf16_pair(const void* A, const void* B, void* C, const void
   ELL_PAIR_CASE(false, true, kOutF32, false)
 #undef ELL_PAIR_CASE
   return -3;
+}
+
+// Slots of cross-entropy partials the CTA-pair epilogue fills (one per 128 columns).
+ELL_API int ell_gemm_ce_slots_pair(int N) { return 2 * ((N + 255) / 256); }
+
+// logits[M, N] (bf16) = X[M, K] · W[N, K]^T on CTA pairs with the cross-entropy statistics fused into the epilogue:
+// part[slots][3][M] = (max, sum exp(x - max), logit of the target if it falls in the slot else 0) over the first
+// `valid_cols` columns; target holds global vocabulary ids, column 0 is id vocab_start.
+ELL_API int ell_gemm_ce_pair(const void* X, const void* W, void* logits, const long long* target, float* part, int M,
+                             int N, int K, long long vocab_start, int valid_cols, int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  return ell::pair::gemm_ce(X, W, logits, target, part, M, N, K, vocab_start, valid_cols, nullptr, nullptr, err, stream);
+}
+
+// Total CTAs of a fused CTA-pair launch (communication CTAs included): the host advances its copy of the CTA
+// counter by this (reduce forms) or by this minus n_comm (gather forms) per launch.
+ELL_API int ell_gemm_pair_fused_grid() {
+  const int r = ell::pair::resident_clusters();
+  return r > 0 ? 2 * r : -1;
+}
+
+// All-gather -> GEMM on CTA pairs (contract of ell_gemm_ag; rows_per_rank % 256 == 0, n_comm even).  With
+// ce_target != nullptr the epilogue also emits the cross-entropy partials of ell_gemm_ce_pair (LM head).
+ELL_API int ell_gemm_ag_pair(const void* x_local, const void* W, void* out, const void* bias, int rows_per_rank, int N,
+                             int K, int b_mn, int rank, int tp, unsigned int epoch, int n_comm,
+                             void* const* gathered_ptrs, void* const* flag_ptrs, void* const* done_ptrs, void* counter,
+                             unsigned int counter_base, int flags_per_src, const long long* ce_target, float* ce_part,
+                             long long ce_vocab_start, int ce_valid, int* err, cudaStream_t stream) {
+  using namespace ell::pair;
+  if (tp < 1 || tp > kMaxTp || rows_per_rank % kTileM || rows_per_rank / kBM > flags_per_src) return -2;
+  if (b_mn && (bias || ce_target)) return -2;
+  if (n_comm < 2 || (n_comm & 1)) return -2;
+  const int M = rows_per_rank * tp;
+  FuseArgs f{};
+  fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, gathered_ptrs, flag_ptrs, nullptr, done_ptrs,
+            counter, counter_base);
+  f.x_local = (const __nv_bfloat16*)x_local;
+  if (ce_target) {
+    if (bias) return -2;
+    return gemm_ce(gathered_ptrs[rank], W, out, ce_target, ce_part, M, N, K, ce_vocab_start, ce_valid, &f, x_local, err,
+                   stream);
+  }
+  CUtensorMap tA, tB, tC, tBh, tX;
+  int rc = make_tmap_bf16_2d(&tA, gathered_ptrs[rank], (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBK, kHalfM);
+  if (rc) return rc;
+  if (!b_mn) rc = make_tmap_bf16_2d(&tB, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, kBK, kHalfN);
+  else       rc = make_tmap_bf16_2d(&tB, W, (uint64_t)N, (uint64_t)K, (uint64_t)N * 2, 64, kBK);
+  if (rc) return rc;
+  tBh = tB;
+  if (!b_mn) {
+    rc = make_tmap_bf16_2d(&tBh, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, kBK, kHalfN / 2);
+    if (rc) return rc;
+  }
+  rc = make_tmap_bf16_2d(&tC, out, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 128);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tX, x_local, (uint64_t)K, (uint64_t)rows_per_rank, (uint64_t)K * 2, kBK, kHalfM);
+  if (rc) return rc;
+  const __nv_bfloat16* bp = (const __nv_bfloat16*)bias;
+  if (b_mn) return launch<false, true, kOutBf16, false, kFuseAG>(tA, tB, tC, tBh, tX, f, bp, M, N, K, err, stream);
+  if (bias) return launch<false, false, kOutBf16, true, kFuseAG>(tA, tB, tC, tBh, tX, f, bp, M, N, K, err, stream);
+  return launch<false, false, kOutBf16, false, kFuseAG>(tA, tB, tC, tBh, tX, f, bp, M, N, K, err, stream);
+}
+
+// Weight gradient behind the all-gather of its reduction rows, on CTA pairs:
+//   dW[Nout, Kin] (fp32) += dy[T, Nout]^T · gather(x_local)[T, Kin],   T = tp * rows_per_rank.
+// The communication CTAs push this rank's x rows to the peers' gathered buffers; every output tile starts its k-loop
+// on the local rows and waits for a remote row tile right before its first k-block.
+ELL_API int ell_gemm_agk_wgrad_pair(const void* dy, const void* x_local, void* dW, int rows_per_rank, int Nout, int Kin,
+                                    int rank, int tp, unsigned int epoch, int n_comm, void* const* gathered_ptrs,
+                                    void* const* flag_ptrs, void* const* done_ptrs, void* counter,
+                                    unsigned int counter_base, int flags_per_src, int* err, cudaStream_t stream) {
+  using namespace ell::pair;
+  if (tp < 1 || tp > kMaxTp || rows_per_rank % kTileM || rows_per_rank / kBM > flags_per_src) return -2;
+  if (n_comm < 2 || (n_comm & 1) || Nout % 8 || Kin % 8) return -2;
+  const int T = rows_per_rank * tp;
+  CUtensorMap tA, tB, tC, tX;
+  int rc = make_tmap_bf16_2d(&tA, dy, (uint64_t)Nout, (uint64_t)T, (uint64_t)Nout * 2, 64, kBK);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tB, gathered_ptrs[rank], (uint64_t)Kin, (uint64_t)T, (uint64_t)Kin * 2, 64, kBK);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tX, x_local, (uint64_t)Kin, (uint64_t)rows_per_rank, (uint64_t)Kin * 2, 64, kBK);
+  if (rc) return rc;
+  rc = make_tmap_f32_2d(&tC, dW, (uint64_t)Kin, (uint64_t)Nout, (uint64_t)Kin * 4, 32, 128);
+  if (rc) return rc;
+  FuseArgs f{};
+  fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, gathered_ptrs, flag_ptrs, nullptr, done_ptrs,
+            counter, counter_base);
+  f.x_local = (const __nv_bfloat16*)x_local;
+  return launch<true, true, kOutF32Accum, false, kFuseAGK>(tA, tB, tC, tB, tX, f, nullptr, Nout, Kin, T, err, stream);
+}
+
+// GEMM -> reduce-scatter (all_reduce = 0; contract of ell_gemm_rs) or GEMM -> all-reduce (all_reduce = 1: y is the
+// full [tp * rows_per_rank, N] output and red_ptrs[r] rank r's "tile reduced" flags) on CTA pairs.
+// rows_per_rank % 256 == 0, N % 256 == 0, n_comm even.
+ELL_API int ell_gemm_rs_pair(const void* x, const void* W, void* y, int rows_per_rank, int N, int K, int b_mn, int rank,
+                             int tp, unsigned int epoch, int n_comm, void* const* stage_ptrs, void* const* flag_ptrs,
+                             void* const* red_ptrs, void* const* done_ptrs, void* counter, unsigned int counter_base,
+                             int flags_per_src, unsigned int queue_base, int all_reduce, int* err,
+                             cudaStream_t stream) {
+  using namespace ell::pair;
+  if (tp < 1 || tp > kMaxTp || rows_per_rank % kTileM || N % kTileN) return -2;
+  if (n_comm & 1) return -2;
+  if (all_reduce && !red_ptrs) return -2;
+  const int M = rows_per_rank * tp;
+  const int tiles_n = N / kTileN;
+  if ((rows_per_rank / kBM) * tiles_n > flags_per_src) return -2;
+  CUtensorMap tA, tB, tC;
+  int rc = make_tmap_bf16_2d(&tA, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBK, kHalfM);
+  if (rc) return rc;
+  if (!b_mn) rc = make_tmap_bf16_2d(&tB, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, kBK, kHalfN);
+  else       rc = make_tmap_bf16_2d(&tB, W, (uint64_t)N, (uint64_t)K, (uint64_t)N * 2, 64, kBK);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tC, stage_ptrs[rank], (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 128);
+  if (rc) return rc;
+  FuseArgs f{};
+  fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, stage_ptrs, flag_ptrs, red_ptrs, done_ptrs,
+            counter, counter_base);
+  f.y_local = (__nv_bfloat16*)y;
+  f.queue_base = queue_base;
+  if (all_reduce) {
+    if (b_mn) return launch<false, true, kOutBf16, false, kFuseAR>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream);
+    return launch<false, false, kOutBf16, false, kFuseAR>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream);
+  }
+  if (b_mn) return launch<false, true, kOutBf16, false, kFuseRS>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream);
+  return launch<false, false, kOutBf16, false, kFuseRS>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream);
 }

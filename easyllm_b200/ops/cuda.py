@@ -92,7 +92,8 @@ def check_err_flag():
     v = int(f.item())
     if v:
         f.zero_()
-        raise KernelError(f"a kernel gave up a bounded wait (code {v}: 1 producer, 2 mma, 3 epilogue; 11-13 the same roles of the CTA-pair GEMM)")
+        raise KernelError(f"a kernel gave up a bounded wait (code {v}: 1 producer, 2 mma, 3 epilogue, 4 communication "
+                          "role, 5 peer flag; 11-15 the same roles of the CTA-pair GEMM; 21 cross-entropy exchange)")
 
 
 def scratch(nelem, dtype=torch.float32, tag="default"):
@@ -172,6 +173,14 @@ def accum_bf16_to_f32(src, dst):
     _check(lib().ell_accum_bf16_to_f32(_p(src), _p(dst), c_longlong(src.numel()), _stream()), "accum")
 
 
+def colsum_(x, out32):
+    """``out32 [cols] += x.sum(0)`` for a bf16 matrix ``x [rows, cols]``, in fp32, without an fp32 copy of ``x``."""
+    _bf16c(x, "x")
+    rows, cols = x.shape
+    _check(lib().ell_colsum_bf16(_p(x), _p(out32), c_int(rows), c_int(cols), _stream()), "colsum")
+    return out32
+
+
 # ---- optimizer --------------------------------------------------------------------------------
 def adam(p, g, m, v, p_lowp, lr, beta1, beta2, eps, weight_decay, step, adamw=True, grad_scale=1.0,
          scale_ptr=None, bias_correction=True):
@@ -234,6 +243,10 @@ def ce_bwd_(logits, target, lse, scale, vocab_start, valid_cols):
 
 # ---- GEMM -------------------------------------------------------------------------------------
 _GEMM_PAIR = os.environ.get("ELL_GEMM_PAIR", "1") != "0"
+
+
+def gemm_pair_enabled():
+    return _GEMM_PAIR
 
 
 def set_gemm_pair(enabled):
@@ -308,15 +321,14 @@ def flash_fwd_plan(row_start):
     return [tuple(out[3 * i:3 * i + 3]) for i in range(2 * n_pairs)]
 
 
-def gemm_work_units(M, N, bn=256, fuse=0, tp=1, rank=0, rs_ring=False, ctas=148, allow_split=True):
+def gemm_work_units(M, N, bn=256, fuse=0, tp=1, rank=0, ctas=148, allow_split=True):
     """Host-only: the (row tile, column tile, first column, width) work units of a single-CTA GEMM launch in the
     order the kernel walks them, produced by the kernel's own tile-order code (no GPU is touched).
     ``fuse``: 0 plain, 1 all-gather→GEMM, 2 GEMM→reduce-scatter."""
     cap = 2 * ((M + 127) // 128) * ((N + bn - 1) // bn) + 8
     buf = (c_int * (4 * cap))()
     n = lib().ell_gemm_enumerate_units(c_int(M), c_int(N), c_int(bn), c_int(fuse), c_int(tp), c_int(rank),
-                                       c_int(1 if rs_ring else 0), c_int(ctas), c_int(1 if allow_split else 0), buf,
-                                       c_int(cap))
+                                       c_int(ctas), c_int(1 if allow_split else 0), buf, c_int(cap))
     if n < 0:
         raise KernelError(f"gemm_work_units failed with code {n}")
     return [tuple(buf[4 * i:4 * i + 4]) for i in range(n)]
@@ -332,26 +344,43 @@ def gemm_pair_tiles(M, N):
     return [tuple(buf[2 * i:2 * i + 2]) for i in range(n)]
 
 
-def gemm_pair_units(M, N, resident=74, allow_split=True):
+def gemm_pair_units(M, N, resident=74, allow_split=True, fuse=0, tp=1, rank=0, n_comm=0):
     """Host-only: the (row tile, column tile, first column, width) work units of a CTA-pair GEMM launch on a device
     where ``resident`` two-CTA clusters fit, in the order the kernel walks them (unit ``u`` runs on cluster
-    ``u % clusters``).  Returns ``(clusters, units)``; an under-filled last wave shows up as 128-wide units."""
+    ``u % clusters``).  Returns ``(clusters, units)``; an under-filled last wave shows up as 128-wide units.
+    ``fuse``: 0 plain, 1 all-gather→GEMM, 2 GEMM→reduce-scatter, 3 GEMM→all-reduce, 4 gather of the reduction
+    rows; fused launches run on ``resident - n_comm / 2`` GEMM clusters."""
     tiles = ((M + 255) // 256) * ((N + 255) // 256)
-    lib().ell_gemm_set_tail_split(c_int(1 if allow_split else 0))
-    try:
-        clusters = lib().ell_gemm_pair_launch_clusters(c_int(tiles), c_int(resident))
-    finally:
-        lib().ell_gemm_set_tail_split(c_int(1))
+    if fuse:
+        clusters = resident - n_comm // 2
+    else:
+        lib().ell_gemm_set_tail_split(c_int(1 if allow_split else 0))
+        try:
+            clusters = lib().ell_gemm_pair_launch_clusters(c_int(tiles), c_int(resident))
+        finally:
+            lib().ell_gemm_set_tail_split(c_int(1))
     cap = 2 * tiles + 2
     buf = (c_int * (4 * cap))()
-    n = lib().ell_gemm_pair_enumerate_units(c_int(M), c_int(N), c_int(clusters), c_int(1 if allow_split else 0), buf,
-                                            c_int(cap))
+    n = lib().ell_gemm_pair_enumerate_units(c_int(M), c_int(N), c_int(clusters), c_int(1 if allow_split else 0),
+                                            c_int(fuse), c_int(tp), c_int(rank), buf, c_int(cap))
     if n < 0:
         raise KernelError(f"gemm_pair_units failed with code {n}")
     return clusters, [tuple(buf[4 * i:4 * i + 4]) for i in range(n)]
 
 
-def gemm_ce(x, w, target, vocab_start, valid_cols):
+def reduce_tile_order(rows_per_rank, tiles_n, tp, pair=True):
+    """Host-only: the order in which the reduce role of the fused GEMM→reduce-scatter kernels takes the 128-row
+    tiles a rank owns: ``[(row tile inside the shard, column tile), ...]`` by queue position."""
+    cap = (rows_per_rank // 128) * tiles_n
+    buf = (c_int * (2 * max(cap, 1)))()
+    n = lib().ell_gemm_owned_tile_order(c_int(rows_per_rank), c_int(tiles_n), c_int(tp), c_int(1 if pair else 0), buf,
+                                        c_int(cap))
+    if n < 0:
+        raise KernelError(f"reduce_tile_order failed with code {n}")
+    return [tuple(buf[2 * i:2 * i + 2]) for i in range(n)]
+
+
+def gemm_ce(x, w, target, vocab_start, valid_cols, pair=None):
     """LM-head GEMM with the cross-entropy statistics fused into its epilogue.
 
     Returns ``(logits [T, V] bf16, parts [T, 3] fp32)`` with parts = (row max, Σ exp(l − max), target logit or 0)
@@ -362,12 +391,14 @@ def gemm_ce(x, w, target, vocab_start, valid_cols):
     if K % 8 or V % 8:
         raise ValueError("gemm_ce: K and V must be multiples of 8")
     logits = torch.empty(T, V, dtype=torch.bfloat16, device=x.device)
-    tiles = lib().ell_gemm_ce_tiles(c_int(V))
+    use_pair = _use_pair(T, V, 0) if pair is None else pair
+    tiles = lib().ell_gemm_ce_slots_pair(c_int(V)) if use_pair else lib().ell_gemm_ce_tiles(c_int(V))
     part = scratch(tiles * 3 * T, tag="gemm_ce_part")
     parts = torch.empty(T, 3, dtype=torch.float32, device=x.device)
     tgt = target if target.dtype == torch.int64 else target.to(torch.int64)
-    rc = lib().ell_gemm_ce(_p(x), _p(w), _p(logits), _p(tgt.contiguous()), _p(part), c_int(T), c_int(V), c_int(K),
-                           c_longlong(vocab_start), c_int(valid_cols), _p(err_flag(x.device)), _stream())
+    fn = lib().ell_gemm_ce_pair if use_pair else lib().ell_gemm_ce
+    rc = fn(_p(x), _p(w), _p(logits), _p(tgt.contiguous()), _p(part), c_int(T), c_int(V), c_int(K),
+            c_longlong(vocab_start), c_int(valid_cols), _p(err_flag(x.device)), _stream())
     _check(rc, "gemm_ce")
     rc = lib().ell_ce_combine(_p(part), _p(parts), c_int(tiles), c_int(T), _stream())
     _check(rc, "ce_combine")

@@ -2,8 +2,10 @@
 
     python -m easyllm_b200.ops.profile_cases <case> [--iters 6]
 
-Cases: gemm_nt, gemm_nt_n4096, gemm_dgrad, gemm_wgrad (single-CTA kernel), gemm_pair_nt, gemm_pair_dgrad,
-gemm_pair_wgrad (CTA-pair kernel), gemm_ag, gemm_rs, flash_fwd, flash_bwd, rmsnorm_fwd, rmsnorm_bwd, swiglu, rope, adam, ce.
+Cases: gemm_nt, gemm_nt_n4096, gemm_dgrad, gemm_wgrad, gemm_ag, gemm_rs, gemm_ar (single-CTA kernel), the same with
+the prefix gemm_pair_ (CTA-pair kernel) plus gemm_pair_agk (gather of the reduction rows into the weight-gradient
+GEMM) and gemm_pair_ce (LM head with the cross-entropy epilogue), flash_fwd, flash_bwd, rmsnorm_fwd, rmsnorm_bwd,
+swiglu, rope, adam, ce.
 Inputs are larger than L2 (126 MB) where the op is memory-bound but hold well under a few GB,
 so a full-section profiler capture of 1-3 launches ends by itself in a minute or two.
 """
@@ -56,7 +58,11 @@ def main():
         dqkv = torch.empty_like(qkv)
         dq, dk, dv = (dqkv[:, i * 4096:(i + 1) * 4096].view(4096, 32, 128) for i in range(3))
         fn = lambda: cu.flash_attn_bwd(do, q, k, v, out, lse, rs, 128 ** -0.5, dq, dk, dv)   # noqa: E731
-    elif c in ("gemm_ag", "gemm_rs"):
+    elif c == "gemm_ce":
+        x = torch.randn(4096, 4096, **bf); w = torch.randn(32000, 4096, **bf) * 0.02
+        t = torch.randint(0, 32000, (4096,), device="cuda")
+        fn = lambda: cu.gemm_ce(x, w, t, 0, 32000)                                    # noqa: E731
+    elif c in ("gemm_ag", "gemm_rs", "gemm_ar", "gemm_agk"):
         # the fused tensor-parallel kernels on a one-rank group: same kernel, flags and staging path, no peers
         import os
         import torch.distributed as dist
@@ -70,9 +76,13 @@ def main():
         if c == "gemm_ag":
             x = torch.randn(4096, 4096, **bf); w = torch.randn(22016, 4096, **bf)
             fn = lambda: ws.ag_gemm(x, w)                                             # noqa: E731
+        elif c == "gemm_agk":
+            dy = torch.randn(4096, 11008, **bf); x = torch.randn(4096, 4096, **bf)
+            acc = torch.zeros(11008, 4096, device="cuda")
+            fn = lambda: ws.agk_wgrad(dy, x, acc)                                     # noqa: E731
         else:
             x = torch.randn(4096, 11008, **bf); w = torch.randn(4096, 11008, **bf)
-            fn = lambda: ws.gemm_rs(x, w)                                             # noqa: E731
+            fn = lambda: ws.gemm_rs(x, w, all_reduce=(c == "gemm_ar"))                # noqa: E731
     elif c in ("rmsnorm_fwd", "rmsnorm_bwd"):
         x = torch.randn(16384, 4096, **bf); r = torch.randn_like(x); w = torch.ones(4096, **bf)
         y, h, rstd = cu.rmsnorm_fwd(x, r, w, 1e-5)

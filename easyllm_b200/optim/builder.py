@@ -59,4 +59,4 @@ def build_optimizer(cfg_optim, model, zero_stage=0, grad_clip=0.0, fp16=False, n
         return inner
     # the engines drive every optimizer through the ZeroOptimizer surface
     from .torch_adapter import TorchOptimizerAdapter
-    return TorchOptimizerAdapter(inner, model.named_parameters(), grad_clip=grad_clip, nan_policy=nan_policy)
+    return TorchOptimizerAdapter(inner, model.named_parameters(), grad_clip=grad_clip, nan_policy=nan_policy, fp16=fp16)

@@ -24,7 +24,9 @@ from ..parallel.grid import get_grid
 class TorchOptimizerAdapter:
     stage = 0
 
-    def __init__(self, optimizer: torch.optim.Optimizer, named_params, grad_clip=0.0, nan_policy="count"):
+    def __init__(self, optimizer: torch.optim.Optimizer, named_params, grad_clip=0.0, nan_policy="count", fp16=False,
+                 loss_scale_cfg=None):
+        from .zero import DynamicLossScaler
         self.inner = optimizer
         self.grid = get_grid()
         self.grad_clip, self.nan_policy = grad_clip, nan_policy
@@ -34,6 +36,21 @@ class TorchOptimizerAdapter:
                 self.names.append(n)
                 self.params.append(p)
                 p.main_grad = torch.zeros_like(p, dtype=torch.float32)
+        # fp32 master copies: the wrapped optimizer never sees a bf16 / fp16 parameter (at fine-tuning learning
+        # rates most updates are below half a bf16 ulp and would be rounded away); it updates the masters and the
+        # model parameters are refreshed from them after every step
+        self.masters = {}
+        for group in self.inner.param_groups:
+            swapped = []
+            for p in group["params"]:
+                if p.dtype != torch.float32 and p.requires_grad:
+                    m = p.detach().clone().float().requires_grad_(True)
+                    self.masters[p] = m
+                    swapped.append(m)
+                else:
+                    swapped.append(p)
+            group["params"] = swapped
+        self.scaler = DynamicLossScaler(**(loss_scale_cfg or {})) if fp16 else None
         self.skipped_steps = 0
         self.step_count = 0
         self._norm = None
@@ -45,18 +62,23 @@ class TorchOptimizerAdapter:
 
     @property
     def cur_scale(self):
-        return 1.0
+        return self.scaler.cur_scale if self.scaler else 1.0
 
     def get_global_grad_norm(self):
         return None if self._norm is None else float(self._norm)
 
     def refresh_fp32_params(self):
-        pass                                               # the wrapped optimizer updates the parameters in place
+        """Re-read the masters from the model parameters (after weights were loaded into the model)."""
+        with torch.no_grad():
+            for p, m in self.masters.items():
+                m.copy_(p)
 
     def zero_grad(self):
         for p in self.params:
             p.main_grad.zero_()
             p.grad = None
+        for m in self.masters.values():
+            m.grad = None
 
     def accumulate_grads(self):
         for p in self.params:
@@ -83,24 +105,37 @@ class TorchOptimizerAdapter:
             sq = sq + p.main_grad.pow(2).sum()
         if dist.is_initialized() and g.mp_group is not None and g.tp * g.pp > 1:
             dist.all_reduce(sq, group=g.mp_group)
-        return sq.sqrt()
+        return sq.sqrt() / self.cur_scale
 
     def step(self, **kw):
         self._reduce()
         norm = self._global_norm()
         self._norm = norm
-        if self.nan_policy in ("skip", "abort") and not bool(torch.isfinite(norm)):
-            if self.nan_policy == "abort":
-                raise FloatingPointError("non-finite gradient norm")
-            self.skipped_steps += 1
-            self.zero_grad()
-            return False
-        coef = 1.0
+        if self.scaler is not None or self.nan_policy in ("skip", "abort"):
+            ok = bool(torch.isfinite(norm))
+            if not ok:
+                if self.scaler is not None:
+                    self.scaler.update(True)           # overflow: skip the step, lower the scale
+                elif self.nan_policy == "abort":
+                    raise FloatingPointError("non-finite gradient norm")
+                self.skipped_steps += 1
+                self.zero_grad()
+                return False
+        coef = 1.0 / self.cur_scale
         if self.grad_clip and self.grad_clip > 0:
-            coef = min(1.0, float(self.grad_clip / (norm + 1e-6)))
+            coef *= min(1.0, float(self.grad_clip / (norm + 1e-6)))
         for p in self.params:
-            p.grad = (p.main_grad * coef).to(p.dtype)
+            m = self.masters.get(p)
+            if m is not None:
+                m.grad = p.main_grad * coef            # fp32 all the way
+            else:
+                p.grad = (p.main_grad * coef).to(p.dtype)
         self.inner.step(**kw)
+        with torch.no_grad():
+            for p, m in self.masters.items():
+                p.copy_(m)
+        if self.scaler is not None:
+            self.scaler.update(False)
         self.step_count += 1
         self.zero_grad()
         return True
@@ -108,8 +143,23 @@ class TorchOptimizerAdapter:
     # ---- checkpoint -------------------------------------------------------------------------------------------
     def state_dict(self):
         return {"inner": self.inner.state_dict(), "step": self.step_count, "skipped_steps": self.skipped_steps,
-                "names": self.names, "kind": type(self.inner).__name__}
+                "names": self.names, "kind": type(self.inner).__name__,
+                "masters": [self.masters[p].detach().cpu() if p in self.masters else None for p in self.params],
+                "scaler": self.scaler.state_dict() if self.scaler else None}
 
     def load_state_dict(self, sd, **_):
+        if sd.get("kind") not in (None, type(self.inner).__name__):
+            raise ValueError(f"checkpoint holds {sd.get('kind')} state, the run builds {type(self.inner).__name__}")
+        if list(sd.get("names", self.names)) != list(self.names):
+            raise ValueError("optimizer state was saved for a different set of trainable parameters "
+                             f"({len(sd.get('names', []))} saved, {len(self.names)} now)")
         self.inner.load_state_dict(sd["inner"])
         self.step_count, self.skipped_steps = sd.get("step", 0), sd.get("skipped_steps", 0)
+        saved = sd.get("masters")
+        if saved is not None:
+            with torch.no_grad():
+                for p, m in zip(self.params, saved):
+                    if m is not None and p in self.masters:
+                        self.masters[p].copy_(m)
+        if self.scaler and sd.get("scaler"):
+            self.scaler.load_state_dict(sd["scaler"])

@@ -136,12 +136,14 @@ class HFRunner:
         cfg_optim = {"type": tr["optimizer"].get("type", "AdamW"), "kwargs": dict(tr["optimizer"].get("kwargs") or {})}
         self.optimizer = build_optimizer(cfg_optim, self.model, zero_stage=stage,
                                          grad_clip=self.ds_config.get("gradient_clipping", 0.0),
-                                         fp16=self.dtype == torch.float16 and self.deepspeed, engine_contract=True)
+                                         fp16=self.dtype == torch.float16, engine_contract=True)
         lr_cfg = {"type": tr["lr_scheduler"]["type"], "kwargs": dict(tr["lr_scheduler"].get("kwargs") or {})}
         self.lr_scheduler = build_learning_rate_scheduler(lr_cfg, self.optimizer)
         self.engine = ZeroDPEngine(self.model, self.optimizer, self.lr_scheduler,
                                    dict(self.ds_config, gradient_accumulation_steps=self.gradient_accumulation_steps))
-        self.scaler = None if self.deepspeed else ShardedGradScaler(enabled=self.dtype == torch.float16)
+        # fp16 loss scaling lives in the optimizer (``optimizer.cur_scale``; an overflowing step is skipped and the
+        # scale halved) with and without the ZeRO engine; ``ShardedGradScaler`` stays available to user loops
+        self.scaler = None
 
     def get_cur_train_epoch(self):
         return self.cur_iter // self.train_epoch_size + 1

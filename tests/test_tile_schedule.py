@@ -67,10 +67,6 @@ def test_fused_launch_orders(cu, tp, rank):
         _coverage(rs, M, N, bn)
         first = [mt // rows_per_rank_tiles for mt, *_ in rs[:tp]]
         assert sorted(first) == list(range(tp))           # reduce-scatter: consecutive tiles feed different owners
-        ring = cu.gemm_work_units(M, N, bn=bn, fuse=2, tp=tp, rank=rank, rs_ring=True)
-        _coverage(ring, M, N, bn)
-        assert {mt // rows_per_rank_tiles for mt, *_ in ring[:per_phase]} == {(rank + 1) % tp}
-        assert {mt // rows_per_rank_tiles for mt, *_ in ring[-per_phase:]} == {rank}
 
 
 @pytest.mark.parametrize("M,N", [(256, 256), (4096, 12288), (1000, 520), (384, 320), (22016, 4096), (4352, 1280)])
@@ -105,6 +101,46 @@ def test_pair_kernel_units_cover_the_output_once_and_halve_only_the_tail(cu, M, 
         assert all(u[3] == 256 for u in units[:len(units) - want])     # only the last wave is cut
         if want:                                                        # and it now fits half a wave's worth of clusters
             assert want <= clusters
+
+
+@pytest.mark.parametrize("tp", [2, 4, 8])
+@pytest.mark.parametrize("M,N", [(4096, 4096), (4096, 6144), (8192, 2048)])
+def test_pair_kernel_fused_orders(cu, tp, M, N):
+    """CTA-pair fused launches: every 256-row tile once; all-gather form starts on the local shard and takes the
+    others in ring order; reduce forms feed every owner from the first tiles on and are never halved."""
+    tm, tn = M // 256, (N + 255) // 256
+    tpr = tm // tp
+    for rank in (0, tp - 1):
+        clusters, ag = cu.gemm_pair_units(M, N, resident=74, fuse=1, tp=tp, rank=rank, n_comm=8)
+        assert clusters == 70
+        cover = {}
+        for mt, nt, n0, bn in ag:
+            for c in range(n0, n0 + bn, 128):
+                assert (mt, c) not in cover
+                cover[(mt, c)] = 1
+        assert len(cover) == tm * tn * 2
+        whole = [u for u in ag if u[3] == 256]
+        per_phase = tpr * tn
+        for phase in range(tp - 1):           # the last phase may end in half-width units
+            owners = {mt // tpr for mt, *_ in whole[phase * per_phase:(phase + 1) * per_phase]}
+            assert owners == {(rank + phase) % tp}
+        for fuse in (2, 3):
+            _, rs = cu.gemm_pair_units(M, N, resident=74, fuse=fuse, tp=tp, rank=rank, n_comm=8)
+            assert all(u[3] == 256 for u in rs) and len(rs) == tm * tn
+            assert sorted((u[0], u[1]) for u in rs) == sorted(itertools.product(range(tm), range(tn)))
+            assert sorted(mt // tpr for mt, *_ in rs[:tp]) == list(range(tp))
+        # the reduce role's queue visits every owned 128-row tile once, in the order the owner's tiles are emitted
+        order = cu.reduce_tile_order(M // tp, tn, tp, pair=True)
+        assert sorted(order) == sorted(itertools.product(range(2 * tpr), range(tn)))
+        emitted = []
+        for mt, nt, *_ in rs:
+            if mt // tpr == rank:
+                emitted += [(2 * (mt - rank * tpr), nt), (2 * (mt - rank * tpr) + 1, nt)]
+        assert order == emitted
+        single = cu.reduce_tile_order(M // tp, tn, tp, pair=False)
+        assert sorted(single) == sorted(order)
+        rs1 = cu.gemm_work_units(M, N, bn=256, fuse=2, tp=tp, rank=rank)
+        assert single == [(mt - rank * 2 * tpr, nt) for mt, nt, *_ in rs1 if mt // (2 * tpr) == rank]
 
 
 def _row_starts(T, doc_lens):
