@@ -100,7 +100,9 @@ class PipelineEngine:
             return t.to(dev, non_blocking=True) if torch.is_tensor(t) else t
         io = None
         if self.g.is_first_stage():
-            io = self.module.parse_batch(tuple(mv(t) for t in inputs))
+            # parsed where the loader left the tensors (the host), then copied: no read-back from the GPU
+            from ..models.llama import StageIO
+            io = inputs if isinstance(inputs, StageIO) else self.module.parse_batch(inputs, device=dev)
         if self.g.is_last_stage() and labels is not None:
             labels = tuple(mv(t) for t in labels) if isinstance(labels, (tuple, list)) else (mv(labels),)
         else:
@@ -136,6 +138,13 @@ class PipelineEngine:
         self._range_end()
         return inp.grad if inp is not None else None
 
+    def _check_kernel_errors(self):
+        """A fused kernel whose bounded wait on a peer expired returns with a partial result and an error code;
+        refuse to apply an optimizer step computed from it (``ops.cuda.KernelError``)."""
+        if next(self.module.parameters()).is_cuda:
+            from ..ops import cuda as cu
+            cu.check_step_errors()
+
     # ---- train --------------------------------------------------------------------------------
     def train_batch(self, data_iter=None, dynamic=True, sequence_parallel=None):
         if self.optimizer is None:
@@ -153,6 +162,7 @@ class PipelineEngine:
                 losses.append(loss.detach())
         else:
             losses = self._train_1f1b(data_iter, M, P)
+        self._check_kernel_errors()
         self._range("optimizer")
         stepped = self.optimizer.step()
         self._range_end()

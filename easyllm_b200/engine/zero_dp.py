@@ -53,6 +53,9 @@ class ZeroDPEngine:
         self.micro_steps += 1
         if not boundary:
             return False
+        if next(self.module.parameters()).is_cuda:
+            from ..ops import cuda as cu
+            cu.check_step_errors()           # a kernel that gave up a bounded wait left a partial result: do not apply it
         ok = self.optimizer.step()
         self.global_steps += 1
         if not ok:

@@ -147,7 +147,7 @@ class Attention(nn.Module):
             # training / full-sequence path: RoPE + attention on the packed projection, one packed gradient back
             sl = self.slopes.to(x.device) if self.slopes is not None else None
             o = ops.flash_attention_packed(qkv, hq, hk, d, meta["cu_seqlens"], meta["max_seqlen"], alibi_slopes=sl,
-                                           rope=rope)
+                                           rope=rope, row_start=meta.get("row_start"))
             return ops.linear(o, self.o_proj.weight, self.o_proj.bias)
         if rope is not None:
             qkv = ops.rope_packed(qkv, cos, sin, pos, hq, hk, d)
@@ -248,10 +248,13 @@ class Decoder(nn.Module):
         self.norm = RMSNorm(a.hidden_size, a.rms_norm_eps, dtype)
 
 
-def build_meta(input_ids, attention_mask=None, position_ids=None, cu_seqlens=None):
-    """Token-major metadata.  Padding becomes its own segments so real tokens never see it."""
+def build_meta(input_ids, attention_mask=None, position_ids=None, cu_seqlens=None, device=None):
+    """Token-major metadata.  Padding becomes its own segments so real tokens never see it.
+    Everything is computed where ``input_ids`` lives and then moved to ``device``: with a batch still on the host
+    (as a loader delivers it) the scalars below cost no device→host synchronisation."""
     b, s = input_ids.shape
     dev = input_ids.device
+    out_dev = torch.device(device) if device is not None else dev
     if cu_seqlens is not None:
         cu = torch.unique_consecutive(cu_seqlens.reshape(-1).to(torch.int32))
         if int(cu[-1]) < b * s:
@@ -270,8 +273,15 @@ def build_meta(input_ids, attention_mask=None, position_ids=None, cu_seqlens=Non
         else:
             position_ids = torch.arange(s, device=dev).unsqueeze(0).expand(b, s)
     pos = position_ids.reshape(-1).to(torch.int32)
-    return {"position_ids": pos, "cu_seqlens": cu, "max_seqlen": int((cu[1:] - cu[:-1]).max()), "batch": b,
-            "max_position": max(s, int(pos.max()) + 1)}
+    meta = {"max_seqlen": int((cu[1:] - cu[:-1]).max()), "batch": b, "max_position": max(s, int(pos.max()) + 1)}
+    row_start = None
+    if out_dev.type == "cuda":
+        from ...ops import cuda as cu_ops
+        if cu_ops.available():
+            row_start = cu_ops.row_start_of(cu, b * s, out_dev)   # once per batch, not once per layer
+    meta.update(position_ids=pos.to(out_dev, non_blocking=True), cu_seqlens=cu.to(out_dev, non_blocking=True),
+                row_start=row_start)
+    return meta
 
 
 class CausalLM(nn.Module):
@@ -322,7 +332,12 @@ class CausalLM(nn.Module):
     def forward(self, input_ids=None, attention_mask=None, labels=None, position_ids=None, cu_seqlens=None,
                 inputs_embeds=None, return_dict=True, **_):
         b, s = input_ids.shape
-        meta = build_meta(input_ids, attention_mask, position_ids, cu_seqlens)
+        dev = self.lm_head.weight.device
+        # a batch handed over on the host is parsed there and copied (no read-back from the GPU per micro-batch)
+        meta = build_meta(input_ids, attention_mask, position_ids, cu_seqlens, device=dev)
+        input_ids = input_ids.to(dev, non_blocking=True)
+        if labels is not None:
+            labels = labels.to(dev, non_blocking=True)
         h = self.hidden_states(input_ids, meta, inputs_embeds=inputs_embeds)
         out = {}
         if labels is not None:

@@ -130,10 +130,19 @@ class VocabParallelEmbedding(nn.Module):
         if not skip_init:
             _init_normal_(self.weight.data, sigma, sharded=g.tp > 1)
 
+    def check_ids(self, ids):
+        """Token ids must lie inside the table.  CPU tensors are checked here; on the GPU the lookup kernel checks
+        every id itself and reports through the device error word (no ``max()`` read-back per micro-batch)."""
+        if not ids.is_cuda and ids.numel():
+            hi, lo = int(ids.max()), int(ids.min())
+            if hi >= self.num_embeddings or lo < 0:
+                raise ValueError(f"An input token id {hi if hi >= self.num_embeddings else lo} is out of bounds of "
+                                 f"the embedding table (vocab size {self.num_embeddings})")
+
     def lookup(self, ids):
         """Local partial lookup (no reduction): rows for foreign ids are zero."""
         if self.weight.is_cuda and self.weight.dtype == torch.bfloat16:
-            return ops.embedding(ids, self.weight, self.vocab_start)
+            return ops.embedding(ids, self.weight, self.vocab_start, self.num_embeddings)
         if get_grid().tp == 1:
             return F.embedding(ids, self.weight)
         mask = (ids < self.vocab_start) | (ids >= self.vocab_end)
@@ -142,7 +151,9 @@ class VocabParallelEmbedding(nn.Module):
         return out.masked_fill(mask.unsqueeze(-1), 0.0)
 
     def forward(self, ids):
-        if ids.numel() and int(ids.max()) >= self.num_embeddings:
+        self.check_ids(ids)
+        if ids.is_cuda and not (self.weight.dtype == torch.bfloat16) and ids.numel() and \
+                int(ids.max()) >= self.num_embeddings:       # fp32 / fp16 tables on a GPU take the PyTorch lookup
             raise ValueError(f"An input token id {int(ids.max())} is out of bounds of the embedding table "
                              f"(vocab size {self.num_embeddings})")
         return mp.reduce_from_tensor_model_parallel_region(self.lookup(ids))
@@ -291,7 +302,8 @@ class ParallelAttention(nn.Module):
         if kv_cache is None and self.args.use_flash_attn:
             slopes = self.alibi.to(qkv.device) if self.alibi is not None else None
             o = ops.flash_attention_packed(qkv, self.hq, self.hk, self.D, meta.get("cu_seqlens"),
-                                           meta.get("max_seqlen"), alibi_slopes=slopes, rope=rope)
+                                           meta.get("max_seqlen"), alibi_slopes=slopes, rope=rope,
+                                           row_start=meta.get("row_start"))
             return self.o_proj(o)
         if rope is not None:
             qkv = ops.rope_packed(qkv, cos, sin, pos, self.hq, self.hk, self.D)
@@ -422,8 +434,7 @@ class Embedding(nn.Module):
     def forward(self, ids_flat, position_ids_flat):
         g = get_grid()
         emb = self.word_embeddings
-        if ids_flat.numel() and int(ids_flat.max()) >= emb.num_embeddings:
-            raise ValueError(f"An input token id {int(ids_flat.max())} is out of bounds of the embedding table")
+        emb.check_ids(ids_flat)
         x = emb.lookup(ids_flat)
         if self.position_embeddings is not None:
             pe = self.position_embeddings(position_ids_flat)

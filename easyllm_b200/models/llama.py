@@ -48,10 +48,15 @@ class StageIO:
     seq: int
     max_seqlen: int
     max_position: int = 0
+    row_start: Optional[torch.Tensor] = None  # [T] int32: first token of each token's document (attention mask)
+    tokens: Optional[torch.Tensor] = None     # [T] token ids (first stage only)
 
     def meta(self):
+        if self.row_start is None and self.position_ids.is_cuda:
+            from ..ops import cuda as cu
+            self.row_start = cu.row_start_of(self.cu_seqlens, self.position_ids.numel(), self.position_ids.device)
         return {"position_ids": self.position_ids, "cu_seqlens": self.cu_seqlens, "max_seqlen": self.max_seqlen,
-                "batch": self.batch, "max_position": self.max_position}
+                "batch": self.batch, "max_position": self.max_position, "row_start": self.row_start}
 
 
 def _block_params(a: ModelArgs):
@@ -173,17 +178,30 @@ class LlamaModelPipe(nn.Module):
         return [True] * n
 
     # ---- batch parsing ---------------------------------------------------------------------
-    def parse_batch(self, inputs) -> StageIO:
-        """First-stage input ``(tokens [b,s], position_ids [b,s], attention_mask[, cu_seqlens])``."""
+    def parse_batch(self, inputs, device=None) -> StageIO:
+        """First-stage input ``(tokens [b,s], position_ids [b,s], attention_mask[, cu_seqlens])`` → StageIO on
+        ``device`` (default: where the tokens are).  Batches from a loader arrive on the host: every scalar the
+        kernels need (longest document, highest position, the id range check) is read there, before the copy to
+        the GPU, so a training micro-batch costs no device→host synchronisation.  Device-resident inputs with
+        ``cu_seqlens`` still work but read those scalars back."""
         if torch.is_tensor(inputs):
             inputs = (inputs,)
         tokens = inputs[0]
         b, s = tokens.shape
-        dev = tokens.device
+        src = tokens.device
+        dev = torch.device(device) if device is not None else src
+        host = src.type == "cpu"
+        if host and self.has_embedding:
+            self.layers["1"].word_embeddings.check_ids(tokens)
+        max_position = s
         if len(inputs) > 1 and inputs[1] is not None:
             pos = inputs[1].reshape(-1).to(torch.int32)
+            if host or inputs[1].device.type == "cpu":
+                max_position = max(s, int(pos.max()) + 1 if pos.numel() else 1)
+            else:
+                max_position = 0                              # resolved below / by the first consumer
         else:
-            pos = torch.arange(s, dtype=torch.int32, device=dev).repeat(b)
+            pos = torch.arange(s, dtype=torch.int32, device=src).repeat(b)
         cu = inputs[3] if len(inputs) > 3 else None
         max_seqlen = s
         if cu is not None:
@@ -194,9 +212,19 @@ class LlamaModelPipe(nn.Module):
                 cu = torch.cat((cu, cu.new_tensor([b * s])))
             max_seqlen = int((cu[1:] - cu[:-1]).max())
         elif b > 1:
-            cu = torch.arange(0, (b + 1) * s, s, dtype=torch.int32, device=dev)
-        io = StageIO(None, pos, cu, b, s, max_seqlen, max_position=max(s, int(pos.max()) + 1 if pos.numel() else 1))
-        io.tokens = tokens.reshape(-1)
+            cu = torch.arange(0, (b + 1) * s, s, dtype=torch.int32, device=src)
+        if max_position == 0:
+            max_position = max(s, int(pos.max()) + 1 if pos.numel() else 1)
+        row_start = None
+        if dev.type == "cuda":
+            from ..ops import cuda as cu_ops
+            if cu_ops.available():
+                row_start = cu_ops.row_start_of(cu, b * s, dev)
+
+        def mv(t):
+            return t if t is None or t.device == dev else t.to(dev, non_blocking=True)
+        io = StageIO(None, mv(pos), mv(cu), b, s, max_seqlen, max_position=max_position, row_start=row_start)
+        io.tokens = mv(tokens.reshape(-1))
         return io
 
     # ---- forward of this stage ---------------------------------------------------------------

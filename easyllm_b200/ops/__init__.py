@@ -326,11 +326,11 @@ def linear_parts(x, weights, biases=None):
 # ---------------------------------------------------------------------------------------------
 class _Embedding(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, ids, weight, vocab_start):
+    def forward(ctx, ids, weight, vocab_start, vocab_total):
         ctx.save_for_backward(ids)
         ctx.wref = weight
         ctx.start = vocab_start
-        return _cu().embedding_fwd(ids, weight, vocab_start)
+        return _cu().embedding_fwd(ids, weight, vocab_start, vocab_total)
 
     @staticmethod
     def backward(ctx, dout):
@@ -340,17 +340,18 @@ class _Embedding(torch.autograd.Function):
         dout = dout.contiguous()
         if mg is not None:
             _cu().embedding_bwd_(ids, dout, mg, ctx.start)
-            return None, None, None
+            return None, None, None, None
         g32 = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
         _cu().embedding_bwd_(ids, dout, g32, ctx.start)
-        return None, g32.to(w.dtype), None
+        return None, g32.to(w.dtype), None, None
 
 
-def embedding(ids, weight, vocab_start=0):
-    """``weight[ids - vocab_start]`` with zero rows for ids outside this rank's vocabulary range."""
+def embedding(ids, weight, vocab_start=0, vocab_total=0):
+    """``weight[ids - vocab_start]`` with zero rows for ids outside this rank's vocabulary range.  On the kernel
+    path ``vocab_total`` turns on the device-side range check of the ids (error word, no host sync)."""
     if _kern(weight):
         if weight.shape[1] % 8 == 0 and weight.is_contiguous():
-            return _Embedding.apply(ids, weight, vocab_start)
+            return _Embedding.apply(ids, weight, vocab_start, vocab_total)
         note_fallback("embedding", weight, "the table must be contiguous with a row length that is a multiple of 8")
     rows = weight.shape[0]
     mask = (ids < vocab_start) | (ids >= vocab_start + rows)
@@ -474,9 +475,11 @@ def flash_attention(q, k, v, cu_seqlens=None, max_seqlen=None, causal=True, scal
 
 
 def flash_attention_packed(qkv, n_q_heads, n_kv_heads, head_dim, cu_seqlens=None, max_seqlen=None, scale=None,
-                           alibi_slopes=None, rope=None):
+                           alibi_slopes=None, rope=None, row_start=None):
     """(RoPE +) causal attention on the fused projection output ``qkv [T, (Hq+2Hk)·D]`` (layout q|k|v)
-    → ``[T, Hq·D]``.  ``rope`` = (cos, sin, position_ids) rotates the q and k heads first.
+    → ``[T, Hq·D]``.  ``rope`` = (cos, sin, position_ids) rotates the q and k heads first.  ``row_start``
+    (int32 ``[T]``, the first token of each token's document) may be passed when the caller has it, so it is built
+    once per micro-batch and not once per layer.
 
     On the kernel path the rotation is in place and the backward writes one packed gradient."""
     T = qkv.shape[0]
@@ -490,7 +493,8 @@ def flash_attention_packed(qkv, n_q_heads, n_kv_heads, head_dim, cu_seqlens=None
         if rope is not None:
             cos, sin, pos = rope
             rope = (cos, sin, pos if pos.dtype == torch.int32 else pos.to(torch.int32))
-        return _cu().flash_attention_packed(qkv, n_q_heads, n_kv_heads, head_dim, cu_seqlens, max_seqlen, scale, rope)
+        return _cu().flash_attention_packed(qkv, n_q_heads, n_kv_heads, head_dim, cu_seqlens, max_seqlen, scale, rope,
+                                            row_start)
     if rope is not None:
         qkv = rope_packed(qkv, rope[0], rope[1], rope[2], n_q_heads, n_kv_heads, head_dim)
     q = qkv[:, :nq].view(T, n_q_heads, head_dim)

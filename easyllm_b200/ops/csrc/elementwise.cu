@@ -154,12 +154,16 @@ ELL_API int ell_accum_bf16_to_f32(const void* in, float* out, long long n, cudaS
 namespace ell {
 
 // out[t, :] = ids[t] in [vocab_start, vocab_start + rows) ? weight[ids[t] - vocab_start, :] : 0
+// An id outside [0, vocab_total) is reported through the error word (code 31) instead of a host-side max() of the
+// ids, which would cost a device synchronisation per micro-batch; its row is written as zeros.
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ weight,
                                      __nv_bfloat16* __restrict__ out, int T, int cols, long long vocab_start,
-                                     long long rows) {
+                                     long long rows, long long vocab_total, int* __restrict__ err) {
   const int nvec = cols / 8;
   for (int t = blockIdx.x; t < T; t += gridDim.x) {
-    const long long loc = ids[t] - vocab_start;
+    const long long id = ids[t];
+    if (err != nullptr && threadIdx.x == 0 && (id < 0 || id >= vocab_total)) atomicCAS(err, 0, 31);
+    const long long loc = id - vocab_start;
     const bool mine = loc >= 0 && loc < rows;
     const bf16x8* src = reinterpret_cast<const bf16x8*>(weight + (mine ? loc : 0) * cols);
     bf16x8* dst = reinterpret_cast<bf16x8*>(out + (size_t)t * cols);
@@ -188,13 +192,15 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const __
 
 }  // namespace ell
 
+// vocab_total > 0 with err != nullptr: ids outside [0, vocab_total) set *err to 31.
 ELL_API int ell_embedding_fwd(const long long* ids, const void* weight, void* out, int T, int cols,
-                              long long vocab_start, long long rows, cudaStream_t stream) {
+                              long long vocab_start, long long rows, long long vocab_total, int* err,
+                              cudaStream_t stream) {
   if (T == 0) return 0;
   if (cols % 8) return -1;
   const int grid = T < ell::kNumSMs * 16 ? T : ell::kNumSMs * 16;
   ell::embedding_fwd_kernel<<<grid, 128, 0, stream>>>(ids, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, T, cols,
-                                                       vocab_start, rows);
+                                                       vocab_start, rows, vocab_total, vocab_total > 0 ? err : nullptr);
   return ell::launch_status();
 }
 

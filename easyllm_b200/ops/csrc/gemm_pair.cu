@@ -130,6 +130,7 @@ __host__ __device__ __forceinline__ void raster(int idx, int tiles_m, int tiles_
 // units [0, num_full) are whole tiles, unit num_full + 2i + h is half h of tile num_full + i.
 struct Unit {
   int mt, nt, n0, bn;
+  int kphase;   // kFuseAGK: which half of the (rotated) reduction range this unit accumulates
 };
 
 __host__ __device__ inline int split_tail(int num_tiles, int clusters, bool allowed) {
@@ -139,6 +140,9 @@ __host__ __device__ inline int split_tail(int num_tiles, int clusters, bool allo
 
 // Tile order of the fused forms (256-row tiles): all-gather -> GEMM walks the local shard's row tiles first and the
 // other shards in ring order; GEMM -> reduce-scatter / all-reduce interleaves the owners so each is fed evenly.
+// The gather of the reduction rows (kFuseAGK) walks every tile twice: first over the half of the k-range that
+// starts at the local rows (while the peers' rows are still arriving), then over the other half; the output is an
+// fp32 accumulation, so the two passes simply add up.
 __host__ __device__ __forceinline__ Unit decode_unit(int unit, int tiles_m, int tiles_n, int num_full, int fuse, int rank,
                                                      int tp) {
   Unit u;
@@ -146,6 +150,12 @@ __host__ __device__ __forceinline__ Unit decode_unit(int unit, int tiles_m, int 
   if (unit >= num_full) {
     tile = num_full + ((unit - num_full) >> 1);
     half = (unit - num_full) & 1;
+  }
+  u.kphase = 0;
+  if (fuse == kFuseAGK) {
+    const int per_pass = tiles_m * tiles_n;
+    u.kphase = tile / per_pass;
+    tile -= u.kphase * per_pass;
   }
   if (fuse == kFuseAG) {
     const int tpr = tiles_m / tp, per_phase = tpr * tiles_n;
@@ -196,7 +206,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t cta_rank = cluster_cta_rank();       // 0: leader, 1: peer
   const bool is_leader = cta_rank == 0;
   const int cluster_id = ((int)blockIdx.x - n_comm) >> 1, n_clusters = ((int)gridDim.x - n_comm) >> 1;
-  const int num_tiles = tiles_m * tiles_n;
+  const int num_tiles = tiles_m * tiles_n * (FUSE == kFuseAGK ? 2 : 1);   // kFuseAGK: two k-passes per tile
   const int num_kb = (K + kBK - 1) / kBK;
   const int n_split = split_tail(num_tiles, n_clusters, !kReduce && !fuse.no_tail_split);
   const int num_full = num_tiles - n_split, num_units = num_tiles + n_split;
@@ -264,7 +274,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             fence_proxy_async_all();   // peer writes -> TMA reads (async proxy)
           }
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb_lo = FUSE == kFuseAGK ? u.kphase * (num_kb / 2) : 0;
+        const int kb_hi = FUSE == kFuseAGK && u.kphase == 0 ? num_kb / 2 : num_kb;
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           int kk = kb;                       // k-block actually loaded
           const CUtensorMap* bk_map = &tmB;  // kFuseAGK: map of the B k-block
           int bk_row = 0;
@@ -351,7 +363,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kTileN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int n_kb = num_kb;
+        if (FUSE == kFuseAGK) {
+          const int kphase = (unit >= num_full ? num_full + ((unit - num_full) >> 1) : unit) / (tiles_m * tiles_n);
+          n_kb = kphase == 0 ? num_kb / 2 : num_kb - num_kb / 2;
+        }
+        for (int kb = 0; kb < n_kb; ++kb) {
           if (!mbar_wait(&sh->full[stage], phase, abort_flag)) {
             ok = false;
             break;
@@ -737,7 +754,7 @@ ELL_API int ell_gemm_pair_enumerate_units(int M, int N, int clusters, int allow_
                                           int* out, int max_units) {
   using namespace ell::pair;
   const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + kTileN - 1) / kTileN;
-  const int num_tiles = tiles_m * tiles_n;
+  const int num_tiles = tiles_m * tiles_n * (fuse == kFuseAGK ? 2 : 1);
   const bool reduce = fuse == kFuseRS || fuse == kFuseAR;
   const int n_split = split_tail(num_tiles, clusters, allow_split != 0 && !reduce);
   const int num_full = num_tiles - n_split, num_units = num_tiles + n_split;

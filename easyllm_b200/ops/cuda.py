@@ -93,7 +93,22 @@ def check_err_flag():
     if v:
         f.zero_()
         raise KernelError(f"a kernel gave up a bounded wait (code {v}: 1 producer, 2 mma, 3 epilogue, 4 communication "
-                          "role, 5 peer flag; 11-15 the same roles of the CTA-pair GEMM; 21 cross-entropy exchange)")
+                          "role, 5 peer flag; 11-15 the same roles of the CTA-pair GEMM; 21 cross-entropy exchange; "
+                          "31 a token id outside the embedding table)")
+
+
+def waiting_kernels_in_use():
+    """True once a kernel that waits on peers or on its own pipeline with a bounded wait has been given an error
+    word in this process (the GEMM / attention kernels, the fused TP and ZeRO kernels)."""
+    return bool(_err_flags)
+
+
+def check_step_errors():
+    """Once per optimizer step, before the update is applied: raise if any kernel of the step gave up a bounded
+    wait (a peer that arrived later than the wait limit leaves a partially computed tile behind; the step must
+    not be applied on top of it).  One device→host read; a no-op on machines without the kernel library."""
+    if _err_flags and torch.cuda.is_available():
+        check_err_flag()
 
 
 def scratch(nelem, dtype=torch.float32, tag="default"):
@@ -197,15 +212,18 @@ def sumsq(x, out):
 
 
 # ---- embedding ----------------------------------------------------------------------------
-def embedding_fwd(ids, weight, vocab_start):
-    """Rows of ``weight [rows, h]`` for the ids in ``[vocab_start, vocab_start+rows)``, zeros for the others."""
+def embedding_fwd(ids, weight, vocab_start, vocab_total=0):
+    """Rows of ``weight [rows, h]`` for the ids in ``[vocab_start, vocab_start+rows)``, zeros for the others.
+    With ``vocab_total`` an id outside ``[0, vocab_total)`` sets the device error word (read once per step by
+    ``check_step_errors``) instead of being checked on the host."""
     _bf16c(weight, "weight")
     flat = ids.reshape(-1).contiguous()
     if flat.dtype != torch.int64:
         flat = flat.to(torch.int64)
     out = torch.empty(flat.numel(), weight.shape[1], dtype=torch.bfloat16, device=weight.device)
     rc = lib().ell_embedding_fwd(_p(flat), _p(weight), _p(out), c_int(flat.numel()), c_int(weight.shape[1]),
-                                 c_longlong(vocab_start), c_longlong(weight.shape[0]), _stream())
+                                 c_longlong(vocab_start), c_longlong(weight.shape[0]), c_longlong(vocab_total),
+                                 _p(err_flag(weight.device)), _stream())
     _check(rc, "embedding_fwd")
     return out.view(*ids.shape, weight.shape[1])
 
@@ -414,11 +432,31 @@ def has_symbol(name):
 
 
 # ---- flash attention -------------------------------------------------------------------------
+_zero_rows = {}
+
+
 def _row_start(cu_seqlens, T, device):
+    """Document start of every token (int32 [T]): what the attention kernels mask with.  Models compute it once
+    per micro-batch (``row_start_of``) and pass it down; this is the per-call fallback."""
     if cu_seqlens is None:
-        return torch.zeros(T, dtype=torch.int32, device=device)
+        z = _zero_rows.get((device, T))
+        if z is None:
+            z = _zero_rows[(device, T)] = torch.zeros(T, dtype=torch.int32, device=device)
+        return z
     cu = cu_seqlens.to(device=device, dtype=torch.int64)
     return torch.repeat_interleave(cu[:-1], cu[1:] - cu[:-1], output_size=T).to(torch.int32)
+
+
+def row_start_of(cu_seqlens, T, device):
+    """``row_start[t]`` = first token of the document token ``t`` belongs to, from ``cu_seqlens`` (None: one
+    document).  Built on the host when ``cu_seqlens`` is a CPU tensor (no device synchronisation)."""
+    if cu_seqlens is not None and not cu_seqlens.is_cuda:
+        cu = cu_seqlens.to(torch.int64)
+        rs = torch.repeat_interleave(cu[:-1], cu[1:] - cu[:-1])
+        if rs.numel() != T:
+            raise ValueError(f"cu_seqlens cover {rs.numel()} tokens, the batch has {T}")
+        return rs.to(torch.int32).to(device, non_blocking=True)
+    return _row_start(cu_seqlens, T, device)
 
 
 def flash_attn_fwd(q, k, v, row_start, scale):
@@ -519,9 +557,9 @@ class _FlashAttnPacked(torch.autograd.Function):
     slice gradients nor a copy for the rotary backward are materialised."""
 
     @staticmethod
-    def forward(ctx, qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, cos, sin, pos):
+    def forward(ctx, qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, cos, sin, pos, row_start):
         T = qkv.shape[0]
-        rs = _row_start(cu_seqlens, T, qkv.device)
+        rs = row_start if row_start is not None else _row_start(cu_seqlens, T, qkv.device)
         if cos is not None:
             rope_(qkv, cos, sin, pos, hq + hk, D)
         q, k, v = _split_packed(qkv, hq, hk, D)
@@ -548,12 +586,12 @@ class _FlashAttnPacked(torch.autograd.Function):
             dq.copy_(gq); dk.copy_(gk); dv.copy_(gv)
         if has_rope:
             rope_(dqkv, cos, sin, pos, hq + hk, D, backward=True)
-        return (dqkv,) + (None,) * 9
+        return (dqkv,) + (None,) * 10
 
 
-def flash_attention_packed(qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, rope=None):
+def flash_attention_packed(qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, rope=None, row_start=None):
     cos, sin, pos = rope if rope is not None else (None, None, None)
-    return _FlashAttnPacked.apply(qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, cos, sin, pos)
+    return _FlashAttnPacked.apply(qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, cos, sin, pos, row_start)
 
 
 def flash_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale):

@@ -65,6 +65,8 @@ def main():
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--reduce-ctas", default="", help="comma list: time the reduce-scatter forms with these numbers "
+                                                      "of dedicated reduce CTAs instead of the per-launch choice")
     a = ap.parse_args()
     tp = int(os.environ.get("WORLD_SIZE", "1"))
     initialize_distributed(tp=tp, pp=1, backend="nccl")
@@ -79,7 +81,10 @@ def main():
 
     def report(name, kind, M, N, K, t_fused, t_comp):
         fl = 2.0 * M * N * K
-        link_bytes = (tp - 1) / tp * M * (K if kind == "ag" else N) * 2
+        # bytes one GPU must receive: its peers' shards of the gathered operand (ag: rows of A, agk: rows of the
+        # reduction operand), the peers' partials of its own rows (rs), or both phases of the two-shot all-reduce
+        per_kind = {"ag": M * K, "agk": K * N, "rs": M * N, "ar": 2 * M * N}[kind]
+        link_bytes = (tp - 1) / tp * per_kind * 2
         bound_ms = max(fl / (peak * 1e9), link_bytes / (LINK_GBS * 1e6))
         row = {"name": name, "kind": kind, "M": M, "N": N, "K": K, "tp": tp, "fused_ms": t_fused, "nccl_gemm_ms": t_comp,
                "speedup": t_comp / t_fused, "roofline_ms": bound_ms, "frac_of_roofline": bound_ms / t_fused,
@@ -107,6 +112,33 @@ def main():
         def comp():
             return mp.reduce_scatter_first_dim(ops.matmul_nt(x, w))
         report(name, "rs", T, H, K, t_f, timed(comp, a.iters, g.tp_group))
+        for n in [int(v) for v in a.reduce_ctas.split(",") if v]:
+            ws.n_comm_rs_fixed = n
+            t_n = timed(lambda: ws.gemm_rs(x, w), a.iters, g.tp_group)
+            ws.n_comm_rs_fixed = None
+            if g.rank == 0:
+                print(f"    {name} with {n} reduce CTAs: {t_n:7.3f} ms (default {ws._reduce_ctas(K)}: {t_f:7.3f} ms)", flush=True)
+    # the backward and non-sequence-parallel forms, on the widest layer of the model
+    K = (F // tp + 7) // 8 * 8
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(H, K, device="cuda", dtype=torch.bfloat16) * 0.02
+    t_f = timed(lambda: ws.gemm_rs(x, w, all_reduce=True), a.iters, g.tp_group)
+
+    def comp_ar():
+        y = ops.matmul_nt(x, w)
+        dist.all_reduce(y, group=g.tp_group)
+        return y
+    report("down gemm->allreduce", "ar", T, H, K, t_f, timed(comp_ar, a.iters, g.tp_group))
+    N = 2 * F // tp
+    dy = torch.randn(T, N, device="cuda", dtype=torch.bfloat16)
+    acc = torch.zeros(N, H, device="cuda")
+    if ws._pair(rows, N):
+        t_f = timed(lambda: ws.agk_wgrad(dy, x_local, acc), a.iters, g.tp_group)
+
+        def comp_wg():
+            xg = mp.gather_first_dim(x_local)
+            return ops.matmul_tn_accum(dy, xg, acc)
+        report("gate_up ag->wgrad", "agk", N, H, T, t_f, timed(comp_wg, a.iters, g.tp_group))
     torch.cuda.synchronize()
     cu.check_err_flag()
     if a.json and g.rank == 0:

@@ -34,7 +34,6 @@ from .grid import get_grid
 
 _MAX_FLAGS = 8192        # flag words per source rank
 _N_COMM_AG = 8           # communication CTAs of a gather launch (even: whole two-CTA clusters)
-_N_COMM_RS = 8           # dedicated reduce CTAs of a reduce launch
 
 
 def _u32(v):
@@ -42,13 +41,14 @@ def _u32(v):
 
 
 class FusedTPWorkspace:
-    def __init__(self, max_tokens, hidden, group=None, n_comm_ag=_N_COMM_AG, n_comm_rs=_N_COMM_RS):
+    def __init__(self, max_tokens, hidden, group=None, n_comm_ag=_N_COMM_AG, n_comm_rs=None):
         import torch.distributed._symmetric_memory as symm_mem
         g = get_grid()
         self.group = group if group is not None else g.tp_group
         self.tp, self.rank = g.tp, g.tp_rank
         self.max_tokens, self.hidden = max_tokens, hidden
-        self.n_comm_ag, self.n_comm_rs = int(n_comm_ag), int(n_comm_rs)
+        self.n_comm_ag = int(n_comm_ag)
+        self.n_comm_rs_fixed = None if n_comm_rs is None else int(n_comm_rs)   # None: chosen per launch from K
         dev = torch.device("cuda", torch.cuda.current_device())
         data_elems = max_tokens * hidden
         set_words = self.tp * _MAX_FLAGS + 64                     # flags of one kind + its done words
@@ -110,6 +110,16 @@ class FusedTPWorkspace:
         if why is not None:
             self._refuse(op, t, why)
         return why is None
+
+    def _reduce_ctas(self, K):
+        """Dedicated reduce CTAs of a GEMM→reduce-scatter launch.  The reduction moves a fixed number of bytes per
+        output tile while the GEMM time per tile grows with K: a short reduction dimension needs more CTAs summing
+        tiles during the main loop, or the whole reduction is left for the tail (about 30000 / K of them keep
+        pace; even, because the CTA-pair kernel hands out whole clusters)."""
+        if self.n_comm_rs_fixed is not None:
+            return self.n_comm_rs_fixed
+        n = int(round(30000.0 / max(K, 1)))
+        return max(4, min(32, n + (n & 1)))
 
     def _pair(self, rows_per_rank, N):
         return self.use_pair and rows_per_rank % 256 == 0 and N >= 256
@@ -228,10 +238,11 @@ class FusedTPWorkspace:
         self.epoch_rs += 1
         lib = cu.lib()
         pair = self._pair(rows, N)
+        n_comm = self._reduce_ctas(K)
         grid = self.grid_pair if pair else self.grid_single
         fn = lib.ell_gemm_rs_pair if pair else lib.ell_gemm_rs
         rc = fn(cu._p(x), cu._p(w), cu._p(y), c_int(rows), c_int(N), c_int(K), c_int(1 if b_mn else 0),
-                c_int(self.rank), c_int(self.tp), _u32(self.epoch_rs), c_int(self.n_comm_rs),
+                c_int(self.rank), c_int(self.tp), _u32(self.epoch_rs), c_int(n_comm),
                 self._arr(self.stage_ptrs), self._arr(self.rs_flags), self._arr(self.red_flags), self._arr(self.rs_done),
                 c_void_p(self.counters.data_ptr() + 8), _u32(self.rs_count), c_int(_MAX_FLAGS), _u32(self.rs_queue),
                 c_int(1 if all_reduce else 0), cu._p(cu.err_flag(x.device)), cu._stream())

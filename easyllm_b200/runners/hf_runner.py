@@ -216,7 +216,9 @@ class HFRunner:
         except StopIteration:
             it = self.data_iterators[kind] = iter(self.data_loaders[kind])
             batch = next(it)
-        batch = {k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()}
+        # the batch stays on the host: the model parses it there (document boundaries, longest document, highest
+        # position) and copies what the kernels need, so no micro-batch waits for a read-back from the GPU
+        batch = dict(batch)
         batch.setdefault("position_ids", None)
         batch.setdefault("cu_seqlens", None)
         return batch

@@ -100,3 +100,32 @@ def test_hf_style_model_kernel_path_matches_library_path():
         for n, p in m.named_parameters():
             g_ref = res["torch"][1][n]
             assert (g_ref - p.main_grad.float()).abs().max().item() / (g_ref.abs().max().item() + 1e-6) < 8e-2, (fam, n)
+
+
+def test_train_batch_refuses_a_step_after_a_kernel_gave_up_a_wait():
+    """A fused kernel whose bounded wait expired writes the error word and leaves a partial result: the engine
+    must raise before the optimizer update instead of training on it.  The word is set by hand here (no wait runs
+    out, no kernel misbehaves)."""
+    _need_gpu()
+    from easyllm_b200.engine import PipelineEngine
+    from easyllm_b200.models import llama_custom
+    from easyllm_b200.optim import ZeroOptimizer
+    from easyllm_b200.data.synthetic import synthetic_batches
+    import easyllm_b200.ops.cuda as cu
+    torch.manual_seed(0)
+    m = llama_custom(num_layers=1, hidden_size=256, num_attention_heads=2, num_kv_attention_heads=2,
+                     intermediate_size=512, vocab_size=1024, bf16=True, seq_length=128, checkpoint_activations=False)
+    opt = ZeroOptimizer(m.named_parameters(), lr=1e-3, stage=1)
+    eng = PipelineEngine(m, opt, None, {"train_micro_batch_size_per_gpu": 1, "gradient_accumulation_steps": 2,
+                                        "bf16": {"enabled": True}})
+    it = synthetic_batches(1024, 128, 1, seed=0)
+    eng.train_batch(it)                                   # a clean step passes
+    before = [p.detach().clone() for p in m.parameters()]
+    cu.err_flag().fill_(5)                                # what a timed-out peer-flag wait would have written
+    with pytest.raises(cu.KernelError):
+        eng.train_batch(it)
+    for p, q in zip(m.parameters(), before):              # the update was not applied
+        assert torch.equal(p.detach(), q)
+    opt.zero_grad()
+    eng.train_batch(it)                                   # the word was cleared by the read: training goes on
+    cu.check_err_flag()
