@@ -224,6 +224,14 @@ def column_sum(x):
     return x.float().sum(0)
 
 
+def matmul_tn(a, b):
+    """aᵀ [K,M]ᵀ·b [K,N] → [M,N] in the operands' dtype: a weight gradient handed to autograd (no fp32 ``main_grad``
+    to accumulate into), rounded once in the GEMM epilogue."""
+    if _gemm_ok("matmul_tn", a, a.shape[-1], b.shape[-1]):
+        return _cu().gemm(a, b, a_mn=True, b_mn=True, out_mode=0)
+    return a.t() @ b
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias):
@@ -242,7 +250,7 @@ class _Linear(torch.autograd.Function):
             if mg is not None:
                 matmul_tn_accum(dy, x, mg)
             else:
-                dw = matmul_tn_accum(dy, x).to(w.dtype)
+                dw = matmul_tn(dy, x)
         db = None
         if ctx.bref is not None and ctx.needs_input_grad[2]:
             db = _grad_to(ctx.bref, column_sum(dy))
@@ -306,7 +314,7 @@ class _LinearParts(torch.autograd.Function):
                     matmul_tn_accum(dy[:, r0:r0 + w.shape[0]].contiguous(), x, m)
                     r0 += w.shape[0]
             return (dx, db) + (None,) * len(ws)
-        dW = matmul_tn_accum(dy, x).to(W.dtype)
+        dW = matmul_tn(dy, x)
         return (dx, db) + tuple(dW.split([w.shape[0] for w in ws], 0))
 
 
@@ -616,7 +624,7 @@ class _LMHeadCE(torch.autograd.Function):
             if mg is not None:
                 matmul_tn_accum(dlogits, hidden, mg)
             else:
-                dw = matmul_tn_accum(dlogits, hidden).to(weight.dtype)
+                dw = matmul_tn(dlogits, hidden)
         return dx, dw, None, None
 
 
@@ -649,19 +657,20 @@ class _LMHeadCESP(torch.autograd.Function):
         ws = _tp_workspace()
         dlogits = _cu().ce_bwd_(logits, tflat, lse, g.reshape(-1).float().contiguous(), start, valid)
         dx = None
+        mg = getattr(ctx.wref, "main_grad", None)
         if ctx.needs_input_grad[0]:
-            dx = ws.gemm_rs(dlogits, weight, b_mn=True)
+            can_push = mg is not None and ctx.needs_input_grad[1] and ws.agk_accepts(dlogits, x_local, mg)
+            dx = ws.gemm_rs(dlogits, weight, b_mn=True, push=x_local if can_push else None)
             if dx is None:
                 dx = mp.reduce_scatter_first_dim(matmul_nn(dlogits, weight))
         dw = None
         if ctx.needs_input_grad[1]:
-            mg = getattr(ctx.wref, "main_grad", None)
             if mg is None or ws.agk_wgrad(dlogits, x_local, mg) is None:
                 xg = mp.gather_first_dim(x_local)
                 if mg is not None:
                     matmul_tn_accum(dlogits, xg, mg)
                 else:
-                    dw = matmul_tn_accum(dlogits, xg).to(weight.dtype)
+                    dw = matmul_tn(dlogits, xg)
         return dx, dw, None, None
 
 

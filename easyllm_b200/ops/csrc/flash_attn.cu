@@ -16,6 +16,8 @@
 // the other's arithmetic, and each K/V tile fetched serves 256 queries.
 // Documents: row_start[t] is the first token of the document that token t belongs to; key j is
 // visible to query i iff row_start[i] <= j <= i, so tiles may straddle document boundaries.
+// ALiBi: with per-head slopes the score of (query i, key j) gets the bias slope_h * (j - i) before the softmax
+// (llm/models/hf_models/baichuan2/model_13b/modeling_baichuan.py:63-73 builds the same bias as a mask tensor).
 //
 // Replaces flash_attn_varlen_{qkv,kv}packed_func of the reference
 // (llm/models/mg_models/llama/transformer.py:65-143).
@@ -70,7 +72,7 @@ __global__ void __launch_bounds__(kFaThreads, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
                  float* __restrict__ lse, const int* __restrict__ row_start, int T, int Hq, int Hk,
-                 float scale_log2, int* __restrict__ err) {
+                 float scale_log2, const float* __restrict__ alibi_slopes, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;                          // 2 query tiles
@@ -228,6 +230,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint8_t* p_row = sP + t * kFaTileBytes + r * 128;
     const int sw = r & 7;
     float m_used = -1e30f, l = 0.f;
+    // ALiBi bias in units of the raw score: (slope / scale) * (key - query), so that score * scale_log2 carries it
+    const float alibi_s = alibi_slopes != nullptr ? alibi_slopes[h] * 1.4426950408889634f / scale_log2 : 0.f;
     bool ok = true;
     auto fail = [&]() {
       ok = false;
@@ -257,6 +261,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const int kidx = k0 + i;
           if (kidx > row || kidx < my_start) s[i] = 0xff800000u;   // -inf
         }
+      }
+      if (alibi_slopes != nullptr) {
+        const float d0 = (float)(k0 - row);
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          s[i] = __float_as_uint(fmaf(alibi_s, d0 + (float)i, __uint_as_float(s[i])));   // -inf stays -inf
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
@@ -392,9 +402,10 @@ ELL_API int ell_flash_fwd_plan(const int* row_start, int T, int* out) {
 // q [T, Hq, 128] / k, v [T, Hk, 128] bf16 with row strides (in elements) q_stride / kv_stride (views
 // into the packed QKV GEMM output are fine); out [T, Hq, 128] contiguous; lse [Hq, T] fp32;
 // row_start [T] int32 (document start of every token).  Causal.
+// alibi_slopes: fp32 [Hq] or null.
 ELL_API int ell_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* row_start,
-                               int T, int Hq, int Hk, int q_stride, int kv_stride, float scale, int* err,
-                               cudaStream_t stream) {
+                               int T, int Hq, int Hk, int q_stride, int kv_stride, float scale,
+                               const float* alibi_slopes, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (Hq % Hk) return -2;
   CUtensorMap tq, tk, tv;
@@ -412,6 +423,6 @@ ELL_API int ell_flash_attn_fwd(const void* q, const void* k, const void* v, void
   }
   dim3 grid((T + 2 * kFaM - 1) / (2 * kFaM), Hq);
   flash_fwd_kernel<<<grid, kFaThreads, kFaSmemBytes, stream>>>(tq, tk, tv, (__nv_bfloat16*)out, lse, row_start, T, Hq,
-                                                               Hk, scale * 1.4426950408889634f, err);
+                                                               Hk, scale * 1.4426950408889634f, alibi_slopes, err);
   return launch_status();
 }

@@ -76,7 +76,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                  const float* __restrict__ delta, const int* __restrict__ row_start,
                  __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, int dkv_stride,
                  float* __restrict__ dkv_acc, int nsplit, int T, int Hq, int Hk, float scale,
-                 int* __restrict__ err) {
+                 const float* __restrict__ alibi_slopes, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
@@ -260,6 +260,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int my_start = row_valid ? row_start[row] : 0x7fffffff;
         const float lse2 = row_valid ? lse[(size_t)h * T + row] * 1.4426950408889634f : 0.f;
         const float dlt = row_valid ? delta[(size_t)h * T + row] : 0.f;
+        // ALiBi: P is recomputed with the forward's bias slope * (key - query) (a constant of q and k: no gradient)
+        const float slope2 = alibi_slopes != nullptr ? alibi_slopes[h] * 1.4426950408889634f : 0.f;
         const bool need_mask = (i == j) || (row_start[min(q0 + kFbTile, T) - 1] > k0) || (q0 + kFbTile > T);
         uint32_t pk[32];                         // P of this thread's 64 columns, packed bf16x2
         if (threadIdx.x == 64) FB_TRACE(1, it, 0);
@@ -276,7 +278,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             float p[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-              p[e] = exp2f(fmaf(__uint_as_float(v[g8 * 8 + e]), scale_log2, -lse2));
+              float off = -lse2;
+              if (alibi_slopes != nullptr) off = fmaf(slope2, (float)(k0 + col_base + c * 32 + g8 * 8 + e - row), -lse2);
+              p[e] = exp2f(fmaf(__uint_as_float(v[g8 * 8 + e]), scale_log2, off));
               if (need_mask) {
                 const int kidx = k0 + col_base + c * 32 + g8 * 8 + e;
                 if (kidx > row || kidx < my_start || !row_valid) p[e] = 0.f;
@@ -460,7 +464,7 @@ ELL_API int ell_flash_bwd_set_trace(long long* buf) {
 ELL_API int ell_flash_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
                                const float* lse, const int* row_start, void* dq, void* dk, void* dv, float* dq_acc,
                                float* delta, float* dkv_acc, int T, int Hq, int Hk, int q_stride, int kv_stride, int dq_stride,
-                               int dkv_stride, float scale, int* err, cudaStream_t stream) {
+                               int dkv_stride, float scale, const float* alibi_slopes, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (Hq % Hk) return -2;
   if ((dq_stride % 8) || (dkv_stride % 8)) return -3;
@@ -501,7 +505,7 @@ ELL_API int ell_flash_attn_bwd(const void* q, const void* k, const void* v, cons
   dim3 grid(Hk * nsplit, n_kt);
   flash_bwd_kernel<<<grid, kFbThreads, kFbSmemBytes, stream>>>(tq, tk, tv, tdo, tdq, lse, delta, row_start,
                                                                (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dkv_stride,
-                                                               dkv_acc, nsplit, T, Hq, Hk, scale, err);
+                                                               dkv_acc, nsplit, T, Hq, Hk, scale, alibi_slopes, err);
   if (nsplit > 1) {
     const int Wk = Hk * kFbD;
     const size_t n = (size_t)T * (Wk / 8);

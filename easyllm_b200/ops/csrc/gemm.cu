@@ -129,7 +129,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_units = num_tiles + n_split;
 
   if (FUSE != kFuseNone && (int)blockIdx.x < n_comm) {
-    if (FUSE == kFuseAG) ag_comm_role(fuse, K, err, smem);
+    if (FUSE == kFuseAG) ag_comm_role(fuse, K, err, smem, 0, n_comm);
     else rs_reduce_role<BN>(fuse, N, tiles_n, err, smem, (int)gridDim.x, false, FUSE == kFuseAR);
     return;
   }

@@ -64,6 +64,8 @@ struct FuseArgs {
   long long ce_vocab_start;
   int ce_valid;
   int no_tail_split;                     // 1 disables the half-width units of an under-filled last wave
+  int shard_k;                           // row length of x_local when this struct describes a bare push (see below)
+  int k_passes;                          // AGK: 2 walks every tile twice (local half of the k-range first), 1 once
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -104,8 +106,11 @@ struct CommShared {
 };
 
 // All-gather side: copy the local shard, tile by tile, into the gathered buffer of every other rank.
-// (The local GEMM reads its own shard in place; nothing is copied to self.)  `K` is the row length of the shard.
-__device__ inline void ag_comm_role(const FuseArgs& f, int K, int* err, uint8_t* smem) {
+// (The local GEMM reads its own shard in place; nothing is copied to self.)  `K` is the row length of the shard;
+// CTAs [first_cta, first_cta + n_ctas) of the grid share the work.
+// A reduce-scatter launch can carry such a push for the NEXT kernel on the stream (the weight-gradient GEMM that
+// follows a dgrad -> reduce-scatter needs the gathered x): its transfer then hides behind this kernel's main loop.
+__device__ inline void ag_comm_role(const FuseArgs& f, int K, int* err, uint8_t* smem, int first_cta, int n_ctas) {
   CommShared* cs = reinterpret_cast<CommShared*>(smem + kCommStages * kCommChunkBytes);
   if (threadIdx.x != 0) return;
   for (int s = 0; s < kCommStages; ++s) mbar_init(&cs->full[s], 1);
@@ -126,7 +131,7 @@ __device__ inline void ag_comm_role(const FuseArgs& f, int K, int* err, uint8_t*
   // and each destination's flag is raised as soon as its copy of the tile has landed.
   const int n_dest = f.tp - 1;
   const int n_items = tiles * n_dest;
-  for (int item = blockIdx.x; item < n_items; item += f.n_comm) {
+  for (int item = (int)blockIdx.x - first_cta; item < n_items; item += n_ctas) {
     const int t = item / n_dest;
     const int dest = (f.rank - 1 - item % n_dest + f.tp) % f.tp;   // the rank that needs this shard soonest first
     const uint8_t* src = reinterpret_cast<const uint8_t*>(f.x_local) + (size_t)t * tile_bytes;
@@ -224,6 +229,10 @@ __device__ inline void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int
     while (ok) {
       const int j = (int)(atomicAdd(f.queue, 1u) - queue_base);
       if (j >= total) break;
+      if (j < 0) {   // the host's copy of the queue ran ahead of the device's: refuse to index with it
+        ok = false;
+        break;
+      }
       if (j < owned) {
         int mi, nt;
         owned_tile_of(j, tpr, tiles_n, f.tp, pair, mi, nt);

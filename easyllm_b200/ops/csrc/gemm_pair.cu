@@ -182,18 +182,26 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmBh,
                  const __grid_constant__ CUtensorMap tmX, const __grid_constant__ FuseArgs fuse,
-                 const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int* __restrict__ err) {
+                 const __grid_constant__ FuseArgs push, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
+                 int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr bool kReduce = (FUSE == kFuseRS || FUSE == kFuseAR);
   constexpr bool kGather = (FUSE == kFuseAG || FUSE == kFuseAGK);
-  const int n_comm = FUSE == kFuseNone ? 0 : fuse.n_comm;
+  const int n_red = FUSE == kFuseNone ? 0 : fuse.n_comm;
+  // reduce forms may carry the all-gather push of the next kernel's operand in CTAs [n_red, n_red + n_push)
+  const int n_push = kReduce ? push.n_comm : 0;
+  const int n_comm = n_red + n_push;                   // CTAs that do not run the GEMM
   const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + kTileN - 1) / kTileN;
 
-  if (FUSE != kFuseNone && (int)blockIdx.x < n_comm) {
+  if (FUSE != kFuseNone && (int)blockIdx.x < n_red) {
     // communication role; both CTAs of such a cluster take it, neither touches TMEM or the cluster barrier
-    if (kGather) ag_comm_role(fuse, FUSE == kFuseAG ? K : N, err, smem);
-    else rs_reduce_role<kTileN>(fuse, N, tiles_n, err, smem, (int)gridDim.x, true, FUSE == kFuseAR);
+    if (kGather) ag_comm_role(fuse, FUSE == kFuseAG ? K : N, err, smem, 0, n_red);
+    else rs_reduce_role<kTileN>(fuse, N, tiles_n, err, smem, (int)gridDim.x - n_push, true, FUSE == kFuseAR);
+    return;
+  }
+  if (kReduce && (int)blockIdx.x < n_comm) {
+    ag_comm_role(push, push.shard_k, err, smem, n_red, n_push);
     return;
   }
 
@@ -206,7 +214,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t cta_rank = cluster_cta_rank();       // 0: leader, 1: peer
   const bool is_leader = cta_rank == 0;
   const int cluster_id = ((int)blockIdx.x - n_comm) >> 1, n_clusters = ((int)gridDim.x - n_comm) >> 1;
-  const int num_tiles = tiles_m * tiles_n * (FUSE == kFuseAGK ? 2 : 1);   // kFuseAGK: two k-passes per tile
+  const int k_passes = FUSE == kFuseAGK ? (fuse.k_passes == 2 ? 2 : 1) : 1;
+  const int num_tiles = tiles_m * tiles_n * k_passes;   // kFuseAGK while the rows still arrive: two k-passes per tile
   const int num_kb = (K + kBK - 1) / kBK;
   const int n_split = split_tail(num_tiles, n_clusters, !kReduce && !fuse.no_tail_split);
   const int num_full = num_tiles - n_split, num_units = num_tiles + n_split;
@@ -274,8 +283,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             fence_proxy_async_all();   // peer writes -> TMA reads (async proxy)
           }
         }
-        const int kb_lo = FUSE == kFuseAGK ? u.kphase * (num_kb / 2) : 0;
-        const int kb_hi = FUSE == kFuseAGK && u.kphase == 0 ? num_kb / 2 : num_kb;
+        const int kb_lo = k_passes == 2 ? u.kphase * (num_kb / 2) : 0;
+        const int kb_hi = k_passes == 2 && u.kphase == 0 ? num_kb / 2 : num_kb;
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
           int kk = kb;                       // k-block actually loaded
           const CUtensorMap* bk_map = &tmB;  // kFuseAGK: map of the B k-block
@@ -364,7 +373,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kTileN;
         int n_kb = num_kb;
-        if (FUSE == kFuseAGK) {
+        if (k_passes == 2) {
           const int kphase = (unit >= num_full ? num_full + ((unit - num_full) >> 1) : unit) / (tiles_m * tiles_n);
           n_kb = kphase == 0 ? num_kb / 2 : num_kb - num_kb / 2;
         }
@@ -589,7 +598,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // the main loop is done: this CTA now helps summing the staged tiles its rank owns (the dedicated CTAs
     // [0, n_comm) have been doing so since launch)
     __syncthreads();
-    rs_reduce_role<kTileN>(fuse, N, tiles_n, err, smem, (int)gridDim.x, true, FUSE == kFuseAR);
+    rs_reduce_role<kTileN>(fuse, N, tiles_n, err, smem, (int)gridDim.x - n_push, true, FUSE == kFuseAR);
   }
   if (kGather && threadIdx.x == 0) {
     // last GEMM CTA of this rank: tell every peer that its pushes of this epoch were consumed
@@ -638,7 +647,7 @@ static int max_clusters(const void* kern) {
 template <bool A_MN, bool B_MN, int OUT, bool HAS_BIAS, int FUSE = kFuseNone>
 static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, const CUtensorMap& tBh,
                   const CUtensorMap& tX, const FuseArgs& fuse, const __nv_bfloat16* bias, int M, int N, int K, int* err,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const FuseArgs* push = nullptr) {
   auto kern = gemm_pair_kernel<A_MN, B_MN, OUT, HAS_BIAS, FUSE>;
   static bool configured = false;
   if (!configured) {
@@ -653,9 +662,12 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   if (FUSE == kFuseNone) {
     grid = 2 * launch_clusters(tiles, resident);
   } else {
-    if ((fuse.n_comm & 1) || fuse.n_comm >= 2 * resident) return -2;
+    const int n_role = fuse.n_comm + (push ? push->n_comm : 0);
+    if ((fuse.n_comm & 1) || (n_role & 1) || n_role >= 2 * resident) return -2;
     grid = 2 * resident;
   }
+  FuseArgs no_push{};
+  const FuseArgs& push_args = push ? *push : no_push;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
@@ -668,7 +680,7 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tA, tB, tC, tBh, tX, fuse, bias, M, N, K, err);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tA, tB, tC, tBh, tX, fuse, push_args, bias, M, N, K, err);
   if (e != cudaSuccess) {
     cudaGetLastError();   // a refused launch is reported to the caller, not left behind for the next launch
     return (int)e;
@@ -898,7 +910,8 @@ ELL_API int ell_gemm_agk_wgrad_pair(const void* dy, const void* x_local, void* d
                                     unsigned int counter_base, int flags_per_src, int* err, cudaStream_t stream) {
   using namespace ell::pair;
   if (tp < 1 || tp > kMaxTp || rows_per_rank % kTileM || rows_per_rank / kBM > flags_per_src) return -2;
-  if (n_comm < 2 || (n_comm & 1) || Nout % 8 || Kin % 8) return -2;
+  // n_comm = 0: the rows were pushed by an earlier launch of this epoch (ell_gemm_rs_pair with a push)
+  if (n_comm < 0 || (n_comm & 1) || Nout % 8 || Kin % 8) return -2;
   const int T = rows_per_rank * tp;
   CUtensorMap tA, tB, tC, tX;
   int rc = make_tmap_bf16_2d(&tA, dy, (uint64_t)Nout, (uint64_t)T, (uint64_t)Nout * 2, 64, kBK);
@@ -913,16 +926,22 @@ ELL_API int ell_gemm_agk_wgrad_pair(const void* dy, const void* x_local, void* d
   fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, gathered_ptrs, flag_ptrs, nullptr, done_ptrs,
             counter, counter_base);
   f.x_local = (const __nv_bfloat16*)x_local;
+  f.k_passes = n_comm > 0 ? 2 : 1;   // rows pushed by this launch arrive during the first pass over the local half
   return launch<true, true, kOutF32Accum, false, kFuseAGK>(tA, tB, tC, tB, tX, f, nullptr, Nout, Kin, T, err, stream);
 }
 
 // GEMM -> reduce-scatter (all_reduce = 0; contract of ell_gemm_rs) or GEMM -> all-reduce (all_reduce = 1: y is the
 // full [tp * rows_per_rank, N] output and red_ptrs[r] rank r's "tile reduced" flags) on CTA pairs.
 // rows_per_rank % 256 == 0, N % 256 == 0, n_comm even.
+// push_x != nullptr: n_push more CTAs copy the shard push_x [push_rows, push_k] into the peers' gathered buffers
+// (gathered_ptrs / ag_flag_ptrs / ag_done_ptrs, epoch push_epoch) for the kernel that follows on the stream
+// (ell_gemm_agk_wgrad_pair with n_comm = 0 and the same epoch).
 ELL_API int ell_gemm_rs_pair(const void* x, const void* W, void* y, int rows_per_rank, int N, int K, int b_mn, int rank,
                              int tp, unsigned int epoch, int n_comm, void* const* stage_ptrs, void* const* flag_ptrs,
                              void* const* red_ptrs, void* const* done_ptrs, void* counter, unsigned int counter_base,
-                             int flags_per_src, unsigned int queue_base, int all_reduce, int* err,
+                             int flags_per_src, unsigned int queue_base, int all_reduce, const void* push_x,
+                             int push_rows, int push_k, unsigned int push_epoch, int n_push,
+                             void* const* gathered_ptrs, void* const* ag_flag_ptrs, void* const* ag_done_ptrs, int* err,
                              cudaStream_t stream) {
   using namespace ell::pair;
   if (tp < 1 || tp > kMaxTp || rows_per_rank % kTileM || N % kTileN) return -2;
@@ -944,10 +963,20 @@ ELL_API int ell_gemm_rs_pair(const void* x, const void* W, void* y, int rows_per
             counter, counter_base);
   f.y_local = (__nv_bfloat16*)y;
   f.queue_base = queue_base;
-  if (all_reduce) {
-    if (b_mn) return launch<false, true, kOutBf16, false, kFuseAR>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream);
-    return launch<false, false, kOutBf16, false, kFuseAR>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream);
+  FuseArgs ps{};
+  const FuseArgs* pp = nullptr;
+  if (push_x != nullptr && n_push > 0) {
+    if ((n_push & 1) || push_rows % kBM || push_rows / kBM > flags_per_src || push_k % 8) return -2;
+    fill_fuse(ps, rank, tp, n_push, push_rows, flags_per_src, push_epoch, gathered_ptrs, ag_flag_ptrs, nullptr,
+              ag_done_ptrs, counter, 0);
+    ps.x_local = (const __nv_bfloat16*)push_x;
+    ps.shard_k = push_k;
+    pp = &ps;
   }
-  if (b_mn) return launch<false, true, kOutBf16, false, kFuseRS>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream);
-  return launch<false, false, kOutBf16, false, kFuseRS>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream);
+  if (all_reduce) {
+    if (b_mn) return launch<false, true, kOutBf16, false, kFuseAR>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream, pp);
+    return launch<false, false, kOutBf16, false, kFuseAR>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream, pp);
+  }
+  if (b_mn) return launch<false, true, kOutBf16, false, kFuseRS>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream, pp);
+  return launch<false, false, kOutBf16, false, kFuseRS>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream, pp);
 }

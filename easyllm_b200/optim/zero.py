@@ -10,6 +10,13 @@ llm/runners/base_llm_runner.py:194-213) re-designed around three flat buffers:
   wgrad GEMM / norm kernels accumulate into directly across micro-batches.
 * ``master / m / v`` — fp32, only this DP rank's shard when ``stage >= 1``.
 
+Stage 2 partitions the gradients as well (DeepSpeed ZeRO-2 with ``overlap_comm``, ``reduce_scatter``,
+``contiguous_gradients``: configs/huggingface/template.yaml:13-21, scripts/ds_zero2_no_offload.json:11-19 of the
+reference): there is no full ``grad_buf``.  Parameter gradients arrive through autograd hooks in the compute
+dtype, are packed into a bucket (a few hundred MB, taken from a small pool), and a full bucket is reduced to the
+owners of its ranges on a side stream while backward carries on; the owner adds its part into ``grad_acc``, its
+fp32 shard, which is all that survives a micro-batch.  bf16 on the wire, fp32 accumulation over micro-batches.
+
 One step = [TP all-reduce of sequence-parallel replicated grads] → DP reduce-scatter
 (stage ≥ 1) or all-reduce (stage 0) of ``grad_buf`` → squared-norm partials → one world
 all-reduce → clip coefficient kept on the device → fused Adam over the shard (writes the
@@ -64,13 +71,21 @@ class DynamicLossScaler:
         self.cur_scale, self._good, self._hyst = s["cur_scale"], s["good"], s["hyst"]
 
 
+class _NullCtx:
+    def __enter__(self): return self
+    def __exit__(self, *a): return False
+
+
 class ZeroOptimizer:
     def __init__(self, named_params: Iterable, lr=1e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
                  adamw=True, stage=1, grad_clip=0.0, fp16=False, bias_correction=True, loss_scale_cfg=None,
-                 nan_policy="count"):
+                 nan_policy="count", bucket_numel=1 << 27, max_buckets_in_flight=3):
         g = get_grid()
         self.grid = g
         self.stage = stage
+        # ZeRO-2: gradients are partitioned too (only with a DP group to partition over)
+        self.partitioned = stage >= 2 and g.dp > 1
+        self.bucket_numel, self.max_buckets_in_flight = int(bucket_numel), int(max_buckets_in_flight)
         self.dp, self.dp_rank, self.dp_group = g.dp, g.dp_rank, g.dp_group
         self.defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
         self.param_groups = [dict(self.defaults, name="all")]   # lr schedulers poke param_groups[i]['lr']
@@ -124,12 +139,16 @@ class ZeroOptimizer:
             self._alloc_symmetric()
         if self.param_buf is None:
             self.param_buf = torch.zeros(self.total, dtype=self.dtype, device=self.device)
+        if self.grad_buf is None and not self.partitioned:
             self.grad_buf = torch.zeros(self.total, dtype=torch.float32, device=self.device)
         for p, o in zip(self.params, self.offsets):
             view = self.param_buf[o:o + p.numel()].view_as(p)
             view.copy_(p.data)
             p.data = view
-            p.main_grad = self.grad_buf[o:o + p.numel()].view_as(p)
+            if not self.partitioned:
+                p.main_grad = self.grad_buf[o:o + p.numel()].view_as(p)
+        if self.partitioned:
+            self._init_partitioned_grads()
         self.master = self.param_buf[self.shard_lo:self.shard_hi].to(torch.float32, copy=True)
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
@@ -151,14 +170,18 @@ class ZeroOptimizer:
                 symm_mem.enable_symm_mem_for_group(name)
             except Exception:
                 pass
-            gbuf = symm_mem.empty(self.total, dtype=torch.float32, device=self.device)
+            # ZeRO-2 keeps no full gradient buffer: only the parameter all-gather runs over symmetric memory
+            gbuf = None if self.partitioned else symm_mem.empty(self.total, dtype=torch.float32, device=self.device)
             pbuf = symm_mem.empty(self.total, dtype=self.dtype, device=self.device)
-            gbuf.zero_(); pbuf.zero_()
-            gh = symm_mem.rendezvous(gbuf, group=name)
+            pbuf.zero_()
+            gh = None
+            if gbuf is not None:
+                gbuf.zero_()
+                gh = symm_mem.rendezvous(gbuf, group=name)
             ph = symm_mem.rendezvous(pbuf, group=name)
             torch.cuda.synchronize()
             dist.barrier(group=self.dp_group)
-            self._grad_ptrs = [int(x) for x in gh.buffer_ptrs]
+            self._grad_ptrs = [int(x) for x in gh.buffer_ptrs] if gh is not None else None
             self._param_ptrs = [int(x) for x in ph.buffer_ptrs]
             self._symm_handles = (gh, ph)
             self.grad_buf, self.param_buf = gbuf, pbuf
@@ -166,8 +189,9 @@ class ZeroOptimizer:
             self._dp_token = torch.zeros(1, dtype=torch.float32, device=self.device)
             self._have_sumsq2 = False
             self.fused = True
-            logger.info(f"ZeRO-{self.stage}: fused reduce-scatter / Adam+all-gather kernels over {self.dp} ranks "
-                        f"({self.total * 6 / 2**30:.1f} GiB symmetric memory)")
+            logger.info(f"ZeRO-{self.stage}: fused " + ("" if self.partitioned else "reduce-scatter / ")
+                        + f"Adam+all-gather kernels over {self.dp} ranks "
+                        f"({self.total * (2 if self.partitioned else 6) / 2**30:.1f} GiB symmetric memory)")
         except Exception as e:   # no symmetric memory on this system: NCCL collectives instead
             logger.warning(f"ZeRO fused path unavailable ({type(e).__name__}: {e}); using NCCL collectives")
             self.fused = False
@@ -183,8 +207,135 @@ class ZeroOptimizer:
     def cur_scale(self):
         return self.scaler.cur_scale if self.scaler else 1.0
 
+    # ---- ZeRO-2: bucketed, overlapped reduction of partitioned gradients ------------------------------------
+    def _init_partitioned_grads(self):
+        """Buckets over the flat index space (whole parameters, at least ``bucket_numel`` elements each), the
+        ranges of every bucket each DP rank owns, and an autograd hook per parameter."""
+        self.grad_acc = torch.zeros(self.shard_size, dtype=torch.float32, device=self.device)
+        self._buckets = []
+        cur = None
+        for i, (p, o) in enumerate(zip(self.params, self.offsets)):
+            if cur is None:
+                cur = {"lo": o, "params": [], "hi": o}
+            cur["params"].append(i)
+            cur["hi"] = o + (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
+            if cur["hi"] - cur["lo"] >= self.bucket_numel:
+                self._buckets.append(cur)
+                cur = None
+        if cur is not None:
+            self._buckets.append(cur)
+        self._bucket_of = {}
+        for bi, b in enumerate(self._buckets):
+            b["segments"] = []
+            for r in range(self.dp):
+                lo, hi = max(b["lo"], r * self.shard_size), min(b["hi"], (r + 1) * self.shard_size)
+                if hi > lo:
+                    b["segments"].append((r, lo, hi))
+            # gradients of TP-replicated parameters under sequence parallelism are summed over TP first
+            b["tp_range"] = (max(b["lo"], self.start_sp), min(b["hi"], self.used))
+            b.update(buf=None, got=set(), fired=False)
+            for i in b["params"]:
+                self._bucket_of[id(self.params[i])] = (bi, i)
+        self._bucket_cap = max(b["hi"] - b["lo"] for b in self._buckets)
+        self._free_bufs, self._inflight = [], []
+        self._n_bufs = 0
+        self._dp_ranks = dist.get_process_group_ranks(self.dp_group) if dist.is_initialized() else [0]
+        self._comm_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
+        self._hooks = [p.register_post_accumulate_grad_hook(self._grad_hook) for p in self.params]
+        logger.info(f"ZeRO-2: gradients partitioned over {self.dp} ranks, {len(self._buckets)} buckets of up to "
+                    f"{self._bucket_cap * self.param_buf.element_size() / 2**20:.0f} MiB")
+
+    def _acquire_bucket_buffer(self):
+        if self._free_bufs:
+            return self._free_bufs.pop()
+        if self._n_bufs >= self.max_buckets_in_flight and self._inflight:
+            buf, done = self._inflight.pop(0)          # the oldest reduction: the compute stream waits for it
+            if done is not None:
+                torch.cuda.current_stream().wait_event(done)
+            return buf
+        self._n_bufs += 1
+        return torch.empty(self._bucket_cap, dtype=self.dtype, device=self.device)
+
+    def _grad_hook(self, p):
+        """Runs inside backward as soon as ``p.grad`` is final for this micro-batch: pack it into its bucket,
+        free it, and reduce the bucket once every one of its parameters has arrived."""
+        bi, i = self._bucket_of[id(p)]
+        b = self._buckets[bi]
+        if b["fired"]:
+            raise RuntimeError(f"gradient of {self.names[i]} arrived after its bucket was reduced; a parameter "
+                               "that receives gradients twice per backward needs ZeRO stage <= 1")
+        if b["buf"] is None:
+            b["buf"] = self._acquire_bucket_buffer()
+        o = self.offsets[i] - b["lo"]
+        view = b["buf"][o:o + p.numel()].view_as(p)
+        if i in b["got"]:
+            view.add_(p.grad)
+        else:
+            view.copy_(p.grad)
+            b["got"].add(i)
+        p.grad = None
+        if len(b["got"]) == len(b["params"]):
+            self._reduce_bucket(b)
+
+    def _reduce_bucket(self, b):
+        """Reduce every range of the bucket to the rank that owns it (its part of the ZeRO shard) and let the owner
+        add it into ``grad_acc``; on a GPU this runs on a side stream, overlapped with the rest of backward."""
+        b["fired"] = True
+        if b["buf"] is None:
+            b["buf"] = self._acquire_bucket_buffer()
+        buf = b["buf"]
+        for i in b["params"]:                          # parameters without a gradient this time count as zero
+            if i not in b["got"]:
+                o = self.offsets[i] - b["lo"]
+                buf[o:o + self.params[i].numel()].zero_()
+        g = self.grid
+        tlo, thi = b["tp_range"]
+        if g.tp > 1 and thi > tlo:
+            dist.all_reduce(buf[tlo - b["lo"]:thi - b["lo"]], group=g.tp_group)
+        cuda = self._comm_stream is not None
+        if cuda:
+            ready = torch.cuda.Event()
+            ready.record()
+            self._comm_stream.wait_event(ready)
+        ctx = torch.cuda.stream(self._comm_stream) if cuda else _NullCtx()
+        with ctx:
+            for owner, lo, hi in b["segments"]:
+                seg = buf[lo - b["lo"]:hi - b["lo"]]
+                dist.reduce(seg, dst=self._dp_ranks[owner], group=self.dp_group)
+                if owner == self.dp_rank:
+                    dst = self.grad_acc[lo - self.shard_lo:hi - self.shard_lo]
+                    if cuda and seg.dtype == torch.bfloat16 and ops.get_backend() == "b200":
+                        from ..ops import cuda as cu
+                        cu.accum_bf16_to_f32(seg, dst)
+                    else:
+                        dst.add_(seg.float())
+            done = None
+            if cuda:
+                done = torch.cuda.Event()
+                done.record(self._comm_stream)
+        self._inflight.append((buf, done))
+        b["buf"] = None
+
+    def _flush_buckets(self):
+        """End of a micro-batch's backward: reduce what the hooks have not (the same sequence of collectives on
+        every rank, whatever gradients were produced), then make the compute stream wait for the reductions."""
+        for b in self._buckets:
+            if not b["fired"]:
+                self._reduce_bucket(b)
+        for buf, done in self._inflight:
+            if done is not None:
+                torch.cuda.current_stream().wait_event(done)
+            self._free_bufs.append(buf)
+        self._inflight = []
+        for b in self._buckets:
+            b.update(buf=None, got=set(), fired=False)
+
     def accumulate_grads(self):
-        """Fold autograd ``.grad`` tensors (reference / CPU path) into ``main_grad``."""
+        """Fold autograd ``.grad`` tensors (reference / CPU path) into ``main_grad``; with partitioned gradients
+        (ZeRO-2) finish this micro-batch's bucket reductions instead."""
+        if self.partitioned:
+            self._flush_buckets()
+            return
         for p in self.params:
             if p.grad is not None:
                 if p.grad.is_cuda and p.grad.dtype == torch.bfloat16 and ops.get_backend() == "b200" \
@@ -196,7 +347,7 @@ class ZeroOptimizer:
                 p.grad = None
 
     def zero_grad(self):
-        self.grad_buf.zero_()
+        (self.grad_acc if self.partitioned else self.grad_buf).zero_()
         for p in self.params:
             p.grad = None
 
@@ -207,13 +358,17 @@ class ZeroOptimizer:
         return ops.sumsq(self._grad_shard()[lo - self.shard_lo:hi - self.shard_lo])
 
     def _grad_shard(self):
+        if self.partitioned:
+            return self.grad_acc
         return self.grad_buf[self.shard_lo:self.shard_hi]
 
     def reduce_gradients(self):
         g = self.grid
+        if self.partitioned:
+            return                                    # reduced bucket by bucket during the backward passes
         if g.tp > 1 and self.start_sp < self.used:
             dist.all_reduce(self.grad_buf[self.start_sp:self.used], group=g.tp_group)
-        if self.fused:
+        if self.fused and not self.partitioned:
             from ctypes import c_int, c_longlong, c_void_p
             from ..ops import cuda as cu
             self._dp_fence()                      # every rank's backward (and TP reduce) is complete
@@ -251,9 +406,13 @@ class ZeroOptimizer:
                 dist.all_reduce(sq)                       # dp shards × tp × pp
             elif g.mp_group is not None and g.tp * g.pp > 1:
                 dist.all_reduce(sq, group=g.mp_group)
-        norm = sq.sqrt() / self.cur_scale
+        # ZeRO-2 accumulates the SUM over the DP ranks; the mean's 1/dp is folded in here and into the update
+        norm = sq.sqrt() / (self.cur_scale * self._dp_sum_factor())
         self._global_grad_norm = norm
         return norm
+
+    def _dp_sum_factor(self):
+        return float(self.dp) if self.partitioned else 1.0
 
     def get_global_grad_norm(self):
         return None if self._global_grad_norm is None else float(self._global_grad_norm)
@@ -281,7 +440,9 @@ class ZeroOptimizer:
         self.step_count += 1
         pg = self.param_groups[0]
         lr, betas, eps, wd = pg["lr"], pg["betas"], pg["eps"], pg["weight_decay"]
-        inv_scale = 1.0 / self.cur_scale
+        inv_scale = 1.0 / (self.cur_scale * self._dp_sum_factor())
+        if self.fused and self.partitioned:
+            self._dp_fence()                      # every rank is done with the old parameters
         # weight decay applies to [0, start_shard_nd) ∪ [start_rep, start_rep_nd)
         cuts = [0, self.start_shard_nd, self.start_rep, self.start_rep_nd, self.total]
         wds = [wd, 0.0, wd, 0.0]

@@ -83,6 +83,7 @@ class FusedTPWorkspace:
         self.ce_bufs = [b + off_flags + 4 * set_bytes for b in base]
         self.counters = torch.zeros(4, dtype=torch.int32, device=dev)   # [ag cta count, -, rs cta count, rs queue]
         self.epoch_ag = self.epoch_rs = self.epoch_ce = 0
+        self._pushed = None                                     # (ptr, rows, K, epoch) of a push awaiting its consumer
         self.ag_count = self.rs_count = self.rs_queue = 0       # host copies of the device counters
         self._arr = lambda ptrs: (c_void_p * len(ptrs))(*ptrs)
         from ..ops import cuda as cu
@@ -187,9 +188,20 @@ class FusedTPWorkspace:
         self._last_ag = (x_local, rows, K, self._gathered_off[self.epoch_ag & 1])
         return logits, parts
 
+    def agk_accepts(self, dy, x_local, dw32):
+        """Whether ``agk_wgrad`` takes these operands (asked before a push is attached to the preceding launch: a
+        pushed epoch must be consumed)."""
+        rows, K = x_local.shape
+        T, N = dy.shape
+        return (rows % 128 == 0 and rows * self.tp <= self.max_tokens and K <= self.hidden and K % 8 == 0
+                and self._pair(rows, N) and T == rows * self.tp and N % 8 == 0 and K >= 256 and dw32 is not None
+                and dw32.dtype == torch.float32 and dw32.is_contiguous() and tuple(dw32.shape) == (N, K)
+                and x_local.is_contiguous())
+
     def agk_wgrad(self, dy, x_local, dw32):
         """``dw32 [N, K] += dyᵀ · gather(x_local)`` in one kernel (the gather runs along the reduction rows).
-        Returns True, or None when the shape is unsupported."""
+        When the preceding ``gemm_rs(..., push=x_local)`` already carried the push of ``x_local``, this launch only
+        consumes the flagged rows.  Returns True, or None when the shape is unsupported."""
         from ..ops import cuda as cu
         rows, K = x_local.shape
         T, N = dy.shape
@@ -200,11 +212,18 @@ class FusedTPWorkspace:
             return self._refuse("agk_wgrad", x_local, "needs rows per rank a multiple of 256 and a contiguous fp32 [N, K] gradient")
         x_local = x_local.contiguous()
         dy = dy.contiguous()
-        ptrs = self._ag_args()
+        pushed = self._pushed is not None and self._pushed == (x_local.data_ptr(), rows, K, self.epoch_ag)
+        self._pushed = None
+        n_comm = 0 if pushed else self.n_comm_ag
+        if pushed:      # same epoch and gathered buffer as the push
+            ptrs = (self._arr(self.gathered_ptrs[self.epoch_ag & 1]), self._arr(self.ag_flags), self._arr(self.ag_done),
+                    c_void_p(self.counters.data_ptr()), _u32(self.ag_count), c_int(_MAX_FLAGS))
+        else:
+            ptrs = self._ag_args()
         rc = cu.lib().ell_gemm_agk_wgrad_pair(cu._p(dy), cu._p(x_local), cu._p(dw32), c_int(rows), c_int(N), c_int(K),
                                               c_int(self.rank), c_int(self.tp), _u32(self.epoch_ag),
-                                              c_int(self.n_comm_ag), *ptrs, cu._p(cu.err_flag(dy.device)), cu._stream())
-        self.ag_count += self.grid_pair - self.n_comm_ag
+                                              c_int(n_comm), *ptrs, cu._p(cu.err_flag(dy.device)), cu._stream())
+        self.ag_count += self.grid_pair - n_comm
         cu._check(rc, "gemm_agk_wgrad")
         self._last_ag = (x_local, rows, K, self._gathered_off[self.epoch_ag & 1])
         return True
@@ -217,9 +236,11 @@ class FusedTPWorkspace:
         full[self.rank * rows:(self.rank + 1) * rows].copy_(x_local)
         return full
 
-    def gemm_rs(self, x, w, b_mn=False, all_reduce=False):
+    def gemm_rs(self, x, w, b_mn=False, all_reduce=False, push=None):
         """reduce-scatter over TP of ``x · op(w)``: this rank's ``[T/tp, N]`` rows; with ``all_reduce`` the full
-        ``[T, N]`` sum on every rank.  None when the shape is unsupported."""
+        ``[T, N]`` sum on every rank.  None when the shape is unsupported.
+        ``push``: a sequence shard ``[T/tp, K']`` whose all-gather the NEXT fused call (``agk_wgrad`` on the same
+        tensor) needs: a few more CTAs of this launch copy it to the peers while the main loop runs."""
         from ..ops import cuda as cu
         op = "gemm_ar" if all_reduce else "gemm_rs"
         M, K = x.shape
@@ -240,16 +261,33 @@ class FusedTPWorkspace:
         pair = self._pair(rows, N)
         n_comm = self._reduce_ctas(K)
         grid = self.grid_pair if pair else self.grid_single
-        fn = lib.ell_gemm_rs_pair if pair else lib.ell_gemm_rs
-        rc = fn(cu._p(x), cu._p(w), cu._p(y), c_int(rows), c_int(N), c_int(K), c_int(1 if b_mn else 0),
+        head = (cu._p(x), cu._p(w), cu._p(y), c_int(rows), c_int(N), c_int(K), c_int(1 if b_mn else 0),
                 c_int(self.rank), c_int(self.tp), _u32(self.epoch_rs), c_int(n_comm),
                 self._arr(self.stage_ptrs), self._arr(self.rs_flags), self._arr(self.red_flags), self._arr(self.rs_done),
                 c_void_p(self.counters.data_ptr() + 8), _u32(self.rs_count), c_int(_MAX_FLAGS), _u32(self.rs_queue),
-                c_int(1 if all_reduce else 0), cu._p(cu.err_flag(x.device)), cu._stream())
+                c_int(1 if all_reduce else 0))
+        tail = (cu._p(cu.err_flag(x.device)), cu._stream())
+        n_push = 0
+        self._pushed = None
+        if pair:
+            push_args = (c_void_p(0), c_int(0), c_int(0), c_uint(0), c_int(0), self._arr(self.gathered_ptrs[0]),
+                         self._arr(self.ag_flags), self._arr(self.ag_done))
+            if push is not None and push.dim() == 2 and push.shape[0] == rows and push.shape[1] % 8 == 0 \
+                    and push.shape[1] <= self.hidden and push.is_contiguous() and self.tp > 1:
+                self.epoch_ag += 1
+                n_push = self.n_comm_ag
+                push_args = (cu._p(push), c_int(rows), c_int(push.shape[1]), _u32(self.epoch_ag), c_int(n_push),
+                             self._arr(self.gathered_ptrs[self.epoch_ag & 1]), self._arr(self.ag_flags),
+                             self._arr(self.ag_done))
+                self._pushed = (push.data_ptr(), rows, push.shape[1], self.epoch_ag)
+            rc = lib.ell_gemm_rs_pair(*head, *push_args, *tail)
+        else:
+            rc = lib.ell_gemm_rs(*head, *tail)
         cu._check(rc, op)
-        self.rs_count += grid
+        self.rs_count += grid - n_push
+        # every CTA that runs the reduce role (all but the push CTAs) overshoots the queue by one
         self.rs_queue += lib.ell_gemm_rs_queue_advance(c_int(rows), c_int(N), c_int(self.tp),
-                                                       c_int(1 if all_reduce else 0), c_int(grid))
+                                                       c_int(1 if all_reduce else 0), c_int(grid - n_push))
         return y
 
     def ce_combine(self, parts):
@@ -290,10 +328,13 @@ def install(max_tokens, hidden, allow_single_rank=False):
             return None
         return (y, _WS.gathered() if want_gathered else None)
 
-    def rs(x, w, b_mn=False, all_reduce=False):
-        return _WS.gemm_rs(x, w, b_mn, all_reduce)
+    def rs(x, w, b_mn=False, all_reduce=False, push=None):
+        return _WS.gemm_rs(x, w, b_mn, all_reduce, push)
 
-    tp_linear.set_fused_impl(ag, rs, _WS.agk_wgrad)
+    def agk(dy, x, dw32, dry_run=False):
+        return _WS.agk_accepts(dy, x, dw32) if dry_run else _WS.agk_wgrad(dy, x, dw32)
+
+    tp_linear.set_fused_impl(ag, rs, agk)
     return _WS
 
 

@@ -27,8 +27,8 @@ _FUSED = {"ag_gemm": None, "gemm_rs": None, "agk_wgrad": None}
 
 def set_fused_impl(ag_gemm=None, gemm_rs=None, agk_wgrad=None):
     """Install fused kernels: ``ag_gemm(x_local, w, bias, b_mn=False, want_gathered=False) -> (y, x_gathered)``,
-    ``gemm_rs(x, w, b_mn=False, all_reduce=False) -> y`` and ``agk_wgrad(dy, x_local, dw32) -> True`` (each may
-    return None for an unsupported shape).  ``None`` restores the composition."""
+    ``gemm_rs(x, w, b_mn=False, all_reduce=False, push=None) -> y`` and ``agk_wgrad(dy, x_local, dw32,
+    dry_run=False) -> True`` (each may return None for an unsupported shape; ``dry_run`` only asks).  ``None`` restores the composition."""
     _FUSED["ag_gemm"], _FUSED["gemm_rs"], _FUSED["agk_wgrad"] = ag_gemm, gemm_rs, agk_wgrad
 
 
@@ -62,7 +62,7 @@ def _wgrad(ctx_w, dy, x):
     if mg is not None:
         ops.matmul_tn_accum(dy, x, mg)
         return None
-    return ops.matmul_tn_accum(dy, x).to(ctx_w.dtype)
+    return ops.matmul_tn(dy, x)
 
 
 class _ColumnSP(torch.autograd.Function):
@@ -88,11 +88,13 @@ class _ColumnSP(torch.autograd.Function):
         fused_wg = _FUSED["agk_wgrad"] if _use_fused(dy) else None
         mg = getattr(ctx.wref, "main_grad", None)
         # weight gradient behind the re-gather of x in ONE kernel when it accumulates into the fp32 main_grad
-        wg_fused = fused_wg is not None and mg is not None and ctx.needs_input_grad[1]
+        wg_fused = (fused_wg is not None and mg is not None and ctx.needs_input_grad[1]
+                    and fused_wg(dy, x, mg, dry_run=True))
         ag_work = xg = None
         if ctx.needs_input_grad[1] and not wg_fused:
             xg, ag_work = _ag_start(x, "sp_gather_bwd")      # re-gather ‖ dgrad GEMM
-        dx = fused_rs(dy, w, b_mn=True) if fused_rs is not None else None
+        # the dgrad -> reduce-scatter launch also pushes x to the peers for the weight-gradient kernel behind it
+        dx = (fused_rs(dy, w, b_mn=True, push=x if wg_fused else None)) if fused_rs is not None else None
         rs_work = None
         if dx is None:
             dxg = ops.matmul_nn(dy, w)

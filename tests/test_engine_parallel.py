@@ -31,7 +31,7 @@ def _load_sliced(model, full):
     model.load_state_dict(sd)
 
 
-def _train(rank, world, tp, pp, stage, sp, full, recompute=False):
+def _train(rank, world, tp, pp, stage, sp, full, recompute=False, bucket_numel=1 << 27, clip=0.0, probe=None):
     from easyllm_b200.parallel.grid import initialize_model_parallel
     from easyllm_b200.models import llama_custom
     from easyllm_b200.optim import ZeroOptimizer
@@ -44,11 +44,17 @@ def _train(rank, world, tp, pp, stage, sp, full, recompute=False):
     model = llama_custom(**cfg)
     _load_sliced(model, full)
     opt = ZeroOptimizer(model.named_parameters(), lr=1e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
-                        adamw=False, stage=stage, grad_clip=0.0)
+                        adamw=False, stage=stage, grad_clip=clip, bucket_numel=bucket_numel)
     eng = PipelineEngine(model, opt, None, {"train_micro_batch_size_per_gpu": MBS,
                                             "gradient_accumulation_steps": GBS // (MBS * g.dp)})
     it = synthetic_batches(32000, SEQ, MBS, seed=0)
-    return [float(eng.train_batch(it)) for _ in range(STEPS)]
+    losses = [float(eng.train_batch(it)) for _ in range(STEPS)]
+    if probe == "zero2":
+        return losses, float(eng.get_global_grad_norm()), len(opt._buckets), opt.grad_buf is None, \
+            not any(hasattr(p, "main_grad") for p in model.parameters()), opt._n_bufs
+    if probe == "norm":
+        return losses, float(eng.get_global_grad_norm())
+    return losses
 
 
 def _single(full):
@@ -71,6 +77,29 @@ def test_single_process_loss_is_sane(baseline):
 def test_two_ranks_match_single(baseline, tp, pp, stage, sp):
     full, ref = baseline
     outs = run_ranks(2, _train, tp, pp, stage, sp, full)
+    for losses in outs:
+        assert max(abs(a - b) for a, b in zip(losses, ref)) < 2e-5, (losses, ref)
+
+
+def test_zero2_partitions_gradients_and_reduces_in_buckets(baseline):
+    """ZeRO-2 over two DP ranks: no full gradient buffer and no ``main_grad`` views exist, the gradients travel in
+    several buckets that are reduced from autograd hooks (a pool of at most three buffers), and losses, clipping
+    and the global gradient norm match the single-process run; also with activation recompute."""
+    full, _ = baseline
+    ref_losses, ref_norm = _train(0, 1, 1, 1, 0, False, full, clip=0.3, probe="norm")
+    for recompute in (False, True):
+        outs = run_ranks(2, _train, 1, 1, 2, False, full, recompute, 200_000, 0.3, "zero2")
+        for losses, norm, n_buckets, no_grad_buf, no_main_grad, n_bufs in outs:
+            assert max(abs(a - b) for a, b in zip(losses, ref_losses)) < 2e-5, (losses, ref_losses)
+            assert abs(norm - ref_norm) < 1e-4 * max(1.0, ref_norm)
+            assert n_buckets >= 4 and no_grad_buf and no_main_grad and n_bufs <= 3
+
+
+def test_zero2_with_tensor_and_sequence_parallelism(baseline):
+    """tp2 x dp2, sequence parallel, ZeRO-2: the gradients of TP-replicated norm weights are summed over TP inside
+    their bucket before the DP reduction."""
+    full, ref = baseline
+    outs = run_ranks(4, _train, 2, 1, 2, True, full, False, 200_000)
     for losses in outs:
         assert max(abs(a - b) for a, b in zip(losses, ref)) < 2e-5, (losses, ref)
 

@@ -66,6 +66,11 @@ for it in range(4):                                    # repeated calls exercise
         dw = torch.ones(w_col.shape[0], H, device="cuda")
         assert ws.agk_wgrad(dy, x_local, dw) and ws.agk_wgrad(dy, x_local, dw)
         rel(dw - 1, 2 * (dy.float().t() @ full_x.float()))
+        # the same gather carried by the preceding dgrad -> reduce-scatter launch (its push CTAs), consumed here
+        dw2 = torch.zeros(w_col.shape[0], H, device="cuda")
+        rel(ws.gemm_rs(dy, w_col, b_mn=True, push=x_local), part[g.tp_rank * rows:(g.tp_rank + 1) * rows])
+        assert ws.agk_wgrad(dy, x_local, dw2)
+        rel(dw2, dy.float().t() @ full_x.float())
         # LM head: gather -> GEMM -> cross-entropy statistics, then the cross-rank exchange
         tgt = torch.randint(0, V, (T,), device="cuda")
         dist.broadcast(tgt, 0)

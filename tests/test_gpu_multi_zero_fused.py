@@ -79,3 +79,74 @@ def _run(nproc):
 
 def test_zero_fused_2gpu():
     _run(2)
+
+
+WORKER_Z2 = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["ELL_ROOT"])
+from easyllm_b200.parallel.grid import initialize_distributed, get_grid
+from easyllm_b200.models import llama_custom
+from easyllm_b200.optim import ZeroOptimizer
+from easyllm_b200.engine import PipelineEngine
+from easyllm_b200.data.synthetic import synthetic_batches
+from easyllm_b200 import ops
+import easyllm_b200.ops.cuda as cu
+initialize_distributed(tp=1, pp=1, backend="nccl", launcher="torch", timeout_s=120)
+g = get_grid()
+ops.set_strict(True)
+
+def run(stage):
+    torch.manual_seed(0)
+    model = llama_custom(num_layers=4, hidden_size=1024, num_attention_heads=8, num_kv_attention_heads=8,
+                         intermediate_size=2816, vocab_size=8192, bf16=True, seq_length=512,
+                         checkpoint_activations=False)
+    opt = ZeroOptimizer(model.named_parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1, stage=stage,
+                        grad_clip=1.0, bucket_numel=8 << 20)
+    eng = PipelineEngine(model, opt, None, {"train_micro_batch_size_per_gpu": 1, "gradient_accumulation_steps": 4,
+                                            "bf16": {"enabled": True}})
+    it = synthetic_batches(8192, 512, 1, seed=0, pin=True)
+    torch.cuda.synchronize(); torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    losses = [float(eng.train_batch(it)) for _ in range(4)]
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    peak = torch.cuda.max_memory_allocated()
+    flat = torch.cat([p.detach().float().flatten() for p in model.parameters()])
+    out = (losses, float(eng.get_global_grad_norm()), peak, base, flat, len(getattr(opt, "_buckets", [])),
+           getattr(opt, "_n_bufs", 0))
+    del eng, opt, model
+    torch.cuda.empty_cache()
+    return out
+
+l1, n1, peak1, base1, p1, _, _ = run(1)
+l2, n2, peak2, base2, p2, nb, nbuf = run(2)
+ref = p2.clone(); dist.broadcast(ref, src=0)
+same = bool((p2 == ref).all())
+print(f"RANK{g.rank} zero2 losses={l2} vs zero1={l1} norm {n2:.4f}/{n1:.4f} peak {peak2/2**20:.0f}/{peak1/2**20:.0f} MiB "
+      f"resident {base2/2**20:.0f}/{base1/2**20:.0f} MiB buckets={nb} bufs={nbuf} same={same}", flush=True)
+assert max(abs(a - b) for a, b in zip(l1, l2)) < 3e-2, (l1, l2)       # bf16 gradients on the wire vs fp32
+assert abs(n1 - n2) < 2e-2 * n1
+assert (p1 - p2).abs().max().item() < 2e-2
+assert nb >= 4 and nbuf <= 3 and same
+assert base2 < base1 and peak2 < peak1, "ZeRO-2 must hold less gradient memory than ZeRO-1"
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+def test_zero2_partitioned_gradients_2gpu():
+    """ZeRO-2 on 2 GPUs against ZeRO-1 on the same model and data: same losses / norm / parameters within bf16
+    wire precision, several buckets through a pool of at most three buffers, every rank ends with the same
+    parameters, and both the resident and the peak memory are lower than with ZeRO-1's full fp32 gradient buffer."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.path.join(tempfile.mkdtemp(prefix="ell_zero2_"), "worker.py")
+    with open(path, "w") as f:
+        f.write(WORKER_Z2)
+    env = dict(os.environ, ELL_ROOT=root, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29614", path]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("zero2 losses") == 2
