@@ -181,6 +181,11 @@ def update_model_cfg(cfg) -> ModelArgs:
         v, uv = sh["vocab_size"], sh["unpad_vocab_size"]
         if v is not None and uv is not None and v != uv:
             loss_kwargs["cut_size"] = v - uv
+    if float(tl.get("attention_dropout", 0) or 0) > 0 and tl.get("use_flash_attn", sh["use_flash_attn"]):
+        # the fused attention kernels carry no dropout: refuse the combination here, where the config is expanded,
+        # instead of training without the dropout the config asks for
+        raise ValueError("attention_dropout > 0 needs transformer_layer_params.use_flash_attn: False (the separate "
+                         "scores / softmax / value path applies it); the fused attention kernels have no dropout")
     return ModelArgs(
         num_layers=sh["num_layers"], hidden_size=h, num_attention_heads=nh,
         num_kv_attention_heads=sh["num_kv_attention_heads"], intermediate_size=sh["intermediate_size"],

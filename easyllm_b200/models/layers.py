@@ -189,8 +189,9 @@ class RMSNorm(nn.Module):
 
 
 class LayerNorm(nn.Module):
-    """Affine LayerNorm computed in fp32 (the reference's MixedFusedLayerNorm, unused by the
-    Llama presets)."""
+    """Affine LayerNorm with fp32 statistics and fp32 parameter gradients on the sm_100a kernel
+    (``ops/csrc/layernorm.cu``; the reference's MixedFusedLayerNorm, fused_layer_norm.py:74-140; unused by the
+    Llama presets), optionally fused with the residual add in front of it."""
 
     def __init__(self, normalized_shape, eps=1e-5, sequence_parallel=False, dtype=torch.float32, **_ignored):
         super().__init__()
@@ -202,10 +203,7 @@ class LayerNorm(nn.Module):
         self.bias.sequence_parallel = sp
 
     def forward(self, x, residual=None):
-        if residual is not None:
-            h = x + residual
-            return F.layer_norm(h.float(), h.shape[-1:], self.weight.float(), self.bias.float(), self.eps).to(h.dtype), h
-        return F.layer_norm(x.float(), x.shape[-1:], self.weight.float(), self.bias.float(), self.eps).to(x.dtype)
+        return ops.layernorm(x, self.weight, self.bias, self.eps, residual)
 
 
 def build_layer_norm(args: ModelArgs):
@@ -324,7 +322,11 @@ class ParallelAttention(nn.Module):
             if not self.args.use_flash_attn:
                 # ``use_flash_attn: False``: scores, fp32 masked softmax and the value product as separate ops
                 # (the reference's baddbmm + scale-mask-softmax + bmm path, transformer.py:492-592)
-                o = ref.attention_varlen(q, k, v, meta.get("cu_seqlens"), True, None, slopes).reshape(T, nq)
+                # dropout of the attention probabilities under the model-parallel RNG, as transformer.py:489,556 of
+                # the reference forks the tracker around its attention dropout
+                with get_rng_tracker().fork():
+                    o = ref.attention_varlen(q, k, v, meta.get("cu_seqlens"), True, None, slopes,
+                                             self.args.attention_dropout if self.training else 0.0).reshape(T, nq)
             else:
                 o = ops.flash_attention(q, k, v, meta.get("cu_seqlens"), meta.get("max_seqlen"), causal=True,
                                         alibi_slopes=slopes).reshape(T, nq)

@@ -176,6 +176,55 @@ def add_rmsnorm(x, residual, weight, eps=1e-6):
 
 
 # ---------------------------------------------------------------------------------------------
+# Affine LayerNorm (+ residual add), mixed precision
+# ---------------------------------------------------------------------------------------------
+class _LayerNorm(torch.autograd.Function):
+    """LayerNorm(x (+ residual)) · w + b on the sm_100a kernel; parameter gradients in fp32, straight into
+    ``main_grad`` when the parameters carry one."""
+
+    @staticmethod
+    def forward(ctx, x, residual, w, b, eps):
+        y, h, mean, rstd = _cu().layernorm_fwd(x, residual, w, b, eps)
+        ctx.save_for_backward(h, w, mean, rstd)
+        ctx.refs = (w, b)
+        ctx.has_res = residual is not None
+        if residual is None:
+            return y
+        ctx.mark_non_differentiable()
+        return y, h
+
+    @staticmethod
+    def backward(ctx, dy, dh_in=None):
+        h, w, mean, rstd = ctx.saved_tensors
+        wref, bref = ctx.refs
+        mgw, mgb = getattr(wref, "main_grad", None), getattr(bref, "main_grad", None)
+        direct = mgw is not None and mgb is not None
+        dw = mgw if direct else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        db = mgb if direct else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        dres = dh_in.contiguous() if (ctx.has_res and dh_in is not None) else None
+        dh = _cu().layernorm_bwd(dy.contiguous(), h, w, mean, rstd, dres, dw, db)
+        gw, gb = (None, None) if direct else (dw.to(w.dtype), db.to(w.dtype))
+        return dh, (dh if ctx.has_res else None), gw, gb, None
+
+
+def layernorm(x, weight, bias, eps=1e-5, residual=None):
+    """Affine LayerNorm over the last dim with fp32 statistics.  With ``residual`` returns
+    ``(norm(x + residual), x + residual)``."""
+    if _kern(x):
+        if x.shape[-1] % 8 == 0 and weight.dtype == torch.bfloat16:
+            H = x.shape[-1]
+            x2 = x.reshape(-1, H).contiguous()
+            if residual is None:
+                return _LayerNorm.apply(x2, None, weight, bias, eps).view(x.shape)
+            y, h = _LayerNorm.apply(x2, residual.reshape(-1, H).contiguous(), weight, bias, eps)
+            return y.view(x.shape), h.view(x.shape)
+        note_fallback("layernorm", x, "the row length must be a multiple of 8 and the parameters bf16")
+    h = x if residual is None else x + residual
+    y = F.layer_norm(h.float(), h.shape[-1:], weight.float(), bias.float(), eps).to(h.dtype)
+    return y if residual is None else (y, h)
+
+
+# ---------------------------------------------------------------------------------------------
 # Linear:  y = x · Wᵀ (+ b)
 # ---------------------------------------------------------------------------------------------
 def _gemm_ok(op, a, *dims):
@@ -447,32 +496,40 @@ def _library_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale):
         return flash_attn_varlen_func(q, k, v, cs, cs, max_seqlen, max_seqlen, softmax_scale=scale, causal=causal)
 
 
-def _attn_kernel_reason(dtype, head_dim, alibi_slopes, dropout_p=0.0):
+def _attn_kernel_reason(dtype, head_dim):
     """None when the sm_100a attention kernels take the call, else why not."""
     if _BACKEND != "b200" or _ATTN not in ("auto", "kernel"):
         return "backend"
     if dtype != torch.bfloat16:
         return "dtype"
-    if head_dim != 128:
-        return f"head_dim {head_dim} (the kernels are built for 128)"
-    if alibi_slopes is not None:
-        return "ALiBi bias"
-    if dropout_p:
-        return "attention dropout"
+    if head_dim > 128 or head_dim % 8:
+        return f"head_dim {head_dim} (the kernels take up to 128, in multiples of 8)"
     return None
 
 
+def _pad_heads(t, D):
+    """[T, H, d] → [T, H, D] with zero columns: scores and outputs of the padded columns are exactly zero, so the
+    128-wide kernels serve smaller heads (their tiles are half empty, which only small test models pay)."""
+    return F.pad(t, (0, D - t.shape[-1]))
+
+
 def flash_attention(q, k, v, cu_seqlens=None, max_seqlen=None, causal=True, scale=None, alibi_slopes=None):
-    """Attention over packed documents: q ``[T,Hq,D]``, k/v ``[T,Hk,D]`` → ``[T,Hq,D]``.
+    """Attention over packed documents: q ``[T,Hq,D]``, k/v ``[T,Hk,D]`` → ``[T,Hq,D]``.  ``alibi_slopes``
+    (one per query head) adds ``slope · (key − query)`` to the scores.
     Pass ``max_seqlen`` (a Python int) with ``cu_seqlens``: deriving it here costs a device→host sync."""
+    D = q.shape[-1]
     if scale is None:
-        scale = 1.0 / math.sqrt(q.shape[-1])
+        scale = 1.0 / math.sqrt(D)
     if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16):
         if max_seqlen is None:
             max_seqlen = q.shape[0] if cu_seqlens is None else int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
-        why = _attn_kernel_reason(q.dtype, q.shape[-1], alibi_slopes) or (None if causal else "non-causal")
+        why = _attn_kernel_reason(q.dtype, D) or (None if causal else "non-causal")
         if why is None:
-            return _cu().flash_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+            if D < 128:
+                o = _cu().flash_attention(_pad_heads(q, 128), _pad_heads(k, 128), _pad_heads(v, 128), cu_seqlens,
+                                          max_seqlen, causal, scale, alibi_slopes)
+                return o[..., :D]
+            return _cu().flash_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale, alibi_slopes)
         if _ATTN == "kernel":
             raise RuntimeError(f"attention kernel does not support this call: {why}")
         if why not in ("backend", "dtype"):
@@ -489,12 +546,12 @@ def flash_attention_packed(qkv, n_q_heads, n_kv_heads, head_dim, cu_seqlens=None
     (int32 ``[T]``, the first token of each token's document) may be passed when the caller has it, so it is built
     once per micro-batch and not once per layer.
 
-    On the kernel path the rotation is in place and the backward writes one packed gradient."""
+    On the kernel path (head_dim 128) the rotation is in place and the backward writes one packed gradient."""
     T = qkv.shape[0]
     nq, nk = n_q_heads * head_dim, n_kv_heads * head_dim
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
-    if _kern(qkv) and qkv.dim() == 2 and _attn_kernel_reason(qkv.dtype, head_dim, alibi_slopes) is None:
+    if _kern(qkv) and qkv.dim() == 2 and head_dim == 128 and _attn_kernel_reason(qkv.dtype, head_dim) is None:
         qkv = qkv.contiguous()
         if max_seqlen is None:
             max_seqlen = T if cu_seqlens is None else int((cu_seqlens[1:] - cu_seqlens[:-1]).max())
@@ -502,7 +559,7 @@ def flash_attention_packed(qkv, n_q_heads, n_kv_heads, head_dim, cu_seqlens=None
             cos, sin, pos = rope
             rope = (cos, sin, pos if pos.dtype == torch.int32 else pos.to(torch.int32))
         return _cu().flash_attention_packed(qkv, n_q_heads, n_kv_heads, head_dim, cu_seqlens, max_seqlen, scale, rope,
-                                            row_start)
+                                            row_start, alibi_slopes)
     if rope is not None:
         qkv = rope_packed(qkv, rope[0], rope[1], rope[2], n_q_heads, n_kv_heads, head_dim)
     q = qkv[:, :nq].view(T, n_q_heads, head_dim)

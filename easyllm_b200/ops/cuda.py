@@ -155,6 +155,37 @@ def rmsnorm_bwd(dy, h, w, rstd, dres=None, dw_out=None, accumulate=False):
     return dh, dw
 
 
+def layernorm_fwd(x, residual, w, b, eps):
+    """Affine LayerNorm with fp32 statistics.  Returns (y, h, mean, rstd); h is x (+ residual) or x itself."""
+    _bf16c(x, "x"); _bf16c(w, "weight"); _bf16c(b, "bias")
+    rows, cols = x.shape
+    y = torch.empty_like(x)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    h = torch.empty_like(x) if residual is not None else x
+    if residual is not None:
+        _bf16c(residual, "residual")
+    rc = lib().ell_layernorm_fwd(_p(x), _p(residual), _p(w), _p(b), _p(y), _p(h if residual is not None else None),
+                                 _p(mean), _p(rstd), c_int(rows), c_int(cols), c_float(eps), _stream())
+    _check(rc, "layernorm_fwd")
+    return y, h, mean, rstd
+
+
+def layernorm_bwd(dy, h, w, mean, rstd, dres, dw32, db32):
+    """Returns dh; the fp32 ``dw32`` / ``db32`` ``[cols]`` are accumulated into."""
+    _bf16c(dy, "dy"); _bf16c(h, "h")
+    rows, cols = h.shape
+    dh = torch.empty_like(h)
+    if dres is not None:
+        _bf16c(dres, "dres")
+    rc = lib().ell_layernorm_bwd(_p(dy), _p(h), _p(w), _p(mean), _p(rstd), _p(dres), _p(dh), _p(dw32), _p(db32),
+                                 c_int(rows), c_int(cols), _stream())
+    _check(rc, "layernorm_bwd")
+    global LAUNCHES
+    LAUNCHES += 1  # the parameter-gradient column pass is a second launch
+    return dh
+
+
 # ---- rope / swiglu ----------------------------------------------------------------------------
 def rope_(qkv, cos, sin, pos, n_rot_heads, head_dim, backward=False):
     """In-place rotary embedding on the first ``n_rot_heads`` heads of each row of ``qkv [T, W]``."""
@@ -459,8 +490,18 @@ def row_start_of(cu_seqlens, T, device):
     return _row_start(cu_seqlens, T, device)
 
 
-def flash_attn_fwd(q, k, v, row_start, scale):
-    """q [T,Hq,128], k/v [T,Hk,128] (last two dims contiguous, any row stride) → (out, lse [Hq,T])."""
+def _slopes(alibi_slopes, Hq, device):
+    if alibi_slopes is None:
+        return None
+    sl = alibi_slopes.to(device=device, dtype=torch.float32).contiguous()
+    if sl.numel() != Hq:
+        raise ValueError(f"alibi_slopes must hold one slope per query head ({Hq}), got {sl.numel()}")
+    return sl
+
+
+def flash_attn_fwd(q, k, v, row_start, scale, alibi_slopes=None):
+    """q [T,Hq,128], k/v [T,Hk,128] (last two dims contiguous, any row stride) → (out, lse [Hq,T]).
+    ``alibi_slopes`` fp32 [Hq]: adds ``slope_h · (key − query)`` to the scores."""
     T, Hq, D = q.shape
     Hk = k.shape[1]
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
@@ -470,14 +511,15 @@ def flash_attn_fwd(q, k, v, row_start, scale):
         raise ValueError("flash_attn_fwd: head_dim must be 128 and k/v must share a row stride")
     out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
     lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+    sl = _slopes(alibi_slopes, Hq, q.device)
     rc = lib().ell_flash_attn_fwd(_p(q), _p(k), _p(v), _p(out), _p(lse), _p(row_start), c_int(T), c_int(Hq), c_int(Hk),
-                                  c_int(q.stride(0)), c_int(k.stride(0)), c_float(scale), _p(err_flag(q.device)),
-                                  _stream())
+                                  c_int(q.stride(0)), c_int(k.stride(0)), c_float(scale), _p(sl),
+                                  _p(err_flag(q.device)), _stream())
     _check(rc, "flash_attn_fwd")
     return out, lse
 
 
-def flash_attn_bwd(do, q, k, v, out, lse, row_start, scale, dq=None, dk=None, dv=None):
+def flash_attn_bwd(do, q, k, v, out, lse, row_start, scale, dq=None, dk=None, dv=None, alibi_slopes=None):
     """Gradients of the causal attention.  ``dq/dk/dv`` may be views into one packed ``[T, (Hq+2Hk)·128]``
     buffer (row stride shared by dk and dv); they are allocated (contiguous) when not given."""
     T, Hq, D = q.shape
@@ -498,7 +540,7 @@ def flash_attn_bwd(do, q, k, v, out, lse, row_start, scale, dq=None, dk=None, dv
     rc = lib().ell_flash_attn_bwd(_p(q), _p(k), _p(v), _p(out), _p(do), _p(lse), _p(row_start), _p(dq), _p(dk), _p(dv),
                                   _p(acc), _p(delta), _p(kv_acc), c_int(T), c_int(Hq), c_int(Hk), c_int(q.stride(0)),
                                   c_int(k.stride(0)), c_int(dq.stride(0)), c_int(dk.stride(0)), c_float(scale),
-                                  _p(err_flag(q.device)), _stream())
+                                  _p(_slopes(alibi_slopes, Hq, q.device)), _p(err_flag(q.device)), _stream())
     _check(rc, "flash_attn_bwd")
     global LAUNCHES
     LAUNCHES += 3  # memset, delta and dq-convert launches beside the main kernel
@@ -524,23 +566,24 @@ def _library_bwd(q, k, v, do, cu, has_cu, max_seqlen, scale):
 
 class _FlashAttn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, scale):
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, scale, slopes):
         T = q.shape[0]
         rs = _row_start(cu_seqlens, T, q.device)
-        out, lse = flash_attn_fwd(q, k, v, rs, scale)
+        out, lse = flash_attn_fwd(q, k, v, rs, scale, slopes)
         ctx.save_for_backward(q, k, v, out, lse, rs, cu_seqlens if cu_seqlens is not None else torch.empty(0))
         ctx.meta = (max_seqlen, scale, cu_seqlens is not None)
+        ctx.slopes = slopes
         return out
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, out, lse, rs, cu = ctx.saved_tensors
         max_seqlen, scale, has_cu = ctx.meta
-        if _FA_BWD == "kernel":
-            dq, dk, dv = flash_attn_bwd(do, q, k, v, out, lse, rs, scale)
+        if _FA_BWD == "kernel" or ctx.slopes is not None:
+            dq, dk, dv = flash_attn_bwd(do, q, k, v, out, lse, rs, scale, alibi_slopes=ctx.slopes)
         else:
             dq, dk, dv = _library_bwd(q, k, v, do, cu, has_cu, max_seqlen, scale)
-        return dq, dk, dv, None, None, None
+        return dq, dk, dv, None, None, None, None
 
 
 def _split_packed(qkv, hq, hk, D):
@@ -557,13 +600,14 @@ class _FlashAttnPacked(torch.autograd.Function):
     slice gradients nor a copy for the rotary backward are materialised."""
 
     @staticmethod
-    def forward(ctx, qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, cos, sin, pos, row_start):
+    def forward(ctx, qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, cos, sin, pos, row_start, slopes):
         T = qkv.shape[0]
         rs = row_start if row_start is not None else _row_start(cu_seqlens, T, qkv.device)
         if cos is not None:
             rope_(qkv, cos, sin, pos, hq + hk, D)
         q, k, v = _split_packed(qkv, hq, hk, D)
-        out, lse = flash_attn_fwd(q, k, v, rs, scale)
+        ctx.slopes = slopes
+        out, lse = flash_attn_fwd(q, k, v, rs, scale, slopes)
         none = torch.empty(0)
         ctx.save_for_backward(qkv, out, lse, rs, cu_seqlens if cu_seqlens is not None else none,
                               *((cos, sin, pos) if cos is not None else (none, none, none)))
@@ -579,22 +623,24 @@ class _FlashAttnPacked(torch.autograd.Function):
         dqkv = torch.empty_like(qkv)
         dq, dk, dv = _split_packed(dqkv, hq, hk, D)
         do = do.reshape(T, hq, D)
-        if _FA_BWD == "kernel":
-            flash_attn_bwd(do, q, k, v, out, lse, rs, scale, dq, dk, dv)
+        if _FA_BWD == "kernel" or ctx.slopes is not None:
+            flash_attn_bwd(do, q, k, v, out, lse, rs, scale, dq, dk, dv, alibi_slopes=ctx.slopes)
         else:
             gq, gk, gv = _library_bwd(q, k, v, do, cu, has_cu, max_seqlen, scale)
             dq.copy_(gq); dk.copy_(gk); dv.copy_(gv)
         if has_rope:
             rope_(dqkv, cos, sin, pos, hq + hk, D, backward=True)
-        return (dqkv,) + (None,) * 10
+        return (dqkv,) + (None,) * 11
 
 
-def flash_attention_packed(qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, rope=None, row_start=None):
+def flash_attention_packed(qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, rope=None, row_start=None,
+                           alibi_slopes=None):
     cos, sin, pos = rope if rope is not None else (None, None, None)
-    return _FlashAttnPacked.apply(qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, cos, sin, pos, row_start)
+    return _FlashAttnPacked.apply(qkv, hq, hk, D, cu_seqlens, max_seqlen, scale, cos, sin, pos, row_start,
+                                  alibi_slopes)
 
 
-def flash_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale):
+def flash_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale, alibi_slopes=None):
     if not causal:
         raise ValueError("the attention kernel is causal-only")
-    return _FlashAttn.apply(q, k, v, cu_seqlens, max_seqlen, scale)
+    return _FlashAttn.apply(q, k, v, cu_seqlens, max_seqlen, scale, alibi_slopes)

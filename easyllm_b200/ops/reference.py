@@ -107,9 +107,10 @@ def _segments(cu_seqlens, T):
     return list(zip(cs[:-1], cs[1:]))
 
 
-def attention_varlen(q, k, v, cu_seqlens=None, causal=True, scale=None, alibi_slopes=None):
+def attention_varlen(q, k, v, cu_seqlens=None, causal=True, scale=None, alibi_slopes=None, dropout_p=0.0):
     """Exact attention over packed documents.  q ``[T,Hq,D]``, k/v ``[T,Hk,D]`` (GQA when
-    Hk < Hq: query head h reads kv head ``h // (Hq/Hk)``).  fp32 softmax."""
+    Hk < Hq: query head h reads kv head ``h // (Hq/Hk)``).  fp32 softmax; ``dropout_p`` drops attention
+    probabilities (training only: the caller passes 0 in eval mode)."""
     T, Hq, D = q.shape
     Hk = k.shape[1]
     rep = Hq // Hk
@@ -133,6 +134,8 @@ def attention_varlen(q, k, v, cu_seqlens=None, causal=True, scale=None, alibi_sl
             m = torch.ones(n, n, dtype=torch.bool, device=q.device).tril_()
             s = s.masked_fill(~m, float("-inf"))
         p = torch.softmax(s, dim=-1)
+        if dropout_p:
+            p = torch.nn.functional.dropout(p, dropout_p)
         out[a:b] = torch.matmul(p, vs).transpose(0, 1).to(q.dtype)
     return out
 

@@ -150,3 +150,47 @@ def test_packed_attention_with_rope_matches_reference(cu):
     of.backward(do.float())
     assert (o.float() - of).abs().max().item() < 3e-2
     assert (x.grad.float() - xf.grad).abs().max().item() < 3e-2 * max(1.0, xf.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("T,Hq,Hk,D,cu_list", [(384, 4, 4, 128, None), (640, 8, 2, 128, [0, 130, 300, 640]),
+                                               (300, 4, 4, 64, None), (512, 4, 2, 64, [0, 100, 512]),
+                                               (256, 2, 2, 96, None)])
+@pytest.mark.parametrize("alibi", [False, True])
+def test_attention_kernel_with_alibi_and_small_heads(cu, T, Hq, Hk, D, cu_list, alibi):
+    """ALiBi slopes (the bias slope · (key − query) inside the kernel's softmax, forward and backward) and head
+    dimensions below 128 (zero-padded to the kernel's 128 columns), forced onto the kernel path, against the fp32
+    statement of the same attention; forward output and all three gradients."""
+    from easyllm_b200 import ops
+    from easyllm_b200.models.layers import alibi_slopes
+    from easyllm_b200.ops import reference as ref
+    torch.manual_seed(T + D + Hq)
+    q, k, v = (torch.randn(T, h, D, device="cuda", dtype=torch.bfloat16, requires_grad=True) for h in (Hq, Hk, Hk))
+    cs = torch.tensor(cu_list, dtype=torch.int32, device="cuda") if cu_list else None
+    slopes = torch.tensor(alibi_slopes(Hq), dtype=torch.float32, device="cuda") if alibi else None
+    ops.set_attention_backend("kernel")
+    ops.set_strict(True)
+    try:
+        o = ops.flash_attention(q, k, v, cs, T, True, alibi_slopes=slopes)
+        do = torch.randn_like(o)
+        o.backward(do)
+    finally:
+        ops.set_attention_backend("auto")
+        ops.set_strict(False)
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    of = ref.attention_varlen(qf, kf, vf, cs, True, None, slopes)
+    of.backward(do.float())
+    assert (o.float() - of).abs().max().item() < 2e-2
+    for a, b in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
+        assert (a.float() - b).abs().max().item() < 5e-2 * max(1.0, b.abs().max().item())
+        assert ((a.float() - b).norm() / b.norm()).item() < 2e-2
+
+
+def test_attention_dropout_is_rejected_with_the_fused_kernels_and_applied_on_the_eager_path():
+    from easyllm_b200.models.config import update_model_cfg
+    base = dict(num_layers=1, hidden_size=128, num_attention_heads=2, vocab_size=256, seq_length=32)
+    with pytest.raises(ValueError, match="attention_dropout"):
+        update_model_cfg(dict(base, transformer_layer_params={"attention_dropout": 0.1}))
+    args = update_model_cfg(dict(base, transformer_layer_params={"attention_dropout": 0.1, "use_flash_attn": False}))
+    assert args.attention_dropout == 0.1 and not args.use_flash_attn

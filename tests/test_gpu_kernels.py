@@ -183,3 +183,36 @@ def test_bounded_wait_gives_up_and_reports(cu):
     torch.cuda.synchronize()
     assert int(waited) < 1e8
     cu.check_err_flag()
+
+
+@pytest.mark.parametrize("rows,cols,res", [(64, 512, False), (300, 1024, True), (1000, 4096, True), (17, 8200, False)])
+def test_layernorm_kernel_matches_fp32(cu, rows, cols, res):
+    """Affine LayerNorm forward and backward (input, residual, weight and bias gradients) against F.layer_norm in
+    fp32 on the same bf16 inputs."""
+    from easyllm_b200 import ops
+    torch.manual_seed(rows + cols)
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    x = (torch.randn(rows, cols, **bf) * 2 + 0.5).requires_grad_()
+    r = torch.randn(rows, cols, **bf).requires_grad_() if res else None
+    w = (1 + 0.1 * torch.randn(cols, **bf)).requires_grad_()
+    b = (0.1 * torch.randn(cols, **bf)).requires_grad_()
+    out = ops.layernorm(x, w, b, 1e-5, r)
+    y, h = out if res else (out, None)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    cu.check_err_flag()
+    xf = x.detach().float().requires_grad_(); wf = w.detach().float().requires_grad_(); bf32 = b.detach().float().requires_grad_()
+    rf = r.detach().float().requires_grad_() if res else None
+    hf = (xf + rf).to(torch.bfloat16).float() if res else xf      # the kernel stores the sum in bf16 and normalises that
+    if res:
+        hf = hf + (xf + rf - (xf + rf).detach())                  # straight-through for the rounding
+    yf = torch.nn.functional.layer_norm(hf, (cols,), wf, bf32, 1e-5)
+    yf.backward(dy.float())
+    assert (y.float() - yf).abs().max().item() < 4e-2
+    assert (x.grad.float() - xf.grad).abs().max().item() < 4e-2 * max(1.0, xf.grad.abs().max().item())
+    if res:
+        assert torch.equal(x.grad, r.grad)
+        assert (h.float() - (x.detach().float() + r.detach().float())).abs().max().item() < 4e-2
+    for got, want in ((w.grad, wf.grad), (b.grad, bf32.grad)):
+        assert ((got.float() - want).norm() / want.norm()).item() < 2e-2
