@@ -176,52 +176,53 @@ class PipelineEngine:
         return self.total_loss
 
     def _train_1f1b(self, data_iter, M, P):
+        """1F1B with asynchronous stage links: every send returns at once, and the receive of the next message of a
+        direction is posted right after the send of the current one, so it lands while this stage computes."""
         g, link = self.g, self.link
         first, last = g.is_first_stage(), g.is_last_stage()
         warm = min(P - g.pp_rank - 1, M)
         steady = M - warm
         queue = []          # (input hidden, output) of forwards awaiting backward, FIFO
         losses = []
-        pending_recv = None  # StageIO already received for the next forward
+        n_fwd = n_bwd = 0
 
-        def do_forward(io_in):
+        def forward_one():
+            nonlocal n_fwd
+            io_in = link.wait_recv_fwd() if not first else None
             io, labels = self._next_batch(data_iter)
             if not first:
                 io = io_in
             inp, out = self._forward(io, labels)
             queue.append((inp, out))
+            n_fwd += 1
             if last:
                 losses.append(out.detach())
-            return out
+            else:
+                link.send_fwd(out)
+            if not first and n_fwd < M:
+                link.post_recv_fwd()                     # the next input travels during the compute that follows
 
-        # warm-up forwards
-        for i in range(warm):
-            io_in = None
-            if not first:
-                io_in, _ = link.exchange(recv_fwd=True)
-            out = do_forward(io_in)
-            link.exchange(send_fwd=out)            # warm-up stages are never the last stage
-        if steady > 0 and not first:
-            pending_recv, _ = link.exchange(recv_fwd=True)
-        # steady state: 1 forward, 1 backward
-        for i in range(steady):
-            out = do_forward(pending_recv)
-            pending_recv = None
-            grad = None
-            if not last:
-                _, grad = link.exchange(send_fwd=out, recv_bwd_like=out.hidden)
+        def backward_one():
+            nonlocal n_bwd
             inp, o = queue.pop(0)
+            grad = link.wait_recv_bwd(o.hidden) if not last else None
             dgrad = self._backward(inp, o, grad)
-            more = i + 1 < steady
+            n_bwd += 1
             if not first:
-                pending_recv, _ = link.exchange(send_bwd=dgrad, recv_fwd=more)
-        # drain
-        for i in range(warm):
-            inp, o = queue.pop(0)
-            _, grad = link.exchange(recv_bwd_like=o.hidden)
-            dgrad = self._backward(inp, o, grad)
-            if not first:
-                link.exchange(send_bwd=dgrad)
+                link.send_bwd(dgrad)
+            if not last and queue:
+                link.post_recv_bwd(queue[0][1].hidden)   # gradient of the oldest forward still waiting
+
+        if not first:
+            link.post_recv_fwd()
+        for _ in range(warm):
+            forward_one()
+        for _ in range(steady):
+            forward_one()
+            backward_one()
+        for _ in range(warm):
+            backward_one()
+        link.flush()
         return losses
 
     def _aggregate_loss(self, losses):
@@ -255,13 +256,15 @@ class PipelineEngine:
         for _ in range(M):
             io, labels = self._next_batch(data_iter)
             if P > 1 and not g.is_first_stage():
-                io, _ = self.link.exchange(recv_fwd=True)
+                io = self.link.wait_recv_fwd()
             out = self.module.forward_stage(io, labels if compute_loss else None,
                                             return_logits=not compute_loss)
             if P > 1 and not g.is_last_stage():
-                self.link.exchange(send_fwd=out)
+                self.link.send_fwd(out)
             elif g.is_last_stage():
                 outs.append(out)
+        if P > 1:
+            self.link.flush()
         self.fwd_outputs = outs
         if compute_loss:
             return self._aggregate_loss(outs)
@@ -279,11 +282,12 @@ class PipelineEngine:
             io = self.module.parse_batch((tokens, position_ids, None))
         if g.pp > 1 and not g.is_first_stage():
             self.link.dynamic = True
-            io, _ = self.link.exchange(recv_fwd=True)
+            io = self.link.wait_recv_fwd()
         out = self.module.forward_stage(io, None, return_logits=True)
         if g.pp > 1 and not g.is_last_stage():
             self.link.dynamic = True
-            self.link.exchange(send_fwd=out)
+            self.link.send_fwd(out)
+            self.link.flush()
             return None
         return out
 

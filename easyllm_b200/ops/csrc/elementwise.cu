@@ -13,9 +13,11 @@
 namespace ell {
 
 // One thread rotates 8 (x1) + 8 (x2) elements of one head: D/2 must be a multiple of 8.
+// A position outside the cos / sin tables is reported through the error word (code 32) and its row left unrotated,
+// instead of reading past the tables.
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cos_t,
                             const float* __restrict__ sin_t, const int* __restrict__ pos, int T, int row_stride,
-                            int n_rot_heads, int D, float sin_sign) {
+                            int n_rot_heads, int D, float sin_sign, int table_rows, int* __restrict__ err) {
   const int half = D / 2, vec_per_head = half / 8;
   const long long total = (long long)T * n_rot_heads * vec_per_head;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -24,6 +26,10 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __rest
     const int hd = (int)((i / vec_per_head) % n_rot_heads);
     const int t = (int)(i / ((long long)vec_per_head * n_rot_heads));
     const int p = pos[t];
+    if (p < 0 || p >= table_rows) {
+      if (err != nullptr) atomicCAS(err, 0, 32);
+      continue;
+    }
     __nv_bfloat16* base = qkv + (size_t)t * row_stride + (size_t)hd * D + v * 8;
     float x1[8], x2[8], c[8], s[8];
     unpack8(*reinterpret_cast<const bf16x8*>(base), x1);
@@ -112,13 +118,14 @@ inline int ew_grid(long long work_items, int threads) {
 
 using namespace ell;
 
+// cos_t / sin_t: fp32 [table_rows, D/2]; positions outside [0, table_rows) set *err to 32.
 ELL_API int ell_rope(void* qkv, const float* cos_t, const float* sin_t, const int* pos, int T, int row_stride,
-                     int n_rot_heads, int D, int backward, cudaStream_t stream) {
+                     int n_rot_heads, int D, int backward, int table_rows, int* err, cudaStream_t stream) {
   if (D % 16) return -1;
   long long total = (long long)T * n_rot_heads * (D / 16);
   if (total == 0) return 0;
   rope_kernel<<<ew_grid(total, 256), 256, 0, stream>>>((__nv_bfloat16*)qkv, cos_t, sin_t, pos, T, row_stride,
-                                                       n_rot_heads, D, backward ? -1.f : 1.f);
+                                                       n_rot_heads, D, backward ? -1.f : 1.f, table_rows, err);
   return launch_status();
 }
 

@@ -365,8 +365,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           named_bar_sync(1, kEpiThreads);
           if (leader) {
             if (FUSE == kFuseRS || FUSE == kFuseAR) {
-              bulk_store(reinterpret_cast<uint8_t*>(fuse.data_ptrs[fuse.rank]) + stage_block<BN>(mt, nt, j, tiles_n),
-                         buf, kEpiBufBytes);
+              const size_t off = stage_block<BN>(mt, nt, j, tiles_n);
+              if (fuse_in_bounds(fuse, 0, off + kEpiBufBytes, err))
+                bulk_store(reinterpret_cast<uint8_t*>(fuse.data_ptrs[fuse.rank]) + off, buf, kEpiBufBytes);
             } else if (n0 + j * 64 < N) {
               tma_store_2d(&tmC, buf, n0 + j * 64, m0);
             }
@@ -576,7 +577,11 @@ ELL_API int ell_bounded_wait_selftest(const void* flag, unsigned int want, int* 
 
 namespace ell {
 int g_no_tail_split = 0;   // shared with gemm_pair.cu
+unsigned long long g_fuse_data_bytes = 0;
 }
+// Size in bytes of each gathered / staging buffer of the fused-TP workspace: the fused kernels check every tile offset
+// they compute against it (0 switches the offset check off; flag indices are always checked).
+ELL_API void ell_gemm_set_fused_buffer_bytes(unsigned long long bytes) { ell::g_fuse_data_bytes = bytes; }
 // Tuning switch: 0 (default) cuts the tiles of an under-filled last wave in two, 1 keeps whole tiles.
 ELL_API void ell_gemm_set_tail_split(int enabled) { g_no_tail_split = enabled ? 0 : 1; }
 
@@ -705,6 +710,7 @@ static void fill_fuse(FuseArgs& f, int rank, int tp, int n_comm, int rows_per_ra
   f.counter = (unsigned int*)counter;
   f.counter_base = counter_base;
   f.queue = f.counter + 1;
+  f.data_bytes = g_fuse_data_bytes;
 }
 
 // Total CTAs of a fused single-CTA launch (communication CTAs included): the host advances its copy of the CTA

@@ -40,7 +40,7 @@ constexpr int kEpiBufBytes = 128 * 64 * 2; // one 128x64 bf16 store box
 // kOutBf16CE: bf16 C plus, per row and column slot, the cross-entropy statistics (max, sum-exp, target logit)
 // of the rounded logits, computed in the epilogue while the tile is in registers.
 enum GemmOut { kOutBf16 = 0, kOutF32Accum = 1, kOutF32 = 2, kOutBf16CE = 3 };
-enum GemmErr { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3, kErrComm = 4, kErrFlagWait = 5 };
+enum GemmErr { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3, kErrComm = 4, kErrFlagWait = 5, kErrBounds = 6 };
 enum GemmFuse { kFuseNone = 0, kFuseAG = 1, kFuseRS = 2, kFuseAR = 3, kFuseAGK = 4 };
 constexpr int kMaxTp = 8;
 
@@ -66,7 +66,19 @@ struct FuseArgs {
   int no_tail_split;                     // 1 disables the half-width units of an under-filled last wave
   int shard_k;                           // row length of x_local when this struct describes a bare push (see below)
   int k_passes;                          // AGK: 2 walks every tile twice (local half of the k-range first), 1 once
+  unsigned long long data_bytes;         // size of each data_ptrs[] buffer: every computed offset is checked against it
 };
+
+// Tile-granular bounds check of the fused kernels (always on: a few compares per 128-row tile).  A tile whose flag
+// index or buffer offset falls outside what the host allocated is reported (kErrBounds) and skipped, never accessed.
+__device__ __forceinline__ bool fuse_in_bounds(const FuseArgs& f, long long flag_idx, unsigned long long end_offset,
+                                               int* err) {
+  if (flag_idx < 0 || flag_idx >= f.flags_per_src || (f.data_bytes != 0 && end_offset > f.data_bytes)) {
+    atomicCAS(err, 0, kErrBounds);
+    return false;
+  }
+  return true;
+}
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -135,8 +147,9 @@ __device__ inline void ag_comm_role(const FuseArgs& f, int K, int* err, uint8_t*
     const int t = item / n_dest;
     const int dest = (f.rank - 1 - item % n_dest + f.tp) % f.tp;   // the rank that needs this shard soonest first
     const uint8_t* src = reinterpret_cast<const uint8_t*>(f.x_local) + (size_t)t * tile_bytes;
-    uint8_t* dst = reinterpret_cast<uint8_t*>(f.data_ptrs[dest]) +
-                   ((size_t)f.rank * f.rows_per_rank + (size_t)t * kBM) * K * 2;
+    const size_t dst_off = ((size_t)f.rank * f.rows_per_rank + (size_t)t * kBM) * K * 2;
+    if (!fuse_in_bounds(f, t, dst_off + tile_bytes, err)) return;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(f.data_ptrs[dest]) + dst_off;
     int next_load = 0;
     auto issue_load = [&](int c) {
       const uint32_t st = issued % kCommStages;
@@ -236,6 +249,12 @@ __device__ inline void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int
       if (j < owned) {
         int mi, nt;
         owned_tile_of(j, tpr, tiles_n, f.tp, pair, mi, nt);
+        if (mi < 0 || mi >= tpr || nt < 0 || nt >= tiles_n ||
+            !fuse_in_bounds(f, (long long)mi * tiles_n + nt,
+                            stage_block<BN>(f.rank * tpr + mi, nt, kSub - 1, tiles_n) + kEpiBufBytes, err)) {
+          ok = false;
+          break;
+        }
         for (int s = 0; s < f.tp && ok; ++s) {
           const uint32_t* fl = f.flag_ptrs[f.rank] + (size_t)s * f.flags_per_src + mi * tiles_n + nt;
           ok = wait_flag_ge(fl, f.epoch, abort_flag);
@@ -263,6 +282,12 @@ __device__ inline void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int
         const int o = (f.rank + 1 + j2 / owned) % f.tp;
         int mi, nt;
         owned_tile_of(j2 % owned, tpr, tiles_n, f.tp, pair, mi, nt);
+        if (mi < 0 || mi >= tpr || nt < 0 || nt >= tiles_n ||
+            !fuse_in_bounds(f, (long long)mi * tiles_n + nt,
+                            stage_block<BN>(o * tpr + mi, nt, kSub - 1, tiles_n) + kEpiBufBytes, err)) {
+          ok = false;
+          break;
+        }
         const uint32_t* fl = f.red_ptrs[f.rank] + (size_t)o * f.flags_per_src + mi * tiles_n + nt;
         if (!wait_flag_ge(fl, f.epoch, abort_flag)) { ok = false; break; }
         fence_proxy_async_all();
@@ -370,5 +395,6 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_
 int make_tmap_f32_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                      uint32_t box_inner, uint32_t box_outer);
 extern int g_no_tail_split;   // 1 keeps whole tiles in an under-filled last wave (ell_gemm_set_tail_split)
+extern unsigned long long g_fuse_data_bytes;   // size of every gathered / staging buffer (ell_gemm_set_fused_buffer_bytes)
 
 }  // namespace ell

@@ -247,7 +247,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
-    if (lane == 0) {
+    // Two lanes share the issue work: lane 0 loads this CTA's A rows, lane 1 its B rows (the MN-major forms need
+    // two 64-wide boxes per operand and k-block, and one thread issuing all four copies plus the barrier traffic
+    // per 64-deep k-block was the slowest role of the weight-gradient GEMMs).  Both lanes walk the same units and
+    // stages and wait on the same barriers; only the leader's lane 0 posts the expected byte count.
+    if (lane < 2) {
+      const bool loads_a = lane == 0;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -255,7 +260,30 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int seen[kMaxTp];
 #pragma unroll
       for (int i = 0; i < kMaxTp; ++i) seen[i] = 0;
-      const int kb_rot = FUSE == kFuseAGK ? fuse.rank * (fuse.rows_per_rank / kBK) : 0;
+      const int kpr = FUSE == kFuseAGK ? fuse.rows_per_rank / kBK : 1;   // k-blocks per source rank
+      const int kb_rot = FUSE == kFuseAGK ? fuse.rank * kpr : 0;
+      // one k-block: wait for the stage, post the byte count, issue this lane's copies
+      auto load_kblock = [&](int kk, const CUtensorMap* a_map, int a_row, int m0, const CUtensorMap* b_map, int nb0,
+                             int b_rows, int b_krow, uint32_t stage_tx) -> bool {
+        if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) return false;
+        if (is_leader && loads_a) mbar_expect_tx(&sh->full[stage], stage_tx);
+        const uint32_t bar = map_to_cta(smem_u32(&sh->full[stage]), 0);
+        // the same instruction stream for both lanes (selects, no divergent branches): a K-major operand is one
+        // 64 x 128 box at (k, row), an MN-major operand one 64 x 64 box per 64 rows at (row + 64 i, k)
+        const bool mn = loads_a ? A_MN : B_MN;
+        uint8_t* dst = loads_a ? sA + stage * kABytes : sB + stage * kBBytes;
+        const CUtensorMap* map = loads_a ? (A_MN ? &tmA : a_map) : b_map;
+        const int row = loads_a ? (A_MN ? m0 : a_row) : nb0;
+        const int kcoord = loads_a ? kk * kBK : (B_MN ? b_krow : kk * kBK);
+        const int n_box = mn ? (loads_a ? kHalfM / 64 : b_rows / 64) : 1;
+        for (int i = 0; i < n_box; ++i)
+          tma_load_2d_pair(dst + i * (64 * kBK * 2), map, bar, mn ? row + i * 64 : kcoord, mn ? kcoord : row);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+        return true;
+      };
       for (int unit = cluster_id; unit < num_units && ok; unit += n_clusters) {
         const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp);
         const int b_rows = u.bn / 2;                                // B rows staged by one CTA (128, or 64 in a half unit)
@@ -283,59 +311,42 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             fence_proxy_async_all();   // peer writes -> TMA reads (async proxy)
           }
         }
-        const int kb_lo = k_passes == 2 ? u.kphase * (num_kb / 2) : 0;
-        const int kb_hi = k_passes == 2 && u.kphase == 0 ? num_kb / 2 : num_kb;
-        for (int kb = kb_lo; kb < kb_hi; ++kb) {
-          int kk = kb;                       // k-block actually loaded
-          const CUtensorMap* bk_map = &tmB;  // kFuseAGK: map of the B k-block
-          int bk_row = 0;
-          if (FUSE == kFuseAGK) {
-            kk = kb + kb_rot;
-            if (kk >= num_kb) kk -= num_kb;
-            const int t0 = kk * kBK, src = t0 / fuse.rows_per_rank, loc = t0 - src * fuse.rows_per_rank;
-            bk_row = t0;
-            if (src == fuse.rank) {
-              bk_map = &tmX;
-              bk_row = loc;
-            } else if (loc / kBM >= seen[src]) {
-              const uint32_t* fl = fuse.flag_ptrs[fuse.rank] + (size_t)src * fuse.flags_per_src + loc / kBM;
-              if (!wait_flag_ge(fl, fuse.epoch, abort_flag)) {
+        if (FUSE != kFuseAGK) {
+          for (int kb = 0; kb < num_kb && ok; ++kb)
+            ok = load_kblock(kb, a_map, a_row, m0, b_map, nb0, b_rows, kb * kBK, stage_tx);
+          continue;
+        }
+        // kFuseAGK: the k-range of this unit in rotated order (position r is k-block (r + kb_rot) mod num_kb, so the
+        // walk starts at this rank's own rows), cut into runs that stay inside one source rank's rows: everything
+        // that depends on the source is computed once per run, not once per k-block.
+        int r = k_passes == 2 ? u.kphase * (num_kb / 2) : 0;
+        const int r_hi = k_passes == 2 && u.kphase == 0 ? num_kb / 2 : num_kb;
+        while (r < r_hi && ok) {
+          int kk = r + kb_rot;
+          if (kk >= num_kb) kk -= num_kb;
+          const int src = kk / kpr;
+          const int k_in = kk - src * kpr;                           // k-block inside the source's shard
+          const int run = min(kpr - k_in, r_hi - r);
+          const bool local = src == fuse.rank;
+          const CUtensorMap* bk_map = local ? &tmX : &tmB;          // own rows in place, the others from the gathered buffer
+          const int row0 = local ? 0 : src * fuse.rows_per_rank;
+          int seen_src = seen[src];
+          const uint32_t* flags = fuse.flag_ptrs[fuse.rank] + (size_t)src * fuse.flags_per_src;
+          for (int i = 0; i < run && ok; ++i) {
+            const int ki = k_in + i, tile = ki >> 1;                 // two 64-row k-blocks per flagged 128-row tile
+            if (!local && tile >= seen_src) {
+              if (!wait_flag_ge(flags + tile, fuse.epoch, abort_flag)) {
                 ok = false;
                 atomicCAS(err, 0, kErrPairFlagWait);
                 break;
               }
               fence_proxy_async_all();
-              seen[src] = loc / kBM + 1;
+              seen_src = tile + 1;
             }
+            ok = load_kblock(kk + i, a_map, a_row, m0, bk_map, nb0, b_rows, row0 + ki * kBK, stage_tx);
           }
-          if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) {
-            ok = false;
-            break;
-          }
-          if (is_leader) mbar_expect_tx(&sh->full[stage], stage_tx);
-          const uint32_t bar = map_to_cta(smem_u32(&sh->full[stage]), 0);
-          uint8_t* a_dst = sA + stage * kABytes;
-          uint8_t* b_dst = sB + stage * kBBytes;
-          if (!A_MN) {
-            tma_load_2d_pair(a_dst, a_map, bar, kk * kBK, a_row);
-          } else {
-#pragma unroll
-            for (int i = 0; i < kHalfM / 64; ++i)
-              tma_load_2d_pair(a_dst + i * (64 * kBK * 2), &tmA, bar, m0 + i * 64, kk * kBK);
-          }
-          if (!B_MN) {
-            tma_load_2d_pair(b_dst, b_map, bar, kk * kBK, nb0);
-          } else {
-#pragma unroll
-            for (int i = 0; i < kHalfN / 64; ++i)
-              if (i * 64 < b_rows)
-                tma_load_2d_pair(b_dst + i * (64 * kBK * 2), FUSE == kFuseAGK ? bk_map : &tmB, bar, nb0 + i * 64,
-                                 FUSE == kFuseAGK ? bk_row : kk * kBK);
-          }
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1;
-          }
+          seen[src] = seen_src;
+          r += run;
         }
       }
       // the leader's last commits on this CTA's empty barriers must have landed before the CTA may exit
@@ -498,9 +509,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           named_bar_sync(1, kEpiThreads);
           if (store_thread) {
             if (kReduce) {
-              bulk_store(reinterpret_cast<uint8_t*>(fuse.data_ptrs[fuse.rank]) +
-                             stage_block<kTileN>(m0 / kBM, u.nt, j, tiles_n),
-                         buf, kEpiBufBytes);
+              const size_t off = stage_block<kTileN>(m0 / kBM, u.nt, j, tiles_n);
+              if (fuse_in_bounds(fuse, 0, off + kEpiBufBytes, err))
+                bulk_store(reinterpret_cast<uint8_t*>(fuse.data_ptrs[fuse.rank]) + off, buf, kEpiBufBytes);
             } else if (n0 + j * 64 < N && m0 < M) {
               tma_store_2d(&tmC, buf, n0 + j * 64, m0);
             }
@@ -712,6 +723,7 @@ static void fill_fuse(FuseArgs& f, int rank, int tp, int n_comm, int rows_per_ra
   f.counter_base = counter_base;
   f.queue = f.counter + 1;
   f.no_tail_split = g_no_tail_split;
+  f.data_bytes = g_fuse_data_bytes;
 }
 
 // LM-head form: logits + cross-entropy partials, optionally behind the all-gather of the hidden rows.

@@ -94,7 +94,8 @@ def check_err_flag():
         f.zero_()
         raise KernelError(f"a kernel gave up a bounded wait (code {v}: 1 producer, 2 mma, 3 epilogue, 4 communication "
                           "role, 5 peer flag; 11-15 the same roles of the CTA-pair GEMM; 21 cross-entropy exchange; "
-                          "31 a token id outside the embedding table)")
+                          "31 a token id outside the embedding table; 32 a position outside the rotary tables; "
+                          "6 / 16 a tile index outside a fused kernel's buffers)")
 
 
 def waiting_kernels_in_use():
@@ -194,7 +195,8 @@ def rope_(qkv, cos, sin, pos, n_rot_heads, head_dim, backward=False):
         pos = pos.to(torch.int32)
     T, W = qkv.shape
     rc = lib().ell_rope(_p(qkv), _p(cos), _p(sin), _p(pos), c_int(T), c_int(W), c_int(n_rot_heads),
-                        c_int(head_dim), c_int(1 if backward else 0), _stream())
+                        c_int(head_dim), c_int(1 if backward else 0), c_int(cos.shape[0]), _p(err_flag(qkv.device)),
+                        _stream())
     _check(rc, "rope")
     return qkv
 

@@ -82,14 +82,22 @@ class ParallelGrid:
         self.tp_group, self.tp_ranks = self._make(self.layout.tp_groups)
         self.pp_group, self.pp_ranks = self._make(self.layout.pp_groups)
         self.emb_group, self.emb_ranks = self._make(self.layout.emb_groups)
+        # pipeline p2p: one group (one communicator, one stream) per direction, so activations flowing down and
+        # gradients flowing up never queue behind each other, and a CPU group for the shape headers of dynamic
+        # micro-batches (read on the host without touching the GPU)
+        self.pp_fwd_group = self.pp_bwd_group = self.pp_host_group = None
+        if self.pp > 1:
+            self.pp_fwd_group, _ = self._make(self.layout.pp_groups)
+            self.pp_bwd_group, _ = self._make(self.layout.pp_groups)
+            self.pp_host_group, _ = self._make(self.layout.pp_groups, backend="gloo")
         self._gloo_world = None
         self.virtual_pp_rank = None
         self.virtual_pp_world = None
 
-    def _make(self, tables):
+    def _make(self, tables, backend=None):
         mine, mine_ranks = None, None
         for ranks in tables:
-            grp = dist.new_group(ranks, timeout=self._timeout)
+            grp = dist.new_group(ranks, timeout=self._timeout, backend=backend)
             if self.rank in ranks:
                 mine, mine_ranks = grp, list(ranks)
         return mine, mine_ranks
@@ -135,6 +143,7 @@ class _Solo:
     world = tp = pp = dp = 1
     rank = pp_rank = dp_rank = tp_rank = 0
     dp_group = mp_group = tp_group = pp_group = emb_group = None
+    pp_fwd_group = pp_bwd_group = pp_host_group = None
     dp_ranks = mp_ranks = tp_ranks = pp_ranks = emb_ranks = [0]
     virtual_pp_rank = virtual_pp_world = None
     layout = grid_layout(1, 1, 1)

@@ -88,6 +88,8 @@ class FusedTPWorkspace:
         self._arr = lambda ptrs: (c_void_p * len(ptrs))(*ptrs)
         from ..ops import cuda as cu
         lib = cu.lib()
+        from ctypes import c_ulonglong
+        lib.ell_gemm_set_fused_buffer_bytes(c_ulonglong(data_elems * 2))   # the kernels check tile offsets against it
         self.grid_single = lib.ell_gemm_fused_grid()
         self.grid_pair = lib.ell_gemm_pair_fused_grid()
         self.use_pair = cu.gemm_pair_enabled() and self.grid_pair > 0

@@ -205,8 +205,6 @@ def test_layernorm_kernel_matches_fp32(cu, rows, cols, res):
     xf = x.detach().float().requires_grad_(); wf = w.detach().float().requires_grad_(); bf32 = b.detach().float().requires_grad_()
     rf = r.detach().float().requires_grad_() if res else None
     hf = (xf + rf).to(torch.bfloat16).float() if res else xf      # the kernel stores the sum in bf16 and normalises that
-    if res:
-        hf = hf + (xf + rf - (xf + rf).detach())                  # straight-through for the rounding
     yf = torch.nn.functional.layer_norm(hf, (cols,), wf, bf32, 1e-5)
     yf.backward(dy.float())
     assert (y.float() - yf).abs().max().item() < 4e-2
@@ -216,3 +214,29 @@ def test_layernorm_kernel_matches_fp32(cu, rows, cols, res):
         assert (h.float() - (x.detach().float() + r.detach().float())).abs().max().item() < 4e-2
     for got, want in ((w.grad, wf.grad), (b.grad, bf32.grad)):
         assert ((got.float() - want).norm() / want.norm()).item() < 2e-2
+
+
+def test_out_of_range_indices_are_reported_not_dereferenced(cu):
+    """Bounds checks that are always on: a rotary position beyond the cos / sin tables and a token id beyond the
+    embedding table set the device error word (the host raises at its next read) instead of reading past a buffer;
+    the offending rows are left unrotated / zero."""
+    from easyllm_b200.ops.reference import rope_tables
+    torch.manual_seed(0)
+    cos, sin = rope_tables(128, 64, device="cuda")                  # positions 0..63 only
+    qkv = torch.randn(16, 3 * 128, device="cuda", dtype=torch.bfloat16)
+    before = qkv.clone()
+    pos = torch.arange(16, dtype=torch.int32, device="cuda")
+    pos[5] = 4096                                                    # outside the tables
+    cu.rope_(qkv, cos, sin, pos, 2, 128)
+    torch.cuda.synchronize()
+    with pytest.raises(cu.KernelError, match="code 32"):
+        cu.check_err_flag()
+    assert torch.equal(qkv[5], before[5]) and not torch.equal(qkv[4], before[4])
+    w = torch.randn(100, 64, device="cuda", dtype=torch.bfloat16)
+    ids = torch.tensor([1, 2, 250, 3], device="cuda")
+    out = cu.embedding_fwd(ids, w, 0, 100)
+    torch.cuda.synchronize()
+    with pytest.raises(cu.KernelError, match="code 31"):
+        cu.check_err_flag()
+    assert torch.equal(out[2], torch.zeros_like(out[2])) and torch.equal(out[1], w[2])
+    cu.check_err_flag()                                              # cleared

@@ -144,6 +144,18 @@ for it in range(n_soak):
         rel(out, ref)
 torch.cuda.synchronize()
 cu.check_err_flag()
+
+# deterministic order: the owner sums the partials rank by rank whatever the arrival order, so a re-run in which another
+# rank arrives late must reproduce the reduce-scatter and the all-reduce bit for bit
+first = (ws.gemm_rs(a, w_row).clone(), ws.gemm_rs(a, w_row, all_reduce=True).clone(), ws.ag_gemm(x_local, w_col).clone())
+for late in range(tp):
+    if g.tp_rank == late:
+        torch.cuda.synchronize(); time.sleep(0.03)
+    again = (ws.gemm_rs(a, w_row), ws.gemm_rs(a, w_row, all_reduce=True), ws.ag_gemm(x_local, w_col))
+    for u, v in zip(first, again):
+        assert torch.equal(u, v), "fused TP kernels are not run-to-run deterministic"
+torch.cuda.synchronize()
+cu.check_err_flag()
 assert not ops.fallbacks(), ops.fallbacks()
 print(f"RANK{g.rank} worst_rel_err={worst:.5f} pair={expect_pair}", flush=True)
 dist.barrier()
