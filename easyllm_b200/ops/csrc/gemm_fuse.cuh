@@ -375,6 +375,8 @@ __device__ inline void rs_reduce_role(const FuseArgs& f, int N, int tiles_n, int
                 *reinterpret_cast<const bf16x8*>(base + q * 16);
         }
       }
+      // the stage is refilled by a bulk load (async proxy): order this thread's generic-proxy reads before it
+      fence_proxy_async_smem();
       mbar_arrive(&cs->empty[st]);
     }
   }

@@ -22,9 +22,15 @@
 // The same kernel carries the tensor-parallel fusions of gemm_fuse.cuh (all-gather -> GEMM on the A rows or on
 // the reduction rows, GEMM -> reduce-scatter / all-reduce) and the cross-entropy epilogue of the LM head.  In a
 // fused launch CTAs [0, n_comm) (whole clusters: n_comm is even) run the communication role; each CTA of a GEMM
-// pair waits for the flag of its own 128 A rows, stages and flags its own 128 x 256 block of partial sums, and
-// joins the reduction when the main loop is done.  Any M, N, K that the single-CTA kernel accepts (out-of-range
+// pair waits for the flag of its own 128 A rows.  Any M, N, K that the single-CTA kernel accepts (out-of-range
 // parts of a tile are zero-filled on load and clipped on store); fused launches need rows_per_rank % 256 == 0.
+//
+// GEMM -> reduce-scatter here sums in the EPILOGUE, without a separate reduction pass: a tile that another rank
+// owns is written (bf16, bulk stores through peer pointers) straight into that rank's staging buffer and flagged
+// there; a tile this rank owns is computed `lag` rounds after the peers computed theirs, a seventh warp prefetches
+// the peers' partial sums from the LOCAL staging buffer into the two epilogue buffers, and the epilogue adds them
+// to the fp32 accumulator in a fixed source order before the one rounding to bf16 (deterministic; the own partial
+// is never rounded).  GEMM -> all-reduce keeps the staged two-phase reduction of gemm_fuse.cuh.
 #include "gemm_fuse.cuh"
 
 namespace ell {
@@ -33,6 +39,7 @@ namespace pair {
 constexpr int kTileM = 256, kTileN = 256;   // per cluster
 constexpr int kHalfM = 128, kHalfN = 128;   // rows of A / rows of B staged by one CTA
 constexpr int kThreads = kGemmThreads;      // warp 0 producer, warp 1 MMA issuer + TMEM owner, warps 2-5 epilogue
+constexpr int kThreadsRS = kGemmThreads + 32;   // reduce-scatter form: warp 6 prefetches the peers' partial sums
 constexpr int kStages = 6;
 constexpr int kABytes = kHalfM * kBK * 2;   // 16 KiB
 constexpr int kBBytes = kHalfN * kBK * 2;   // 16 KiB
@@ -47,6 +54,9 @@ struct Shared {
   uint64_t empty[8];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t part_full[2];    // reduce-scatter: a peer's partial 128 x 64 block has landed in epilogue buffer i
+  uint64_t part_empty[2];   // ... and all 128 epilogue threads have added it
+  uint64_t stage_free;      // ... the epilogue buffers are no longer read by bulk stores of staged blocks
   uint32_t tmem_base;
   int abort_flag;
   int epi_abort;
@@ -143,8 +153,39 @@ __host__ __device__ inline int split_tail(int num_tiles, int clusters, bool allo
 // The gather of the reduction rows (kFuseAGK) walks every tile twice: first over the half of the k-range that
 // starts at the local rows (while the peers' rows are still arriving), then over the other half; the output is an
 // fp32 accumulation, so the two passes simply add up.
+// Rounds by which a rank's own tiles trail the peers' in the reduce-scatter order: about two waves of tiles, so a
+// partial sum has been computed, sent and flagged well before the owner's epilogue asks for it.
+__host__ __device__ __forceinline__ int rs_lag(int tiles_per_owner, int n_clusters, int tp) {
+  if (tp <= 1) return 0;
+  const int lag = (2 * n_clusters + tp - 1) / tp;
+  return lag < tiles_per_owner ? lag : tiles_per_owner;
+}
+
+// Reduce-scatter order of rank `rank`: round k computes tile k (raster order inside a shard) of every OTHER owner,
+// nearest ring successor first, then the rank's own tile k - lag; the last `lag` own tiles close the launch.
+// Returns the owner and sets `tile`.
+__host__ __device__ __forceinline__ int rs_order(int pos, int n, int tp, int lag, int rank, int& tile) {
+  const int head = lag * (tp - 1);
+  if (pos < head) {
+    tile = pos / (tp - 1);
+    return (rank + 1 + pos % (tp - 1)) % tp;
+  }
+  pos -= head;
+  if (pos < (n - lag) * tp) {
+    const int k = lag + pos / tp, i = pos % tp;
+    if (i < tp - 1) {
+      tile = k;
+      return (rank + 1 + i) % tp;
+    }
+    tile = k - lag;
+    return rank;
+  }
+  tile = n - lag + (pos - (n - lag) * tp);
+  return rank;
+}
+
 __host__ __device__ __forceinline__ Unit decode_unit(int unit, int tiles_m, int tiles_n, int num_full, int fuse, int rank,
-                                                     int tp) {
+                                                     int tp, int n_clusters) {
   Unit u;
   int tile = unit, half = -1;
   if (unit >= num_full) {
@@ -163,7 +204,13 @@ __host__ __device__ __forceinline__ Unit decode_unit(int unit, int tiles_m, int 
     int mi;
     raster(tile % per_phase, tpr, tiles_n, mi, u.nt);
     u.mt = ((rank + phase) % tp) * tpr + mi;
-  } else if (fuse == kFuseRS || fuse == kFuseAR) {
+  } else if (fuse == kFuseRS) {
+    const int tpr = tiles_m / tp, n = tpr * tiles_n;
+    int k, mi;
+    const int owner = rs_order(tile, n, tp, rs_lag(n, n_clusters, tp), rank, k);
+    raster(k, tpr, tiles_n, mi, u.nt);
+    u.mt = owner * tpr + mi;
+  } else if (fuse == kFuseAR) {
     int mp;
     raster(tile, tiles_m, tiles_n, mp, u.nt);
     u.mt = (mp % tp) * (tiles_m / tp) + mp / tp;
@@ -178,7 +225,7 @@ __host__ __device__ __forceinline__ Unit decode_unit(int unit, int tiles_m, int 
 // tmX: the local shard of the gathered operand (kFuseAG: A rows, box 128 x 64; kFuseAGK: reduction rows of B,
 // box 64 x 64); tmBh: B with a box of 64 rows for the half-width units.
 template <bool A_MN, bool B_MN, int OUT, bool HAS_BIAS, int FUSE>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(FUSE == kFuseRS ? kThreadsRS : kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmBh,
                  const __grid_constant__ CUtensorMap tmX, const __grid_constant__ FuseArgs fuse,
@@ -188,7 +235,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr bool kReduce = (FUSE == kFuseRS || FUSE == kFuseAR);
   constexpr bool kGather = (FUSE == kFuseAG || FUSE == kFuseAGK);
-  const int n_red = FUSE == kFuseNone ? 0 : fuse.n_comm;
+  constexpr bool kStagedReduce = FUSE == kFuseAR;     // reduction as a separate role over staged tiles
+  const int n_red = (FUSE == kFuseNone || FUSE == kFuseRS) ? 0 : fuse.n_comm;
   // reduce forms may carry the all-gather push of the next kernel's operand in CTAs [n_red, n_red + n_push)
   const int n_push = kReduce ? push.n_comm : 0;
   const int n_comm = n_red + n_push;                   // CTAs that do not run the GEMM
@@ -228,7 +276,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int a = 0; a < 2; ++a) {
       mbar_init(&sh->tmem_full[a], 1);
       mbar_init(&sh->tmem_empty[a], 2 * kEpiThreads);
+      mbar_init(&sh->part_full[a], 1);
+      mbar_init(&sh->part_empty[a], kEpiThreads);
     }
+    mbar_init(&sh->stage_free, 1);
     sh->abort_flag = 0;
     sh->epi_abort = 0;
     fence_barrier_init();
@@ -285,7 +336,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         return true;
       };
       for (int unit = cluster_id; unit < num_units && ok; unit += n_clusters) {
-        const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp);
+        const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp, n_clusters);
         const int b_rows = u.bn / 2;                                // B rows staged by one CTA (128, or 64 in a half unit)
         const int m0 = u.mt * kTileM + (int)cta_rank * kHalfM;     // A rows of this CTA
         const int nb0 = u.n0 + (int)cta_rank * b_rows;             // B rows of this CTA
@@ -415,6 +466,55 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         atomicCAS(err, 0, kErrPairMma);
       }
     }
+  } else if (warp >= 6) {
+    // ------------------------------ partial-sum prefetch (reduce-scatter form) -------------
+    // For every tile this rank owns: wait until all peers have flagged their partial block, then stream the
+    // (tp - 1) x 4 staged 128 x 64 blocks from the LOCAL staging buffer through the two epilogue buffers, in the
+    // order the epilogue adds them.
+    if (FUSE == kFuseRS && lane == 0 && fuse.tp > 1) {
+      const int tpr = fuse.rows_per_rank / kBM;
+      bool ok = true;
+      uint32_t item = 0, own_idx = 0;
+      for (int unit = cluster_id; unit < num_units && ok; unit += n_clusters) {
+        const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp, n_clusters);
+        const int m0 = u.mt * kTileM + (int)cta_rank * kHalfM;
+        if (m0 / fuse.rows_per_rank != fuse.rank) continue;
+        const int mi = (m0 - fuse.rank * fuse.rows_per_rank) / kBM;
+        const long long fidx = (long long)mi * tiles_n + u.nt;
+        if (ok && !fuse_in_bounds(fuse, fidx,
+                                  stage_block<kTileN>((fuse.tp - 1) * tpr + mi, u.nt, kTileN / 64 - 1, tiles_n) + kEpiBufBytes,
+                                  err))
+          ok = false;
+        for (int si = 1; si < fuse.tp && ok; ++si) {
+          const int src = (fuse.rank + si) % fuse.tp;
+          ok = wait_flag_ge(fuse.flag_ptrs[fuse.rank] + (size_t)src * fuse.flags_per_src + fidx, fuse.epoch, abort_flag);
+        }
+        // the epilogue buffers stage the blocks of other owners' tiles in between: they are handed over when the
+        // epilogue reaches this tile (the flags above, the long wait, have been taken ahead of it)
+        if (ok) ok = mbar_wait(&sh->stage_free, own_idx & 1, abort_flag);
+        ++own_idx;
+        if (!ok) break;
+        fence_proxy_async_all();       // peers' writes -> bulk loads (async proxy)
+        for (int j = 0; j < kTileN / 64 && ok; ++j)
+          for (int si = 1; si < fuse.tp; ++si, ++item) {
+            const int src = (fuse.rank + si) % fuse.tp;
+            const uint32_t slot = item & 1;
+            if (!mbar_wait(&sh->part_empty[slot], ((item >> 1) & 1) ^ 1, abort_flag)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(&sh->part_full[slot], kEpiBufBytes);
+            bulk_load(sC + slot * kEpiBufBytes,
+                      reinterpret_cast<const uint8_t*>(fuse.data_ptrs[fuse.rank]) +
+                          stage_block<kTileN>(src * tpr + mi, u.nt, j, tiles_n),
+                      kEpiBufBytes, &sh->part_full[slot]);
+          }
+      }
+      if (!ok) {
+        sh->abort_flag = 1;
+        atomicCAS(err, 0, kErrPairFlagWait);
+      }
+    }
   } else {
     // ------------------------------ epilogue (both CTAs, own 128 rows) --------------------
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
@@ -425,6 +525,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int it = 0;
     uint32_t store_count = 0;
     uint32_t* pending_flag = nullptr;   // reduce forms: flag of the last staged block, raised once its stores completed
+    uint32_t part_item = 0;             // reduce-scatter: partial blocks consumed so far (selects buffer and parity)
     if (kReduce && store_thread) {
       // peers must have finished reading last epoch's staged tiles before they are overwritten
       for (int p = 0; p < fuse.tp; ++p)
@@ -434,7 +535,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
     }
     for (int unit = cluster_id; unit < num_units; unit += n_clusters, ++it) {
-      const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp);
+      const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp, n_clusters);
       const int m0 = u.mt * kTileM + (int)cta_rank * kHalfM, n0 = u.n0;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -452,7 +553,70 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (tc >= 0 && tc < u.bn && tc + n0 < fuse.ce_valid) ce_tcol = (int)tc;
         }
       }
-      if (OUT == kOutBf16 || OUT == kOutBf16CE) {
+      const bool own_tile = FUSE == kFuseRS && m0 / fuse.rows_per_rank == fuse.rank;
+      if (own_tile && store_thread && pending_flag != nullptr) {
+        // the staged block of the previous tile is published before this CTA turns to a tile of its own
+        tma_store_wait_all<0>();
+        fence_proxy_async_all();
+        __threadfence_system();
+        st_release_sys(pending_flag, fuse.epoch);
+        pending_flag = nullptr;
+      }
+      if (own_tile && fuse.tp > 1) {
+        // A tile this rank owns: add the peers' partial sums (prefetched by warp 6) and write the output shard.
+        if (store_thread) {
+          // the epilogue buffers may still be read by the bulk stores of a staged block: hand them to warp 6 after that
+          tma_store_wait_read<0>();
+          mbar_arrive(&sh->stage_free);
+        }
+        const int row0_local = m0 - fuse.rank * fuse.rows_per_rank;
+#pragma unroll 1
+        for (int j = 0; j < kTileN / 64; ++j) {
+          uint32_t r[64];
+          tmem_ld_32x32(t_row + j * 64, r);
+          tmem_ld_32x32(t_row + j * 64 + 32, r + 32);
+          tmem_ld_wait();
+          for (int si = 1; si < fuse.tp; ++si, ++part_item) {
+            const uint32_t slot = part_item & 1;
+            if (!mbar_wait(&sh->part_full[slot], (part_item >> 1) & 1, abort_flag)) {
+              sh->epi_abort = 1;
+              sh->abort_flag = 1;
+            }
+            uint8_t* prow = sC + slot * kEpiBufBytes + row_in_tile * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              float t[8];
+              unpack8(*reinterpret_cast<const bf16x8*>(prow + ((c ^ (row_in_tile & 7)) << 4)), t);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) r[c * 8 + e] = __float_as_uint(__uint_as_float(r[c * 8 + e]) + t[e]);
+            }
+            if (si == fuse.tp - 1) {
+              // last source: the sum replaces the partial block in place (every thread rewrites the 128 bytes it just
+              // read) and leaves through a tensor store; the buffer goes back to warp 6 once that store has read it
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                float t[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) t[e] = __uint_as_float(r[c * 8 + e]);
+                *reinterpret_cast<bf16x8*>(prow + ((c ^ (row_in_tile & 7)) << 4)) = pack8(t);
+              }
+              fence_proxy_async_smem();
+              named_bar_sync(1, kEpiThreads);
+              if (store_thread) {
+                tma_store_2d(&tmC, sC + slot * kEpiBufBytes, n0 + j * 64, row0_local);
+                tma_store_commit();
+                tma_store_wait_read<0>();
+              }
+              mbar_arrive(&sh->part_empty[slot]);
+            } else {
+              // The buffer goes back to warp 6, whose next bulk load (async proxy) overwrites it as soon as the 128th
+              // arrive lands.  These reads went through the generic proxy: a proxy fence orders them before that write.
+              fence_proxy_async_smem();
+              mbar_arrive(&sh->part_empty[slot]);
+            }
+          }
+        }
+      } else if (OUT == kOutBf16 || OUT == kOutBf16CE) {
 #pragma unroll 1
         for (int j = 0; j < u.bn / 64; ++j) {
           uint8_t* buf = sC + (store_count & 1) * kEpiBufBytes;
@@ -508,7 +672,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           fence_proxy_async_smem();
           named_bar_sync(1, kEpiThreads);
           if (store_thread) {
-            if (kReduce) {
+            if (own_tile) {
+              // one-rank group: nothing to add, the tile is the output
+              tma_store_2d(&tmC, buf, n0 + j * 64, m0 - fuse.rank * fuse.rows_per_rank);
+            } else if (FUSE == kFuseRS) {
+              // the owner's staging buffer, slot of this source rank
+              const int owner = m0 / fuse.rows_per_rank;
+              const int mi = (m0 - owner * fuse.rows_per_rank) / kBM;
+              const size_t off = stage_block<kTileN>(fuse.rank * (fuse.rows_per_rank / kBM) + mi, u.nt, j, tiles_n);
+              if (fuse_in_bounds(fuse, 0, off + kEpiBufBytes, err))
+                bulk_store(reinterpret_cast<uint8_t*>(fuse.data_ptrs[owner]) + off, buf, kEpiBufBytes);
+            } else if (kReduce) {
               const size_t off = stage_block<kTileN>(m0 / kBM, u.nt, j, tiles_n);
               if (fuse_in_bounds(fuse, 0, off + kEpiBufBytes, err))
                 bulk_store(reinterpret_cast<uint8_t*>(fuse.data_ptrs[fuse.rank]) + off, buf, kEpiBufBytes);
@@ -535,12 +709,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
         }
-        if (kReduce && store_thread) {
+        if (kReduce && store_thread && !own_tile) {
           // Publish the flag of the PREVIOUS block: its bulk stores were committed 4 groups ago, so waiting until
           // at most 4 groups are pending does not stall behind this block's stores.
           if (pending_flag != nullptr) {
             tma_store_wait_all<kTileN / 64>();
             fence_proxy_async_all();
+            if (FUSE == kFuseRS) __threadfence_system();   // the blocks were written into a peer's memory
             st_release_sys(pending_flag, fuse.epoch);
           }
           const int owner = m0 / fuse.rows_per_rank;
@@ -586,6 +761,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tma_store_wait_all<0>();
       if (kReduce && pending_flag != nullptr) {
         fence_proxy_async_all();
+        if (FUSE == kFuseRS) __threadfence_system();
         st_release_sys(pending_flag, fuse.epoch);
       }
     }
@@ -605,14 +781,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc_pair(tmem_base);
   }
-  if (kReduce) {
+  if (kStagedReduce) {
     // the main loop is done: this CTA now helps summing the staged tiles its rank owns (the dedicated CTAs
     // [0, n_comm) have been doing so since launch)
     __syncthreads();
     rs_reduce_role<kTileN>(fuse, N, tiles_n, err, smem, (int)gridDim.x - n_push, true, FUSE == kFuseAR);
   }
-  if (kGather && threadIdx.x == 0) {
-    // last GEMM CTA of this rank: tell every peer that its pushes of this epoch were consumed
+  if ((kGather || FUSE == kFuseRS) && threadIdx.x == 0) {
+    // last GEMM CTA of this rank: tell every peer that its pushes (gathered rows, or partial sums) of this epoch
+    // were consumed
     __threadfence();
     const unsigned int old = atomicAdd(fuse.counter, 1u);
     if (old + 1 - fuse.counter_base == gridDim.x - (unsigned int)n_comm) {
@@ -681,7 +858,7 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   const FuseArgs& push_args = push ? *push : no_push;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(FUSE == kFuseRS ? kThreadsRS : kThreads, 1, 1);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr;
@@ -784,7 +961,7 @@ ELL_API int ell_gemm_pair_enumerate_units(int M, int N, int clusters, int allow_
   const int num_full = num_tiles - n_split, num_units = num_tiles + n_split;
   if (num_units > max_units) return -1;
   for (int u = 0; u < num_units; ++u) {
-    const Unit t = decode_unit(u, tiles_m, tiles_n, num_full, fuse, rank, tp < 1 ? 1 : tp);
+    const Unit t = decode_unit(u, tiles_m, tiles_n, num_full, fuse, rank, tp < 1 ? 1 : tp, clusters);
     out[4 * u + 0] = t.mt;
     out[4 * u + 1] = t.nt;
     out[4 * u + 2] = t.n0;
@@ -968,11 +1145,14 @@ ELL_API int ell_gemm_rs_pair(const void* x, const void* W, void* y, int rows_per
   if (!b_mn) rc = make_tmap_bf16_2d(&tB, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, kBK, kHalfN);
   else       rc = make_tmap_bf16_2d(&tB, W, (uint64_t)N, (uint64_t)K, (uint64_t)N * 2, 64, kBK);
   if (rc) return rc;
-  rc = make_tmap_bf16_2d(&tC, stage_ptrs[rank], (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 128);
+  // all-reduce stages whole tiles locally; reduce-scatter writes the tiles it owns straight into the output shard
+  if (all_reduce) rc = make_tmap_bf16_2d(&tC, stage_ptrs[rank], (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 128);
+  else            rc = make_tmap_bf16_2d(&tC, y, (uint64_t)N, (uint64_t)rows_per_rank, (uint64_t)N * 2, 64, 128);
   if (rc) return rc;
   FuseArgs f{};
-  fill_fuse(f, rank, tp, n_comm, rows_per_rank, flags_per_src, epoch, stage_ptrs, flag_ptrs, red_ptrs, done_ptrs,
-            counter, counter_base);
+  // the reduce-scatter form sums in its epilogue: no reduce CTAs, no tile queue
+  fill_fuse(f, rank, tp, all_reduce ? n_comm : 0, rows_per_rank, flags_per_src, epoch, stage_ptrs, flag_ptrs, red_ptrs,
+            done_ptrs, counter, counter_base);
   f.y_local = (__nv_bfloat16*)y;
   f.queue_base = queue_base;
   FuseArgs ps{};

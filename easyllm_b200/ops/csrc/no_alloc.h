@@ -32,7 +32,10 @@ extern "C" {
 //
 // The call allocates nothing: no cudaMalloc/cudaFree, no library routine that allocates.
 // Set-up: the first call on each device (with that device current) looks up the device address of the
-// scratch array and caches it; make that first call outside any stream capture.
+// scratch array and caches it; make that first call outside any stream capture.  The cached address belongs
+// to the device's primary context and stays valid for as long as that context lives; after cudaDeviceReset
+// (or a driver-API context that is not the primary one) the library must be reloaded before the next call.
+// With rows == 0 the call launches no kernel; dw is set to zero when accumulate_dw is 0 and left alone otherwise.
 // The scratch is shared by every call on a device and keeps its last contents.  Nothing in it has to
 // start at zero: every partial row that the reduction reads is written in full by the same call first.
 // Two calls on one device that overlap in time (different streams, or different threads) race on the

@@ -306,7 +306,10 @@ ELL_API int ell_rmsnorm_bwd(const void* dy, const void* h, const void* w, const 
                             void* dh, float* dw, float* scratch, int rows, int cols, int accumulate_dw,
                             cudaStream_t stream) {
   if (cols % 8 || cols > kNormMaxCols) return -1;
-  if (rows == 0) return 0;
+  if (rows == 0) {
+    if (!accumulate_dw && dw) cudaMemsetAsync(dw, 0, sizeof(float) * (size_t)cols, stream);
+    return launch_status();
+  }
   run_norm_bwd(norm_grid(rows, cols, true), stream, dy, h, w, rstd, dres, dh, dw, scratch, rows, cols, accumulate_dw);
   return launch_status();
 }
@@ -359,7 +362,14 @@ ELL_API int ell_rmsnorm_bwd_static(const void* dy, const void* h, const void* w,
                                    void* dh, float* dw, int rows, int cols, int accumulate_dw, cudaStream_t stream) {
   if (cols <= 0 || cols % 8 || rows < 0) return ELL_STATIC_ERR_SHAPE;
   if (cols > ELL_STATIC_NORM_MAX_COLS) return ELL_STATIC_ERR_TOO_LARGE;
-  if (rows == 0) return ELL_STATIC_OK;
+  if (rows == 0) {
+    // no rows: the sum over rows is empty, so a dw that is not accumulated into becomes zero (a memset allocates nothing)
+    if (!accumulate_dw && dw) {
+      cudaError_t e = cudaMemsetAsync(dw, 0, sizeof(float) * (size_t)cols, stream);
+      if (e != cudaSuccess) return (int)e;
+    }
+    return ELL_STATIC_OK;
+  }
   float* scratch = nullptr;
   if (int rc = static_scratch_for_current_device(&scratch)) return rc;
   int parts = norm_grid(rows, cols, true);
@@ -368,6 +378,5 @@ ELL_API int ell_rmsnorm_bwd_static(const void* dy, const void* h, const void* w,
   // Every partial row [0, parts) is written in full by the first kernel before the second reads it,
   // so stale contents of the shared scratch are never observed.
   run_norm_bwd(parts, stream, dy, h, w, rstd, dres, dh, dw, scratch, rows, cols, accumulate_dw);
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? ELL_STATIC_OK : (int)e;
+  return launch_status();                                 // 0 == ELL_STATIC_OK, else the cudaError_t of the launch
 }

@@ -37,6 +37,9 @@ def main():
     elif c == "gemm_nt_n4096":      # few output tiles, long K: the o_proj / down_proj forward class
         x = torch.randn(4096, 11008, **bf); w = torch.randn(4096, 11008, **bf)
         fn = lambda: cu.gemm(x, w)                                                   # noqa: E731
+    elif c == "gemm_nt_k2048":      # short reduction: the o_proj forward at tp 2 (epilogue-heavy: 32 k-blocks per tile)
+        x = torch.randn(4096, 2048, **bf); w = torch.randn(4096, 2048, **bf)
+        fn = lambda: cu.gemm(x, w)                                                   # noqa: E731
     elif c == "gemm_dgrad":
         x = torch.randn(4096, 11008, **bf); w = torch.randn(11008, 4096, **bf)
         fn = lambda: cu.gemm(x, w, b_mn=True)                                        # noqa: E731
@@ -62,7 +65,7 @@ def main():
         x = torch.randn(4096, 4096, **bf); w = torch.randn(32000, 4096, **bf) * 0.02
         t = torch.randint(0, 32000, (4096,), device="cuda")
         fn = lambda: cu.gemm_ce(x, w, t, 0, 32000)                                    # noqa: E731
-    elif c in ("gemm_ag", "gemm_rs", "gemm_ar", "gemm_agk"):
+    elif c in ("gemm_ag", "gemm_rs", "gemm_rs_k2048", "gemm_ar", "gemm_agk"):
         # the fused tensor-parallel kernels on a one-rank group: same kernel, flags and staging path, no peers
         import os
         import torch.distributed as dist
@@ -81,7 +84,8 @@ def main():
             acc = torch.zeros(11008, 4096, device="cuda")
             fn = lambda: ws.agk_wgrad(dy, x, acc)                                     # noqa: E731
         else:
-            x = torch.randn(4096, 11008, **bf); w = torch.randn(4096, 11008, **bf)
+            k = 2048 if c.endswith("k2048") else 11008
+            x = torch.randn(4096, k, **bf); w = torch.randn(4096, k, **bf)
             fn = lambda: ws.gemm_rs(x, w, all_reduce=(c == "gemm_ar"))                # noqa: E731
     elif c in ("rmsnorm_fwd", "rmsnorm_bwd"):
         x = torch.randn(16384, 4096, **bf); r = torch.randn_like(x); w = torch.ones(4096, **bf)

@@ -37,7 +37,11 @@ def _peak():
     return 1590.0, "fallback"
 
 
-def timed(fn, iters, group):
+def timed(fn, iters, group, burst=1):
+    """Median CUDA-event time of ``fn`` (max over ranks).  ``burst`` > 1 times that many back-to-back calls and
+    divides: the ranks leave the barrier and the busy-wait below a few tens of microseconds apart (their clocks
+    differ), and a single fused call charges that skew to whichever rank started first; in a burst the kernels'
+    own handshakes keep the ranks in step, as the surrounding collectives do in a training step."""
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     for _ in range(3):
         fn()
@@ -48,12 +52,13 @@ def timed(fn, iters, group):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         # keep the device busy while the host prepares the launch (tensor maps, allocations), so the interval
         # between the two events is device time of the kernels only
-        torch.cuda._sleep(400000)
+        torch.cuda._sleep(400000 * burst)
         a.record()
-        fn()
+        for _ in range(burst):
+            fn()
         b.record()
         b.synchronize()
-        ts.append(a.elapsed_time(b))
+        ts.append(a.elapsed_time(b) / burst)
     t = torch.tensor([statistics.median(ts)], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return float(t)
@@ -65,6 +70,8 @@ def main():
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--burst", type=int, default=0, help="also time this many back-to-back calls per op (divided by "
+                    "the count): free of the start skew between ranks, but the operands stay in L2")
     ap.add_argument("--reduce-ctas", default="", help="comma list: time the reduce-scatter forms with these numbers "
                                                       "of dedicated reduce CTAs instead of the per-launch choice")
     a = ap.parse_args()
@@ -79,7 +86,10 @@ def main():
     x_local = torch.randn(rows, H, device="cuda", dtype=torch.bfloat16)
     results = []
 
-    def report(name, kind, M, N, K, t_fused, t_comp):
+    def burst_of(fn):
+        return timed(fn, max(4, a.iters // 2), g.tp_group, a.burst) if a.burst > 1 else None
+
+    def report(name, kind, M, N, K, t_fused, t_comp, b_fused=None, b_comp=None):
         fl = 2.0 * M * N * K
         # bytes one GPU must receive: its peers' shards of the gathered operand (ag: rows of A, agk: rows of the
         # reduction operand), the peers' partials of its own rows (rs), or both phases of the two-shot all-reduce
@@ -94,6 +104,10 @@ def main():
             print(f"{name:22s} tp{tp} {M}x{N}x{K}  fused {t_fused:7.3f} ms ({fl / t_fused / 1e9:6.0f} TF, "
                   f"{100 * row['frac_of_roofline']:5.1f}% of roofline [{src} peak])  nccl+gemm {t_comp:7.3f} ms  "
                   f"x{row['speedup']:.2f}", flush=True)
+            if b_fused is not None:
+                row["fused_burst_ms"], row["nccl_gemm_burst_ms"] = b_fused, b_comp
+                print(f"{'':22s} burst of {a.burst} (no start skew, operands L2-warm): fused {b_fused:7.3f} ms "
+                      f"({100 * bound_ms / b_fused:5.1f}% of roofline)  nccl+gemm {b_comp:7.3f} ms", flush=True)
 
     for name, N in (("qkv ag->gemm", 3 * QD // tp), ("gate_up ag->gemm", 2 * F // tp)):
         w = torch.randn(N, H, device="cuda", dtype=torch.bfloat16) * 0.02
@@ -102,7 +116,7 @@ def main():
         def comp():
             xg = mp.gather_first_dim(x_local)
             return ops.matmul_nt(xg, w)
-        report(name, "ag", T, N, H, t_f, timed(comp, a.iters, g.tp_group))
+        report(name, "ag", T, N, H, t_f, timed(comp, a.iters, g.tp_group), burst_of(lambda: ws.ag_gemm(x_local, w)), burst_of(comp))
     for name, K in (("o_proj gemm->rs", QD // tp), ("down gemm->rs", F // tp)):
         K = (K + 7) // 8 * 8
         x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
@@ -111,7 +125,7 @@ def main():
 
         def comp():
             return mp.reduce_scatter_first_dim(ops.matmul_nt(x, w))
-        report(name, "rs", T, H, K, t_f, timed(comp, a.iters, g.tp_group))
+        report(name, "rs", T, H, K, t_f, timed(comp, a.iters, g.tp_group), burst_of(lambda: ws.gemm_rs(x, w)), burst_of(comp))
         for n in [int(v) for v in a.reduce_ctas.split(",") if v]:
             ws.n_comm_rs_fixed = n
             t_n = timed(lambda: ws.gemm_rs(x, w), a.iters, g.tp_group)
@@ -128,7 +142,8 @@ def main():
         y = ops.matmul_nt(x, w)
         dist.all_reduce(y, group=g.tp_group)
         return y
-    report("down gemm->allreduce", "ar", T, H, K, t_f, timed(comp_ar, a.iters, g.tp_group))
+    report("down gemm->allreduce", "ar", T, H, K, t_f, timed(comp_ar, a.iters, g.tp_group),
+           burst_of(lambda: ws.gemm_rs(x, w, all_reduce=True)), burst_of(comp_ar))
     N = 2 * F // tp
     dy = torch.randn(T, N, device="cuda", dtype=torch.bfloat16)
     acc = torch.zeros(N, H, device="cuda")
@@ -138,7 +153,8 @@ def main():
         def comp_wg():
             xg = mp.gather_first_dim(x_local)
             return ops.matmul_tn_accum(dy, xg, acc)
-        report("gate_up ag->wgrad", "agk", N, H, T, t_f, timed(comp_wg, a.iters, g.tp_group))
+        report("gate_up ag->wgrad", "agk", N, H, T, t_f, timed(comp_wg, a.iters, g.tp_group),
+               burst_of(lambda: ws.agk_wgrad(dy, x_local, acc)), burst_of(comp_wg))
     torch.cuda.synchronize()
     cu.check_err_flag()
     if a.json and g.rank == 0:

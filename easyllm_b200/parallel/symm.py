@@ -287,9 +287,11 @@ class FusedTPWorkspace:
             rc = lib.ell_gemm_rs(*head, *tail)
         cu._check(rc, op)
         self.rs_count += grid - n_push
-        # every CTA that runs the reduce role (all but the push CTAs) overshoots the queue by one
-        self.rs_queue += lib.ell_gemm_rs_queue_advance(c_int(rows), c_int(N), c_int(self.tp),
-                                                       c_int(1 if all_reduce else 0), c_int(grid - n_push))
+        if all_reduce or not pair:
+            # the staged reduction hands tiles out through a queue that every CTA running the reduce role (all but
+            # the push CTAs) overshoots by one; the CTA-pair reduce-scatter sums in its epilogue and has no queue
+            self.rs_queue += lib.ell_gemm_rs_queue_advance(c_int(rows), c_int(N), c_int(self.tp),
+                                                           c_int(1 if all_reduce else 0), c_int(grid - n_push))
         return y
 
     def ce_combine(self, parts):

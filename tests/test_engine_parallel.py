@@ -148,3 +148,4 @@ def test_optimizer_adapter_matches_the_native_path_on_every_layout(baseline):
         for losses, norm in run_ranks(2, _train_adapter, tp, pp, sp, full, False):
             assert max(abs(a - b) for a, b in zip(losses, ref_losses)) < 5e-5, (tp, pp, sp, losses, ref_losses)
             assert abs(norm - ref_norm) < 1e-3 * ref_norm, (tp, pp, sp, norm, ref_norm)
+

@@ -129,3 +129,36 @@ def test_train_batch_refuses_a_step_after_a_kernel_gave_up_a_wait():
     opt.zero_grad()
     eng.train_batch(it)                                   # the word was cleared by the read: training goes on
     cu.check_err_flag()
+
+
+def test_synchronizing_reads_do_not_grow_with_the_number_of_micro_batches():
+    """A step may synchronise a few times (the gradient norm, the returned loss), but nothing per micro-batch: the
+    batch is parsed on the host and the kernels range-check token ids themselves.  PyTorch's sync debug mode warns on
+    every synchronising call; the count inside ``train_batch`` must be the same for 2 and for 6 micro-batches."""
+    _need_gpu()
+    import warnings
+    from easyllm_b200.engine import PipelineEngine
+    from easyllm_b200.models import llama_custom
+    from easyllm_b200.optim import ZeroOptimizer
+    from easyllm_b200.data.synthetic import synthetic_batches
+    counts = []
+    for accum in (2, 6):
+        torch.manual_seed(0)
+        m = llama_custom(num_layers=1, hidden_size=256, num_attention_heads=2, num_kv_attention_heads=2,
+                         intermediate_size=512, vocab_size=1024, bf16=True, seq_length=128,
+                         checkpoint_activations=False)
+        opt = ZeroOptimizer(m.named_parameters(), lr=1e-3, stage=1, grad_clip=1.0)
+        eng = PipelineEngine(m, opt, None, {"train_micro_batch_size_per_gpu": 1,
+                                            "gradient_accumulation_steps": accum, "bf16": {"enabled": True}})
+        it = synthetic_batches(1024, 128, 1, seed=0)
+        eng.train_batch(it)                               # set-up work of the first step may synchronise
+        torch.cuda.synchronize()
+        torch.cuda.set_sync_debug_mode("warn")
+        try:
+            with warnings.catch_warnings(record=True) as seen:
+                warnings.simplefilter("always")
+                eng.train_batch(it)
+        finally:
+            torch.cuda.set_sync_debug_mode("default")
+        counts.append(sum("synchroniz" in str(w.message).lower() for w in seen))
+    assert counts[0] == counts[1], counts

@@ -125,10 +125,30 @@ def test_pair_kernel_fused_orders(cu, tp, M, N):
             owners = {mt // tpr for mt, *_ in whole[phase * per_phase:(phase + 1) * per_phase]}
             assert owners == {(rank + phase) % tp}
         for fuse in (2, 3):
-            _, rs = cu.gemm_pair_units(M, N, resident=74, fuse=fuse, tp=tp, rank=rank, n_comm=8)
+            ncl, rs = cu.gemm_pair_units(M, N, resident=74, fuse=fuse, tp=tp, rank=rank, n_comm=8 if fuse == 3 else 0)
             assert all(u[3] == 256 for u in rs) and len(rs) == tm * tn
             assert sorted((u[0], u[1]) for u in rs) == sorted(itertools.product(range(tm), range(tn)))
-            assert sorted(mt // tpr for mt, *_ in rs[:tp]) == list(range(tp))
+            if fuse == 3:
+                assert sorted(mt // tpr for mt, *_ in rs[:tp]) == list(range(tp))
+                continue
+            # reduce-scatter (summed in the epilogue): every owner's tiles come in the same (raster) order on every
+            # rank, and an own tile trails the position where the peers compute the same tile by about two waves
+            n = tpr * tn
+            lag = min(n, -(-2 * ncl // tp))
+            per_owner = {o: [(mt - o * tpr, nt) for mt, nt, *_ in rs if mt // tpr == o] for o in range(tp)}
+            assert all(per_owner[o] == per_owner[rank] for o in range(tp))
+            pos = {(mt, nt): i for i, (mt, nt, *_) in enumerate(rs)}
+            for k, (mi, nt) in enumerate(per_owner[rank]):
+                own_at = pos[(rank * tpr + mi, nt)]
+                for o in range(tp):
+                    if o != rank:
+                        # position of tile k of owner `rank` in the PEER's order equals, by symmetry, the position
+                        # of tile k of owner o' = (o shifted) here; the peers' tiles of round k sit at or before it
+                        assert pos[(o * tpr + mi, nt)] <= own_at
+                if k + lag < n:
+                    assert own_at > pos[((rank + 1) % tp * tpr + per_owner[rank][k + lag][0], per_owner[rank][k + lag][1])]
+            assert [mt // tpr for mt, *_ in rs[-lag:]] == [rank] * lag
+        _, rs = cu.gemm_pair_units(M, N, resident=74, fuse=3, tp=tp, rank=rank, n_comm=8)
         # the reduce role's queue visits every owned 128-row tile once, in the order the owner's tiles are emitted
         order = cu.reduce_tile_order(M // tp, tn, tp, pair=True)
         assert sorted(order) == sorted(itertools.product(range(2 * tpr), range(tn)))
