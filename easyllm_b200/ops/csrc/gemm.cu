@@ -577,6 +577,7 @@ ELL_API int ell_bounded_wait_selftest(const void* flag, unsigned int want, int* 
 
 namespace ell {
 int g_no_tail_split = 0;   // shared with gemm_pair.cu
+int g_rs_lag_q = 0;
 unsigned long long g_fuse_data_bytes = 0;
 }
 // Size in bytes of each gathered / staging buffer of the fused-TP workspace: the fused kernels check every tile offset

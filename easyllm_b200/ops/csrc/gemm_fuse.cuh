@@ -67,6 +67,7 @@ struct FuseArgs {
   int shard_k;                           // row length of x_local when this struct describes a bare push (see below)
   int k_passes;                          // AGK: 2 walks every tile twice (local half of the k-range first), 1 once
   unsigned long long data_bytes;         // size of each data_ptrs[] buffer: every computed offset is checked against it
+  int rs_lag_q;                          // CTA-pair reduce-scatter: own tiles trail the peers' by this many quarter waves (0: default)
 };
 
 // Tile-granular bounds check of the fused kernels (always on: a few compares per 128-row tile).  A tile whose flag
@@ -397,6 +398,7 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_
 int make_tmap_f32_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                      uint32_t box_inner, uint32_t box_outer);
 extern int g_no_tail_split;   // 1 keeps whole tiles in an under-filled last wave (ell_gemm_set_tail_split)
+extern int g_rs_lag_q;        // see FuseArgs::rs_lag_q (ell_gemm_set_rs_lag)
 extern unsigned long long g_fuse_data_bytes;   // size of every gathered / staging buffer (ell_gemm_set_fused_buffer_bytes)
 
 }  // namespace ell

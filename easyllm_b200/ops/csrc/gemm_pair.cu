@@ -39,13 +39,14 @@ namespace pair {
 constexpr int kTileM = 256, kTileN = 256;   // per cluster
 constexpr int kHalfM = 128, kHalfN = 128;   // rows of A / rows of B staged by one CTA
 constexpr int kThreads = kGemmThreads;      // warp 0 producer, warp 1 MMA issuer + TMEM owner, warps 2-5 epilogue
-constexpr int kThreadsRS = kGemmThreads + 32;   // reduce-scatter form: warp 6 prefetches the peers' partial sums
+constexpr int kThreadsRS = kGemmThreads + 64;   // reduce-scatter form: warp 6 prefetches the peers' partial sums,
+                                                // warp 7 sends staged blocks to their owners and raises the flags
 constexpr int kStages = 6;
 constexpr int kABytes = kHalfM * kBK * 2;   // 16 KiB
 constexpr int kBBytes = kHalfN * kBK * 2;   // 16 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 2 * kTileN;       // two accumulator buffers
-constexpr int kSmemBytes = kStages * kStageBytes + 2 * kEpiBufBytes + 1024 + 256;
+constexpr int kSmemBytes = kStages * kStageBytes + 2 * kEpiBufBytes + 1024 + 512;
 constexpr int kGroupM = 8;                  // rasterisation: 8 M-tiles x all N-tiles per group
 enum Err { kErrPairProducer = 11, kErrPairMma = 12, kErrPairEpilogue = 13, kErrPairFlagWait = 15 };
 
@@ -57,6 +58,10 @@ struct Shared {
   uint64_t part_full[2];    // reduce-scatter: a peer's partial 128 x 64 block has landed in epilogue buffer i
   uint64_t part_empty[2];   // ... and all 128 epilogue threads have added it
   uint64_t stage_free;      // ... the epilogue buffers are no longer read by bulk stores of staged blocks
+  uint64_t chunk_ready[2];  // reduce-scatter: a staged 128 x 64 block sits in epilogue buffer i (128 writers)
+  uint64_t buf_free[2];     // ... and the bulk store that sends it has read the buffer
+  unsigned long long post_dst[2];   // where block i goes (a peer's staging buffer; 0: nowhere)
+  unsigned long long post_flag[2];  // the flag to raise once the block and its predecessors of the tile have landed (0: none)
   uint32_t tmem_base;
   int abort_flag;
   int epi_abort;
@@ -155,10 +160,21 @@ __host__ __device__ inline int split_tail(int num_tiles, int clusters, bool allo
 // fp32 accumulation, so the two passes simply add up.
 // Rounds by which a rank's own tiles trail the peers' in the reduce-scatter order: about two waves of tiles, so a
 // partial sum has been computed, sent and flagged well before the owner's epilogue asks for it.
-__host__ __device__ __forceinline__ int rs_lag(int tiles_per_owner, int n_clusters, int tp) {
+__host__ __device__ __forceinline__ int rs_lag(int tiles_per_owner, int n_clusters, int tp, int lag_q) {
   if (tp <= 1) return 0;
-  const int lag = (2 * n_clusters + tp - 1) / tp;
+  const int q = lag_q > 0 ? lag_q : 8;                        // quarter waves; default two waves
+  int lag = (q * n_clusters + 4 * tp - 1) / (4 * tp);
+  if (lag < 1) lag = 1;
   return lag < tiles_per_owner ? lag : tiles_per_owner;
+}
+
+// Half-width units in the last wave of a reduce-scatter launch: only when every tile of that wave is one the rank
+// owns (the closing `lag` tiles of its order are), because the peers' flags cover whole tiles.
+__host__ __device__ __forceinline__ int rs_split_tail(int tiles_m, int tiles_n, int n_clusters, int tp, int lag_q,
+                                                      bool allowed) {
+  const int n = (tiles_m / (tp < 1 ? 1 : tp)) * tiles_n;
+  const int tail = split_tail(tiles_m * tiles_n, n_clusters, allowed);
+  return (tp <= 1 || tail <= rs_lag(n, n_clusters, tp, lag_q)) ? tail : 0;
 }
 
 // Reduce-scatter order of rank `rank`: round k computes tile k (raster order inside a shard) of every OTHER owner,
@@ -185,7 +201,7 @@ __host__ __device__ __forceinline__ int rs_order(int pos, int n, int tp, int lag
 }
 
 __host__ __device__ __forceinline__ Unit decode_unit(int unit, int tiles_m, int tiles_n, int num_full, int fuse, int rank,
-                                                     int tp, int n_clusters) {
+                                                     int tp, int n_clusters, int lag_q = 0) {
   Unit u;
   int tile = unit, half = -1;
   if (unit >= num_full) {
@@ -207,7 +223,7 @@ __host__ __device__ __forceinline__ Unit decode_unit(int unit, int tiles_m, int 
   } else if (fuse == kFuseRS) {
     const int tpr = tiles_m / tp, n = tpr * tiles_n;
     int k, mi;
-    const int owner = rs_order(tile, n, tp, rs_lag(n, n_clusters, tp), rank, k);
+    const int owner = rs_order(tile, n, tp, rs_lag(n, n_clusters, tp, lag_q), rank, k);
     raster(k, tpr, tiles_n, mi, u.nt);
     u.mt = owner * tpr + mi;
   } else if (fuse == kFuseAR) {
@@ -265,7 +281,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int k_passes = FUSE == kFuseAGK ? (fuse.k_passes == 2 ? 2 : 1) : 1;
   const int num_tiles = tiles_m * tiles_n * k_passes;   // kFuseAGK while the rows still arrive: two k-passes per tile
   const int num_kb = (K + kBK - 1) / kBK;
-  const int n_split = split_tail(num_tiles, n_clusters, !kReduce && !fuse.no_tail_split);
+  const int n_split = FUSE == kFuseRS ? rs_split_tail(tiles_m, tiles_n, n_clusters, fuse.tp, fuse.rs_lag_q, !fuse.no_tail_split)
+                                      : split_tail(num_tiles, n_clusters, !kReduce && !fuse.no_tail_split);
   const int num_full = num_tiles - n_split, num_units = num_tiles + n_split;
 
   if (threadIdx.x == 0) {
@@ -278,6 +295,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&sh->tmem_empty[a], 2 * kEpiThreads);
       mbar_init(&sh->part_full[a], 1);
       mbar_init(&sh->part_empty[a], kEpiThreads);
+      mbar_init(&sh->chunk_ready[a], kEpiThreads);
+      mbar_init(&sh->buf_free[a], 1);
     }
     mbar_init(&sh->stage_free, 1);
     sh->abort_flag = 0;
@@ -336,7 +355,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         return true;
       };
       for (int unit = cluster_id; unit < num_units && ok; unit += n_clusters) {
-        const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp, n_clusters);
+        const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp, n_clusters, fuse.rs_lag_q);
         const int b_rows = u.bn / 2;                                // B rows staged by one CTA (128, or 64 in a half unit)
         const int m0 = u.mt * kTileM + (int)cta_rank * kHalfM;     // A rows of this CTA
         const int nb0 = u.n0 + (int)cta_rank * b_rows;             // B rows of this CTA
@@ -466,7 +485,50 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         atomicCAS(err, 0, kErrPairMma);
       }
     }
-  } else if (warp >= 6) {
+  } else if (warp == 7) {
+    // ------------------------------ sender of staged blocks (reduce-scatter form) ----------
+    // One thread issues every bulk store into the peers' staging buffers and raises the tile flags, so no epilogue
+    // thread ever waits for a transfer over NVLink to complete or for a system-scope fence.
+    if (FUSE == kFuseRS && lane == 0 && fuse.tp > 1) {
+      bool ok = true;
+      uint32_t sent = 0, freed = 0;
+      auto release_read = [&](uint32_t upto) {      // buffers of blocks [freed, upto) have been read by their stores
+        for (; freed < upto; ++freed) mbar_arrive(&sh->buf_free[freed & 1]);
+      };
+      for (int unit = cluster_id; unit < num_units && ok; unit += n_clusters) {
+        const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp, n_clusters, fuse.rs_lag_q);
+        if ((u.mt * kTileM) / fuse.rows_per_rank == fuse.rank) continue;
+        for (int j = 0; j < u.bn / 64 && ok; ++j) {
+          const uint32_t b = sent & 1;
+          if (!mbar_wait(&sh->chunk_ready[b], (sent >> 1) & 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* dst = reinterpret_cast<uint8_t*>(sh->post_dst[b]);
+          uint32_t* flag = reinterpret_cast<uint32_t*>(sh->post_flag[b]);
+          if (dst != nullptr) bulk_store(dst, sC + b * kEpiBufBytes, kEpiBufBytes);
+          tma_store_commit();
+          ++sent;
+          if (flag == nullptr) {
+            tma_store_wait_read<1>();               // the store before this one has read its buffer
+            release_read(sent - 1);
+          } else {
+            tma_store_wait_read<0>();
+            release_read(sent);
+            tma_store_wait_all<0>();                // the whole tile has landed on its owner
+            fence_proxy_async_all();
+            __threadfence_system();
+            st_release_sys(flag, fuse.epoch);
+          }
+        }
+      }
+      tma_store_wait_all<0>();
+      if (!ok) {
+        sh->abort_flag = 1;
+        atomicCAS(err, 0, kErrPairEpilogue);
+      }
+    }
+  } else if (warp == 6) {
     // ------------------------------ partial-sum prefetch (reduce-scatter form) -------------
     // For every tile this rank owns: wait until all peers have flagged their partial block, then stream the
     // (tp - 1) x 4 staged 128 x 64 blocks from the LOCAL staging buffer through the two epilogue buffers, in the
@@ -476,7 +538,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       uint32_t item = 0, own_idx = 0;
       for (int unit = cluster_id; unit < num_units && ok; unit += n_clusters) {
-        const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp, n_clusters);
+        const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp, n_clusters, fuse.rs_lag_q);
         const int m0 = u.mt * kTileM + (int)cta_rank * kHalfM;
         if (m0 / fuse.rows_per_rank != fuse.rank) continue;
         const int mi = (m0 - fuse.rank * fuse.rows_per_rank) / kBM;
@@ -495,7 +557,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         ++own_idx;
         if (!ok) break;
         fence_proxy_async_all();       // peers' writes -> bulk loads (async proxy)
-        for (int j = 0; j < kTileN / 64 && ok; ++j)
+        const int j0 = (u.n0 - u.nt * kTileN) / 64;      // a half-width unit covers chunks 0-1 or 2-3 of its tile
+        for (int j = j0; j < j0 + u.bn / 64 && ok; ++j)
           for (int si = 1; si < fuse.tp; ++si, ++item) {
             const int src = (fuse.rank + si) % fuse.tp;
             const uint32_t slot = item & 1;
@@ -526,6 +589,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t store_count = 0;
     uint32_t* pending_flag = nullptr;   // reduce forms: flag of the last staged block, raised once its stores completed
     uint32_t part_item = 0;             // reduce-scatter: partial blocks consumed so far (selects buffer and parity)
+    uint32_t staged = 0;                // reduce-scatter: blocks handed to warp 7 so far
     if (kReduce && store_thread) {
       // peers must have finished reading last epoch's staged tiles before they are overwritten
       for (int p = 0; p < fuse.tp; ++p)
@@ -535,7 +599,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
     }
     for (int unit = cluster_id; unit < num_units; unit += n_clusters, ++it) {
-      const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp, n_clusters);
+      const Unit u = decode_unit(unit, tiles_m, tiles_n, num_full, FUSE, fuse.rank, fuse.tp, n_clusters, fuse.rs_lag_q);
       const int m0 = u.mt * kTileM + (int)cta_rank * kHalfM, n0 = u.n0;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -554,24 +618,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       const bool own_tile = FUSE == kFuseRS && m0 / fuse.rows_per_rank == fuse.rank;
-      if (own_tile && store_thread && pending_flag != nullptr) {
-        // the staged block of the previous tile is published before this CTA turns to a tile of its own
-        tma_store_wait_all<0>();
-        fence_proxy_async_all();
-        __threadfence_system();
-        st_release_sys(pending_flag, fuse.epoch);
-        pending_flag = nullptr;
-      }
       if (own_tile && fuse.tp > 1) {
         // A tile this rank owns: add the peers' partial sums (prefetched by warp 6) and write the output shard.
         if (store_thread) {
-          // the epilogue buffers may still be read by the bulk stores of a staged block: hand them to warp 6 after that
-          tma_store_wait_read<0>();
+          // the epilogue buffers may still be read by warp 7's stores of the last two staged blocks: hand them to
+          // warp 6 after that
+          for (uint32_t d = 1; d <= 2 && d <= staged; ++d) {
+            const uint32_t c = staged - d;
+            if (!mbar_wait(&sh->buf_free[c & 1], (c >> 1) & 1, abort_flag)) {
+              sh->epi_abort = 1;
+              sh->abort_flag = 1;
+            }
+          }
           mbar_arrive(&sh->stage_free);
         }
         const int row0_local = m0 - fuse.rank * fuse.rows_per_rank;
 #pragma unroll 1
-        for (int j = 0; j < kTileN / 64; ++j) {
+        for (int j = 0; j < u.bn / 64; ++j) {
           uint32_t r[64];
           tmem_ld_32x32(t_row + j * 64, r);
           tmem_ld_32x32(t_row + j * 64 + 32, r + 32);
@@ -617,11 +680,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       } else if (OUT == kOutBf16 || OUT == kOutBf16CE) {
+        // reduce-scatter, a tile another rank owns: the blocks go to warp 7 instead of being stored from here
+        const bool to_sender = FUSE == kFuseRS && !own_tile;
 #pragma unroll 1
         for (int j = 0; j < u.bn / 64; ++j) {
-          uint8_t* buf = sC + (store_count & 1) * kEpiBufBytes;
-          if (store_thread) tma_store_wait_read<1>();
-          named_bar_sync(1, kEpiThreads);
+          uint8_t* buf = sC + ((to_sender ? staged : store_count) & 1) * kEpiBufBytes;
+          if (to_sender) {
+            if (!mbar_wait(&sh->buf_free[staged & 1], ((staged >> 1) & 1) ^ 1, abort_flag)) {
+              sh->epi_abort = 1;
+              sh->abort_flag = 1;
+            }
+          } else {
+            if (store_thread) tma_store_wait_read<1>();
+            named_bar_sync(1, kEpiThreads);
+          }
           uint32_t r[64];
           tmem_ld_32x32(t_row + j * 64, r);
           tmem_ld_32x32(t_row + j * 64 + 32, r + 32);
@@ -670,18 +742,30 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             *reinterpret_cast<uint4*>(row_ptr + ((c ^ (row_in_tile & 7)) << 4)) = v;  // 128B swizzle
           }
           fence_proxy_async_smem();
+          if (to_sender) {
+            if (store_thread) {
+              // the owner's staging buffer, slot of this source rank; the tile's last block carries its flag
+              const int owner = m0 / fuse.rows_per_rank;
+              const int mi = (m0 - owner * fuse.rows_per_rank) / kBM;
+              const size_t off = stage_block<kTileN>(fuse.rank * (fuse.rows_per_rank / kBM) + mi, u.nt, j, tiles_n);
+              const long long fidx = (long long)mi * tiles_n + u.nt;
+              const bool ok_idx = fuse_in_bounds(fuse, fidx, off + kEpiBufBytes, err);
+              sh->post_dst[staged & 1] =
+                  ok_idx ? reinterpret_cast<unsigned long long>(reinterpret_cast<uint8_t*>(fuse.data_ptrs[owner]) + off) : 0ull;
+              sh->post_flag[staged & 1] =
+                  (ok_idx && j == u.bn / 64 - 1)
+                      ? reinterpret_cast<unsigned long long>(fuse.flag_ptrs[owner] + (size_t)fuse.rank * fuse.flags_per_src + fidx)
+                      : 0ull;
+            }
+            mbar_arrive(&sh->chunk_ready[staged & 1]);
+            ++staged;
+            continue;
+          }
           named_bar_sync(1, kEpiThreads);
           if (store_thread) {
             if (own_tile) {
               // one-rank group: nothing to add, the tile is the output
               tma_store_2d(&tmC, buf, n0 + j * 64, m0 - fuse.rank * fuse.rows_per_rank);
-            } else if (FUSE == kFuseRS) {
-              // the owner's staging buffer, slot of this source rank
-              const int owner = m0 / fuse.rows_per_rank;
-              const int mi = (m0 - owner * fuse.rows_per_rank) / kBM;
-              const size_t off = stage_block<kTileN>(fuse.rank * (fuse.rows_per_rank / kBM) + mi, u.nt, j, tiles_n);
-              if (fuse_in_bounds(fuse, 0, off + kEpiBufBytes, err))
-                bulk_store(reinterpret_cast<uint8_t*>(fuse.data_ptrs[owner]) + off, buf, kEpiBufBytes);
             } else if (kReduce) {
               const size_t off = stage_block<kTileN>(m0 / kBM, u.nt, j, tiles_n);
               if (fuse_in_bounds(fuse, 0, off + kEpiBufBytes, err))
@@ -709,13 +793,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
         }
-        if (kReduce && store_thread && !own_tile) {
+        if (kStagedReduce && store_thread) {
           // Publish the flag of the PREVIOUS block: its bulk stores were committed 4 groups ago, so waiting until
           // at most 4 groups are pending does not stall behind this block's stores.
           if (pending_flag != nullptr) {
             tma_store_wait_all<kTileN / 64>();
             fence_proxy_async_all();
-            if (FUSE == kFuseRS) __threadfence_system();   // the blocks were written into a peer's memory
             st_release_sys(pending_flag, fuse.epoch);
           }
           const int owner = m0 / fuse.rows_per_rank;
@@ -759,9 +842,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     if (store_thread) {
       tma_store_wait_all<0>();
-      if (kReduce && pending_flag != nullptr) {
+      if (kStagedReduce && pending_flag != nullptr) {
         fence_proxy_async_all();
-        if (FUSE == kFuseRS) __threadfence_system();
         st_release_sys(pending_flag, fuse.epoch);
       }
     }
@@ -901,6 +983,7 @@ static void fill_fuse(FuseArgs& f, int rank, int tp, int n_comm, int rows_per_ra
   f.queue = f.counter + 1;
   f.no_tail_split = g_no_tail_split;
   f.data_bytes = g_fuse_data_bytes;
+  f.rs_lag_q = g_rs_lag_q;
 }
 
 // LM-head form: logits + cross-entropy partials, optionally behind the all-gather of the hidden rows.
@@ -957,11 +1040,12 @@ ELL_API int ell_gemm_pair_enumerate_units(int M, int N, int clusters, int allow_
   const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + kTileN - 1) / kTileN;
   const int num_tiles = tiles_m * tiles_n * (fuse == kFuseAGK ? 2 : 1);
   const bool reduce = fuse == kFuseRS || fuse == kFuseAR;
-  const int n_split = split_tail(num_tiles, clusters, allow_split != 0 && !reduce);
+  const int n_split = fuse == kFuseRS ? rs_split_tail(tiles_m, tiles_n, clusters, tp < 1 ? 1 : tp, g_rs_lag_q, allow_split != 0)
+                                      : split_tail(num_tiles, clusters, allow_split != 0 && !reduce);
   const int num_full = num_tiles - n_split, num_units = num_tiles + n_split;
   if (num_units > max_units) return -1;
   for (int u = 0; u < num_units; ++u) {
-    const Unit t = decode_unit(u, tiles_m, tiles_n, num_full, fuse, rank, tp < 1 ? 1 : tp, clusters);
+    const Unit t = decode_unit(u, tiles_m, tiles_n, num_full, fuse, rank, tp < 1 ? 1 : tp, clusters, g_rs_lag_q);
     out[4 * u + 0] = t.mt;
     out[4 * u + 1] = t.nt;
     out[4 * u + 2] = t.n0;
@@ -980,6 +1064,9 @@ ELL_API int ell_gemm_owned_tile_order(int rows_per_rank, int tiles_n, int tp, in
 }
 
 // Two-CTA clusters of the pair kernel that fit on the current device at once (needs a GPU; <= 0 if it cannot run).
+// Rounds by which a rank's own tiles trail the peers' in the CTA-pair reduce-scatter, in quarter waves (0: default).
+ELL_API void ell_gemm_set_rs_lag(int quarter_waves) { ell::g_rs_lag_q = quarter_waves < 0 ? 0 : quarter_waves; }
+
 ELL_API int ell_gemm_pair_resident_clusters() { return ell::pair::resident_clusters(); }
 
 // Clusters the kernel would launch for `tiles` tiles when `resident` clusters fit on the device.
@@ -1146,6 +1233,12 @@ ELL_API int ell_gemm_rs_pair(const void* x, const void* W, void* y, int rows_per
   else       rc = make_tmap_bf16_2d(&tB, W, (uint64_t)N, (uint64_t)K, (uint64_t)N * 2, 64, kBK);
   if (rc) return rc;
   // all-reduce stages whole tiles locally; reduce-scatter writes the tiles it owns straight into the output shard
+  // B with a box of 64 rows for the half-width units that may close a reduce-scatter launch
+  CUtensorMap tBh = tB;
+  if (!b_mn) {
+    rc = make_tmap_bf16_2d(&tBh, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, kBK, kHalfN / 2);
+    if (rc) return rc;
+  }
   if (all_reduce) rc = make_tmap_bf16_2d(&tC, stage_ptrs[rank], (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 128);
   else            rc = make_tmap_bf16_2d(&tC, y, (uint64_t)N, (uint64_t)rows_per_rank, (uint64_t)N * 2, 64, 128);
   if (rc) return rc;
@@ -1169,6 +1262,6 @@ ELL_API int ell_gemm_rs_pair(const void* x, const void* W, void* y, int rows_per
     if (b_mn) return launch<false, true, kOutBf16, false, kFuseAR>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream, pp);
     return launch<false, false, kOutBf16, false, kFuseAR>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream, pp);
   }
-  if (b_mn) return launch<false, true, kOutBf16, false, kFuseRS>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream, pp);
-  return launch<false, false, kOutBf16, false, kFuseRS>(tA, tB, tC, tB, tA, f, nullptr, M, N, K, err, stream, pp);
+  if (b_mn) return launch<false, true, kOutBf16, false, kFuseRS>(tA, tB, tC, tBh, tA, f, nullptr, M, N, K, err, stream, pp);
+  return launch<false, false, kOutBf16, false, kFuseRS>(tA, tB, tC, tBh, tA, f, nullptr, M, N, K, err, stream, pp);
 }

@@ -126,11 +126,19 @@ def test_pair_kernel_fused_orders(cu, tp, M, N):
             assert owners == {(rank + phase) % tp}
         for fuse in (2, 3):
             ncl, rs = cu.gemm_pair_units(M, N, resident=74, fuse=fuse, tp=tp, rank=rank, n_comm=8 if fuse == 3 else 0)
-            assert all(u[3] == 256 for u in rs) and len(rs) == tm * tn
-            assert sorted((u[0], u[1]) for u in rs) == sorted(itertools.product(range(tm), range(tn)))
             if fuse == 3:
+                assert all(u[3] == 256 for u in rs) and len(rs) == tm * tn
+                assert sorted((u[0], u[1]) for u in rs) == sorted(itertools.product(range(tm), range(tn)))
                 assert sorted(mt // tpr for mt, *_ in rs[:tp]) == list(range(tp))
                 continue
+            # an under-filled last wave is cut into half-width units only where every tile of it is the rank's own
+            halves = [u for u in rs if u[3] == 128]
+            assert all(mt // tpr == rank for mt, *_ in halves) and len(halves) % 2 == 0
+            assert len(halves) // 2 <= min(tpr * tn, -(-2 * ncl // tp))
+            cover = sorted((mt, c) for mt, nt, n0, bn in rs for c in range(n0, n0 + bn, 128))
+            assert cover == sorted(itertools.product(range(tm), range(0, tn * 256, 128)))
+            rs = [u for i, u in enumerate(rs) if u[3] == 256 or rs[i - 1][:2] != u[:2] or rs[i - 1][3] == 256]
+            assert len(rs) == tm * tn
             # reduce-scatter (summed in the epilogue): every owner's tiles come in the same (raster) order on every
             # rank, and an own tile trails the position where the peers compute the same tile by about two waves
             n = tpr * tn
