@@ -82,7 +82,7 @@ def test_zero_fused_2gpu():
 
 
 WORKER_Z2 = r'''
-import os, sys, torch, torch.distributed as dist
+import gc, os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["ELL_ROOT"])
 from easyllm_b200.parallel.grid import initialize_distributed, get_grid
 from easyllm_b200.models import llama_custom
@@ -114,20 +114,24 @@ def run(stage, fused):
     torch.cuda.synchronize()
     cu.check_err_flag()
     peak = torch.cuda.max_memory_allocated()
-    flat = torch.cat([p.detach().float().flatten() for p in model.parameters()])
+    # the copy of the parameters goes to the host: a 4-byte copy of the model left on the device would count as
+    # resident memory of the next run
+    flat = torch.cat([p.detach().float().flatten() for p in model.parameters()]).cpu()
     out = (losses, float(eng.get_global_grad_norm()), peak, base, flat, len(getattr(opt, "_buckets", [])),
            getattr(opt, "_n_bufs", 0))
     del eng, opt, model
+    gc.collect()
     torch.cuda.empty_cache()
     return out
 
 l1, n1, peak1, base1, p1, _, _ = run(1, False)
 l2, n2, peak2, base2, p2, nb, nbuf = run(2, False)
 l3, n3, _, _, p3, _, _ = run(2, True)                     # Adam + parameter all-gather by peer stores
-ref = p2.clone(); dist.broadcast(ref, src=0)
-same = bool((p2 == ref).all())
-ref3 = p3.clone(); dist.broadcast(ref3, src=0)
-same = same and bool((p3 == ref3).all())
+ref = p2.cuda(); dist.broadcast(ref, src=0)
+same = bool((p2 == ref.cpu()).all())
+ref3 = p3.cuda(); dist.broadcast(ref3, src=0)
+same = same and bool((p3 == ref3.cpu()).all())
+del ref, ref3
 # two Adam kernels round the same fp32 update to bf16: a parameter may differ by one bf16 ulp (0.0078 near 1.0)
 assert max(abs(a - b) for a, b in zip(l2, l3)) < 1e-3 and (p2 - p3).abs().max().item() < 1e-2, (l2, l3)
 assert (p2 - p3).abs().mean().item() < 1e-4
