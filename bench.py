@@ -119,6 +119,8 @@ def main():
     ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "cublas"])
     ap.add_argument("--ops", default=None, choices=[None, "b200", "torch"])
     ap.add_argument("--recompute-layers", type=int, default=0, help="leading layers per stage to recompute")
+    ap.add_argument("--dc-map", default="", help="Dynamic Checkpoint size map 'tokens:layers,...': a micro-batch with at "
+                    "most that many tokens recomputes that many leading layers per stage (chosen per micro-batch)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--runner", default="megatron", choices=["megatron", "hf"],
                     help="megatron: 3D-parallel LlamaModelPipe + PipelineEngine; hf: HF-style decoder + ZeRO data-parallel engine")
@@ -166,6 +168,8 @@ def main():
     dc = None
     if args.recompute_layers:
         dc = {"enabled": True, "size_map": {1 << 30: args.recompute_layers}}
+    if args.dc_map:
+        dc = {"enabled": True, "size_map": {int(k): int(v) for k, v in (kv.split(":") for kv in args.dc_map.split(","))}}
     if args.runner == "hf":
         if g.tp > 1 or g.pp > 1:
             raise SystemExit("--runner hf is data-parallel only: pass --tp 1 --pp 1")
@@ -311,7 +315,7 @@ def main():
                           "runner": args.runner,
                           "micro_batch": 1, "grad_accum": n_micro, "optimizer": "fused Adam wd 0.1 clip 1.0",
                           "gemm": ops.get_gemm_backend(), "gemm_cta_pair": _pair_on(ops), "ops": ops.get_backend(), "fused_tp": fused_tp,
-                          "recompute_layers": args.recompute_layers,
+                          "recompute_layers": args.recompute_layers, "dynamic_checkpoint_map": args.dc_map or None,
                           "l2": "inputs (weights+activations) far larger than L2; no flush",
                           "vs_baseline_note": "per-GPU tokens/s over the published 4304 tok/s/GPU "
                                               "(7B seq 4096 ZeRO-1 row, other hardware)"},
