@@ -275,13 +275,32 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_ld_wait();
 #pragma unroll
           for (int g8 = 0; g8 < 4; ++g8) {
+            // exp2(s * scale - lse): the exponentials and the two bf16 conversions of a score share the 4-lane
+            // special-function pipe; three of every four 8-column groups use the FMA-pipe polynomial instead
             float p[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              float off = -lse2;
-              if (alibi_slopes != nullptr) off = fmaf(slope2, (float)(k0 + col_base + c * 32 + g8 * 8 + e - row), -lse2);
-              p[e] = exp2f(fmaf(__uint_as_float(v[g8 * 8 + e]), scale_log2, off));
-              if (need_mask) {
+            for (int e = 0; e < 8; e += 2) {
+              float off0 = -lse2, off1 = -lse2;
+              if (alibi_slopes != nullptr) {
+                const float d0 = (float)(k0 + col_base + c * 32 + g8 * 8 + e - row);
+                off0 = fmaf(slope2, d0, -lse2);
+                off1 = fmaf(slope2, d0 + 1.f, -lse2);
+              }
+              const float2 x = ffma2(make_float2(__uint_as_float(v[g8 * 8 + e]), __uint_as_float(v[g8 * 8 + e + 1])),
+                                     make_float2(scale_log2, scale_log2), make_float2(off0, off1));
+              float2 pe;
+              if (g8 != 0) {
+                pe = exp2_poly2(x);
+              } else {
+                pe.x = ex2_approx(x.x);
+                pe.y = ex2_approx(x.y);
+              }
+              p[e] = pe.x;
+              p[e + 1] = pe.y;
+            }
+            if (need_mask) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
                 const int kidx = k0 + col_base + c * 32 + g8 * 8 + e;
                 if (kidx > row || kidx < my_start || !row_valid) p[e] = 0.f;
               }

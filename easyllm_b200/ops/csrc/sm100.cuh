@@ -210,5 +210,60 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+
+// ---- packed fp32 pairs and exp2 off the special-function unit --------------------------------
+// fma / add on two fp32 lanes per instruction (f32x2), the three-input maximum, and 2^x evaluated on the FMA
+// pipe.  Per scheduler and clock an SM has 32 FMA lanes, 16 ALU lanes and 4 lanes of the special-function /
+// conversion pipe; a softmax that sends every exponential and every fp32 -> bf16 conversion through the latter
+// spends 0.375 cycles per element there and is bound by it, not by the tensor core.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float d;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(d) : "f"(x));
+  return d;
+}
+// 2^x for two values, x <= 127: round x to the nearest integer n with the 1.5 * 2^23 trick, a cubic for 2^(x - n)
+// on [-0.5, 0.5] (relative error 7.5e-5, well under bf16 rounding), n added to the exponent field.  Inputs below
+// -126 (including -inf) are clamped and come out as ~1e-38.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  constexpr float kMagic = 12582912.f;
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = fadd2(x, make_float2(kMagic, kMagic));
+  const float2 n = fadd2(t, make_float2(-kMagic, -kMagic));
+  const float2 f = ffma2(n, make_float2(-1.f, -1.f), x);
+  float2 p = ffma2(f, make_float2(0.055170249f, 0.055170249f), make_float2(0.24260791f, 0.24260791f));
+  p = ffma2(p, f, make_float2(0.69326091f, 0.69326091f));
+  p = ffma2(p, f, make_float2(0.99992830f, 0.99992830f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+
 }  // namespace sm100
 }  // namespace ell

@@ -72,8 +72,6 @@ def main():
     ap.add_argument("--json", default=None)
     ap.add_argument("--burst", type=int, default=0, help="also time this many back-to-back calls per op (divided by "
                     "the count): free of the start skew between ranks, but the operands stay in L2")
-    ap.add_argument("--reduce-ctas", default="", help="comma list: time the reduce-scatter forms with these numbers "
-                                                      "of dedicated reduce CTAs instead of the per-launch choice")
     a = ap.parse_args()
     tp = int(os.environ.get("WORLD_SIZE", "1"))
     initialize_distributed(tp=tp, pp=1, backend="nccl")
@@ -126,12 +124,6 @@ def main():
         def comp():
             return mp.reduce_scatter_first_dim(ops.matmul_nt(x, w))
         report(name, "rs", T, H, K, t_f, timed(comp, a.iters, g.tp_group), burst_of(lambda: ws.gemm_rs(x, w)), burst_of(comp))
-        for n in [int(v) for v in a.reduce_ctas.split(",") if v]:
-            ws.n_comm_rs_fixed = n
-            t_n = timed(lambda: ws.gemm_rs(x, w), a.iters, g.tp_group)
-            ws.n_comm_rs_fixed = None
-            if g.rank == 0:
-                print(f"    {name} with {n} reduce CTAs: {t_n:7.3f} ms (default {ws._reduce_ctas(K)}: {t_f:7.3f} ms)", flush=True)
     # the backward and non-sequence-parallel forms, on the widest layer of the model
     K = (F // tp + 7) // 8 * 8
     x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
