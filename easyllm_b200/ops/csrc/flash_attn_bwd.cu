@@ -330,12 +330,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_ld_wait();
 #pragma unroll
           for (int g8 = 0; g8 < 4; ++g8) {
+            // dS = P * (dP - delta) * scale, two scores per instruction: (dP * scale - delta * scale), then times P
             float d[8];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float2 pp = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&pk[c * 16 + g8 * 4 + e]));
-              d[2 * e] = pp.x * (__uint_as_float(v[g8 * 8 + 2 * e]) - dlt) * scale;
-              d[2 * e + 1] = pp.y * (__uint_as_float(v[g8 * 8 + 2 * e + 1]) - dlt) * scale;
+              const float2 t = ffma2(make_float2(__uint_as_float(v[g8 * 8 + 2 * e]), __uint_as_float(v[g8 * 8 + 2 * e + 1])),
+                                     make_float2(scale, scale), make_float2(-dlt * scale, -dlt * scale));
+              const float2 ds = ffma2(pp, t, make_float2(0.f, 0.f));
+              d[2 * e] = ds.x;
+              d[2 * e + 1] = ds.y;
             }
             *reinterpret_cast<bf16x8*>(ds_row + (((c * 4 + g8) ^ sw) << 4)) = pack8(d);
           }
