@@ -8,7 +8,7 @@
 //   dV_j += P^T dO_i          dK_j += dS^T Q_i          dQ_i += dS K_j      (fp32, reduced across CTAs)
 // 320 threads:
 //   warp 0      TMA: K_j, V_j once; Q_i, dO_i per step
-//   warp 1      one thread issues the five MMAs of a step; TMEM columns: S|dQ 0-127, dP 128-255,
+//   warp 1      one thread issues the five MMAs of a step; TMEM columns: S 0-127, dP|dQ 128-255,
 //               dV 256-383, dK 384-511.  P and dS reach the tensor core through swizzled shared memory;
 //               the transposed operands (P^T, dS^T, and dO, Q, K as [k x n] operands) are read in place
 //               with MN-major descriptors, so nothing is transposed in memory.
@@ -17,6 +17,9 @@
 //               fp32 staging, half in the dS buffer and half in a dedicated tile -> cp.reduce.async.bulk add
 //               into the fp32 dQ accumulator; nothing waits for the adds until the buffers are needed again),
 //               and at the end write dV_j / dK_j.
+// Order of a step: S_i is issued as soon as Q_i has landed (its columns were read out a step ago), dP_i after the dQ
+// tile of step i-1 has been drained from the columns they share (dP is not needed before the P pass is over), dQ_i
+// before dK_i, so the drain of dQ_i overlaps dK_i: the softmax warps never wait for an MMA that could have run earlier.
 // Every wait is bounded; on expiry the CTA records an error code, runs the remaining steps without
 // touching global memory, frees its TMEM and returns.
 //
@@ -178,21 +181,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int it = 0; it < n_it && ok; ++it) {
         const uint32_t ph = it & 1;
         FB_TRACE(0, it, 0);
-        if (!mbar_wait(&sh->do_full, ph, abort_flag)) { ok = false; break; }
-        FB_TRACE(0, it, 1);
-        tc_fence_after();
-        // dP = dO V^T (the dP columns were released when dS of the previous step was published)
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kFbHalf + (k & 3) * 32;
-          umma_bf16(t_dp, make_smem_desc(do_addr + off, 16, 1024), make_smem_desc(v_addr + off, 16, 1024), idesc_kk,
-                    k != 0);
-        }
-        umma_commit(&sh->dp_full);
-        // S = Q K^T into the columns the previous dQ tile is drained from
+        // S = Q K^T: its columns were read out by the P pass of the previous step long ago
         if (!mbar_wait(&sh->q_full, ph, abort_flag)) { ok = false; break; }
-        if (it > 0 && !mbar_wait(&sh->dq_drained, (it - 1) & 1, abort_flag)) { ok = false; break; }
-        FB_TRACE(0, it, 2);
+        FB_TRACE(0, it, 1);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -201,6 +192,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     k != 0);
         }
         umma_commit(&sh->s_full);
+        // dP = dO V^T into the columns the previous dQ tile is drained from (dP is not needed before the P pass is over)
+        if (!mbar_wait(&sh->do_full, ph, abort_flag)) { ok = false; break; }
+        if (it > 0 && !mbar_wait(&sh->dq_drained, (it - 1) & 1, abort_flag)) { ok = false; break; }
+        FB_TRACE(0, it, 2);
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kFbHalf + (k & 3) * 32;
+          umma_bf16(t_dp, make_smem_desc(do_addr + off, 16, 1024), make_smem_desc(v_addr + off, 16, 1024), idesc_kk,
+                    k != 0);
+        }
+        umma_commit(&sh->dp_full);
         // dV += P^T dO
         if (!mbar_wait(&sh->p_full, ph, abort_flag)) { ok = false; break; }
         FB_TRACE(0, it, 3);
@@ -210,22 +213,23 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_bf16(t_dv, make_smem_desc(p_addr + k * 2048, kFbHalf, 1024),
                     make_smem_desc(do_addr + k * 2048, kFbHalf, 1024), idesc_mm, (it | k) != 0);
         umma_commit(&sh->do_empty);
-        // dK += dS^T Q ; dQ = dS K
+        // dQ = dS K first (into the dP columns, which the dS pass has read out): the softmax warps start draining it
+        // while dK += dS^T Q still runs
         if (!mbar_wait(&sh->ds_full, ph, abort_flag)) { ok = false; break; }
         FB_TRACE(0, it, 4);
         tc_fence_after();
 #pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kFbHalf + (k & 3) * 32;
+          umma_bf16(t_dp, make_smem_desc(ds_addr + off, 16, 1024), make_smem_desc(k_addr + k * 2048, kFbHalf, 1024),
+                    idesc_km, k != 0);
+        }
+        umma_commit(&sh->dq_full);
+#pragma unroll
         for (int k = 0; k < 8; ++k)
           umma_bf16(t_dk, make_smem_desc(ds_addr + k * 2048, kFbHalf, 1024),
                     make_smem_desc(q_addr + k * 2048, kFbHalf, 1024), idesc_mm, (it | k) != 0);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kFbHalf + (k & 3) * 32;
-          umma_bf16(t_s, make_smem_desc(ds_addr + off, 16, 1024), make_smem_desc(k_addr + k * 2048, kFbHalf, 1024),
-                    idesc_km, k != 0);
-        }
-        umma_commit(&sh->dq_full);     // also: dV, dK of this step done; P, dS, Q free
-        umma_commit(&sh->q_empty);
+        umma_commit(&sh->q_empty);     // also: dV, dK of this step done; P, dS, Q free
         FB_TRACE(0, it, 5);
       }
       if (!ok) {
@@ -359,9 +363,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           named_bar_sync(1 + wg, 128);
         }
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = 1 - cc;                  // the half staged in the dedicated tile first
+          // the other half goes into this group's half of the dS buffer, which dK (issued after dQ) reads until q_empty
+          if (c == 0 && !mbar_wait(&sh->q_empty, ph, abort_flag)) fail();
           uint32_t v[32];
-          tmem_ld_32x32(t_s + lane_off + col_base + c * 32, v);
+          tmem_ld_32x32(t_dp + lane_off + col_base + c * 32, v);
           tmem_ld_wait();
           uint8_t* st_row = (c == 0 ? sdS : sStage) + wg * kFbHalf + r * 128;
 #pragma unroll
@@ -385,7 +392,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
     // ---------------- epilogue: dV (group 0) / dK (group 1) -> bf16 -> global ----------------
-    // dq_full of the last step covers every MMA into dV and dK.
+    // Every step's drain waited for q_empty, which is committed after dK (and so after dV) of that step.
     if (n_it > 0 && ok && !*abort_flag && nsplit > 1) {
       // the query-head group is split over CTAs: add into the fp32 accumulators [2][T, Hk*128] (dk, dv)
       const int key = k0 + r;
