@@ -149,3 +149,61 @@ def test_optimizer_adapter_matches_the_native_path_on_every_layout(baseline):
             assert max(abs(a - b) for a, b in zip(losses, ref_losses)) < 5e-5, (tp, pp, sp, losses, ref_losses)
             assert abs(norm - ref_norm) < 1e-3 * ref_norm, (tp, pp, sp, norm, ref_norm)
 
+
+
+def _packed_batches(seq, dp_rank, dp_size, min_len=16):
+    """Micro-batches of one packed sequence each; tokens AND document layout are functions of the global sample
+    index, so every parallel layout trains on the same stream (sample i goes to DP rank i mod dp)."""
+    from easyllm_b200.data.synthetic import SyntheticTokenDataset
+    ds = SyntheticTokenDataset(32000, seq, seed=0)
+    step = 0
+    while True:
+        idx = step * dp_size + dp_rank
+        step += 1
+        row = ds[idx]
+        gen = torch.Generator().manual_seed(1000 + idx)
+        cu, at = [0], 0
+        pos = torch.empty(1, seq, dtype=torch.int64)
+        mask = torch.ones(1, seq, dtype=torch.int64)
+        while at < seq:
+            n = min(int(torch.randint(min_len, seq + 1, (1,), generator=gen)), seq - at)
+            pos[0, at:at + n] = torch.arange(n)
+            mask[0, at + n - 1] = 0
+            at += n
+            cu.append(at)
+        yield (row["input_ids"][None], pos, None, torch.tensor(cu, dtype=torch.int32)), (row["labels"][None], mask)
+
+
+def _train_packed(rank, world, tp, stage, sp, full, size_map):
+    """ZeRO stage `stage`, packed variable-length documents, Dynamic Checkpoint chosen from each micro-batch's tokens."""
+    from easyllm_b200.parallel.grid import get_grid, initialize_model_parallel
+    from easyllm_b200.models import llama_custom
+    from easyllm_b200.optim import ZeroOptimizer
+    from easyllm_b200.engine import PipelineEngine
+    if world > 1:
+        initialize_model_parallel(tp, 1)
+    g = get_grid()
+    dc = {"enabled": True, "size_map": size_map} if size_map else None
+    model = llama_custom(**dict(TINY, sequence_parallel=sp, dynamic_checkpoint=dc))
+    _load_sliced(model, full)
+    opt = ZeroOptimizer(model.named_parameters(), lr=1e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
+                        adamw=False, stage=stage, grad_clip=0.5, bucket_numel=200_000)
+    eng = PipelineEngine(model, opt, None, {"train_micro_batch_size_per_gpu": 1,
+                                            "gradient_accumulation_steps": 4 // g.dp})
+    it = _packed_batches(SEQ, g.dp_rank, g.dp)
+    losses = [float(eng.train_batch(it)) for _ in range(3)]
+    plan = model.recompute_plan(SEQ) if size_map else None      # what a micro-batch of SEQ tokens recomputes
+    return losses, float(eng.get_global_grad_norm()), plan
+
+
+def test_packed_documents_zero2_tp_sp_and_dynamic_checkpoint_match_single_process(baseline):
+    """The ingredients of the Qwen-14B benchmark config in miniature (tp2 x dp2, sequence parallel, ZeRO-2, packed
+    variable-length documents with cu_seqlens, recompute chosen per micro-batch from its token count): losses and the
+    gradient norm match one process that trains on the same stream without recompute."""
+    full, _ = baseline
+    ref_losses, ref_norm, _ = _train_packed(0, 1, 1, 0, False, full, None)
+    assert len(set(ref_losses)) == 3
+    for losses, norm, plan in run_ranks(4, _train_packed, 2, 2, True, full, {64: 0, 128: 1}):
+        assert max(abs(a - b) for a, b in zip(losses, ref_losses)) < 3e-5, (losses, ref_losses)
+        assert abs(norm - ref_norm) < 2e-4 * max(1.0, ref_norm)
+        assert plan == [True, False]                 # 128 tokens: the first of the two layers is recomputed
