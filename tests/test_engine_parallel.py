@@ -207,3 +207,46 @@ def test_packed_documents_zero2_tp_sp_and_dynamic_checkpoint_match_single_proces
         assert max(abs(a - b) for a, b in zip(losses, ref_losses)) < 3e-5, (losses, ref_losses)
         assert abs(norm - ref_norm) < 2e-4 * max(1.0, ref_norm)
         assert plan == [True, False]                 # 128 tokens: the first of the two layers is recomputed
+
+
+def _alternating_batches(dp_rank, dp_size):
+    """Micro-batches whose token count changes from one to the next (128, 64, 128, ...)."""
+    from easyllm_b200.data.synthetic import SyntheticTokenDataset
+    ds = SyntheticTokenDataset(32000, SEQ, seed=0)
+    step = 0
+    while True:
+        idx = step * dp_size + dp_rank
+        n = SEQ if idx % 2 == 0 else SEQ // 2
+        step += 1
+        row = ds[idx]
+        pos = torch.arange(n, dtype=torch.int64)[None]
+        yield (row["input_ids"][None, :n], pos, None), (row["labels"][None, :n], torch.ones(1, n, dtype=torch.int64))
+
+
+def _train_alternating(rank, world, tp, pp, sp, full, dynamic):
+    from easyllm_b200.parallel.grid import get_grid, initialize_model_parallel
+    from easyllm_b200.models import llama_custom
+    from easyllm_b200.optim import ZeroOptimizer
+    from easyllm_b200.engine import PipelineEngine
+    if world > 1:
+        initialize_model_parallel(tp, pp)
+    g = get_grid()
+    model = llama_custom(**dict(TINY, sequence_parallel=sp))
+    _load_sliced(model, full)
+    opt = ZeroOptimizer(model.named_parameters(), lr=1e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
+                        adamw=False, stage=0)
+    eng = PipelineEngine(model, opt, None, {"train_micro_batch_size_per_gpu": 1, "gradient_accumulation_steps": 4 // g.dp})
+    it = _alternating_batches(g.dp_rank, g.dp)
+    return [float(eng.train_batch(it, dynamic=dynamic)) for _ in range(3)]
+
+
+def test_pipeline_links_follow_micro_batches_of_changing_length(baseline):
+    """1F1B over two stages with micro-batches of 128 and 64 tokens in turn: the shape header that travels with every
+    activation (dynamic mode) keeps the stages in step, with and without tensor + sequence parallelism inside a
+    stage; the losses are those of one process on the same stream."""
+    full, _ = baseline
+    ref = _train_alternating(0, 1, 1, 1, False, full, True)
+    for losses in run_ranks(2, _train_alternating, 1, 2, False, full, True):
+        assert max(abs(a - b) for a, b in zip(losses, ref)) < 2e-5, (losses, ref)
+    for losses in run_ranks(4, _train_alternating, 2, 2, True, full, True):
+        assert max(abs(a - b) for a, b in zip(losses, ref)) < 3e-5, (losses, ref)
