@@ -203,3 +203,52 @@ def test_attention_forward_plan_covers_visible_keys_and_skips_masks_only_when_sa
             k0 = kv_lo + j * 128                # an unmasked tile: every (row, key) pair in it must be visible
             assert k0 + 127 < T
             assert all(rs[i] <= k0 and k0 + 127 <= i for i in rows), (idx, j)
+
+
+@pytest.mark.parametrize("tp", [2, 4, 8])
+@pytest.mark.parametrize("M,N,resident", [(4096, 4096, 74), (2048, 1024, 74), (8192, 2048, 70), (4096, 8192, 37)])
+def test_reduce_scatter_schedule_cannot_deadlock_across_ranks(cu, tp, M, N, resident):
+    """The reduce-scatter kernel walks its units in order on every cluster; a tile the rank owns waits for the flags of
+    all peers, a tile another rank owns never waits.  Replay that with the kernel's own unit order for every rank:
+    clusters advance in lock step, a unit finishes when its dependencies finished in an EARLIER round.  Every rank must
+    drain (no cycle of waits between ranks), and an own tile must find its peers' partial sums finished at least one
+    round before its own turn in the steady state, so that the epilogue does not stall the tensor core."""
+    tm = M // 256
+    if tm % tp:
+        pytest.skip("row tiles do not divide over the ranks")
+    tpr = tm // tp
+    order = {}
+    for rank in range(tp):
+        ncl, units = cu.gemm_pair_units(M, N, resident=resident, fuse=2, tp=tp, rank=rank, n_comm=0)
+        order[rank] = (ncl, units)
+    done_round = {}                              # (producer rank, mt, nt) -> round in which its partial was finished
+    ptr = {(r, c): c for r in range(tp) for c in range(order[r][0])}      # next unit of every cluster
+    waits = 0
+    for rnd in range(10000):
+        progressed, finished = False, []
+        for (r, c), u in ptr.items():
+            ncl, units = order[r]
+            if u >= len(units):
+                continue
+            mt, nt, n0, bn = units[u]
+            owner = mt // tpr
+            if owner == r:
+                ready = all(done_round.get((s, mt, nt), 1 << 30) < rnd for s in range(tp) if s != r)
+                if not ready:
+                    waits += 1
+                    continue
+            finished.append((r, c, mt, nt, owner))
+        for r, c, mt, nt, owner in finished:
+            if owner != r:
+                done_round[(r, mt, nt)] = rnd
+            ptr[(r, c)] += order[r][0]
+            progressed = True
+        if all(u >= len(order[r][1]) for (r, c), u in ptr.items()):
+            break
+        assert progressed, f"ranks wait for one another in round {rnd}"
+    else:
+        raise AssertionError("schedule did not drain")
+    n_units = sum(len(order[r][1]) for r in range(tp))
+    ideal_rounds = -(-len(order[0][1]) // order[0][0])
+    assert rnd + 1 <= ideal_rounds + 1, (rnd + 1, ideal_rounds)      # at most one round lost to waiting
+    assert waits <= order[0][0] * tp, (waits, n_units)               # and only around the start
