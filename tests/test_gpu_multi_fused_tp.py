@@ -156,6 +156,26 @@ for late in range(tp):
         assert torch.equal(u, v), "fused TP kernels are not run-to-run deterministic"
 torch.cuda.synchronize()
 cu.check_err_flag()
+
+# a launch whose last wave is cut into half-width units: the rank's own tiles close the reduce-scatter order, so the
+# halves add the peers' partial sums of their two 64-column blocks each
+if expect_pair:
+    Tb, Hb, Kb = 4096, 4096, 512
+    wsb = symm.FusedTPWorkspace(Tb, Hb)
+    _, units = cu.gemm_pair_units(Tb, Hb, resident=wsb.grid_pair // 2, fuse=2, tp=tp, rank=g.tp_rank)
+    halves = sum(1 for u in units if u[3] == 128)
+    ab = bf(Tb, Kb, seed=77 + g.tp_rank)
+    wb = bf(Hb, Kb, scale=0.05, seed=78 + g.tp_rank)
+    pb = ab.float() @ wb.float().t()
+    dist.all_reduce(pb, group=g.tp_group)
+    rb = Tb // tp
+    for _ in range(3):
+        rel(wsb.gemm_rs(ab, wb), pb[g.tp_rank * rb:(g.tp_rank + 1) * rb])
+    print(f"RANK{g.rank} half-width units in the 4096 x 4096 reduce-scatter: {halves}", flush=True)
+    if tp <= 4:
+        assert halves > 0
+    torch.cuda.synchronize()
+    cu.check_err_flag()
 assert not ops.fallbacks(), ops.fallbacks()
 print(f"RANK{g.rank} worst_rel_err={worst:.5f} pair={expect_pair}", flush=True)
 dist.barrier()
