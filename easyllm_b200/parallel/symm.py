@@ -6,8 +6,11 @@ memory mapped on all peers through ``torch.distributed._symmetric_memory``):
   gathered [2][T, hidden] bf16  all-gather→GEMM: rank s copies its sequence shard into rows
                               ``[s·T/tp, (s+1)·T/tp)`` of every rank's buffer; two buffers alternate by
                               call so a following kernel can still read the previous gather
-  staging  [T, hidden] bf16   GEMM→reduce-scatter / all-reduce: this rank's partial product (and, for the
-                              all-reduce, the reduced tiles it owns), read by the peers
+  staging  [T, hidden] bf16   GEMM→reduce-scatter on CTA pairs: rows ``[s·T/tp, (s+1)·T/tp)`` receive rank s's
+                              partial sums of the tiles THIS rank owns (written by s through its peer pointer,
+                              added in the owner's GEMM epilogue); GEMM→all-reduce and the single-CTA
+                              reduce-scatter: this rank's partial product (and, for the all-reduce, the
+                              reduced tiles it owns), read by the peers
   flags / done words          epoch counters written by peers (one set per kernel kind)
   ce      [2][tp][T, 3] fp32  cross-entropy statistics pushed by every rank (two buffers alternate by call)
 
@@ -115,7 +118,8 @@ class FusedTPWorkspace:
         return why is None
 
     def _reduce_ctas(self, K):
-        """Dedicated reduce CTAs of a GEMM→reduce-scatter launch.  The reduction moves a fixed number of bytes per
+        """Dedicated reduce CTAs of a launch with a staged reduction (GEMM→all-reduce, single-CTA reduce-scatter; the
+        CTA-pair reduce-scatter sums in its epilogue and has none).  The reduction moves a fixed number of bytes per
         output tile while the GEMM time per tile grows with K: a short reduction dimension needs more CTAs summing
         tiles during the main loop, or the whole reduction is left for the tail (about 30000 / K of them keep
         pace; even, because the CTA-pair kernel hands out whole clusters)."""
